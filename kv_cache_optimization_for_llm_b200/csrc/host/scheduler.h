@@ -1,0 +1,110 @@
+// Continuous-batching scheduler with chunked prefill and preemption by recompute.
+//
+// Counterpart of the upstream paged build's admitQueuedRequests / enforcePageBudget /
+// preemptSequence / finishSequence (paged_attention/src/engine.cu:294-370,406-454,
+// 640-731,792-838), redesigned around one mixed step: every step carries single
+// decode tokens of running requests beside portions of prompts, under one token
+// budget.  Upstream runs whole prompts in passes of their own and never splits one.
+#pragma once
+
+#include <cstdint>
+#include <deque>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "cache_manager.h"
+
+namespace kvb {
+
+struct SchedulerConfig {
+  int max_num_seqs = 64;              // requests that hold cache at the same time
+  int max_num_batched_tokens = 2048;  // tokens one step may carry
+  int max_model_len = 4096;           // prompt plus output, at most
+  int max_prefill_chunk = 0;          // 0: only the budget limits a prompt portion
+};
+
+enum class FinishReason { None = 0, Stop, Length, ModelLen, CacheExhausted, Aborted };
+const char* finish_reason_name(FinishReason r);
+
+struct PlanEntry {
+  int64_t id = 0;
+  int start = 0;            // position of the first token of this portion
+  std::vector<int> tokens;  // the tokens to run
+  bool sample = false;      // the portion ends at the request's last known token
+};
+
+struct Plan {
+  std::vector<PlanEntry> entries;
+  std::vector<int64_t> preempted;  // sent back to the queue's front in this call
+  std::vector<int64_t> finished;   // ended in this call because the cache cannot hold them
+  int num_tokens = 0;
+};
+
+struct SchedulerStats {
+  int64_t steps = 0, scheduled_tokens = 0, preemptions = 0, recomputed_tokens = 0;
+  int64_t finished = 0;
+};
+
+class Scheduler {
+ public:
+  Scheduler(CacheManager* cache, SchedulerConfig cfg);
+
+  // Queues a request (first come, first served).  Throws std::invalid_argument for
+  // an empty prompt, a live id, max_tokens < 1, or a prompt that can never run
+  // (longer than max_model_len allows, or needing more pages than the pool has).
+  void add(int64_t id, std::vector<int> prompt, int max_tokens);
+
+  // Decides the next step and takes the pages it needs.
+  Plan schedule();
+  // Records that the plan ran: its tokens are in the cache now.
+  void commit(const Plan& plan);
+  // Gives a sampled entry its new token.  A stop token ends the request and is not
+  // kept.  Returns the reason if the request ended, None otherwise.
+  FinishReason append_token(int64_t id, int token, bool is_stop);
+  void abort(int64_t id);
+
+  bool has_unfinished() const { return !running_.empty() || !waiting_.empty(); }
+  int num_running() const { return (int)running_.size(); }
+  int num_waiting() const { return (int)waiting_.size(); }
+  bool is_live(int64_t id) const { return reqs_.count(id) != 0; }
+  bool is_finished(int64_t id) const { return done_.count(id) != 0; }
+
+  const std::vector<int>& tokens(int64_t id) const;  // prompt followed by output
+  int prompt_len(int64_t id) const;
+  std::vector<int> output(int64_t id) const;
+  FinishReason finish_reason(int64_t id) const;
+  int preemptions_of(int64_t id) const;
+  // Forgets a finished request and returns its output.
+  std::vector<int> take_finished(int64_t id);
+
+  const SchedulerStats& stats() const { return stats_; }
+  const SchedulerConfig& config() const { return cfg_; }
+
+ private:
+  struct Req {
+    int64_t id = 0;
+    int64_t arrival = 0;
+    std::vector<int> tokens;
+    int prompt_len = 0;
+    int max_tokens = 0;
+    int computed = 0;
+    int preemptions = 0;
+    FinishReason reason = FinishReason::None;
+  };
+  const Req& any(int64_t id) const;
+  void finish(Req* r, FinishReason why);
+  void preempt(size_t running_index, Plan* plan);
+  int portion(const Req& r, int budget) const;
+
+  CacheManager* cache_;
+  SchedulerConfig cfg_;
+  int64_t arrivals_ = 0;
+  std::unordered_map<int64_t, Req> reqs_;  // waiting or running
+  std::unordered_map<int64_t, Req> done_;
+  std::vector<int64_t> running_;           // in arrival order
+  std::deque<int64_t> waiting_;
+  SchedulerStats stats_;
+};
+
+}  // namespace kvb

@@ -1,0 +1,155 @@
+"""The description of one step's batch, as the kernels read it.
+
+A step carries, for each scheduled request, a run of new tokens that starts where
+its cache ends: a portion of a prompt, or one decoded token.  Upstream builds two
+different sets of descriptor arrays, one for packed whole prompts and one for
+decode rows (base/src/engine.cu:584-633,993-1032); here one layout serves both,
+staged in a single pinned buffer and copied with one transfer.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step."""
+    request_id: int
+    tokens: Sequence[int]        # the new tokens, in order
+    start: int                   # position of tokens[0] in its sequence
+    want: Sequence[int] = ()     # indices into ``tokens`` whose logits are asked for
+
+
+@dataclass
+class StepBatch:
+    num_tokens: int
+    num_reqs: int
+    token_ids: torch.Tensor      # [T] int32
+    positions: torch.Tensor      # [T] int32, index of each token in its own sequence
+    token_req: torch.Tensor      # [T] int32, row of each token's request in this batch
+    q_start: torch.Tensor        # [R+1] int32, first token of each request's run
+    req_start: torch.Tensor      # [R] int32, position of the run's first token
+    ctx_len: torch.Tensor        # [R] int32, tokens in the cache after this step
+    slots: torch.Tensor          # [R] int32, state slot of each request
+    block_tables: List[torch.Tensor]  # per cache group [R, max_pages] int32
+    logit_rows: torch.Tensor     # [n] int32, token rows whose logits are wanted
+    num_logits: int
+    max_q_len: int
+    max_ctx_len: int
+    decode_only: bool            # every run is a single token
+    status: torch.Tensor         # [1] int32 device word that kernels report into
+    host: dict = field(default_factory=dict)  # numpy mirrors of the arrays above
+
+
+class BatchBuilder:
+    """Turns entries plus the cache manager's tables into device arrays.
+
+    All arrays of one step live in one device buffer of fixed layout (so that a
+    captured graph can read them at fixed addresses) and are staged in one pinned
+    host buffer."""
+
+    def __init__(self, max_tokens: int, max_reqs: int, max_pages_per_group: Sequence[int], device,
+                 status: torch.Tensor):
+        self.max_tokens, self.max_reqs = int(max_tokens), int(max_reqs)
+        self.max_pages = [int(m) for m in max_pages_per_group]
+        self.device = torch.device(device)
+        self.status = status
+        T, R = self.max_tokens, self.max_reqs
+        sizes = [("token_ids", T), ("positions", T), ("token_req", T), ("q_start", R + 1),
+                 ("req_start", R), ("ctx_len", R), ("slots", R), ("logit_rows", T)]
+        for g, mp in enumerate(self.max_pages):
+            sizes.append((f"bt{g}", R * mp))
+        self.offsets = {}
+        off = 0
+        for name, n in sizes:
+            self.offsets[name] = (off, n)
+            off += (n + 3) // 4 * 4  # keep every array 16-byte aligned
+        self.total = off
+        use_cuda = self.device.type == "cuda"
+        self.host_buf = torch.zeros(self.total, dtype=torch.int32, pin_memory=use_cuda)
+        self.host_np = self.host_buf.numpy()
+        self.dev_buf = torch.zeros(self.total, dtype=torch.int32, device=self.device)
+
+    def _view(self, buf, name, n=None):
+        off, cap = self.offsets[name]
+        return buf[off:off + (cap if n is None else n)]
+
+    def build(self, entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None) -> StepBatch:
+        """``cache`` is the CacheManager; every entry's pages must already cover
+        ``start + len(tokens)``."""
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        if R == 0 or T == 0:
+            raise ValueError("a step needs at least one token")
+        if R > self.max_reqs:
+            raise ValueError(f"a step holds {R} requests, the engine was built for {self.max_reqs}")
+        if T > self.max_tokens:
+            raise ValueError(f"a step holds {T} tokens, the engine was built for {self.max_tokens}")
+        h = self.host_np
+        tok = self._view(h, "token_ids", T)
+        pos = self._view(h, "positions", T)
+        treq = self._view(h, "token_req", T)
+        qs = self._view(h, "q_start", R + 1)
+        rstart = self._view(h, "req_start", R)
+        ctx = self._view(h, "ctx_len", R)
+        slots = self._view(h, "slots", R)
+        rows: List[int] = []
+        t = 0
+        for r, e in enumerate(entries):
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request_id} brings no token to this step")
+            tok[t:t + n] = e.tokens
+            pos[t:t + n] = np.arange(e.start, e.start + n, dtype=np.int32)
+            treq[t:t + n] = r
+            qs[r] = t
+            rstart[r] = e.start
+            ctx[r] = e.start + n
+            slots[r] = cache.slot_of(e.request_id)
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.request_id}: wanted place {w} is outside its {n} tokens")
+                rows.append(t + w)
+            t += n
+        qs[R] = T
+        if vocab_size is not None and (tok.min() < 0 or tok.max() >= vocab_size):
+            raise ValueError(f"a token id is outside the vocabulary of {vocab_size}")
+        lr = self._view(h, "logit_rows", len(rows))
+        lr[:] = rows
+        for g, mp in enumerate(self.max_pages):
+            bt = self._view(h, f"bt{g}", R * mp).reshape(R, mp)
+            bt.fill(-1)
+            for r, e in enumerate(entries):
+                table = cache.block_table(e.request_id, g)
+                if len(table) > mp:
+                    raise ValueError(f"request {e.request_id} holds {len(table)} pages in group {g}, "
+                                     f"tables were sized for {mp}")
+                bt[r, :len(table)] = table
+        # Block tables lie last, so one copy of the used prefix carries everything.
+        if self.max_pages:
+            g = len(self.max_pages) - 1
+            used = self.offsets[f"bt{g}"][0] + R * self.max_pages[g]
+        else:
+            used = self.total
+        self.dev_buf[:used].copy_(self.host_buf[:used], non_blocking=True)
+        d = self.dev_buf
+        batch = StepBatch(
+            num_tokens=T, num_reqs=R,
+            token_ids=self._view(d, "token_ids", T), positions=self._view(d, "positions", T),
+            token_req=self._view(d, "token_req", T), q_start=self._view(d, "q_start", R + 1),
+            req_start=self._view(d, "req_start", R), ctx_len=self._view(d, "ctx_len", R),
+            slots=self._view(d, "slots", R),
+            block_tables=[self._view(d, f"bt{g}", R * mp).view(R, mp) for g, mp in enumerate(self.max_pages)],
+            logit_rows=self._view(d, "logit_rows", len(rows)), num_logits=len(rows),
+            max_q_len=max(len(e.tokens) for e in entries),
+            max_ctx_len=int(ctx.max()),
+            decode_only=all(len(e.tokens) == 1 for e in entries),
+            status=self.status,
+            host={"q_start": qs.copy(), "ctx_len": ctx.copy(), "req_start": rstart.copy()},
+        )
+        return batch

@@ -1,0 +1,68 @@
+"""A model put together from parts according to its description."""
+
+from __future__ import annotations
+
+from typing import Dict, List, Mapping
+
+import torch
+
+from ..models.spec import ModelSpec, PartSpec, expected_weights
+from ..parts import BuildContext, lookup
+from ..weights.loader import to_compute
+
+
+class DecoderModel:
+    """Embedding, the scheduled layers, final norm and head.
+
+    ``forward`` runs exactly the tokens of the batch, reads and writes the cache
+    through each schedule entry's binding, and returns float32 logits at
+    ``batch.logit_rows`` only."""
+
+    def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], ctx: BuildContext):
+        spec.validate()
+        self.spec, self.ctx = spec, ctx
+        wanted = expected_weights(spec)
+        # One device copy per checkpoint tensor, however many parts name it.
+        dev: Dict[str, torch.Tensor] = {}
+        for name, ws in wanted.items():
+            dev[name] = to_compute(tensors[name], ws, ctx.dtype, ctx.device)
+
+        def make(family: str, ps: PartSpec):
+            cls = lookup(family, ps.kind)
+            return cls(ps.params, {role: dev[name] for role, name in ps.weights.items()}, ctx)
+
+        self.embedding = make("embedding", spec.embedding)
+        self.layers = []
+        for ls in spec.layers:
+            block_cls = lookup("block", ls.block)
+            self.layers.append(block_cls(make("mixer", ls.mixer), make("norm", ls.mixer_norm),
+                                         make("feed_forward", ls.feed_forward), make("norm", ls.ff_norm)))
+        self.final_norm = make("norm", spec.final_norm)
+        self.head = make("head", spec.lm_head)
+        self.schedule = list(spec.schedule)
+
+    def cache_specs(self):
+        """Per schedule entry: what its mixer asks of the cache, and whose cache it reads."""
+        specs = [self.layers[e.layer].mixer.cache_spec() for e in self.schedule]
+        return specs, [e.cache_of for e in self.schedule]
+
+    def kernel_modules(self) -> List[str]:
+        mods: List[str] = []
+        from ..models.spec import iter_parts
+        for family, ps in iter_parts(self.spec):
+            if family == "block":
+                continue
+            for m in lookup(family, ps.kind).kernel_modules(ps.params, self.ctx.dtype):
+                if m not in mods:
+                    mods.append(m)
+        return mods
+
+    def forward(self, batch, cache) -> torch.Tensor:
+        residual = self.embedding.forward(batch)
+        delta = None
+        for i, entry in enumerate(self.schedule):
+            residual, delta = self.layers[entry.layer].forward(residual, delta, batch, cache.binding(i))
+        if batch.num_logits == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
+        x = self.final_norm.forward(residual, delta, rows=batch.logit_rows)
+        return self.head.forward(x)

@@ -1,0 +1,140 @@
+"""Loads a model folder and runs steps on it: the one step function of the engine.
+
+``step`` takes a batch of (request, its next tokens): portions of prompts beside
+single decoded tokens, cut anywhere.  It runs only the tokens it is given, as one
+batch, against the cache that earlier steps left, and returns the logits at the
+wanted places.  Upstream has two separate passes instead, whole packed prompts
+(prefillBatch, base/src/engine.cu:550-979) and one token per running sequence
+(decodeStep, base/src/engine.cu:982-1311), and returns sampled ids only.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.paged_cache import PagedCache
+from ..config import EngineConfig, read_config_json
+from ..models.spec import expected_weights
+from ..parts import BuildContext
+from ..registry import resolve_architecture
+from ..weights.loader import check_and_load
+from .batch import BatchBuilder, StepBatch, StepEntry
+from .model import DecoderModel
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class CacheFull(RuntimeError):
+    """The pool has too few free pages for the step."""
+
+
+def _require_gpu(device: torch.device) -> None:
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("this engine runs on a CUDA device only (its kernels are built for sm_100a); "
+                           "no GPU is visible and there is no CPU path")
+
+
+class ModelRunner:
+    def __init__(self, model_dir, config: Optional[EngineConfig] = None):
+        self.config = config or EngineConfig()
+        self.device = torch.device(self.config.device)
+        _require_gpu(self.device)
+        torch.cuda.set_device(self.device)
+        # float32 means float32: no reduced-precision matrix mode anywhere.
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+        self.model_dir = Path(model_dir)
+        config_dict = read_config_json(self.model_dir)
+        self.arch = resolve_architecture(config_dict)
+        self.model_config = self.arch.parse_config(config_dict)
+        self.spec = self.arch.build_spec(self.model_config)
+        self.dtype = _TORCH_DTYPE[self.config.dtype]
+        tensors = check_and_load(self.model_dir, expected_weights(self.spec))
+        self.max_model_len = int(self.config.max_model_len or self.spec.max_position)
+        if self.max_model_len > self.spec.max_position:
+            raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's "
+                             f"max_position_embeddings {self.spec.max_position}")
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        ctx = BuildContext(dtype=self.dtype, device=self.device, max_positions=self.max_model_len,
+                           status=self.status)
+        self.model = DecoderModel(self.spec, tensors, ctx)
+        del tensors
+        ops.prepare(self.model.kernel_modules())
+        specs, cache_of = self.model.cache_specs()
+        num_pages = self.config.num_pages
+        if num_pages is None:
+            per_token = PagedCache.bytes_per_token(specs, cache_of, self.dtype)
+            free, _total = torch.cuda.mem_get_info(self.device)
+            if per_token == 0:
+                num_pages = self.config.max_num_seqs
+            else:
+                num_pages = int(free * self.config.memory_fraction) // (per_token * self.config.page_size)
+                # More pages than every seat at full length can use are of no use.
+                ceiling = self.config.max_num_seqs * (-(-self.max_model_len // self.config.page_size))
+                num_pages = max(1, min(num_pages, ceiling))
+        self.cache = PagedCache(specs, cache_of, self.config.page_size, num_pages, self.config.max_num_seqs,
+                                self.max_model_len, self.dtype, self.device)
+        self.manager = self.cache.manager
+        self.builder = BatchBuilder(self.config.max_num_batched_tokens, self.config.max_num_seqs,
+                                    self.cache.max_pages, self.device, self.status)
+        self.vocab_size = self.spec.vocab_size
+
+    # ---------------------------------------------------------------- the step function
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch whose pages are already in place.  Returns float32 logits
+        [wanted, vocab] on the device, in the order of the entries and their ``want``."""
+        batch = self.builder.build(entries, self.manager, self.vocab_size)
+        return self.model.forward(batch, self.cache)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """``run`` with the cache kept for the caller: admits unknown requests, takes
+        the pages the step needs (or raises :class:`CacheFull` and changes nothing),
+        and records the new lengths afterwards."""
+        m = self.manager
+        admitted: List[int] = []
+        try:
+            for e in entries:
+                if not m.has(e.request_id):
+                    if m.admit(e.request_id) < 0:
+                        raise CacheFull(f"no state slot is free for request {e.request_id}")
+                    admitted.append(e.request_id)
+                if m.computed(e.request_id) != e.start:
+                    raise ValueError(f"request {e.request_id}: the step starts at position {e.start}, "
+                                     f"its cache holds {m.computed(e.request_id)} tokens")
+                if e.start + len(e.tokens) > self.max_model_len:
+                    raise ValueError(f"request {e.request_id} would grow to {e.start + len(e.tokens)} tokens, "
+                                     f"beyond max_model_len {self.max_model_len}")
+            need = [0] * m.num_groups()
+            for e in entries:
+                for g, n in enumerate(m.pages_needed(e.request_id, e.start + len(e.tokens))):
+                    need[g] += n
+            for g, n in enumerate(need):
+                if n > m.free_pages(g):
+                    raise CacheFull(f"the step needs {n} pages of group {g}, {m.free_pages(g)} are free")
+            for e in entries:
+                if not m.extend(e.request_id, e.start + len(e.tokens)):
+                    raise CacheFull("pages ran out while extending")  # cannot happen after the count above
+        except Exception:
+            for rid in admitted:
+                m.release(rid)
+            raise
+        logits = self.run(entries)
+        for e in entries:
+            m.advance(e.request_id, e.start + len(e.tokens))
+        return logits
+
+    def release(self, request_id: int) -> None:
+        if self.manager.has(request_id):
+            self.manager.release(request_id)
+
+    def check_status(self) -> None:
+        """Raises if a kernel reported an impossible index since the last check
+        (synchronises with the device)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise ops.KernelError(ops.STATUS_TEXT.get(code, f"kernel status {code}"))

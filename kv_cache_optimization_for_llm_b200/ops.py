@@ -1,0 +1,200 @@
+"""Python face of the CUDA kernels: loads each kernel module through ctypes at its
+first use (building it if needed) and wraps the launchers.
+
+There is no fallback: on a machine with a GPU a missing or unbuildable library
+raises, and no operator here has a PyTorch or CPU stand-in.  Matrix products of
+the bfloat16 path go to the library (cuBLAS through ``torch.nn.functional.linear``)
+as upstream's do (cublasGemmEx, base/src/engine.cu:653-671); everything else,
+and every matrix product of the float32 path, is a kernel of this package.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+
+_libs: Dict[str, ctypes.CDLL] = {}
+launch_count = 0  # kernels of this package launched so far (library calls are not counted)
+
+_ERR = {-1: "unsupported dtype", -2: "a size this kernel refuses", -3: "misaligned pointer or stride"}
+
+STATUS_TEXT = {
+    1: "a kernel met a position whose cache page is not mapped",
+    2: "a kernel met a position outside the position-encoding table",
+    3: "a kernel met a token id outside the vocabulary",
+    4: "a bounded wait inside a kernel ran out",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib(name: str) -> ctypes.CDLL:
+    got = _libs.get(name)
+    if got is None:
+        build.ensure_built([name])
+        path = build.kernel_lib_path(name)
+        try:
+            got = ctypes.CDLL(str(path))
+        except OSError as e:
+            raise KernelError(f"the kernel library {path} cannot be loaded: {e}") from e
+        _libs[name] = got
+    return got
+
+
+def prepare(names) -> None:
+    """Builds (in parallel) and loads the named kernel modules."""
+    build.ensure_built(list(names))
+    for n in names:
+        lib(n)
+
+
+def loaded_libraries():
+    return {n: str(build.kernel_lib_path(n)) for n in _libs}
+
+
+def _check(rc: int, what: str) -> None:
+    global launch_count
+    if rc != 0:
+        if rc < 0:
+            raise KernelError(f"{what}: {_ERR.get(rc, rc)}")
+        raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+    launch_count += 1
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return 0
+    if dt == torch.bfloat16:
+        return 1
+    raise KernelError(f"dtype {dt} has no kernels (float32 and bfloat16 do)")
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels of this package run on CUDA tensors only; there is no CPU path")
+
+
+# ------------------------------------------------------------------ elementwise
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """float32 residual rows ``table[ids]``."""
+    _need_cuda(table, ids)
+    V, H = table.shape
+    T = ids.numel()
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    rc = lib("elementwise").kvb_embed_gather(_p(table), dtype_code(table.dtype), _p(ids), _p(out),
+                                             c_int(T), c_int(H), c_int(V), _p(status), _stream())
+    _check(rc, "embed_gather")
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``resid += delta`` (when given, in float32, in place unless ``rows`` selects),
+    then RMSNorm of the sum times ``weight``; ``rows`` (int32) picks the rows to
+    produce, in order, leaving ``resid`` untouched."""
+    _need_cuda(resid, weight)
+    assert resid.dtype == torch.float32 and weight.dtype == torch.float32 and resid.is_contiguous()
+    T, H = resid.shape
+    n = T if rows is None else rows.numel()
+    out = torch.empty((n, H), dtype=out_dtype, device=resid.device)
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.dtype == out_dtype and delta.is_contiguous()
+    rc = lib("elementwise").kvb_add_rmsnorm(_p(resid), _p(delta), _p(weight), _p(out), _p(rows), c_int(n),
+                                            c_int(H), c_float(eps), c_int(dtype_code(out_dtype)), _stream())
+    _check(rc, "add_rmsnorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for rows laid out as [gate | up]."""
+    _need_cuda(gate_up)
+    assert gate_up.is_contiguous()
+    T, two_i = gate_up.shape
+    I = two_i // 2
+    out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
+    rc = lib("elementwise").kvb_silu_mul(_p(gate_up), _p(out), c_int(T), c_int(I),
+                                         c_int(dtype_code(gate_up.dtype)), _stream())
+    _check(rc, "silu_mul")
+    return out
+
+
+def rope_kv_write(qkv, positions, token_req, cos, sin, k_pages, v_pages, block_table, page_size,
+                  nq, nkv, d, rot, status) -> None:
+    """Rotates q (in place) and k, writes k and v into their pages.  ``k_pages`` None:
+    only q is rotated.  ``cos`` None: no rotation."""
+    _need_cuda(qkv)
+    assert qkv.is_contiguous() and qkv.shape[1] == (nq + 2 * nkv) * d
+    T = qkv.shape[0]
+    table_len = 0 if cos is None else cos.shape[0]
+    num_pages = 0 if k_pages is None else k_pages.shape[0]
+    if k_pages is not None:
+        assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype
+        assert tuple(k_pages.shape[1:]) == (nkv, page_size, d), (k_pages.shape, nkv, page_size, d)
+    max_pages = block_table.shape[1]
+    rc = lib("elementwise").kvb_rope_kv_write(
+        _p(qkv), _p(positions), _p(token_req), _p(cos), _p(sin), c_int(table_len), _p(k_pages),
+        _p(v_pages), _p(block_table), c_int(max_pages), c_int(page_size), c_int(num_pages), c_int(T),
+        c_int(nq), c_int(nkv), c_int(d), c_int(rot), c_int(dtype_code(qkv.dtype)), _p(status), _stream())
+    _check(rc, "rope_kv_write")
+
+
+# ------------------------------------------------------------------ attention
+
+def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token_req, nq, nkv, d,
+                            scale, window, status) -> torch.Tensor:
+    """Attention of every token in ``qkv`` (q part) over its request's cached keys."""
+    _need_cuda(qkv, k_pages)
+    T = qkv.shape[0]
+    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+    page_size = k_pages.shape[2]
+    rc = lib("attention").kvb_paged_attention_generic(
+        _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table),
+        c_int(block_table.shape[1]), c_int(page_size), c_int(k_pages.shape[0]), _p(positions),
+        _p(token_req), _p(out), c_int(T), c_int(nq), c_int(nkv), c_int(d), c_float(scale),
+        c_int(int(window or 0)), c_int(dtype_code(qkv.dtype)), _p(status), _stream())
+    _check(rc, "paged_attention_generic")
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x . w^T`` with ``w`` [out, in].  float32: this package's FMA kernel (true
+    32-bit).  bfloat16: the library product with float32 accumulation."""
+    _need_cuda(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and x.dtype == w.dtype
+    if x.dtype == torch.float32:
+        assert x.stride(1) == 1 and w.stride(1) == 1
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        rc = lib("gemm_f32").kvb_sgemm_nt(_p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out),
+                                          c_int(N), c_int(M), c_int(N), c_int(K), _stream())
+        _check(rc, "sgemm_nt")
+        return out
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.mm(x, w.t(), out_dtype=out_dtype)
+    return torch.nn.functional.linear(x, w)
+
+
+def attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window) -> torch.Tensor:
+    """Attention of the step's tokens over their requests' pages; picks the kernel."""
+    return paged_attention_generic(qkv, k_pages, v_pages, block_table, batch.positions, batch.token_req,
+                                   nq, nkv, d, scale, window, batch.status)
