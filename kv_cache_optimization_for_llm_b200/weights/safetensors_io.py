@@ -7,7 +7,6 @@ offsets are used and neither dtype nor shape is looked at).
 from __future__ import annotations
 
 import json
-import mmap
 import struct
 from pathlib import Path
 from typing import Dict, Mapping, Tuple
@@ -59,21 +58,16 @@ def read_tensors(path, names=None) -> Dict[str, torch.Tensor]:
     """Loads tensors (all, or the named ones) in their stored dtype, on the CPU."""
     header, base = read_header(path)
     out: Dict[str, torch.Tensor] = {}
-    with open(path, "rb") as f:
-        mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
-        try:
-            for name, meta in header.items():
-                if names is not None and name not in names:
-                    continue
-                lo, hi = meta["data_offsets"]
-                dt = _TORCH[meta["dtype"]]
-                if hi == lo:
-                    out[name] = torch.empty(meta["shape"], dtype=dt)
-                    continue
-                raw = np.frombuffer(mm, dtype=np.uint8, count=hi - lo, offset=base + lo)
-                out[name] = torch.from_numpy(raw.copy()).view(dt).reshape(meta["shape"])
-        finally:
-            mm.close()
+    for name, meta in header.items():
+        if names is not None and name not in names:
+            continue
+        lo, hi = meta["data_offsets"]
+        dt = _TORCH[meta["dtype"]]
+        if hi == lo:
+            out[name] = torch.empty(meta["shape"], dtype=dt)
+            continue
+        raw = np.fromfile(path, dtype=np.uint8, count=hi - lo, offset=base + lo)
+        out[name] = torch.from_numpy(raw).view(dt).reshape(meta["shape"])
     return out
 
 
