@@ -198,3 +198,27 @@ def attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, wind
     """Attention of the step's tokens over their requests' pages; picks the kernel."""
     return paged_attention_generic(qkv, k_pages, v_pages, block_table, batch.positions, batch.token_req,
                                    nq, nkv, d, scale, window, batch.status)
+
+
+# ------------------------------------------------------------------ sampling
+
+def sample(logits, temperature, seed, key, pos, penalty, mask, slots, out=None) -> torch.Tensor:
+    """One token id per row of float32 ``logits``.  ``temperature`` None: greedy for all
+    rows; ``penalty``/``mask`` None: no repetition penalty."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    rc = lib("sampling").kvb_sample(_p(logits), c_int(R), c_int(V), _p(temperature), _p(seed), _p(key),
+                                    _p(pos), _p(penalty), _p(mask), _p(slots), _p(out), _stream())
+    _check(rc, "sample")
+    return out
+
+
+def reset_mask(mask: torch.Tensor, slot: int, tokens: Optional[torch.Tensor]) -> None:
+    """Clears the slot's row of produced-token marks and marks ``tokens`` (int32, device)."""
+    n = 0 if tokens is None else tokens.numel()
+    rc = lib("sampling").kvb_reset_mask(_p(mask), c_int(slot), c_int(mask.shape[1]), _p(tokens), c_int(n),
+                                        _stream())
+    _check(rc, "reset_mask")

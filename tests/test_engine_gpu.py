@@ -1,0 +1,135 @@
+"""The engine end to end against the plain implementation: greedy generation through
+the Python entry point, sampling with per-request seeds, staggered arrivals that put
+prompt portions beside decode tokens, a pool so small that requests are dropped and
+recomputed, long decoding, and the first tokens of a sequence."""
+
+import numpy as np
+import pytest
+
+import plain_llama as P
+from tiny_models import CONFIGS, model_dir
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompts(cfg, lengths, seed):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg["vocab_size"] - 2, size=n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("name,lengths,page_size", [("tiny_a", [5, 11, 17], 4), ("tiny_c", [3, 20, 9], 16)])
+def test_greedy_generation_through_entry_point(name, lengths, page_size):
+    """float32, greedy: the generated ids equal the plain implementation's."""
+    from kv_cache_optimization_for_llm_b200 import SamplingParams, generate
+    mdir = model_dir(name, "float32")
+    cfg, w = P.read_model_dir(mdir)
+    prompts = _prompts(cfg, lengths, 7)
+    got = generate(mdir, prompts, SamplingParams(max_tokens=8, ignore_eos=True), dtype="float32",
+                   page_size=page_size, num_pages=64, max_num_seqs=4, max_num_batched_tokens=32)
+    for p, g in zip(prompts, got):
+        assert g == P.generate(cfg, w, p, 8)
+
+
+def test_greedy_same_tokens_however_scheduled():
+    """float32, greedy: whole prompts, a budget of 3 tokens per step, and one request
+    at a time all give the same ids."""
+    from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
+    mdir = model_dir("tiny_a", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    prompts = _prompts(cfg, [5, 11, 17], 11)
+    sp = SamplingParams(max_tokens=8, ignore_eos=True)
+    ref = [P.generate(cfg, w, p, 8) for p in prompts]
+    for kw in (dict(max_num_batched_tokens=64), dict(max_num_batched_tokens=4, max_prefill_chunk=3),
+               dict(max_num_seqs=1, max_num_batched_tokens=64)):
+        llm = LLM(mdir, dtype="float32", page_size=4, num_pages=40, **{"max_num_seqs": 4, **kw})
+        assert llm.generate(prompts, sp) == ref, kw
+        assert llm.engine.runner.manager.check() == ""
+        assert llm.engine.runner.manager.free_pages(0) == 40
+
+
+def test_stop_token_ends_request_and_is_not_returned():
+    from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
+    mdir = model_dir("tiny_a", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    prompt = _prompts(cfg, [9], 3)[0]
+    free_run = P.generate(cfg, w, prompt, 12)
+    # Declare the 5th generated token a stop token through a copy of the model folder.
+    import json, os, shutil, tempfile
+    d = tempfile.mkdtemp(prefix="kvb200_eos_")
+    shutil.copy(os.path.join(mdir, "model.safetensors"), d)
+    c = dict(cfg)
+    c["eos_token_id"] = int(free_run[4])
+    json.dump(c, open(os.path.join(d, "config.json"), "w"))
+    cut = free_run.index(free_run[4])
+    llm = LLM(d, dtype="float32", page_size=4, num_pages=40, max_num_seqs=2)
+    assert llm.generate([prompt], SamplingParams(max_tokens=12)) == [free_run[:cut]]
+    assert llm.generate([prompt], SamplingParams(max_tokens=12, ignore_eos=True)) == [free_run]
+
+
+def test_temperature_sampling_with_preemption_tiny_b():
+    """float32, temperature 0.7 with per-request seeds, five prompts arriving two steps
+    apart so that prompt portions share steps with decode tokens, in 14 pages of 16
+    tokens (all five together need 23), so requests are dropped and recomputed.  Every request's
+    tokens still equal the plain implementation's, which knows no cache at all."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, SamplingParams
+    from kv_cache_optimization_for_llm_b200.engine.llm_engine import LLMEngine
+    mdir = model_dir("tiny_b", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    lengths = [1, 9, 33, 70, 120]
+    prompts = _prompts(cfg, lengths, 5)
+    n_new = 16
+    eng = LLMEngine(mdir, EngineConfig(dtype="float32", page_size=16, num_pages=14, max_num_seqs=5,
+                                       max_num_batched_tokens=48, max_model_len=256, seed=99))
+    params = [SamplingParams(max_tokens=n_new, temperature=0.7, seed=1000 + i, ignore_eos=True) for i in range(5)]
+    ids, step = [], 0
+    while len(ids) < 5 or eng.has_unfinished():
+        if step % 2 == 0 and len(ids) < 5:
+            ids.append(eng.add_request(prompts[len(ids)], params[len(ids)]))
+        eng.step()
+        assert eng.runner.manager.check() == ""
+        step += 1
+        assert step < 2000
+    st = eng.stats()
+    assert st["preemptions"] > 0, "the pool was meant to be too small"
+    assert st["free_pages"] == [14]
+    for i, rid in enumerate(ids):
+        ref = P.generate(cfg, w, prompts[i], n_new, temperature=0.7, seed=1000 + i, key=rid)
+        assert eng.output(rid) == ref, f"request {i} (preempted {eng.preemptions_of(rid)} times)"
+
+
+def test_repetition_penalty_matches_plain():
+    from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
+    mdir = model_dir("tiny_a", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    prompt = _prompts(cfg, [6], 21)[0]
+    llm = LLM(mdir, dtype="float32", page_size=4, num_pages=40, max_num_seqs=2)
+    got = llm.generate([prompt], SamplingParams(max_tokens=20, ignore_eos=True, repetition_penalty=1.15))[0]
+    assert got == P.generate(cfg, w, prompt, 20, penalty=1.15)
+    plain = llm.generate([prompt], SamplingParams(max_tokens=20, ignore_eos=True))[0]
+    assert plain == P.generate(cfg, w, prompt, 20)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 4e-2)])
+def test_long_decoding_and_first_tokens(dtype, tol):
+    """A 3-token prompt, then 200 tokens one by one (tiny_b, 256 positions): logits at
+    every step against the plain implementation, the very first positions included."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    mdir = model_dir("tiny_b", "float32" if dtype == "float32" else "bfloat16")
+    cfg, w = P.read_model_dir(mdir)
+    seq = _prompts(cfg, [203], 17)[0]
+    ref = P.forward(cfg, w, seq)
+    r = ModelRunner(mdir, EngineConfig(dtype=dtype, page_size=16, num_pages=13, max_num_seqs=2,
+                                       max_num_batched_tokens=16, max_model_len=208))
+    scale = np.abs(ref).max()
+    got = r.step([StepEntry(0, seq[:1], 0, [0])]).cpu().numpy()          # a request of one token
+    assert np.abs(got - ref[0:1]).max() / scale < tol
+    got = r.step([StepEntry(0, seq[1:3], 1, [0, 1])]).cpu().numpy()
+    assert np.abs(got - ref[1:3]).max() / scale < tol
+    worst = 0.0
+    for i in range(3, len(seq)):
+        got = r.step([StepEntry(0, [seq[i]], i, [0])]).cpu().numpy()
+        worst = max(worst, np.abs(got - ref[i:i + 1]).max() / scale)
+    r.check_status()
+    assert worst < tol, worst
