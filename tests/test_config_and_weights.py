@@ -1,0 +1,166 @@
+"""Configuration parsing, the registry, safetensors round trip, and the loader's one
+error that lists missing tensors, unexpected tensors and wrong shapes."""
+
+import json
+import os
+import shutil
+import tempfile
+
+import pytest
+import torch
+
+from tiny_models import TINY_A, TINY_B, model_dir
+
+from kv_cache_optimization_for_llm_b200.config import ConfigError, EngineConfig, LlamaConfig
+from kv_cache_optimization_for_llm_b200.models.spec import expected_weights
+from kv_cache_optimization_for_llm_b200.registry import known_architectures, resolve_architecture
+from kv_cache_optimization_for_llm_b200.weights import (WeightError, check_and_load, read_header, read_tensors,
+                                                       write_tensors)
+from kv_cache_optimization_for_llm_b200.weights.safetensors_io import SafetensorsError
+
+
+def test_config_reads_every_key():
+    c = LlamaConfig.from_dict(TINY_B)
+    assert (c.vocab_size, c.hidden_size, c.intermediate_size, c.num_hidden_layers) == (1000, 192, 512, 3)
+    assert (c.num_attention_heads, c.num_key_value_heads, c.head_dim) == (6, 1, 32)
+    assert c.rms_norm_eps == 1e-6 and c.rope_theta == 500000.0 and not c.tie_word_embeddings
+    assert c.rope_scaling.factor == 8.0 and c.rope_scaling.original_max_position_embeddings == 64
+    assert c.eos_token_ids == (998, 999) and c.max_position_embeddings == 256
+    assert LlamaConfig.from_dict(c.to_dict()) == c
+
+
+def test_config_defaults_follow_the_format():
+    d = {k: v for k, v in TINY_A.items() if k not in ("num_key_value_heads", "head_dim", "rope_theta")}
+    c = LlamaConfig.from_dict(d)
+    assert c.num_key_value_heads == 4 and c.head_dim == 16 and c.rope_theta == 10000.0
+    assert c.rope_scaling is None and c.eos_token_ids == (255,)
+
+
+@pytest.mark.parametrize("patch,word", [
+    ({"vocab_size": None}, "vocab_size"),
+    ({"num_key_value_heads": 3}, "multiple"),
+    ({"head_dim": 15}, "even"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"attention_bias": True}, "bias"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "yarn"),
+    ({"rope_scaling": {"rope_type": "llama3", "factor": 8.0}}, "low_freq_factor"),
+    ({"rms_norm_eps": 0.0}, "eps"),
+    ({"architectures": []}, "architectures"),
+])
+def test_config_errors_name_the_key(patch, word):
+    d = dict(TINY_A)
+    d.update(patch)
+    with pytest.raises(ConfigError, match=word):
+        LlamaConfig.from_dict(d)
+
+
+def test_registry_knows_llama_and_rejects_others():
+    assert known_architectures() == ["LlamaForCausalLM"]
+    arch = resolve_architecture(TINY_A)
+    spec = arch.build_spec(arch.parse_config(TINY_A))
+    assert len(spec.layers) == 2 and [e.layer for e in spec.schedule] == [0, 1]
+    with pytest.raises(ValueError, match="MistralForCausalLM.*known: LlamaForCausalLM"):
+        resolve_architecture({"architectures": ["MistralForCausalLM"]})
+
+
+def test_expected_weights_tied_and_untied():
+    for cfg, tied in ((TINY_A, True), (TINY_B, False)):
+        arch = resolve_architecture(cfg)
+        names = expected_weights(arch.build_spec(arch.parse_config(cfg)))
+        assert ("lm_head.weight" in names) == (not tied)
+        assert names["model.embed_tokens.weight"].shape == (cfg["vocab_size"], cfg["hidden_size"])
+        assert names["model.layers.0.self_attn.k_proj.weight"].shape == (
+            cfg["num_key_value_heads"] * cfg["head_dim"], cfg["hidden_size"])
+        assert names["model.norm.weight"].kind == "vector"
+        assert len(names) == 2 + 9 * cfg["num_hidden_layers"] + (0 if tied else 1)
+
+
+def test_engine_config_dtype_names():
+    assert EngineConfig(dtype="bf16").dtype == "bfloat16" and EngineConfig(dtype="fp32").dtype == "float32"
+    with pytest.raises(ValueError):
+        EngineConfig(dtype="float16")
+
+
+def test_safetensors_round_trip_keeps_dtypes():
+    d = tempfile.mkdtemp()
+    t = {"a": torch.randn(3, 5), "b": torch.randn(7).to(torch.bfloat16), "c": torch.arange(6, dtype=torch.int32).view(2, 3)}
+    write_tensors(os.path.join(d, "x.safetensors"), t)
+    back = read_tensors(os.path.join(d, "x.safetensors"))
+    for k in t:
+        assert back[k].dtype == t[k].dtype and torch.equal(back[k], t[k])
+    header, _ = read_header(os.path.join(d, "x.safetensors"))
+    assert header["b"]["dtype"] == "BF16" and header["c"]["shape"] == [2, 3]
+
+
+def test_truncated_file_is_reported():
+    src = os.path.join(model_dir("tiny_a"), "model.safetensors")
+    d = tempfile.mkdtemp()
+    data = open(src, "rb").read()
+    open(os.path.join(d, "model.safetensors"), "wb").write(data[:len(data) // 2])
+    with pytest.raises(SafetensorsError, match="truncated"):
+        read_header(os.path.join(d, "model.safetensors"))
+
+
+def _folder_with(tensors, cfg=TINY_A):
+    d = tempfile.mkdtemp()
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    write_tensors(os.path.join(d, "model.safetensors"), tensors)
+    return d
+
+
+def test_loader_lists_missing_unexpected_and_wrong_shapes_in_one_error():
+    arch = resolve_architecture(TINY_A)
+    want = expected_weights(arch.build_spec(arch.parse_config(TINY_A)))
+    good = read_tensors(os.path.join(model_dir("tiny_a"), "model.safetensors"))
+    assert set(check_and_load(model_dir("tiny_a"), want)) == set(want)
+    bad = dict(good)
+    del bad["model.layers.1.mlp.up_proj.weight"]
+    del bad["model.norm.weight"]
+    bad["lm_head.weight"] = torch.zeros(256, 64)                       # tied model: not wanted
+    bad["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(64, 63)  # wrong shape
+    with pytest.raises(WeightError) as ei:
+        check_and_load(_folder_with(bad), want)
+    e = ei.value
+    assert e.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
+    assert e.unexpected == ["lm_head.weight"]
+    assert [w[0] for w in e.wrong_shape] == ["model.layers.0.self_attn.q_proj.weight"]
+    msg = str(e)
+    for word in ("missing (2)", "unexpected (1)", "wrong shape (1)", "stored (64, 63), wanted (64, 64)"):
+        assert word in msg
+
+
+def test_loader_keeps_stored_dtype_and_rejects_integer_matrices():
+    arch = resolve_architecture(TINY_A)
+    want = expected_weights(arch.build_spec(arch.parse_config(TINY_A)))
+    t16 = check_and_load(model_dir("tiny_a", "bfloat16"), want)
+    t32 = check_and_load(model_dir("tiny_a", "float32"), want)
+    assert all(v.dtype == torch.bfloat16 for v in t16.values())
+    assert all(v.dtype == torch.float32 for v in t32.values())
+    bad = dict(t32)
+    bad["model.norm.weight"] = torch.ones(64, dtype=torch.int32)
+    with pytest.raises(WeightError, match="wrong dtype"):
+        check_and_load(_folder_with(bad), want)
+
+
+def test_random_weights_are_a_function_of_config_and_seed():
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+    a, b, c = tempfile.mkdtemp(), tempfile.mkdtemp(), tempfile.mkdtemp()
+    write_random_model(a, TINY_A, 3, 0.02)
+    write_random_model(b, TINY_A, 3, 0.02)
+    write_random_model(c, TINY_A, 4, 0.02)
+    ta, tb, tc = (read_tensors(os.path.join(x, "model.safetensors")) for x in (a, b, c))
+    assert all(torch.equal(ta[k], tb[k]) for k in ta)
+    assert not torch.equal(ta["model.embed_tokens.weight"], tc["model.embed_tokens.weight"])
+    assert abs(float(ta["model.norm.weight"].mean()) - 1.0) < 0.02
+    assert abs(float(ta["model.embed_tokens.weight"].std()) - 0.02) < 0.002
+    assert json.load(open(os.path.join(a, "config.json")))["hidden_size"] == 64
+    for x in (a, b, c):
+        shutil.rmtree(x)
+
+
+def test_no_gpu_means_a_clear_error_not_a_fallback():
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is visible")
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ModelRunner(model_dir("tiny_a"), EngineConfig(dtype="float32", num_pages=4))

@@ -1,0 +1,193 @@
+"""The scheduler's decisions, with the native cache manager and no model: admission in
+order, prompts cut under the token budget, decode beside prefill, finishing, and what
+happens when pages run out (the latest arrival is dropped, goes to the queue's front,
+and is recomputed; a request too large for the pool ends with an error)."""
+
+import random
+
+import pytest
+
+from kv_cache_optimization_for_llm_b200.cache import host_runtime
+
+H = host_runtime()
+
+
+def make(pages=16, page_size=4, slots=4, seqs=4, budget=16, model_len=64, chunk=0):
+    cache = H.CacheManager([H.GroupSpec(page_size, 0)], [pages], slots)
+    return cache, H.Scheduler(cache, H.SchedulerConfig(seqs, budget, model_len, chunk))
+
+
+def run_step(sched, token_of=lambda rid, pos: (rid * 31 + pos) % 97, stop=None):
+    plan = sched.schedule()
+    sched.commit(plan)
+    out = []
+    for e in plan.entries:
+        if e.sample:
+            tok = token_of(e.id, e.start + len(e.tokens))
+            reason = sched.append_token(e.id, tok, stop is not None and tok == stop)
+            out.append((e.id, tok, reason))
+    return plan, out
+
+
+def test_prompt_is_cut_under_the_budget_and_decode_goes_first():
+    cache, s = make(budget=8)
+    s.add(0, list(range(20)), 4)
+    plan, _ = run_step(s)
+    assert [(e.id, e.start, len(e.tokens), e.sample) for e in plan.entries] == [(0, 0, 8, False)]
+    s.add(1, list(range(5)), 4)
+    plan, _ = run_step(s)     # request 0 continues (8 more), nothing left for request 1
+    assert [(e.id, e.start, len(e.tokens)) for e in plan.entries] == [(0, 8, 8)]
+    plan, out = run_step(s)   # 0 finishes its prompt (4 tokens, sampled), 1 gets the other 4
+    assert [(e.id, e.start, len(e.tokens), e.sample) for e in plan.entries] == [(0, 16, 4, True), (1, 0, 4, False)]
+    assert out[0][0] == 0
+    plan, out = run_step(s)   # decode token of 0 beside the last prompt token of 1
+    assert [(e.id, len(e.tokens), e.sample) for e in plan.entries] == [(0, 1, True), (1, 1, True)]
+    assert plan.num_tokens == 2 and cache.check() == ""
+
+
+def test_chunk_cap_and_two_token_portions():
+    _, s = make(budget=64, chunk=2)
+    s.add(0, list(range(7)), 2)
+    sizes = []
+    while s.has_unfinished():
+        plan, _ = run_step(s)
+        sizes.append([len(e.tokens) for e in plan.entries])
+    assert sizes == [[2], [2], [2], [1], [1]]
+    assert s.output(0) == [(0 * 31 + 7) % 97, (0 * 31 + 8) % 97]
+    assert s.finish_reason(0) == H.FinishReason.LENGTH
+
+
+def test_admission_is_fcfs_and_limited_by_seats():
+    cache, s = make(seqs=2, slots=2, budget=64)
+    for i in range(4):
+        s.add(i, [1, 2, 3], 2)
+    plan, _ = run_step(s)
+    assert [e.id for e in plan.entries] == [0, 1] and s.num_waiting() == 2
+    plan, _ = run_step(s)     # both produce their second token and finish
+    assert s.is_finished(0) and s.is_finished(1)
+    plan, _ = run_step(s)
+    assert [e.id for e in plan.entries] == [2, 3]
+    assert cache.check() == ""
+
+
+def test_stop_token_finishes_and_is_not_kept():
+    _, s = make()
+    s.add(5, [9, 9], 10)
+    toks = iter([11, 12, 77])
+    reasons = []
+    while s.has_unfinished():
+        _, out = run_step(s, token_of=lambda rid, pos: next(toks), stop=77)
+        reasons.append(out[0][2])
+    assert s.output(5) == [11, 12] and reasons[-1] == H.FinishReason.STOP
+    assert H.finish_reason_name(s.finish_reason(5)) == "stop"
+
+
+def test_model_len_ends_a_request():
+    _, s = make(model_len=8, budget=64)
+    s.add(0, [1] * 5, 100)
+    while s.has_unfinished():
+        run_step(s)
+    assert len(s.tokens(0)) == 8 and s.finish_reason(0) == H.FinishReason.MODEL_LEN
+
+
+def test_bad_requests_are_refused_at_the_door():
+    _, s = make(pages=4, page_size=4, model_len=64)
+    with pytest.raises(ValueError, match="empty"):
+        s.add(0, [], 4)
+    with pytest.raises(ValueError, match="max_tokens"):
+        s.add(0, [1], 0)
+    with pytest.raises(ValueError, match="pages"):
+        s.add(0, [1] * 16, 4)          # 17 tokens need 5 pages, the pool has 4
+    with pytest.raises(ValueError, match="max_model_len"):
+        s.add(0, [1] * 64, 4)
+    s.add(0, [1], 4)
+    with pytest.raises(ValueError, match="in use"):
+        s.add(0, [1], 4)
+
+
+def test_out_of_pages_drops_the_latest_arrival_and_recomputes_it():
+    cache, s = make(pages=6, page_size=4, budget=64)
+    s.add(0, [1] * 7, 10)     # 2 pages, grows to 5
+    s.add(1, [2] * 7, 10)
+    s.add(2, [3] * 7, 10)
+    plan, _ = run_step(s)     # all admitted: 6 pages taken
+    assert len(plan.entries) == 3 and cache.free_pages(0) == 0
+    plan, _ = run_step(s)     # token 8 of each fits its second page
+    assert plan.preempted == []
+    plan, _ = run_step(s)     # token 9 needs a third page each: 2 (the latest) is dropped, 0 and 1 go on
+    assert plan.preempted == [2] and [e.id for e in plan.entries] == [0, 1]
+    assert s.num_waiting() == 1 and s.preemptions_of(2) == 1 and s.preemptions_of(1) == 0
+    assert cache.check() == "" and cache.live_requests() == 2 and cache.free_pages(0) == 0
+    before = list(s.tokens(2))
+    assert len(before) == 9   # its prompt and the two tokens it had produced
+    came_back = None
+    for _ in range(200):
+        plan, _ = run_step(s)
+        assert cache.check() == ""
+        back = [e for e in plan.entries if e.id == 2]
+        if back:
+            came_back = back[0]
+            break
+    # it is recomputed as one prompt: its own prompt followed by what it had produced
+    assert came_back is not None and came_back.start == 0 and came_back.sample
+    assert list(came_back.tokens)[:9] == before
+    while s.has_unfinished():
+        run_step(s)
+        assert cache.check() == ""
+    for i in range(3):
+        assert len(s.output(i)) == 10 and s.finish_reason(i) == H.FinishReason.LENGTH
+        # no token was produced twice or lost: outputs follow the position rule
+        assert s.output(i) == [(i * 31 + p) % 97 for p in range(7, 17)]
+    assert s.stats().preemptions >= 1 and s.stats().recomputed_tokens > 0
+    assert cache.free_pages(0) == 6 and cache.free_slots() == 4
+
+
+def test_no_admission_in_a_step_that_preempted():
+    cache, s = make(pages=4, page_size=4, budget=64, seqs=4)
+    s.add(0, [1] * 8, 20)
+    s.add(1, [2] * 7, 20)
+    run_step(s)
+    s.add(2, [3] * 2, 5)
+    plan, _ = run_step(s)     # 0 needs a third page: 1 is dropped; 2 must not slip in ahead of it
+    assert plan.preempted == [1] and [e.id for e in plan.entries] == [0]
+    assert s.num_waiting() == 2
+
+
+def test_a_request_too_large_for_the_pool_ends_with_an_error():
+    cache, s = make(pages=3, page_size=4, budget=64, model_len=64)
+    s.add(0, [1] * 10, 30)    # fits at first (3 pages), cannot grow beyond 12 tokens
+    reasons = []
+    while s.has_unfinished():
+        plan, out = run_step(s)
+        reasons += [s.finish_reason(i) for i in plan.finished]
+    assert reasons == [H.FinishReason.CACHE_EXHAUSTED]
+    assert H.finish_reason_name(reasons[0]) == "kv_cache_exhausted"
+    # 12 tokens fill the 3 pages; the 13th (the 3rd produced) can be sampled but not stored
+    assert len(s.output(0)) == 3 and cache.free_pages(0) == 3 and cache.check() == ""
+
+
+def test_random_workloads_finish_with_exact_token_counts():
+    rng = random.Random(4)
+    for trial in range(25):
+        pages = rng.randint(6, 20)
+        cache, s = make(pages=pages, page_size=4, slots=4, seqs=rng.randint(1, 4),
+                        budget=rng.randint(2, 24), model_len=80, chunk=rng.choice([0, 0, 2, 5]))
+        want = {}
+        pending = []
+        for i in range(rng.randint(3, 10)):
+            n_prompt = rng.randint(1, min(4 * pages - 8, 30))
+            n_out = rng.randint(1, max(1, min(20, 4 * pages - n_prompt - 1)))
+            pending.append((i, [rng.randrange(97) for _ in range(n_prompt)], n_out))
+            want[i] = n_out
+        steps = 0
+        while pending or s.has_unfinished():
+            if pending and rng.random() < 0.5:
+                s.add(*pending.pop(0))
+            plan, _ = run_step(s)
+            assert plan.num_tokens <= s.config().max_num_batched_tokens
+            assert cache.check() == ""
+            steps += 1
+            assert steps < 5000, "the scheduler stopped making progress"
+        for i, n in want.items():
+            assert len(s.output(i)) == n and s.finish_reason(i) == H.FinishReason.LENGTH
+        assert cache.free_pages(0) == pages and cache.free_slots() == 4
