@@ -1,0 +1,311 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Llama-3.2-1B size, one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+A "step" is one decode step of ``--batch`` requests.  Each request is a 512-token
+uniform-random prompt; after the prompts are read, W decode steps warm up and
+exactly K are timed, once on the device (CUDA events on the launching stream:
+``value``) and once end to end through the Python entry point (host token ids in,
+sampled ids out at every step: ``e2e``).  Weights are random (N(0, 0.02), norms
+1 + N(0, 0.02)), bfloat16, 16-token pages, context limit 4096.  One JSON line goes
+to standard output; progress goes to standard error.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 128256, "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 131072, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+FULL_LAYERS = LLAMA_1B["num_hidden_layers"]
+CONTEXT_LEN = 4096
+PROMPT_LEN = 512
+NEW_TOKENS = 256
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def log(msg):
+    print(f"[bench] {msg}", file=sys.stderr, flush=True)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in d:
+                out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            return out
+        except Exception as e:  # an unreadable file must not cost the run
+            log(f"MEASURED_PEAKS.json could not be used ({e}); falling back")
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.lines = None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows):
+        """Clocks of the samples that fall inside the timed windows [(t0, t1), ...]."""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.lines:
+            if not any(a <= t <= b for a, b in windows):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def model_numbers(cfg, layers):
+    """Bytes and FLOPs of this model's steps, from the configuration."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    layer_matrix = (nq * d + 2 * nkv * d) * H + H * nq * d + 3 * I * H
+    weight_elems = layers * (layer_matrix + 2 * H) + V * H + H
+    return {
+        "weight_bytes": 2 * weight_elems,                   # bfloat16, every weight read once per step
+        "kv_bytes_per_token": layers * 2 * nkv * d * 2,      # keys and values, bfloat16
+        "layer_matrix_elems": layer_matrix,
+        "attn_flops_per_pair": 4 * nq * d,                   # q.k and p.v per (query, key) pair, all heads
+    }
+
+
+def prefill_flops(cfg, layers, T):
+    n = model_numbers(cfg, layers)
+    gemm = 2 * T * layers * n["layer_matrix_elems"] + 2 * cfg["vocab_size"] * cfg["hidden_size"]
+    attn = layers * n["attn_flops_per_pair"] * T * (T + 1) // 2
+    return gemm + attn
+
+
+def run_decode(llm, batch, steps, warmup, end_to_end, seed):
+    """Reads ``batch`` prompts, warms up, times ``steps`` decode steps.  Returns
+    (seconds, mean context during the timed steps, launches, (t0, t1) wall window)."""
+    import numpy as np
+    import torch
+    from kv_cache_optimization_for_llm_b200 import SamplingParams, ops
+    eng = llm.engine
+    rng = np.random.default_rng(seed)
+    vocab = eng.runner.vocab_size
+    sp = SamplingParams(max_tokens=NEW_TOKENS, ignore_eos=True)
+    ids = [eng.add_request(rng.integers(0, vocab, PROMPT_LEN).tolist(), sp) for _ in range(batch)]
+    produced = {i: 0 for i in ids}
+    while min(produced.values()) < 1:          # read the prompts (mixed steps until every request decodes)
+        for ev in eng.step():
+            if ev.token is not None:
+                produced[ev.request_id] += 1
+    lead = max(produced.values())
+    for _ in range(max(0, warmup - (lead - 1))):
+        eng.step()
+        lead += 1
+    if lead + steps > NEW_TOKENS:
+        raise SystemExit(f"{lead} tokens were produced before timing; {steps} more exceed the budget of {NEW_TOKENS}")
+    torch.cuda.synchronize()
+    ctx0 = PROMPT_LEN + max(len(eng.output(i)) for i in ids)
+    launches0 = ops.launch_count + eng.runner.graph_launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    start.record()
+    n_tok = 0
+    for _ in range(steps):
+        n_tok += sum(1 for ev in eng.step() if ev.token is not None)
+    stop.record()
+    torch.cuda.synchronize()
+    w1 = time.perf_counter()
+    assert n_tok == batch * steps, f"{n_tok} tokens from {batch} requests in {steps} steps"
+    launches = ops.launch_count + eng.runner.graph_launches - launches0
+    seconds = (w1 - w0) if end_to_end else start.elapsed_time(stop) / 1000.0
+    for i in ids:
+        eng.abort(i)
+    assert eng.runner.manager.check() == "" and eng.runner.manager.live_requests() == 0
+    return seconds, ctx0 + (steps - 1) / 2.0, launches, (w0, w1)
+
+
+def run_prefill(llm, reps, warmup, seed):
+    import numpy as np
+    import torch
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    r = llm.engine.runner
+    rng = np.random.default_rng(seed)
+    toks = rng.integers(0, r.vocab_size, PREFILL_TOKENS).tolist()
+    times = []
+    for k in range(warmup + reps):
+        rid = 10_000_000 + k
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        logits = r.step([StepEntry(rid, toks, 0, [PREFILL_TOKENS - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        assert logits.shape == (1, r.vocab_size)
+        r.release(rid)
+        if k >= warmup:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "upstream is a CMake/CUDA program with no setup.py or pyproject.toml (pip: 'not installable'), "
+                          "its sizes are compile-time constants for sm_75 and it needs the real checkpoint"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only (this engine runs on one GPU); got --gpus {args.gpus}")
+        return 2
+    if args.steps < 1 or args.warmup < 3 or args.steps + args.warmup + 2 > NEW_TOKENS:
+        print(f"need steps >= 1, warmup >= 3 and steps + warmup + 2 <= {NEW_TOKENS}")
+        return 2
+
+    import torch
+    from kv_cache_optimization_for_llm_b200 import LLM
+
+    cfg = dict(LLAMA_1B)
+    cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    nums = model_numbers(cfg, args.layers)
+    max_batch = max(args.batch, 1 if args.skip_points else 64)
+    log(f"building Llama-3.2-1B shape, {args.layers} layers, random bfloat16 weights")
+    llm = LLM.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", page_size=PAGE_SIZE,
+                          num_pages=max_batch * (CONTEXT_LEN // PAGE_SIZE) // 4 + PREFILL_TOKENS // PAGE_SIZE,
+                          max_num_seqs=max_batch, max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT_LEN)
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+
+    log(f"decode, batch {args.batch}: device-timed")
+    sec, mean_ctx, launches, win = run_decode(llm, args.batch, args.steps, args.warmup, False, seed=1)
+    windows.append(win)
+    value = args.batch * args.steps / sec
+    ms_per_step = 1000.0 * sec / args.steps
+    log(f"  {value:.0f} tok/s, {ms_per_step:.3f} ms/step, {launches} launches")
+    log(f"decode, batch {args.batch}: end to end")
+    sec_e, _, _, win = run_decode(llm, args.batch, args.steps, args.warmup, True, seed=1)
+    windows.append(win)
+    e2e = args.batch * args.steps / sec_e
+    log(f"  {e2e:.0f} tok/s")
+
+    step_bytes = nums["weight_bytes"] + args.batch * mean_ctx * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_per_step / 1000.0) / 1e9
+    points, prefill = {}, None
+    if not args.skip_points:
+        for b in (1, 64):
+            log(f"decode, batch {b}")
+            s, _, _, win = run_decode(llm, b, args.steps, args.warmup, False, seed=2 + b)
+            windows.append(win)
+            points[f"decode_b{b}"] = round(b * args.steps / s, 1)
+            log(f"  {points[f'decode_b{b}']:.0f} tok/s")
+        log(f"prefill of {PREFILL_TOKENS} tokens")
+        w0 = time.perf_counter()
+        ms = run_prefill(llm, reps=5, warmup=3, seed=9)
+        windows.append((w0, time.perf_counter()))
+        fl = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+        prefill = {"value": round(PREFILL_TOKENS / (ms / 1000.0), 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
+                   "frac": round(fl / (ms / 1000.0) / (pk["bf16_tflops"] * 1e12), 4)}
+        log(f"  {prefill['value']:.0f} tok/s, {ms:.2f} ms, {prefill['frac']:.3f} of {pk['source']} bf16 peak")
+    sampler.stop()
+    clocks = sampler.summary(windows)
+
+    b_in = llm.engine.runner.builder.last_h2d_bytes + 4 * 4 * args.batch   # batch arrays + sampler parameters
+    b_out = 4 * args.batch + 4                                              # sampled ids + the status word
+    line = {
+        "metric": "decode tok/s (Llama-3.2-1B shape, bf16, batch 8, 512-token prompts)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random-init weights N(0,0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.2-1B shape (LlamaForCausalLM)", "layers": args.layers, "layers_full_model": FULL_LAYERS,
+            "hidden_size": cfg["hidden_size"], "intermediate_size": cfg["intermediate_size"],
+            "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "vocab_size": cfg["vocab_size"], "tied_lm_head": True,
+            "global_batch": args.batch, "prompt_len": PROMPT_LEN, "new_tokens": NEW_TOKENS,
+            "context_len": CONTEXT_LEN, "page_size": PAGE_SIZE, "kv_dtype": "bf16", "parallelism": "none (1 GPU)",
+            "l2": "inputs larger than L2: 2.47 GB of weights are streamed every step",
+            "cuda_graphs": bool(llm.engine.config.use_cuda_graphs),
+        },
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(b_in),
+                "d2h_bytes_per_step": int(b_out)},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]},
+        "clocks": clocks,
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    if points:
+        line["points"] = points
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

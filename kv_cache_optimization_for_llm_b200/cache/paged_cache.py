@@ -70,13 +70,23 @@ class PagedCache:
         self.states: Dict[int, torch.Tensor] = {}
         self._entry_specs, self._cache_of = list(entry_specs), list(cache_of)
         if allocate:
+            # One page and one slot more than the manager hands out: padding rows of a
+            # fixed-shape (graph) batch write there.
             for (nkv, d, _w), n in zip(self.group_keys, self.group_entries):
-                self.kv.append(torch.zeros((max(n, 0), 2, self.num_pages, nkv, self.page_size, d),
+                self.kv.append(torch.zeros((max(n, 0), 2, self.num_pages + 1, nkv, self.page_size, d),
                                            dtype=dtype, device=self.device) if n else None)
             for i, spec in enumerate(entry_specs):
                 if isinstance(spec, SlotStateSpec) and cache_of[i] is None:
-                    self.states[i] = torch.zeros((self.num_slots,) + tuple(spec.shape), dtype=spec.dtype,
+                    self.states[i] = torch.zeros((self.num_slots + 1,) + tuple(spec.shape), dtype=spec.dtype,
                                                  device=self.device)
+
+    @property
+    def scratch_page(self) -> int:
+        return self.num_pages
+
+    @property
+    def scratch_slot(self) -> int:
+        return self.num_slots
 
     def bytes_per_page(self) -> int:
         esz = torch.empty((), dtype=self.dtype).element_size()

@@ -131,3 +131,251 @@ KVB_EXPORT int kvb_paged_attention_generic(const void* q, int q_row_stride, cons
                                    (T*)out, nq, nkv, d, scale, window, status)));
   return kvb_launch_result();
 }
+
+// ===========================================================================
+// Decode attention: every request brings one query token.  Split over the keys.
+//
+// Block (kv head, request, key block b) takes the keys [b*KB, (b+1)*KB) of its
+// request and all `group` query heads that share the kv head, so each key and
+// value is read from memory once for the group (upstream reads them once per query
+// head: paged_attention/src/kernels.cu:150-219).  A thread owns one key for the
+// scores (its K row against the group's queries, which sit pre-scaled in shared
+// memory), the block agrees on max and sum per head, then each warp folds its 32
+// values into the output dims its lanes own.  The block writes an unnormalised
+// partial (o, m, l) to scratch; `decode_attention_combine_kernel` merges the key
+// blocks of a (request, head) in ascending order.  Key blocks are cut at absolute
+// positions with a size fixed by the engine, so a token's sums do not depend on
+// the batch it runs in.
+// ===========================================================================
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+
+constexpr int kDecThreads = 128;  // 4 warps, 128 keys per pass
+
+template <typename T, int D, int GMAX>
+__global__ void __launch_bounds__(kDecThreads)
+decode_attention_split_kernel(const T* __restrict__ q_base, int q_row_stride, const T* __restrict__ k_pages,
+                              const T* __restrict__ v_pages, const int* __restrict__ block_table,
+                              int max_pages, int page_size, int num_pages, const int* __restrict__ q_start,
+                              const int* __restrict__ ctx_len, float* __restrict__ part_o,
+                              float* __restrict__ part_ml, int nq, int nkv, int G, float scale, int window,
+                              int KB, int NB, int* status) {
+  constexpr int DPL = D / 32;  // output dims per lane
+  __shared__ __align__(16) float q_s[GMAX][D];
+  __shared__ float red_s[4][GMAX];
+  __shared__ float acc_s[4][GMAX][D];
+
+  const int hk = blockIdx.x, r = blockIdx.y, b = blockIdx.z;
+  const int pos = ctx_len[r] - 1;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int k0 = b * KB;
+  if (k0 > pos || k0 + KB <= lo) return;  // no key of this block is read; combine skips it too
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* table = block_table + (size_t)r * max_pages;
+
+  const T* q = q_base + (size_t)q_start[r] * q_row_stride + (size_t)hk * G * D;
+  for (int i = tid; i < G * D; i += kDecThreads) q_s[i / D][i % D] = to_f32(q[i]) * scale;
+  __syncthreads();
+
+  float m_run[GMAX], l_run[GMAX], acc[GMAX][DPL];
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g) {
+    m_run[g] = -CUDART_INF_F; l_run[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < DPL; ++e) acc[g][e] = 0.f;
+  }
+
+  const int k_end = min(k0 + KB, pos + 1);
+  for (int base = k0; base < k_end; base += kDecThreads) {
+    const int j = base + tid;
+    const bool valid = j < k_end && j >= lo;
+    long long off = -1;
+    float s[GMAX];
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) s[g] = -CUDART_INF_F;
+    if (valid) {
+      const int lp = j / page_size;
+      const int page = lp < max_pages ? table[lp] : -1;
+      if (page < 0 || page >= num_pages) {
+        atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      } else {
+        off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * D;
+        const T* k = k_pages + off;
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g) s[g] = 0.f;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+          float kf[8];
+          Vec8<T>::load(k + c * 8, kf);
+#pragma unroll
+          for (int g = 0; g < GMAX; ++g) {
+            if (g < G) {
+              const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][c * 8]);
+              const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][c * 8 + 4]);
+              float t = s[g];
+              t = fmaf(qa.x, kf[0], t); t = fmaf(qa.y, kf[1], t); t = fmaf(qa.z, kf[2], t); t = fmaf(qa.w, kf[3], t);
+              t = fmaf(qb.x, kf[4], t); t = fmaf(qb.y, kf[5], t); t = fmaf(qb.z, kf[6], t); t = fmaf(qb.w, kf[7], t);
+              s[g] = t;
+            }
+          }
+        }
+      }
+    }
+    // block-wide max per head
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      const float wm = warp_max(g < G ? s[g] : -CUDART_INF_F);
+      if (lane == 0) red_s[warp][g] = wm;
+    }
+    __syncthreads();
+    float p[GMAX], corr[GMAX];
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      const float bm = fmaxf(fmaxf(red_s[0][g], red_s[1][g]), fmaxf(red_s[2][g], red_s[3][g]));
+      const float m_new = fmaxf(m_run[g], bm);
+      corr[g] = (m_run[g] == -CUDART_INF_F) ? 0.f : __expf(m_run[g] - m_new);
+      p[g] = (off >= 0 && g < G) ? __expf(s[g] - m_new) : 0.f;
+      m_run[g] = m_new;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      const float ws = warp_sum(p[g]);
+      if (lane == 0) red_s[warp][g] = ws;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      l_run[g] = l_run[g] * corr[g] + ((red_s[0][g] + red_s[1][g]) + (red_s[2][g] + red_s[3][g]));
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) acc[g][e] *= corr[g];
+    }
+    __syncthreads();
+    // each warp folds the values of its own 32 keys into the dims its lanes own
+    const int n_here = min(32, k_end - (base + warp * 32));
+    for (int jj = 0; jj < n_here; ++jj) {
+      const long long oj = __shfl_sync(0xffffffffu, off, jj);
+      if (oj < 0) continue;
+      float vf[DPL];
+      const T* v = v_pages + oj + lane * DPL;
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) vf[e] = to_f32(v[e]);
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        if (g < G) {
+          const float pj = __shfl_sync(0xffffffffu, p[g], jj);
+#pragma unroll
+          for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
+        }
+      }
+    }
+  }
+  // sum the four warps' partial outputs in a fixed order
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g)
+    if (g < G)
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) acc_s[warp][g][lane * DPL + e] = acc[g][e];
+  __syncthreads();
+  for (int i = tid; i < G * D; i += kDecThreads) {
+    const int g = i / D, dd = i % D;
+    const float o = (acc_s[0][g][dd] + acc_s[1][g][dd]) + (acc_s[2][g][dd] + acc_s[3][g][dd]);
+    part_o[(((size_t)r * nq + hk * G + g) * NB + b) * D + dd] = o;
+  }
+  if (tid < G) {
+    // m_run and l_run are equal in every thread
+    float mm = 0.f, ll = 0.f;
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) if (g == tid) { mm = m_run[g]; ll = l_run[g]; }
+    float* ml = part_ml + (((size_t)r * nq + hk * G + tid) * NB + b) * 2;
+    ml[0] = mm; ml[1] = ll;
+  }
+}
+
+template <typename T, int D>
+__global__ void decode_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                const int* __restrict__ q_start, const int* __restrict__ ctx_len,
+                                                T* __restrict__ out, int nq, int window, int KB, int NB,
+                                                int* status) {
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int pos = ctx_len[r] - 1;
+  if (pos < 0 || pos / KB >= NB) {  // a context beyond the key blocks the scratch was sized for
+    if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
+    return;
+  }
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int b0 = lo / KB, b1 = pos / KB;  // blocks that hold keys
+  const float* ml = part_ml + ((size_t)r * nq + h) * NB * 2;
+  const float* po = part_o + ((size_t)r * nq + h) * NB * D;
+  float M = -CUDART_INF_F;
+  for (int b = b0; b <= b1; ++b) M = fmaxf(M, ml[2 * b]);
+  float L = 0.f;
+  for (int b = b0; b <= b1; ++b) L += ml[2 * b + 1] * __expf(ml[2 * b] - M);
+  T* o = out + ((size_t)q_start[r] * nq + h) * D;
+  for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+    float a = 0.f;
+    for (int b = b0; b <= b1; ++b) a += po[(size_t)b * D + dd] * __expf(ml[2 * b] - M);
+    o[dd] = from_f32<T>(L > 0.f ? a / L : 0.f);
+  }
+}
+
+template <typename T, int D, int GMAX>
+static int launch_decode(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
+                         const int* block_table, int max_pages, int page_size, int num_pages, const int* q_start,
+                         const int* ctx_len, void* out, float* part_o, float* part_ml, int R, int nq, int nkv,
+                         float scale, int window, int KB, int NB, int* status, cudaStream_t stream) {
+  dim3 grid(nkv, R, NB);
+  decode_attention_split_kernel<T, D, GMAX><<<grid, kDecThreads, 0, stream>>>(
+      (const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages, block_table, max_pages, page_size,
+      num_pages, q_start, ctx_len, part_o, part_ml, nq, nkv, nq / nkv, scale, window, KB, NB, status);
+  decode_attention_combine_kernel<T, D><<<dim3(R, nq), D >= 64 ? 64 : 32, 0, stream>>>(
+      part_o, part_ml, q_start, ctx_len, (T*)out, nq, window, KB, NB, status);
+  return kvb_launch_result();
+}
+
+// Returns 1 when (d, group) has a split kernel: d in {32, 64, 128}, group <= 8.
+KVB_EXPORT int kvb_decode_attention_supported(int d, int group) {
+  return (d == 32 || d == 64 || d == 128) && group >= 1 && group <= 8;
+}
+
+// One query token per request: token row q_start[r], position ctx_len[r]-1.
+// Scratch: part_o [R, nq, NB, d] and part_ml [R, nq, NB, 2] float32, NB = key blocks
+// of KB keys (KB a multiple of 128) covering the longest context the caller allows.
+// Two launches.  Refuses what kvb_decode_attention_supported refuses, and R or NB > 65535.
+KVB_EXPORT int kvb_decode_attention(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
+                                    const int* block_table, int max_pages, int page_size, int num_pages,
+                                    const int* q_start, const int* ctx_len, void* out, float* part_o,
+                                    float* part_ml, int R, int nq, int nkv, int d, float scale, int window,
+                                    int KB, int NB, int dtype, int* status, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (nkv < 1 || nq % nkv || !kvb_decode_attention_supported(d, nq / nkv) || KB % kDecThreads || NB < 1 ||
+      R > 65535 || NB > 65535)
+    return KVB_ERR_BAD_SIZE;
+  const int G = nq / nkv;
+#define KVB_DEC(T, D, GM)                                                                                  \
+  return launch_decode<T, D, GM>(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_size,    \
+                                 num_pages, q_start, ctx_len, out, part_o, part_ml, R, nq, nkv, scale,    \
+                                 window, KB, NB, status, stream)
+#define KVB_DEC_D(T, D) do { if (G <= 2) KVB_DEC(T, D, 2); else if (G <= 4) KVB_DEC(T, D, 4); else KVB_DEC(T, D, 8); } while (0)
+#define KVB_DEC_T(T) do { if (d == 32) KVB_DEC_D(T, 32); else if (d == 64) KVB_DEC_D(T, 64); else KVB_DEC_D(T, 128); } while (0)
+  if (dtype == KVB_BF16) KVB_DEC_T(__nv_bfloat16);
+  if (dtype == KVB_F32) KVB_DEC_T(float);
+  return KVB_ERR_BAD_DTYPE;
+}

@@ -74,14 +74,24 @@ class BatchBuilder:
         self.host_buf = torch.zeros(self.total, dtype=torch.int32, pin_memory=use_cuda)
         self.host_np = self.host_buf.numpy()
         self.dev_buf = torch.zeros(self.total, dtype=torch.int32, device=self.device)
+        self.last_h2d_bytes = 0
 
     def _view(self, buf, name, n=None):
         off, cap = self.offsets[name]
         return buf[off:off + (cap if n is None else n)]
 
-    def build(self, entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None) -> StepBatch:
+    def build(self, entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None,
+              pad_reqs_to: int = 0, scratch_page: int = -1, scratch_slot: int = 0) -> StepBatch:
         """``cache`` is the CacheManager; every entry's pages must already cover
-        ``start + len(tokens)``."""
+        ``start + len(tokens)``.
+
+        ``pad_reqs_to`` > len(entries) appends single-token dummy requests (token 0 at
+        position 0, writing to ``scratch_page`` and ``scratch_slot``, which no real
+        request owns) so that a decode batch fills a captured graph's fixed shape;
+        their rows follow the real ones and their logits are never read."""
+        n_real = len(entries)
+        if pad_reqs_to > n_real:
+            entries = list(entries) + [StepEntry(-1, (0,), 0, ()) for _ in range(pad_reqs_to - n_real)]
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         if R == 0 or T == 0:
@@ -110,7 +120,7 @@ class BatchBuilder:
             qs[r] = t
             rstart[r] = e.start
             ctx[r] = e.start + n
-            slots[r] = cache.slot_of(e.request_id)
+            slots[r] = cache.slot_of(e.request_id) if r < n_real else scratch_slot
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request_id}: wanted place {w} is outside its {n} tokens")
@@ -124,7 +134,8 @@ class BatchBuilder:
         for g, mp in enumerate(self.max_pages):
             bt = self._view(h, f"bt{g}", R * mp).reshape(R, mp)
             bt.fill(-1)
-            for r, e in enumerate(entries):
+            bt[n_real:, 0] = scratch_page
+            for r, e in enumerate(entries[:n_real]):
                 table = cache.block_table(e.request_id, g)
                 if len(table) > mp:
                     raise ValueError(f"request {e.request_id} holds {len(table)} pages in group {g}, "
@@ -137,6 +148,7 @@ class BatchBuilder:
         else:
             used = self.total
         self.dev_buf[:used].copy_(self.host_buf[:used], non_blocking=True)
+        self.last_h2d_bytes = 4 * used
         d = self.dev_buf
         batch = StepBatch(
             num_tokens=T, num_reqs=R,

@@ -43,9 +43,9 @@ class _Live:
 
 
 class LLMEngine:
-    def __init__(self, model_dir, config: Optional[EngineConfig] = None):
+    def __init__(self, model_dir, config: Optional[EngineConfig] = None, random_init: Optional[dict] = None):
         self.config = config or EngineConfig()
-        self.runner = ModelRunner(model_dir, self.config)
+        self.runner = ModelRunner(model_dir, self.config, random_init=random_init)
         host = host_runtime()
         self._host = host
         self.scheduler = host.Scheduler(self.runner.manager, host.SchedulerConfig(

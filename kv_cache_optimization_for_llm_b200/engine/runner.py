@@ -39,7 +39,11 @@ def _require_gpu(device: torch.device) -> None:
 
 
 class ModelRunner:
-    def __init__(self, model_dir, config: Optional[EngineConfig] = None):
+    def __init__(self, model_dir, config: Optional[EngineConfig] = None, random_init: Optional[dict] = None):
+        """``model_dir``: folder with config.json and model.safetensors.  Or
+        ``random_init={"config": <config.json dict>, "seed": s, "std": sd}`` with
+        ``model_dir=None``: the same model with random weights drawn on the device,
+        nothing written to disk."""
         self.config = config or EngineConfig()
         self.device = torch.device(self.config.device)
         _require_gpu(self.device)
@@ -47,13 +51,20 @@ class ModelRunner:
         # float32 means float32: no reduced-precision matrix mode anywhere.
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
-        self.model_dir = Path(model_dir)
-        config_dict = read_config_json(self.model_dir)
+        self.model_dir = Path(model_dir) if model_dir is not None else None
+        if self.model_dir is None and not random_init:
+            raise ValueError("a model folder or random_init is required")
+        config_dict = read_config_json(self.model_dir) if self.model_dir is not None else dict(random_init["config"])
         self.arch = resolve_architecture(config_dict)
         self.model_config = self.arch.parse_config(config_dict)
         self.spec = self.arch.build_spec(self.model_config)
         self.dtype = _TORCH_DTYPE[self.config.dtype]
-        tensors = check_and_load(self.model_dir, expected_weights(self.spec))
+        if self.model_dir is not None:
+            tensors = check_and_load(self.model_dir, expected_weights(self.spec))
+        else:
+            from ..weights.random_init import random_tensors_on_device
+            tensors = random_tensors_on_device(expected_weights(self.spec), int(random_init.get("seed", 0)),
+                                               float(random_init.get("std", 0.02)), self.dtype, self.device)
         self.max_model_len = int(self.config.max_model_len or self.spec.max_position)
         if self.max_model_len > self.spec.max_position:
             raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's "
@@ -82,13 +93,63 @@ class ModelRunner:
         self.builder = BatchBuilder(self.config.max_num_batched_tokens, self.config.max_num_seqs,
                                     self.cache.max_pages, self.device, self.status)
         self.vocab_size = self.spec.vocab_size
+        # Captured decode steps, by padded batch size.
+        self._graphs = {}
+        self._graph_pool = None
+        self.graph_launches = 0   # kernels of this package launched through graph replays
+        self.graph_buckets = []
+        if self.config.use_cuda_graphs:
+            b = 1
+            while b < self.config.max_num_seqs:
+                self.graph_buckets.append(b)
+                b *= 2
+            self.graph_buckets.append(self.config.max_num_seqs)
 
     # ---------------------------------------------------------------- the step function
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch whose pages are already in place.  Returns float32 logits
         [wanted, vocab] on the device, in the order of the entries and their ``want``."""
+        if self.graph_buckets and all(len(e.tokens) == 1 for e in entries):
+            return self._run_decode_graph(entries)
         batch = self.builder.build(entries, self.manager, self.vocab_size)
         return self.model.forward(batch, self.cache)
+
+    def _run_decode_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step of single tokens only: padded to the next captured batch size and
+        replayed as one CUDA graph (captured at first use).  The graph reads the
+        batch arrays at their fixed device addresses; only their contents change."""
+        n = len(entries)
+        bucket = next(b for b in self.graph_buckets if b >= n)
+        wants = [bool(e.want) for e in entries]
+        padded = [StepEntry(e.request_id, e.tokens, e.start, (0,)) for e in entries]
+        batch = self.builder.build(padded, self.manager, self.vocab_size, pad_reqs_to=bucket,
+                                   scratch_page=self.cache.scratch_page, scratch_slot=self.cache.scratch_slot)
+        got = self._graphs.get(bucket)
+        if got is None:
+            # Every row's logits are produced; rows are picked after the replay.
+            rows = torch.arange(bucket, dtype=torch.int32, device=self.device)
+            batch.logit_rows, batch.num_logits = rows, bucket
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.model.forward(batch, self.cache)      # warm-up outside the capture
+            torch.cuda.current_stream().wait_stream(side)
+            before = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.model.forward(batch, self.cache)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            got = (graph, out, ops.launch_count - before, rows)
+            self._graphs[bucket] = got
+            ops.launch_count = before                       # captured, not launched
+        graph, out, launches, _rows = got
+        graph.replay()
+        self.graph_launches += launches
+        if all(wants):
+            return out[:n]
+        keep = [i for i, w in enumerate(wants) if w]
+        return out[keep] if keep else out[:0]
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """``run`` with the cache kept for the caller: admits unknown requests, takes

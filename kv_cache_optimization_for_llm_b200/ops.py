@@ -194,8 +194,60 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return torch.nn.functional.linear(x, w)
 
 
-def attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window) -> torch.Tensor:
-    """Attention of the step's tokens over their requests' pages; picks the kernel."""
+_scratch: Dict[tuple, torch.Tensor] = {}
+
+
+def scratch(key: tuple, shape, dtype, device) -> torch.Tensor:
+    """A buffer that lives as long as the process, one per key: kernels that need
+    global memory beyond their inputs and outputs get it here, so that captured
+    graphs see fixed addresses and steps allocate nothing."""
+    t = _scratch.get(key)
+    if t is None or t.shape != tuple(shape):
+        t = torch.empty(shape, dtype=dtype, device=device)
+        _scratch[key] = t
+    return t
+
+
+def decode_key_blocks(max_positions: int):
+    """(keys per block, number of blocks) of the split decode kernel for an engine that
+    allows ``max_positions`` tokens: at most 64 blocks, 128 keys or a multiple."""
+    kb = 128 * max(1, -(-max_positions // (128 * 64)))
+    return kb, -(-max_positions // kb)
+
+
+def decode_attention_supported(d: int, group: int) -> bool:
+    return bool(lib("attention").kvb_decode_attention_supported(c_int(d), c_int(group)))
+
+
+def decode_attention(qkv, k_pages, v_pages, block_table, q_start, ctx_len, nq, nkv, d, scale, window,
+                     max_positions, status, reqs_capacity=None) -> torch.Tensor:
+    """One query token per request, split over key blocks, all heads of a group together."""
+    _need_cuda(qkv, k_pages)
+    R = ctx_len.numel()
+    T = qkv.shape[0]
+    kb, nb = decode_key_blocks(max_positions)
+    cap = max(R, reqs_capacity or 0)
+    part_o = scratch(("dec_o", qkv.device.index, cap, nq, nb, d), (cap, nq, nb, d), torch.float32, qkv.device)
+    part_ml = scratch(("dec_ml", qkv.device.index, cap, nq, nb), (cap, nq, nb, 2), torch.float32, qkv.device)
+    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+    rc = lib("attention").kvb_decode_attention(
+        _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
+        c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len), _p(out), _p(part_o),
+        _p(part_ml), c_int(R), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)),
+        c_int(kb), c_int(nb), c_int(dtype_code(qkv.dtype)), _p(status), _stream())
+    _check(rc, "decode_attention")
+    global launch_count
+    launch_count += 1  # split and combine
+    return out
+
+
+def attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window, max_positions) -> torch.Tensor:
+    """Attention of the step's tokens over their requests' pages; picks the kernel.
+    float32 always takes the general kernel, whose sums follow absolute positions in
+    one fixed order whatever the shape of the step."""
+    if batch.decode_only and qkv.dtype == torch.bfloat16 and decode_attention_supported(d, nq // nkv):
+        return decode_attention(qkv, k_pages, v_pages, block_table, batch.q_start, batch.ctx_len, nq, nkv, d,
+                                scale, window, max_positions, batch.status)
     return paged_attention_generic(qkv, k_pages, v_pages, block_table, batch.positions, batch.token_req,
                                    nq, nkv, d, scale, window, batch.status)
 

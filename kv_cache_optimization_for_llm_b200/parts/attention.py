@@ -67,5 +67,5 @@ class GroupedQueryAttention(Part):
                           cache.k if cache.write else None, cache.v if cache.write else None,
                           table, cache.page_size, self.nq, self.nkv, self.d, rot, batch.status)
         a = ops.attention(qkv, cache.k, cache.v, table, batch, self.nq, self.nkv, self.d, self.scale,
-                          self.window)
+                          self.window, self.ctx.max_positions)
         return ops.linear(a, self.o)

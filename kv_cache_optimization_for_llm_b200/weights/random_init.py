@@ -36,6 +36,22 @@ def random_tensors(expected: Mapping[str, WeightSpec], seed: int, std: float = 0
     return out
 
 
+def random_tensors_on_device(expected: Mapping[str, WeightSpec], seed: int, std: float, dtype: torch.dtype, device):
+    """The same distribution drawn on the device in the compute dtype, for runs that
+    need a large random model and no file (benchmarks)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(int(seed))
+    out = {}
+    for name in sorted(expected):
+        spec = expected[name]
+        if spec.kind == "table":
+            out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+            continue
+        t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * std
+        out[name] = (t + 1.0) if spec.kind == "vector" else t.to(dtype)
+    return out
+
+
 def write_random_model(model_dir, config_dict: dict, seed: int, std: float = 0.02,
                        storage_dtype: str = "float32") -> Path:
     """Builds the model that ``config_dict`` names (through the registry, as a

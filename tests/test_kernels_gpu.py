@@ -1,0 +1,327 @@
+"""Each kernel alone against the plain implementation, at sizes other than the tiny
+models': widths and vocabularies that are no power of two, head sizes 16..256,
+groups 1..8, page edges, a window's edge, and inputs made so that a single far key
+decides the result."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+def dev(x, dtype=None):
+    t = torch.as_tensor(np.asarray(x))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda().contiguous()
+
+
+def as64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def rel_err(got, ref):
+    return np.abs(as64(got) - ref).max() / max(np.abs(ref).max(), 1e-30)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,H", [(1, 48), (5, 1000), (3, 2048), (2, 13000)])
+def test_add_rmsnorm(dtype, T, H):
+    from kv_cache_optimization_for_llm_b200 import ops
+    rng = np.random.default_rng(T * H)
+    resid = rng.normal(size=(T, H)) * 3
+    delta = as64(dev(rng.normal(size=(T, H)), DT[dtype]))
+    w = 1 + 0.1 * rng.normal(size=H)
+    w = as64(dev(w, torch.float32))
+    r0 = as64(dev(resid, torch.float32))
+    rd = dev(resid, torch.float32)
+    out = ops.add_rmsnorm(rd, dev(delta, DT[dtype]), dev(w, torch.float32), 1e-5, DT[dtype])
+    ref_sum = r0 + delta
+    assert np.abs(as64(rd) - ref_sum).max() < 1e-6 * np.abs(ref_sum).max()        # the residual sum is float32
+    assert rel_err(out, P.rms_norm(ref_sum, w, 1e-5)) < TOL[dtype]
+    # no delta; and selected rows only, residual untouched
+    rd2 = dev(resid, torch.float32)
+    out = ops.add_rmsnorm(rd2, None, dev(w, torch.float32), 1e-5, DT[dtype])
+    assert rel_err(out, P.rms_norm(r0, w, 1e-5)) < TOL[dtype] and np.array_equal(as64(rd2), r0)
+    rows = [T - 1, 0]
+    out = ops.add_rmsnorm(rd2, dev(delta, DT[dtype]), dev(w, torch.float32), 1e-5, DT[dtype],
+                          rows=dev(rows, torch.int32))
+    assert rel_err(out, P.rms_norm(ref_sum[rows], w, 1e-5)) < TOL[dtype] and np.array_equal(as64(rd2), r0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul_and_embedding(dtype):
+    from kv_cache_optimization_for_llm_b200 import ops
+    rng = np.random.default_rng(0)
+    gu = as64(dev(rng.normal(size=(7, 2 * 333)) * 4, DT[dtype]))
+    out = ops.silu_mul(dev(gu, DT[dtype]))
+    g, u = gu[:, :333], gu[:, 333:]
+    assert rel_err(out, g / (1 + np.exp(-g)) * u) < TOL[dtype]
+    table = as64(dev(rng.normal(size=(777, 100)), DT[dtype]))
+    ids = [0, 776, 5, 5, 300]
+    st = status()
+    out = ops.embed_gather(dev(table, DT[dtype]), dev(ids, torch.int32), st)
+    assert out.dtype == torch.float32 and np.array_equal(as64(out), table[ids]) and int(st.item()) == 0
+    ops.embed_gather(dev(table, DT[dtype]), dev([3, 777], torch.int32), st)
+    assert int(st.item()) == 3      # a token outside the table is reported, not read
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1000, 192), (5, 77, 33), (70, 130, 517), (64, 64, 16), (3, 128256 // 8, 100)])
+def test_sgemm_is_true_float32_and_row_independent(M, N, K):
+    from kv_cache_optimization_for_llm_b200 import ops
+    rng = np.random.default_rng(M + N + K)
+    a = rng.normal(size=(M, K)).astype(np.float32)
+    w = rng.normal(size=(N, K)).astype(np.float32)
+    out = ops.linear(dev(a), dev(w))
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    # float32 FMA chains of length K: error ~ K * 2^-24 relative to the sum of magnitudes
+    bound = (np.abs(a).astype(np.float64) @ np.abs(w).astype(np.float64).T) * K * 2.0 ** -24
+    assert (np.abs(as64(out) - ref) <= bound + 1e-30).all()
+    # a tf32 product would miss by ~2^-11 relative: make sure we are far below that
+    assert np.abs(as64(out) - ref).max() < 1e-5 * np.abs(ref).max()
+    # a row's result does not depend on the rows beside it: bit for bit
+    one = ops.linear(dev(a[M - 1:M]), dev(w))
+    assert torch.equal(one[0], out[M - 1])
+
+
+def _paged(k, v, page_size, num_pages, rng, dtype):
+    """Scatters one sequence's keys/values [ctx, nkv, d] into randomly chosen pages.
+    Returns (k_pages, v_pages, table)."""
+    ctx, nkv, d = k.shape
+    n = -(-ctx // page_size)
+    table = rng.permutation(num_pages)[:n]
+    kp = np.zeros((num_pages, nkv, page_size, d))
+    vp = np.zeros_like(kp)
+    kp[:] = 7.0   # poison: an unmapped or stale slot read by mistake shows up
+    vp[:] = -9.0
+    for j in range(ctx):
+        kp[table[j // page_size], :, j % page_size] = k[j]
+        vp[table[j // page_size], :, j % page_size] = v[j]
+    return kp, vp, table
+
+
+def _attention_case(dtype, nq, nkv, d, ctxs, q_lens, page_size, window, seed, spike=None):
+    """Several requests, each with ``q_len`` newest tokens as queries over ``ctx`` cached
+    keys.  Returns what the kernels need and the plain result per token."""
+    rng = np.random.default_rng(seed)
+    R = len(ctxs)
+    max_pages = max(-(-c // page_size) for c in ctxs) + 2
+    num_pages = sum(-(-c // page_size) for c in ctxs) + 3
+    kp = np.full((num_pages, nkv, page_size, d), 7.0)
+    vp = np.full((num_pages, nkv, page_size, d), -9.0)
+    free = list(rng.permutation(num_pages))
+    tables = np.full((R, max_pages), -1, dtype=np.int32)
+    qkv_rows, positions, token_req, refs, q_start, ctx_len = [], [], [], [], [0], []
+    for r, (ctx, ql) in enumerate(zip(ctxs, q_lens)):
+        k = as64(dev(rng.normal(size=(ctx, nkv, d)), DT[dtype]))
+        v = as64(dev(rng.normal(size=(ctx, nkv, d)), DT[dtype]))
+        q = as64(dev(rng.normal(size=(ctx, nq, d)), DT[dtype]))
+        if spike is not None:
+            # one far key matches the last query exactly and strongly: if it is skipped
+            # or misplaced the output is visibly wrong
+            j = spike if spike < ctx else 0
+            k[:, :, 0] = 0.0          # no other key answers along dim 0
+            k[j] = 0.0
+            k[j, :, 0] = 1.0
+            q[ctx - 1] = 0.0
+            q[ctx - 1, :, 0] = 12.0 * math.sqrt(d)
+            k[j], q[ctx - 1] = as64(dev(k[j], DT[dtype])), as64(dev(q[ctx - 1], DT[dtype]))
+        for j in range(ctx):
+            lp = j // page_size
+            if tables[r, lp] < 0:
+                tables[r, lp] = free.pop()
+            kp[tables[r, lp], :, j % page_size] = k[j]
+            vp[tables[r, lp], :, j % page_size] = v[j]
+        full = P.attention(q, k, v, window=window)
+        for i in range(ctx - ql, ctx):
+            row = np.concatenate([q[i].reshape(-1), np.zeros(2 * nkv * d)])
+            qkv_rows.append(row)
+            positions.append(i)
+            token_req.append(r)
+            refs.append(full[i].reshape(-1))
+        q_start.append(len(qkv_rows))
+        ctx_len.append(ctx)
+    return dict(qkv=dev(np.array(qkv_rows), DT[dtype]), kp=dev(kp, DT[dtype]), vp=dev(vp, DT[dtype]),
+                table=dev(tables, torch.int32), positions=dev(positions, torch.int32),
+                token_req=dev(token_req, torch.int32), q_start=dev(q_start, torch.int32),
+                ctx_len=dev(ctx_len, torch.int32), ref=np.array(refs))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [
+    (4, 2, 16, 4, None), (6, 1, 32, 16, None), (5, 5, 48, 16, None), (8, 2, 64, 16, None),
+    (3, 1, 128, 32, None), (2, 2, 256, 8, None), (4, 2, 64, 16, 37), (6, 3, 32, 4, 5),
+])
+def test_generic_attention_mixed_runs(dtype, nq, nkv, d, page_size, window):
+    from kv_cache_optimization_for_llm_b200 import ops
+    c = _attention_case(dtype, nq, nkv, d, ctxs=[1, 33, 130, 64, 257], q_lens=[1, 33, 2, 1, 40],
+                        page_size=page_size, window=window, seed=d + nq)
+    st = status()
+    out = ops.paged_attention_generic(c["qkv"], c["kp"], c["vp"], c["table"], c["positions"], c["token_req"],
+                                      nq, nkv, d, 1 / math.sqrt(d), window, st)
+    assert int(st.item()) == 0
+    assert rel_err(out, c["ref"]) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,d,page_size,window,max_pos", [
+    (8, 2, 64, 16, None, 4096), (32, 8, 64, 16, None, 1024), (6, 1, 32, 16, None, 1024), (24, 8, 128, 16, None, 20000),
+    (8, 8, 128, 32, None, 4096), (16, 2, 64, 8, None, 4096), (8, 2, 64, 16, 100, 4096), (4, 4, 32, 4, 129, 2048),
+])
+def test_decode_attention_split_kernel(dtype, nq, nkv, d, page_size, window, max_pos):
+    from kv_cache_optimization_for_llm_b200 import ops
+    ctxs = [1, 128, 129, 640, 300, 2, 1000]
+    c = _attention_case(dtype, nq, nkv, d, ctxs=ctxs, q_lens=[1] * len(ctxs), page_size=page_size,
+                        window=window, seed=nq * d)
+    st = status()
+    assert ops.decode_attention_supported(d, nq // nkv)
+    out = ops.decode_attention(c["qkv"], c["kp"], c["vp"], c["table"], c["q_start"], c["ctx_len"], nq, nkv, d,
+                               1 / math.sqrt(d), window, max_pos, st)
+    assert int(st.item()) == 0
+    assert rel_err(out, c["ref"]) < TOL[dtype]
+    # a context beyond what the scratch was sized for is reported, not computed wrongly
+    ops.decode_attention(c["qkv"], c["kp"], c["vp"], c["table"], c["q_start"], c["ctx_len"], nq, nkv, d,
+                         1 / math.sqrt(d), window, 512, st)
+    assert int(st.item()) == 2
+
+
+@pytest.mark.parametrize("kernel", ["generic", "decode"])
+@pytest.mark.parametrize("spike", [0, 127, 128, 511, 777])
+def test_a_far_key_among_hundreds_is_found(kernel, spike):
+    """The last query matches exactly one key, far back: the output must be that key's
+    value.  A kernel that drops a key at a page edge, a warp's chunk edge or a key
+    block's edge gives something else entirely."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    nq, nkv, d = 8, 2, 64
+    c = _attention_case("bfloat16", nq, nkv, d, ctxs=[900], q_lens=[1], page_size=16, window=None, seed=spike,
+                        spike=spike)
+    st = status()
+    if kernel == "generic":
+        out = ops.paged_attention_generic(c["qkv"], c["kp"], c["vp"], c["table"], c["positions"], c["token_req"],
+                                          nq, nkv, d, 1 / math.sqrt(d), None, st)
+    else:
+        out = ops.decode_attention(c["qkv"], c["kp"], c["vp"], c["table"], c["q_start"], c["ctx_len"], nq, nkv, d,
+                                   1 / math.sqrt(d), None, 4096, st)
+    assert rel_err(out, c["ref"]) < TOL["bfloat16"]
+    # and the reference itself is dominated by that key (weight > 0.99)
+    page, slot = int(c["table"][0, spike // 16]), spike % 16
+    v_spike = as64(c["vp"][page, :, slot])                 # [nkv, d]
+    want = np.repeat(v_spike, nq // nkv, axis=0).reshape(-1)
+    assert np.abs(c["ref"][0] - want).max() < 0.05
+
+
+def test_unmapped_page_is_reported_not_read():
+    from kv_cache_optimization_for_llm_b200 import ops
+    c = _attention_case("float32", 4, 2, 16, ctxs=[40], q_lens=[1], page_size=4, window=None, seed=1)
+    table = c["table"].clone()
+    table[0, 3] = -1
+    st = status()
+    ops.paged_attention_generic(c["qkv"], c["kp"], c["vp"], table, c["positions"], c["token_req"], 4, 2, 16, 0.25,
+                                None, st)
+    assert int(st.item()) == 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,d,rot,page_size", [(4, 2, 16, 16, 4), (6, 1, 32, 32, 16), (5, 5, 48, 48, 16),
+                                                    (8, 2, 64, 32, 8), (2, 1, 128, 128, 16)])
+def test_rope_and_cache_write(dtype, nq, nkv, d, rot, page_size):
+    from kv_cache_optimization_for_llm_b200 import ops
+    from kv_cache_optimization_for_llm_b200.parts.position import rope_inv_freq
+    rng = np.random.default_rng(d)
+    scaling = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
+    inv = rope_inv_freq(rot, 500000.0, scaling).numpy()
+    assert np.allclose(inv, P.rope_inv_freq(rot, 500000.0, scaling), rtol=1e-12)
+    max_pos = 300
+    ang = np.arange(max_pos)[:, None] * inv[None, :]
+    cos_t, sin_t = dev(np.cos(ang), torch.float32), dev(np.sin(ang), torch.float32)
+    # two requests: tokens at positions 250..255 of request 0 and 0..2 of request 1
+    positions = [250, 251, 252, 253, 254, 255, 0, 1, 2]
+    token_req = [0] * 6 + [1] * 3
+    T = len(positions)
+    qkv = as64(dev(rng.normal(size=(T, (nq + 2 * nkv) * d)), DT[dtype]))
+    num_pages, max_pages = 40, 256 // page_size + 1
+    table = np.full((2, max_pages), -1, dtype=np.int32)
+    pages = rng.permutation(num_pages)
+    table[0, 250 // page_size: 255 // page_size + 1] = pages[:255 // page_size - 250 // page_size + 1]
+    table[1, 0] = pages[10]
+    kp = torch.full((num_pages, nkv, page_size, d), 5.0, dtype=DT[dtype], device="cuda")
+    vp = torch.full((num_pages, nkv, page_size, d), 5.0, dtype=DT[dtype], device="cuda")
+    dq = dev(qkv, DT[dtype])
+    st = status()
+    ops.rope_kv_write(dq, dev(positions, torch.int32), dev(token_req, torch.int32), cos_t, sin_t, kp, vp,
+                      dev(table, torch.int32), page_size, nq, nkv, d, rot, st)
+    assert int(st.item()) == 0
+    q = qkv[:, :nq * d].reshape(T, nq, d)
+    k = qkv[:, nq * d:(nq + nkv) * d].reshape(T, nkv, d)
+    v = qkv[:, (nq + nkv) * d:].reshape(T, nkv, d)
+    c, s = np.cos(ang[positions]), np.sin(ang[positions])
+    def rotate(x):
+        out = x.copy()
+        out[..., :rot] = P.apply_rope(x[..., :rot], c, s)
+        return out
+    got = as64(dq)
+    assert np.abs(got[:, :nq * d].reshape(T, nq, d) - rotate(q)).max() < TOL[dtype] * 4
+    assert np.array_equal(got[:, nq * d:], qkv[:, nq * d:])          # k and v stay as they were in the row
+    kr = rotate(k)
+    written = np.zeros((num_pages, page_size), dtype=bool)
+    for t, (p, r) in enumerate(zip(positions, token_req)):
+        page, slot = table[r, p // page_size], p % page_size
+        written[page, slot] = True
+        assert np.abs(as64(kp[page, :, slot]) - kr[t]).max() < TOL[dtype] * 4
+        assert np.array_equal(as64(vp[page, :, slot]), v[t])
+    # nothing else in the pool was touched
+    untouched = ~written
+    assert (as64(kp).transpose(0, 2, 1, 3)[untouched] == 5.0).all() and (as64(vp).transpose(0, 2, 1, 3)[untouched] == 5.0).all()
+    # a position whose page is not mapped is reported and skipped
+    ops.rope_kv_write(dev(qkv, DT[dtype]), dev([100] * T, torch.int32), dev(token_req, torch.int32), cos_t, sin_t,
+                      kp, vp, dev(table, torch.int32), page_size, nq, nkv, d, rot, st)
+    assert int(st.item()) == 1
+
+
+@pytest.mark.parametrize("V", [100, 1000, 128256, 50257])
+def test_sampling_kernel(V):
+    from kv_cache_optimization_for_llm_b200 import ops
+    rng = np.random.default_rng(V)
+    R = 6
+    logits = rng.normal(0, 2.0, size=(R, V)).astype(np.float32)
+    logits[:, rng.choice(V, 5, replace=False)] += 6.0
+    logits[1, [V - 1, 17]] = 50.0          # a tie: the lower index wins
+    logits[2, 0] = 60.0
+    dl = dev(logits)
+    ids = ops.sample(dl, None, None, None, None, None, None, None).cpu().numpy()
+    assert ids.tolist() == [P.argmax_lowest(logits[r].astype(np.float64)) for r in range(R)]
+    assert ids[1] == 17 and ids[2] == 0
+    temps = np.array([0.7, 1.0, 1.5, 0.0, 0.3, 2.0], dtype=np.float32)
+    seeds = np.array([1, 2, 3, 4, 2 ** 32 - 1, 0], dtype=np.uint32)
+    keys = np.array([0, 7, 8 * 31 + 3, 5, 2 ** 31, 9], dtype=np.uint32)
+    for pos in (0, 1, 513, 70000):
+        poss = np.full(R, pos, dtype=np.uint32)
+        got = ops.sample(dl, dev(temps), dev(seeds.view(np.int32)), dev(keys.view(np.int32)),
+                         dev(poss.view(np.int32)), None, None, None).cpu().numpy()
+        for r in range(R):
+            want = P.sample(logits[r].astype(np.float64), float(temps[r]), int(seeds[r]), int(keys[r]), pos)
+            assert got[r] == want, (r, pos)
+    # repetition penalty through the slots' records
+    mask = torch.zeros((4, V), dtype=torch.uint8, device="cuda")
+    seen = {0: [int(ids[0]), 3], 2: [int(ids[2])]}
+    slots = np.array([0, 1, 2, 3, 1, 3], dtype=np.int32)
+    for slot, toks in seen.items():
+        ops.reset_mask(mask, slot, dev(toks, torch.int32))
+    pen = np.array([1.15, 1.0, 2.0, 1.15, 1.0, 1.0], dtype=np.float32)
+    got = ops.sample(dl, None, None, None, None, dev(pen), mask, dev(slots)).cpu().numpy()
+    for r in range(R):
+        want = P.sample(logits[r].astype(np.float64), 0.0, 0, 0, 0, seen=seen.get(int(slots[r]), []), penalty=float(pen[r]))
+        assert got[r] == want, r
+    assert mask[0, got[0]] == 1 and mask[2, got[2]] == 1 and int(mask[1].sum()) == 0   # new tokens are recorded
