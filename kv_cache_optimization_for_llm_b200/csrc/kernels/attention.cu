@@ -379,3 +379,80 @@ KVB_EXPORT int kvb_decode_attention(const void* q, int q_row_stride, const void*
   if (dtype == KVB_F32) KVB_DEC_T(float);
   return KVB_ERR_BAD_DTYPE;
 }
+
+// ===========================================================================
+// The same decode attention for callers that cannot allocate: the scratch between
+// the split and the combine launch is a static device array of this library.
+// Declared and documented in decode_attention_noalloc.h.
+// ===========================================================================
+#include "decode_attention_noalloc.h"
+
+#include <mutex>
+
+static __device__ __align__(256) float g_decode_noalloc_scratch[KVB_DECODE_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};  // device address of the array, per device ordinal
+
+// In host code `g_decode_noalloc_scratch` is only a handle for the runtime, not an
+// address a kernel could use; the device address has to be asked for, once per
+// device, with that device current.
+int noalloc_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return KVB_ERR_SCRATCH_SETUP;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return KVB_ERR_SCRATCH_SETUP;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+KVB_EXPORT unsigned long long kvb_decode_attention_noalloc_scratch_needed(int R, int nq, int NB, int d) {
+  if (R < 0 || nq < 0 || NB < 0 || d < 0) return ~0ull;
+  return (unsigned long long)R * nq * NB * (unsigned long long)(d + 2);
+}
+
+KVB_EXPORT const char* kvb_decode_attention_noalloc_error(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case KVB_ERR_BAD_DTYPE: return "unsupported dtype (0 = float32, 1 = bfloat16)";
+    case KVB_ERR_BAD_SIZE:
+      return "a size the decode kernel refuses (head size must be 32, 64 or 128, group size 1..8, KB a multiple of 128)";
+    case KVB_ERR_SCRATCH_TOO_SMALL:
+      return "R * nq * NB * (d + 2) exceeds the 4 Mi floats of built-in scratch; use kvb_decode_attention with "
+             "caller-provided scratch, or fewer requests / key blocks per call";
+    case KVB_ERR_SCRATCH_SETUP: return "the built-in scratch could not be located on the current device";
+    default: return code > 0 ? "a CUDA runtime error (the code is a cudaError_t)" : "unknown error code";
+  }
+}
+
+KVB_EXPORT int kvb_decode_attention_noalloc(const void* q, int q_row_stride, const void* k_pages,
+                                            const void* v_pages, const int* block_table, int max_pages,
+                                            int page_size, int num_pages, const int* q_start,
+                                            const int* ctx_len, void* out, int R, int nq, int nkv, int d,
+                                            float scale, int window, int KB, int NB, int dtype, int* status,
+                                            cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (nq < 1 || NB < 1 || d < 1) return KVB_ERR_BAD_SIZE;
+  const unsigned long long need = kvb_decode_attention_noalloc_scratch_needed(R, nq, NB, d);
+  if (need > (unsigned long long)KVB_DECODE_NOALLOC_SCRATCH_FLOATS) return KVB_ERR_SCRATCH_TOO_SMALL;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  // partial outputs first, then the (max, sum) pairs; both offsets keep 16-byte alignment
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)R * nq * NB * d;
+  return kvb_decode_attention(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_size, num_pages,
+                              q_start, ctx_len, out, part_o, part_ml, R, nq, nkv, d, scale, window, KB, NB,
+                              dtype, status, stream);
+}
