@@ -169,54 +169,78 @@ template <> struct Vec8<float> {
 
 constexpr int kDecThreads = 128;  // 4 warps, 128 keys per pass
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+// Grid (kv head, request, slot): slot z takes the key blocks z, z + gridDim.z, ... of its
+// request, so no block of an absent key range is ever launched and the grid does not
+// depend on the contexts' lengths.  The partial result of key block b lands in
+// part_*[..., b], whoever computed it.
 template <typename T, int D, int GMAX>
-__global__ void __launch_bounds__(kDecThreads)
+__global__ void __launch_bounds__(kDecThreads, 5)
 decode_attention_split_kernel(const T* __restrict__ q_base, int q_row_stride, const T* __restrict__ k_pages,
                               const T* __restrict__ v_pages, const int* __restrict__ block_table,
                               int max_pages, int page_size, int num_pages, const int* __restrict__ q_start,
                               const int* __restrict__ ctx_len, float* __restrict__ part_o,
                               float* __restrict__ part_ml, int nq, int nkv, int G, float scale, int window,
                               int KB, int NB, int* status) {
-  constexpr int DPL = D / 32;  // output dims per lane
+  constexpr int DPL = D / 32;                    // output dims per lane
+  constexpr int CPK = D * (int)sizeof(T) / 16;   // 16-byte chunks per value row
   __shared__ __align__(16) float q_s[GMAX][D];
   __shared__ float red_s[4][GMAX];
-  __shared__ float acc_s[4][GMAX][D];
+  extern __shared__ __align__(16) unsigned char dec_smem[];
+  T (*v_s)[32][D] = reinterpret_cast<T (*)[32][D]>(dec_smem);  // each warp stages the values of its 32 keys
 
-  const int hk = blockIdx.x, r = blockIdx.y, b = blockIdx.z;
+  const int hk = blockIdx.x, r = blockIdx.y;
   const int pos = ctx_len[r] - 1;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int k0 = b * KB;
-  if (k0 > pos || k0 + KB <= lo) return;  // no key of this block is read; combine skips it too
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if ((int)blockIdx.z * KB > pos) return;
   const int* table = block_table + (size_t)r * max_pages;
 
   const T* q = q_base + (size_t)q_start[r] * q_row_stride + (size_t)hk * G * D;
   for (int i = tid; i < G * D; i += kDecThreads) q_s[i / D][i % D] = to_f32(q[i]) * scale;
   __syncthreads();
 
-  float m_run[GMAX], l_run[GMAX], acc[GMAX][DPL];
+  for (int b = blockIdx.z; b * KB <= pos && b < NB; b += gridDim.z) {
+    const int k0 = b * KB;
+    if (k0 + KB <= lo) continue;  // the window has passed this block; combine skips it too
+    float m_run[GMAX], l_run[GMAX], acc[GMAX][DPL];
 #pragma unroll
-  for (int g = 0; g < GMAX; ++g) {
-    m_run[g] = -CUDART_INF_F; l_run[g] = 0.f;
+    for (int g = 0; g < GMAX; ++g) {
+      m_run[g] = -CUDART_INF_F; l_run[g] = 0.f;
 #pragma unroll
-    for (int e = 0; e < DPL; ++e) acc[g][e] = 0.f;
-  }
-
-  const int k_end = min(k0 + KB, pos + 1);
-  for (int base = k0; base < k_end; base += kDecThreads) {
-    const int j = base + tid;
-    const bool valid = j < k_end && j >= lo;
-    long long off = -1;
-    float s[GMAX];
+      for (int e = 0; e < DPL; ++e) acc[g][e] = 0.f;
+    }
+    const int k_end = min(k0 + KB, pos + 1);
+    for (int base = k0; base < k_end; base += kDecThreads) {
+      const int j = base + tid;
+      const bool valid = j < k_end && j >= lo;
+      long long off = -1;
+      if (valid) {
+        const int lp = j / page_size;
+        const int page = lp < max_pages ? table[lp] : -1;
+        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        else off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * D;
+      }
+      // the values of this warp's keys start their way to shared memory now and
+      // arrive while the scores are computed
 #pragma unroll
-    for (int g = 0; g < GMAX; ++g) s[g] = -CUDART_INF_F;
-    if (valid) {
-      const int lp = j / page_size;
-      const int page = lp < max_pages ? table[lp] : -1;
-      if (page < 0 || page >= num_pages) {
-        atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
-      } else {
-        off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * D;
+      for (int i = 0; i < CPK; ++i) {
+        const int c = i * 32 + lane;
+        const int key = c / CPK, part = c % CPK;
+        const long long oj = __shfl_sync(0xffffffffu, off, key);
+        if (oj >= 0)
+          cp_async_16(reinterpret_cast<char*>(&v_s[warp][key][0]) + part * 16,
+                      reinterpret_cast<const char*>(v_pages + oj) + part * 16);
+      }
+      float s[GMAX];
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) s[g] = -CUDART_INF_F;
+      if (off >= 0) {
         const T* k = k_pages + off;
 #pragma unroll
         for (int g = 0; g < GMAX; ++g) s[g] = 0.f;
@@ -237,75 +261,89 @@ decode_attention_split_kernel(const T* __restrict__ q_base, int q_row_stride, co
           }
         }
       }
-    }
-    // block-wide max per head
-#pragma unroll
-    for (int g = 0; g < GMAX; ++g) {
-      const float wm = warp_max(g < G ? s[g] : -CUDART_INF_F);
-      if (lane == 0) red_s[warp][g] = wm;
-    }
-    __syncthreads();
-    float p[GMAX], corr[GMAX];
-#pragma unroll
-    for (int g = 0; g < GMAX; ++g) {
-      const float bm = fmaxf(fmaxf(red_s[0][g], red_s[1][g]), fmaxf(red_s[2][g], red_s[3][g]));
-      const float m_new = fmaxf(m_run[g], bm);
-      corr[g] = (m_run[g] == -CUDART_INF_F) ? 0.f : __expf(m_run[g] - m_new);
-      p[g] = (off >= 0 && g < G) ? __expf(s[g] - m_new) : 0.f;
-      m_run[g] = m_new;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GMAX; ++g) {
-      const float ws = warp_sum(p[g]);
-      if (lane == 0) red_s[warp][g] = ws;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GMAX; ++g) {
-      l_run[g] = l_run[g] * corr[g] + ((red_s[0][g] + red_s[1][g]) + (red_s[2][g] + red_s[3][g]));
-#pragma unroll
-      for (int e = 0; e < DPL; ++e) acc[g][e] *= corr[g];
-    }
-    __syncthreads();
-    // each warp folds the values of its own 32 keys into the dims its lanes own
-    const int n_here = min(32, k_end - (base + warp * 32));
-    for (int jj = 0; jj < n_here; ++jj) {
-      const long long oj = __shfl_sync(0xffffffffu, off, jj);
-      if (oj < 0) continue;
-      float vf[DPL];
-      const T* v = v_pages + oj + lane * DPL;
-#pragma unroll
-      for (int e = 0; e < DPL; ++e) vf[e] = to_f32(v[e]);
+      // block-wide max per head
 #pragma unroll
       for (int g = 0; g < GMAX; ++g) {
-        if (g < G) {
-          const float pj = __shfl_sync(0xffffffffu, p[g], jj);
-#pragma unroll
-          for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(pj, vf[e], acc[g][e]);
-        }
+        const float wm = warp_max(g < G ? s[g] : -CUDART_INF_F);
+        if (lane == 0) red_s[warp][g] = wm;
       }
+      __syncthreads();
+      float p[GMAX], corr[GMAX];
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        const float bm = fmaxf(fmaxf(red_s[0][g], red_s[1][g]), fmaxf(red_s[2][g], red_s[3][g]));
+        const float m_new = fmaxf(m_run[g], bm);
+        corr[g] = (m_run[g] == -CUDART_INF_F) ? 0.f : __expf(m_run[g] - m_new);
+        p[g] = (off >= 0 && g < G) ? __expf(s[g] - m_new) : 0.f;
+        m_run[g] = m_new;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        const float ws = warp_sum(p[g]);
+        if (lane == 0) red_s[warp][g] = ws;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        l_run[g] = l_run[g] * corr[g] + ((red_s[0][g] + red_s[1][g]) + (red_s[2][g] + red_s[3][g]));
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[g][e] *= corr[g];
+      }
+      // fold the staged values of this warp's 32 keys into the dims its lanes own
+      cp_async_wait_all();
+      __syncwarp();
+      const int n_here = min(32, k_end - (base + warp * 32));
+      for (int jj = 0; jj < n_here; ++jj) {
+        const long long oj = __shfl_sync(0xffffffffu, off, jj);
+        float pj[GMAX];
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g) pj[g] = __shfl_sync(0xffffffffu, p[g], jj);
+        if (oj < 0) continue;
+        float vf[DPL];
+        const T* v = &v_s[warp][jj][lane * DPL];
+        if constexpr (sizeof(T) == 2 && DPL == 2) {
+          const unsigned w = *reinterpret_cast<const unsigned*>(v);
+          vf[0] = __uint_as_float(w << 16); vf[1] = __uint_as_float(w & 0xffff0000u);
+        } else if constexpr (sizeof(T) == 2 && DPL == 4) {
+          const uint2 w = *reinterpret_cast<const uint2*>(v);
+          vf[0] = __uint_as_float(w.x << 16); vf[1] = __uint_as_float(w.x & 0xffff0000u);
+          vf[2] = __uint_as_float(w.y << 16); vf[3] = __uint_as_float(w.y & 0xffff0000u);
+        } else {
+#pragma unroll
+          for (int e = 0; e < DPL; ++e) vf[e] = to_f32(v[e]);
+        }
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g)
+          if (g < G)
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(pj[g], vf[e], acc[g][e]);
+      }
+      __syncthreads();  // red_s and v_s are rewritten by the next pass
     }
-  }
-  // sum the four warps' partial outputs in a fixed order
+    // sum the four warps' partial outputs in a fixed order, through shared memory
+    float* red = reinterpret_cast<float*>(dec_smem);  // the value stage is free again and large enough
+    static_assert(sizeof(T) * 32 >= sizeof(float) * GMAX, "the value stage must hold the warps' partial outputs");
 #pragma unroll
-  for (int g = 0; g < GMAX; ++g)
-    if (g < G)
+    for (int g = 0; g < GMAX; ++g)
+      if (g < G)
 #pragma unroll
-      for (int e = 0; e < DPL; ++e) acc_s[warp][g][lane * DPL + e] = acc[g][e];
-  __syncthreads();
-  for (int i = tid; i < G * D; i += kDecThreads) {
-    const int g = i / D, dd = i % D;
-    const float o = (acc_s[0][g][dd] + acc_s[1][g][dd]) + (acc_s[2][g][dd] + acc_s[3][g][dd]);
-    part_o[(((size_t)r * nq + hk * G + g) * NB + b) * D + dd] = o;
-  }
-  if (tid < G) {
-    // m_run and l_run are equal in every thread
-    float mm = 0.f, ll = 0.f;
+        for (int e = 0; e < DPL; ++e) red[(warp * GMAX + g) * D + lane * DPL + e] = acc[g][e];
+    __syncthreads();
+    for (int i = tid; i < G * D; i += kDecThreads) {
+      const int g = i / D, dd = i % D;
+      const float o = (red[(0 * GMAX + g) * D + dd] + red[(1 * GMAX + g) * D + dd]) +
+                      (red[(2 * GMAX + g) * D + dd] + red[(3 * GMAX + g) * D + dd]);
+      part_o[(((size_t)r * nq + hk * G + g) * NB + b) * D + dd] = o;
+    }
+    if (tid < G) {
+      float mm = 0.f, ll = 0.f;  // m_run and l_run are equal in every thread
 #pragma unroll
-    for (int g = 0; g < GMAX; ++g) if (g == tid) { mm = m_run[g]; ll = l_run[g]; }
-    float* ml = part_ml + (((size_t)r * nq + hk * G + tid) * NB + b) * 2;
-    ml[0] = mm; ml[1] = ll;
+      for (int g = 0; g < GMAX; ++g) if (g == tid) { mm = m_run[g]; ll = l_run[g]; }
+      float* ml = part_ml + (((size_t)r * nq + hk * G + tid) * NB + b) * 2;
+      ml[0] = mm; ml[1] = ll;
+    }
+    __syncthreads();  // red (v_s) is staged into again by the next key block
   }
 }
 
@@ -341,8 +379,17 @@ static int launch_decode(const void* q, int q_row_stride, const void* k_pages, c
                          const int* block_table, int max_pages, int page_size, int num_pages, const int* q_start,
                          const int* ctx_len, void* out, float* part_o, float* part_ml, int R, int nq, int nkv,
                          float scale, int window, int KB, int NB, int* status, cudaStream_t stream) {
-  dim3 grid(nkv, R, NB);
-  decode_attention_split_kernel<T, D, GMAX><<<grid, kDecThreads, 0, stream>>>(
+  // about four blocks per SM in total, never more slots than key blocks
+  int slots = (4 * 148 + nkv * R - 1) / (nkv * R);
+  slots = slots < 1 ? 1 : (slots > NB ? NB : slots);
+  dim3 grid(nkv, R, slots);
+  const size_t smem = (size_t)4 * 32 * D * sizeof(T);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_split_kernel<T, D, GMAX>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  decode_attention_split_kernel<T, D, GMAX><<<grid, kDecThreads, smem, stream>>>(
       (const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages, block_table, max_pages, page_size,
       num_pages, q_start, ctx_len, part_o, part_ml, nq, nkv, nq / nkv, scale, window, KB, NB, status);
   decode_attention_combine_kernel<T, D><<<dim3(R, nq), D >= 64 ? 64 : 32, 0, stream>>>(

@@ -47,15 +47,7 @@ class DecoderModel:
         return specs, [e.cache_of for e in self.schedule]
 
     def kernel_modules(self) -> List[str]:
-        mods: List[str] = []
-        from ..models.spec import iter_parts
-        for family, ps in iter_parts(self.spec):
-            if family == "block":
-                continue
-            for m in lookup(family, ps.kind).kernel_modules(ps.params, self.ctx.dtype):
-                if m not in mods:
-                    mods.append(m)
-        return mods
+        return kernel_modules_of(self.spec, self.ctx.dtype)
 
     def forward(self, batch, cache) -> torch.Tensor:
         residual = self.embedding.forward(batch)
@@ -66,3 +58,16 @@ class DecoderModel:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
         x = self.final_norm.forward(residual, delta, rows=batch.logit_rows)
         return self.head.forward(x)
+
+
+def kernel_modules_of(spec: ModelSpec, dtype: torch.dtype) -> List[str]:
+    """The kernel modules (csrc/kernels/<name>.cu) that the model's parts launch."""
+    from ..models.spec import iter_parts
+    mods: List[str] = []
+    for family, ps in iter_parts(spec):
+        if family == "block":
+            continue
+        for m in lookup(family, ps.kind).kernel_modules(ps.params, dtype):
+            if m not in mods:
+                mods.append(m)
+    return mods

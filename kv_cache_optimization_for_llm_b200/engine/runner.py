@@ -59,6 +59,10 @@ class ModelRunner:
         self.model_config = self.arch.parse_config(config_dict)
         self.spec = self.arch.build_spec(self.model_config)
         self.dtype = _TORCH_DTYPE[self.config.dtype]
+        # Compile, side by side, what this model needs and nothing else.
+        from .. import build
+        from .model import kernel_modules_of
+        build.ensure_built(kernel_modules_of(self.spec, self.dtype) + ["_host"])
         if self.model_dir is not None:
             tensors = check_and_load(self.model_dir, expected_weights(self.spec))
         else:

@@ -241,13 +241,64 @@ def decode_attention(qkv, k_pages, v_pages, block_table, q_start, ctx_len, nq, n
     return out
 
 
+def flash_attention_supported(d: int, group: int, page_size: int) -> bool:
+    return bool(lib("flash_attention").kvb_flash_attention_supported(c_int(d), c_int(group), c_int(page_size)))
+
+
+def flash_tiles(batch, group: int) -> torch.Tensor:
+    """The query tiles of a step for a group size: [n, 4] int32 rows (request row, first
+    token row, tokens, 0), each tile holding consecutive tokens of one request.  Built
+    once per step and group size, kept on the batch."""
+    nt = int(lib("flash_attention").kvb_flash_attention_tokens_per_tile(c_int(group)))
+    cache = batch.host.setdefault("flash_tiles", {})
+    got = cache.get(nt)
+    if got is None:
+        import numpy as np
+        qs = batch.host["q_start"]
+        rows = []
+        for r in range(batch.num_reqs):
+            a, b = int(qs[r]), int(qs[r + 1])
+            starts = np.arange(a, b, nt, dtype=np.int32)
+            tile = np.zeros((len(starts), 4), dtype=np.int32)
+            tile[:, 0] = r
+            tile[:, 1] = starts
+            tile[:, 2] = np.minimum(nt, b - starts)
+            rows.append(tile)
+        host = torch.from_numpy(np.concatenate(rows)).pin_memory()
+        got = host.to(batch.token_ids.device, non_blocking=True)
+        cache[nt] = got
+        cache[("host", nt)] = host   # keep the pinned source alive until the step is over
+    return got
+
+
+def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window) -> torch.Tensor:
+    """Tensor-core attention for steps with runs of query tokens (bfloat16)."""
+    _need_cuda(qkv, k_pages)
+    T = qkv.shape[0]
+    tiles = flash_tiles(batch, nq // nkv)
+    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+    rc = lib("flash_attention").kvb_paged_flash_attention(
+        _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
+        c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]),
+        _p(out), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), _p(batch.status),
+        _stream())
+    _check(rc, "paged_flash_attention")
+    return out
+
+
 def attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window, max_positions) -> torch.Tensor:
     """Attention of the step's tokens over their requests' pages; picks the kernel.
     float32 always takes the general kernel, whose sums follow absolute positions in
-    one fixed order whatever the shape of the step."""
-    if batch.decode_only and qkv.dtype == torch.bfloat16 and decode_attention_supported(d, nq // nkv):
-        return decode_attention(qkv, k_pages, v_pages, block_table, batch.q_start, batch.ctx_len, nq, nkv, d,
-                                scale, window, max_positions, batch.status)
+    one fixed order whatever the shape of the step.  bfloat16: single tokens only ->
+    the split decode kernel; runs of tokens -> the tensor-core kernel; sizes neither
+    takes -> the general kernel."""
+    if qkv.dtype == torch.bfloat16:
+        group, page_size = nq // nkv, k_pages.shape[2]
+        if batch.decode_only and decode_attention_supported(d, group):
+            return decode_attention(qkv, k_pages, v_pages, block_table, batch.q_start, batch.ctx_len, nq, nkv, d,
+                                    scale, window, max_positions, batch.status)
+        if not batch.decode_only and flash_attention_supported(d, group, page_size):
+            return flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window)
     return paged_attention_generic(qkv, k_pages, v_pages, block_table, batch.positions, batch.token_req,
                                    nq, nkv, d, scale, window, batch.status)
 

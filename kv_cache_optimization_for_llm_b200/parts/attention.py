@@ -35,6 +35,8 @@ class GroupedQueryAttention(Part):
     @classmethod
     def kernel_modules(cls, params, dtype):
         mods = ["elementwise", "attention"]
+        if dtype == torch.bfloat16 and params["head_dim"] in (64, 128):
+            mods.append("flash_attention")
         if dtype == torch.float32:
             mods.append("gemm_f32")
         return tuple(mods)

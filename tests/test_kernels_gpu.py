@@ -325,3 +325,42 @@ def test_sampling_kernel(V):
         want = P.sample(logits[r].astype(np.float64), 0.0, 0, 0, 0, seen=seen.get(int(slots[r]), []), penalty=float(pen[r]))
         assert got[r] == want, r
     assert mask[0, got[0]] == 1 and mask[2, got[2]] == 1 and int(mask[1].sum()) == 0   # new tokens are recorded
+
+
+class _FakeBatch:
+    """What ops.flash_attention reads of a step: rows of the runs and their positions."""
+    def __init__(self, c):
+        self.positions, self.token_ids, self.status = c["positions"], c["positions"], status()
+        self.num_reqs = c["ctx_len"].numel()
+        self.host = {"q_start": c["q_start"].cpu().numpy()}
+
+
+@pytest.mark.parametrize("nq,nkv,d,page_size,window", [
+    (8, 2, 64, 16, None), (32, 8, 64, 16, None), (6, 2, 64, 8, None), (5, 5, 64, 4, None), (24, 8, 128, 16, None),
+    (8, 1, 128, 32, None), (16, 1, 64, 64, None), (8, 2, 64, 16, 100), (4, 4, 128, 16, 33), (3, 1, 64, 16, 64),
+])
+def test_flash_attention_mixed_runs(nq, nkv, d, page_size, window):
+    """Tensor-core kernel: whole prompts, continued prompts, a two-token portion and
+    single tokens in one step; runs longer than a tile, contexts across many key tiles."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    assert ops.flash_attention_supported(d, nq // nkv, page_size)
+    c = _attention_case("bfloat16", nq, nkv, d, ctxs=[1, 70, 130, 64, 400, 257, 2], q_lens=[1, 70, 2, 1, 150, 40, 2],
+                        page_size=page_size, window=window, seed=d + nq + page_size)
+    fb = _FakeBatch(c)
+    out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), window)
+    assert int(fb.status.item()) == 0
+    assert rel_err(out, c["ref"]) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("spike", [0, 63, 64, 511, 777])
+def test_flash_attention_finds_a_far_key(spike):
+    from kv_cache_optimization_for_llm_b200 import ops
+    nq, nkv, d = 8, 2, 64
+    c = _attention_case("bfloat16", nq, nkv, d, ctxs=[900], q_lens=[37], page_size=16, window=None, seed=spike,
+                        spike=spike)
+    fb = _FakeBatch(c)
+    out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), None)
+    assert rel_err(out, c["ref"]) < TOL["bfloat16"]
+    page, slot = int(c["table"][0, spike // 16]), spike % 16
+    want = np.repeat(as64(c["vp"][page, :, slot]), nq // nkv, axis=0).reshape(-1)
+    assert np.abs(as64(out)[-1] - want).max() < 0.08      # the last query sees that key's value
