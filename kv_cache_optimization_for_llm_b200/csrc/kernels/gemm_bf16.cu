@@ -1,0 +1,376 @@
+// bfloat16 linear layers on the 5th-generation tensor cores:  C[M,N] = X[M,K] . W[N,K]^T
+// (upstream: cublasGemmEx with bfloat16 operands and float32 accumulation,
+// base/src/engine.cu:643-671).
+//
+// Skinny form, for steps with few rows (decode): the weight matrix is the streamed
+// operand.  A block takes 128 output features (rows of W) and a slice of K; the
+// weights arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle) in tiles of
+// 128 x 64, the step's rows X as tiles of MP x 64 (MP = M padded to 16..256, rows
+// beyond M read as zeros), through a ring of shared-memory stages guarded by
+// mbarriers.  One thread issues tcgen05.mma (kind::f16, M=128, N=MP, K=16) with the
+// accumulator D[feature, row] in tensor memory; tcgen05.commit hands each stage back
+// to the TMA thread.  The four warps then read the accumulator with tcgen05.ld (warp
+// w owns features 32w..32w+31) and store C[row, feature].
+// When N gives too few blocks to pull the whole memory system, K is split over
+// gridDim.y blocks: each writes a float32 partial to scratch, and the block that
+// arrives last at the tile's counter adds the partials in split order and writes
+// the result, so the sum has one fixed order and nobody waits for anybody.
+// Every wait on an mbarrier is bounded; a wait that runs out records
+// KVB_STATUS_WAIT_TIMEOUT, and the block frees its tensor memory and returns.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int TILE_N = 128;  // output features per block = UMMA M
+constexpr int TILE_K = 64;   // one 128-byte swizzle row of bfloat16
+constexpr int kThreads = 128;
+constexpr unsigned kSpinLimit = 20u * 1000u * 1000u;
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  false: the limit ran out.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+  for (unsigned i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(void* holder, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
+// 128 bytes, groups of 8 rows 1024 bytes apart, tile base aligned to 1024 bytes.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+struct Params {
+  int M, N, K, MP;            // MP: rows padded to the UMMA N extent
+  int k_tiles, splits;        // k tiles in all, blocks along K
+  int stages;
+  int out_f32;                // 1: C is float32, 0: bfloat16
+  void* out;                  // [M, N]
+  float* partial;             // [splits, M, N] when splits > 1
+  int* counters;              // [n tiles], all zero between launches
+  int* status;
+};
+
+template <int kUnused = 0>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   const Params p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // carve: stages x (W tile, X tile), then barriers
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int a_bytes = TILE_N * TILE_K * 2;
+  const int b_bytes = p.MP * TILE_K * 2;
+  unsigned char* a_s = base;
+  unsigned char* b_s = base + (size_t)p.stages * a_bytes;
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(b_s + (size_t)p.stages * b_bytes);
+  unsigned long long* empty = full + p.stages;
+  unsigned long long* accum = empty + p.stages;
+  unsigned* tmem_holder = reinterpret_cast<unsigned*>(accum + 1);
+  int* flags = reinterpret_cast<int*>(tmem_holder + 1);  // [0]: abort, [1]: this block reduces the splits
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * TILE_N;
+  const int per = (p.k_tiles + p.splits - 1) / p.splits;
+  const int kt0 = blockIdx.y * per;
+  const int kt1 = min(p.k_tiles, kt0 + per);
+  const int my_tiles = max(0, kt1 - kt0);
+  const unsigned tmem_cols = p.MP < 32 ? 32u : (unsigned)p.MP;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(accum, 1);
+    flags[0] = 0; flags[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_holder, tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_d = *tmem_holder;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer
+    for (int i = 0; i < my_tiles; ++i) {
+      const int s = i % p.stages;
+      const unsigned phase = (i / p.stages) & 1;
+      if (i >= p.stages && !mbar_wait(&empty[s], phase ^ 1)) { atomicExch(&flags[0], 1); break; }
+      mbar_expect_tx(&full[s], a_bytes + b_bytes);
+      tma_load_2d(a_s + (size_t)s * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[s]);
+      tma_load_2d(b_s + (size_t)s * b_bytes, &map_x, (kt0 + i) * TILE_K, 0, &full[s]);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer
+    const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.MP >> 3) << 17) | ((unsigned)(TILE_N >> 4) << 24);
+    bool ok = true;
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      const int s = i % p.stages;
+      const unsigned phase = (i / p.stages) & 1;
+      if (!mbar_wait(&full[s], phase)) { atomicExch(&flags[0], 1); ok = false; break; }
+      tc_fence_after();
+      const unsigned long long ad = smem_desc_sw128(smem_u32(a_s + (size_t)s * a_bytes));
+      const unsigned long long bd = smem_desc_sw128(smem_u32(b_s + (size_t)s * b_bytes));
+#pragma unroll
+      for (int k = 0; k < TILE_K / 16; ++k)  // 32 bytes further along K per step: +2 in the address field
+        umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+      umma_commit(&empty[s]);   // the stage is free once these products have read it
+    }
+    umma_commit(accum);         // everything issued so far has landed in tensor memory
+  }
+  __syncwarp();
+
+  // ---- epilogue: all four warps
+  bool good = true;
+  if (my_tiles > 0) good = mbar_wait(accum, 0);
+  if (!good) atomicExch(&flags[0], 1);
+  tc_fence_after();
+  __syncthreads();
+  const bool aborted = flags[0] != 0;
+  if (aborted && tid == 0) atomicCAS(p.status, 0, KVB_STATUS_WAIT_TIMEOUT);
+
+  const int n = n0 + warp * 32 + lane;           // the feature this thread holds
+  if (!aborted) {
+    if (p.splits == 1) {
+      for (int c = 0; c < p.MP; c += 16) {
+        float v[16];
+        if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c + i;
+            if (m < p.M) {
+              if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = v[i];
+              else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v[i]);
+            }
+          }
+        }
+      }
+    } else {
+      float* mine = p.partial + (size_t)blockIdx.y * p.M * p.N;
+      for (int c = 0; c < p.MP; c += 16) {
+        float v[16];
+        if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c + i < p.M) mine[(size_t)(c + i) * p.N + n] = v[i];
+        }
+      }
+      // the block that arrives last at the tile's counter adds the splits up
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const int old = atomicAdd(&p.counters[blockIdx.x], 1);
+        flags[1] = (old == p.splits - 1);
+      }
+      __syncthreads();
+      if (flags[1]) {
+        __threadfence();
+        if (n < p.N) {
+          for (int m = 0; m < p.M; ++m) {
+            float acc = 0.f;
+            for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + ((size_t)s * p.M + m) * p.N + n);
+            if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = acc;
+            else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(acc);
+          }
+        }
+        if (tid == 0) p.counters[blockIdx.x] = 0;   // ready for the next launch
+      }
+    }
+  } else {
+    // give copies that may still be in flight time to land before the block ends
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix as a 2-D tensor map with boxes of box_rows x 64.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return KVB_ERR_BAD_SIZE;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+struct MapKey {
+  const void* ptr; int rows, K, ld, box;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && ld == o.ld && box == o.box; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 1315423911u ^ (size_t)k.K * 2654435761u ^ (size_t)k.box;
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;  // weights keep their address: encode once
+
+int cached_map(CUtensorMap* out, const void* ptr, int rows, int K, int ld, int box) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  MapKey key{ptr, rows, K, ld, box};
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    CUtensorMap m;
+    const int rc = make_map(&m, ptr, rows, K, ld, box);
+    if (rc) return rc;
+    if (g_maps.size() > 4096) g_maps.clear();
+    it = g_maps.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
+}  // namespace
+
+// How the skinny kernel would cut a problem: splits along K and the float32 scratch
+// it needs.  Returns 0 if it takes the sizes (M <= 256, K a multiple of 8, 16-byte
+// aligned leading dimensions), KVB_ERR_BAD_SIZE otherwise.
+KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, long long* scratch_floats, int* n_tiles) {
+  if (M < 1 || M > 256 || N < 1 || K < 8 || (K & 7)) return KVB_ERR_BAD_SIZE;
+  const int tiles = (N + TILE_N - 1) / TILE_N;
+  const int k_tiles = (K + TILE_K - 1) / TILE_K;
+  int s = 148 / tiles;                       // fill the SMs once
+  if (s > k_tiles / 2) s = k_tiles / 2;      // at least two k tiles per block
+  if (s < 1) s = 1;
+  if (s > 16) s = 16;
+  *splits = s;
+  *n_tiles = tiles;
+  *scratch_floats = s > 1 ? (long long)s * M * N : 0;
+  return 0;
+}
+
+// C[M,N] = X[M,K] . W[N,K]^T, bfloat16 operands (ldx, ldw in elements, multiples of 8),
+// C bfloat16 (out_f32 = 0) or float32, dense [M,N].  partial: float32 scratch of the
+// size kvb_gemm_skinny_plan gives; counters: one int per 128 features, zero on entry
+// (the kernel leaves them zero).  x_is_static: the activation's address is stable
+// (a captured graph), so its tensor map may be cached as the weights' is.
+KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
+                               int K, float* partial, int* counters, int x_is_static, int* status,
+                               cudaStream_t stream) {
+  int splits, tiles;
+  long long scratch;
+  const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &scratch, &tiles);
+  if (rc) return rc;
+  if ((ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return KVB_ERR_ALIGN;
+  if (splits > 1 && (!partial || !counters)) return KVB_ERR_BAD_SIZE;
+  int MP = 16;
+  while (MP < M) MP <<= 1;
+  Params p;
+  p.M = M; p.N = N; p.K = K; p.MP = MP;
+  p.k_tiles = (K + TILE_K - 1) / TILE_K;
+  p.splits = splits;
+  p.out_f32 = out_f32; p.out = out; p.partial = partial; p.counters = counters; p.status = status;
+  const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  const int per = (p.k_tiles + splits - 1) / splits;
+  if (stages > per) stages = per < 2 ? 2 : per;
+  p.stages = stages;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * 8 + 16;
+  CUtensorMap mw, mx;
+  int e = cached_map(&mw, w, N, K, ldw, TILE_N);
+  if (e) return e;
+  e = x_is_static ? cached_map(&mx, x, M, K, ldx, MP) : make_map(&mx, x, M, K, ldx, MP);
+  if (e) return e;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t ce = cudaFuncSetAttribute(gemm_skinny_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (ce != cudaSuccess) return (int)ce;
+    attr_set = true;
+  }
+  dim3 grid(tiles, splits);
+  gemm_skinny_kernel<0><<<grid, kThreads, smem, stream>>>(mw, mx, p);
+  return kvb_launch_result();
+}

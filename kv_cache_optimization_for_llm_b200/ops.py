@@ -325,3 +325,47 @@ def reset_mask(mask: torch.Tensor, slot: int, tokens: Optional[torch.Tensor]) ->
     rc = lib("sampling").kvb_reset_mask(_p(mask), c_int(slot), c_int(mask.shape[1]), _p(tokens), c_int(n),
                                         _stream())
     _check(rc, "reset_mask")
+
+
+# ------------------------------------------------------------------ bfloat16 matrix products (tcgen05)
+
+def gemm_skinny_plan(M: int, N: int, K: int):
+    """(splits, scratch floats, tiles) of the skinny tensor-core kernel, or None if it
+    does not take the sizes."""
+    splits, tiles, scratch_n = c_int(0), c_int(0), c_longlong(0)
+    rc = lib("gemm_bf16").kvb_gemm_skinny_plan(c_int(M), c_int(N), c_int(K), ctypes.byref(splits),
+                                               ctypes.byref(scratch_n), ctypes.byref(tiles))
+    if rc != 0:
+        return None
+    return splits.value, scratch_n.value, tiles.value
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor,
+                x_is_static: bool = False) -> torch.Tensor:
+    """``x . w^T`` for few rows (M <= 256) on tcgen05 tensor cores, weights streamed by TMA."""
+    _need_cuda(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    plan = gemm_skinny_plan(M, N, K)
+    if plan is None:
+        raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
+    splits, scratch_n, tiles = plan
+    dev = x.device
+    partial = None
+    if scratch_n:
+        partial = _scratch.get(("gemm_partial", dev.index))
+        if partial is None or partial.numel() < scratch_n:
+            # grow-only, and never below what the largest decode batch of a common model needs
+            partial = torch.empty(max(scratch_n, 8 * 1024 * 1024), dtype=torch.float32, device=dev)
+            _scratch[("gemm_partial", dev.index)] = partial
+    counters = _scratch.get(("gemm_counters", dev.index))
+    if counters is None or counters.numel() < tiles:
+        counters = torch.zeros(max(tiles, 2048), dtype=torch.int32, device=dev)
+        _scratch[("gemm_counters", dev.index)] = counters
+    out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    rc = lib("gemm_bf16").kvb_gemm_skinny(
+        _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(1 if out_dtype == torch.float32 else 0),
+        c_int(M), c_int(N), c_int(K), _p(partial), _p(counters), c_int(1 if x_is_static else 0), _p(status), _stream())
+    _check(rc, "gemm_skinny")
+    return out
