@@ -11,10 +11,12 @@
 // accumulator D[feature, row] in tensor memory; tcgen05.commit hands each stage back
 // to the TMA thread.  The four warps then read the accumulator with tcgen05.ld (warp
 // w owns features 32w..32w+31) and store C[row, feature].
-// When N gives too few blocks to pull the whole memory system, K is split over
-// gridDim.y blocks: each writes a float32 partial to scratch, and the block that
-// arrives last at the tile's counter adds the partials in split order and writes
-// the result, so the sum has one fixed order and nobody waits for anybody.
+// When N gives too few blocks to pull the whole memory system, K is split over the
+// blocks of a thread-block cluster (gridDim.y = cluster size): each block parks its
+// float32 accumulator in its own shared memory, the cluster meets at its hardware
+// barrier, and block r adds up rows r, r + S, ... of all S blocks through distributed
+// shared memory, always in block order, so the sum has one fixed order.  No scratch in
+// global memory, no counters, no spinning.
 // Every wait on an mbarrier is bounded; a wait that runs out records
 // KVB_STATUS_WAIT_TIMEOUT, and the block frees its tensor memory and returns.
 #include "common.cuh"
@@ -92,6 +94,17 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const void* my_smem_ptr, unsigned rank) {
+  unsigned remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
 // 128 bytes, groups of 8 rows 1024 bytes apart, tile base aligned to 1024 bytes.
 __device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
@@ -104,13 +117,11 @@ struct Params {
   int stages;
   int out_f32;                // 1: C is float32, 0: bfloat16
   void* out;                  // [M, N]
-  float* partial;             // [splits, M, N] when splits > 1
-  int* counters;              // [n tiles], all zero between launches
   int* status;
 };
 
 template <int kUnused = 0>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    const Params p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -208,7 +219,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
       }
     } else {
-      float* mine = p.partial + (size_t)blockIdx.y * p.M * p.N;
+      // park the accumulator as red[m][feature] in the (now idle) first stage buffers
+      float* red = reinterpret_cast<float*>(base);
       for (int c = 0; c < p.MP; c += 16) {
         float v[16];
         if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
@@ -216,34 +228,32 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
         }
-        if (n < p.N) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (c + i < p.M) mine[(size_t)(c + i) * p.N + n] = v[i];
-        }
-      }
-      // the block that arrives last at the tile's counter adds the splits up
-      __threadfence();
-      __syncthreads();
-      if (tid == 0) {
-        const int old = atomicAdd(&p.counters[blockIdx.x], 1);
-        flags[1] = (old == p.splits - 1);
-      }
-      __syncthreads();
-      if (flags[1]) {
-        __threadfence();
-        if (n < p.N) {
-          for (int m = 0; m < p.M; ++m) {
-            float acc = 0.f;
-            for (int s = 0; s < p.splits; ++s) acc += __ldcg(p.partial + ((size_t)s * p.M + m) * p.N + n);
-            if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = acc;
-            else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(acc);
-          }
-        }
-        if (tid == 0) p.counters[blockIdx.x] = 0;   // ready for the next launch
+        for (int i = 0; i < 16; ++i) red[(c + i) * TILE_N + tid] = v[i];
       }
     }
-  } else {
+  }
+  if (p.splits > 1) {
+    // Every block of the cluster comes here, aborted or not: the barrier is collective.
+    cluster_sync_all();
+    if (!aborted) {
+      const float* red = reinterpret_cast<const float*>(base);
+      for (int m = (int)blockIdx.y; m < p.M; m += p.splits) {
+        float t[16];   // all peers' values are requested before the first is used
+#pragma unroll
+        for (int s2 = 0; s2 < 16; ++s2) t[s2] = s2 < p.splits ? ld_peer_f32(red + m * TILE_N + tid, (unsigned)s2) : 0.f;
+        float acc = 0.f;
+#pragma unroll
+        for (int s2 = 0; s2 < 16; ++s2) acc += t[s2];
+        if (n < p.N) {
+          if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = acc;
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(acc);
+        }
+      }
+    }
+    cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
+  }
+  if (aborted) {
     // give copies that may still be in flight time to land before the block ends
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
@@ -313,50 +323,51 @@ int cached_map(CUtensorMap* out, const void* ptr, int rows, int K, int ld, int b
 
 }  // namespace
 
-// How the skinny kernel would cut a problem: splits along K and the float32 scratch
-// it needs.  Returns 0 if it takes the sizes (M <= 256, K a multiple of 8, 16-byte
-// aligned leading dimensions), KVB_ERR_BAD_SIZE otherwise.
-KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, long long* scratch_floats, int* n_tiles) {
+// How the skinny kernel would cut a problem: blocks along K (= cluster size) and tiles
+// along N.  Returns 0 if it takes the sizes (M <= 256, K a multiple of 8),
+// KVB_ERR_BAD_SIZE otherwise.
+KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_tiles) {
   if (M < 1 || M > 256 || N < 1 || K < 8 || (K & 7)) return KVB_ERR_BAD_SIZE;
   const int tiles = (N + TILE_N - 1) / TILE_N;
   const int k_tiles = (K + TILE_K - 1) / TILE_K;
-  int s = 148 / tiles;                       // fill the SMs once
+  int s = (2 * 148) / tiles;                 // two blocks per SM in flight
   if (s > k_tiles / 2) s = k_tiles / 2;      // at least two k tiles per block
+  if (s > 16) s = 16;                        // the largest cluster
   if (s < 1) s = 1;
-  if (s > 16) s = 16;
+  while (s > 1 && (k_tiles + s - 1) / s * (s - 1) >= k_tiles) --s;  // no block without work
   *splits = s;
   *n_tiles = tiles;
-  *scratch_floats = s > 1 ? (long long)s * M * N : 0;
   return 0;
 }
 
 // C[M,N] = X[M,K] . W[N,K]^T, bfloat16 operands (ldx, ldw in elements, multiples of 8),
-// C bfloat16 (out_f32 = 0) or float32, dense [M,N].  partial: float32 scratch of the
-// size kvb_gemm_skinny_plan gives; counters: one int per 128 features, zero on entry
-// (the kernel leaves them zero).  x_is_static: the activation's address is stable
-// (a captured graph), so its tensor map may be cached as the weights' is.
+// C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
+// address is stable (a captured graph), so its tensor map may be cached as the
+// weights' is.  Uses no memory beyond its operands.
 KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
-                               int K, float* partial, int* counters, int x_is_static, int* status,
-                               cudaStream_t stream) {
+                               int K, int x_is_static, int* status, cudaStream_t stream) {
   int splits, tiles;
-  long long scratch;
-  const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &scratch, &tiles);
+  const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &tiles);
   if (rc) return rc;
   if ((ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return KVB_ERR_ALIGN;
-  if (splits > 1 && (!partial || !counters)) return KVB_ERR_BAD_SIZE;
   int MP = 16;
   while (MP < M) MP <<= 1;
   Params p;
   p.M = M; p.N = N; p.K = K; p.MP = MP;
   p.k_tiles = (K + TILE_K - 1) / TILE_K;
   p.splits = splits;
-  p.out_f32 = out_f32; p.out = out; p.partial = partial; p.counters = counters; p.status = status;
+  p.out_f32 = out_f32; p.out = out; p.status = status;
   const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
-  int stages = (200 * 1024) / stage_bytes;
+  // two blocks per SM while the stages stay deep enough, one block otherwise
+  const int budget = MP <= 64 ? 108 * 1024 : 200 * 1024;
+  int stages = budget / stage_bytes;
   if (stages > 8) stages = 8;
   const int per = (p.k_tiles + splits - 1) / splits;
-  if (stages > per) stages = per < 2 ? 2 : per;
+  if (stages > per) stages = per;
+  if (stages < 2) stages = 2;
+  // the split reduction parks MP x 128 floats in the stage buffers
+  while (splits > 1 && stages * stage_bytes < MP * TILE_N * 4) ++stages;
   p.stages = stages;
   const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * 8 + 16;
   CUtensorMap mw, mx;
@@ -368,9 +379,23 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(gemm_skinny_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (ce != cudaSuccess) return (int)ce;
+    ce = cudaFuncSetAttribute(gemm_skinny_kernel<0>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (ce != cudaSuccess) return (int)ce;
     attr_set = true;
   }
-  dim3 grid(tiles, splits);
-  gemm_skinny_kernel<0><<<grid, kThreads, smem, stream>>>(mw, mx, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles, splits, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = splits;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<0>, mw, mx, p);
+  if (le != cudaSuccess) return (int)le;
   return kvb_launch_result();
 }

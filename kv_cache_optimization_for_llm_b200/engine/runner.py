@@ -73,7 +73,7 @@ class ModelRunner:
         if self.max_model_len > self.spec.max_position:
             raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's "
                              f"max_position_embeddings {self.spec.max_position}")
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = ops.kernel_status(self.device)
         ctx = BuildContext(dtype=self.dtype, device=self.device, max_positions=self.max_model_len,
                            status=self.status)
         self.model = DecoderModel(self.spec, tensors, ctx)

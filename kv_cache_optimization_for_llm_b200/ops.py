@@ -175,9 +175,27 @@ def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token
 
 # ------------------------------------------------------------------ matrix products
 
+SKINNY_MAX_ROWS = 256
+_status_word: Dict[int, torch.Tensor] = {}
+
+
+def kernel_status(device) -> torch.Tensor:
+    """The device word into which kernels report impossible indices and waits that ran
+    out; one per device, shared by every engine in the process."""
+    idx = torch.device(device).index or 0
+    t = _status_word.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+        _status_word[idx] = t
+    return t
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """``x . w^T`` with ``w`` [out, in].  float32: this package's FMA kernel (true
-    32-bit).  bfloat16: the library product with float32 accumulation."""
+    """``x . w^T`` with ``w`` [out, in].
+    float32: this package's FMA kernel (true 32-bit).
+    bfloat16, up to 256 rows (decode and short portions): this package's tcgen05/TMA
+    kernel, which streams the weights.  bfloat16 with more rows (long prompt portions):
+    the library product, float32 accumulation, as upstream's cublasGemmEx."""
     _need_cuda(x, w)
     M, K = x.shape
     N = w.shape[0]
@@ -189,6 +207,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
                                           c_int(N), c_int(M), c_int(N), c_int(K), _stream())
         _check(rc, "sgemm_nt")
         return out
+    if M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        return gemm_skinny(x, w, out_dtype or x.dtype, kernel_status(x.device),
+                           x_is_static=torch.cuda.is_current_stream_capturing())
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w.t(), out_dtype=out_dtype)
     return torch.nn.functional.linear(x, w)
@@ -330,14 +351,13 @@ def reset_mask(mask: torch.Tensor, slot: int, tokens: Optional[torch.Tensor]) ->
 # ------------------------------------------------------------------ bfloat16 matrix products (tcgen05)
 
 def gemm_skinny_plan(M: int, N: int, K: int):
-    """(splits, scratch floats, tiles) of the skinny tensor-core kernel, or None if it
+    """(blocks along K, tiles along N) of the skinny tensor-core kernel, or None if it
     does not take the sizes."""
-    splits, tiles, scratch_n = c_int(0), c_int(0), c_longlong(0)
-    rc = lib("gemm_bf16").kvb_gemm_skinny_plan(c_int(M), c_int(N), c_int(K), ctypes.byref(splits),
-                                               ctypes.byref(scratch_n), ctypes.byref(tiles))
+    splits, tiles = c_int(0), c_int(0)
+    rc = lib("gemm_bf16").kvb_gemm_skinny_plan(c_int(M), c_int(N), c_int(K), ctypes.byref(splits), ctypes.byref(tiles))
     if rc != 0:
         return None
-    return splits.value, scratch_n.value, tiles.value
+    return splits.value, tiles.value
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor,
@@ -347,25 +367,11 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
-    plan = gemm_skinny_plan(M, N, K)
-    if plan is None:
-        raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
-    splits, scratch_n, tiles = plan
-    dev = x.device
-    partial = None
-    if scratch_n:
-        partial = _scratch.get(("gemm_partial", dev.index))
-        if partial is None or partial.numel() < scratch_n:
-            # grow-only, and never below what the largest decode batch of a common model needs
-            partial = torch.empty(max(scratch_n, 8 * 1024 * 1024), dtype=torch.float32, device=dev)
-            _scratch[("gemm_partial", dev.index)] = partial
-    counters = _scratch.get(("gemm_counters", dev.index))
-    if counters is None or counters.numel() < tiles:
-        counters = torch.zeros(max(tiles, 2048), dtype=torch.int32, device=dev)
-        _scratch[("gemm_counters", dev.index)] = counters
-    out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     rc = lib("gemm_bf16").kvb_gemm_skinny(
         _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(1 if out_dtype == torch.float32 else 0),
-        c_int(M), c_int(N), c_int(K), _p(partial), _p(counters), c_int(1 if x_is_static else 0), _p(status), _stream())
+        c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), _p(status), _stream())
+    if rc == -2:
+        raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
     _check(rc, "gemm_skinny")
     return out

@@ -37,8 +37,7 @@ class GroupedQueryAttention(Part):
         mods = ["elementwise", "attention"]
         if dtype == torch.bfloat16 and params["head_dim"] in (64, 128):
             mods.append("flash_attention")
-        if dtype == torch.float32:
-            mods.append("gemm_f32")
+        mods.append("gemm_f32" if dtype == torch.float32 else "gemm_bf16")
         return tuple(mods)
 
     def __init__(self, params, weights, ctx):
