@@ -31,6 +31,8 @@ paged_attention_generic_kernel(const T* __restrict__ q_base, int q_row_stride,
   __shared__ float acc_s[kWarps][kMaxHeadDim];
   __shared__ float m_s[kWarps], l_s[kWarps];
 
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int h = blockIdx.y;
   const int hk = h / (nq / nkv);
@@ -125,10 +127,10 @@ KVB_EXPORT int kvb_paged_attention_generic(const void* q, int q_row_stride, cons
   if (T_ <= 0) return 0;
   if (d > kMaxHeadDim || d < 2 || (d & 1) || nkv < 1 || nq % nkv) return KVB_ERR_BAD_SIZE;
   dim3 grid(T_, nq);
-  KVB_DISPATCH_DTYPE(dtype, T, (paged_attention_generic_kernel<T><<<grid, kWarps * 32, 0, stream>>>(
-                                   (const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages,
-                                   block_table, max_pages, page_size, num_pages, positions, token_req,
-                                   (T*)out, nq, nkv, d, scale, window, status)));
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(paged_attention_generic_kernel<T>, grid, dim3(kWarps * 32), 0, stream,
+                                            (const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages,
+                                            block_table, max_pages, page_size, num_pages, positions, token_req,
+                                            (T*)out, nq, nkv, d, scale, window, status)));
   return kvb_launch_result();
 }
 
@@ -194,6 +196,8 @@ decode_attention_split_kernel(const T* __restrict__ q_base, int q_row_stride, co
   extern __shared__ __align__(16) unsigned char dec_smem[];
   T (*v_s)[32][D] = reinterpret_cast<T (*)[32][D]>(dec_smem);  // each warp stages the values of its 32 keys
 
+  pdl_trigger();
+  pdl_wait();
   const int hk = blockIdx.x, r = blockIdx.y;
   const int pos = ctx_len[r] - 1;
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -352,6 +356,8 @@ __global__ void decode_attention_combine_kernel(const float* __restrict__ part_o
                                                 const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                                                 T* __restrict__ out, int nq, int window, int KB, int NB,
                                                 int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
   const int pos = ctx_len[r] - 1;
   if (pos < 0 || pos / KB >= NB) {  // a context beyond the key blocks the scratch was sized for
@@ -389,11 +395,11 @@ static int launch_decode(const void* q, int q_row_stride, const void* k_pages, c
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  decode_attention_split_kernel<T, D, GMAX><<<grid, kDecThreads, smem, stream>>>(
-      (const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages, block_table, max_pages, page_size,
-      num_pages, q_start, ctx_len, part_o, part_ml, nq, nkv, nq / nkv, scale, window, KB, NB, status);
-  decode_attention_combine_kernel<T, D><<<dim3(R, nq), D >= 64 ? 64 : 32, 0, stream>>>(
-      part_o, part_ml, q_start, ctx_len, (T*)out, nq, window, KB, NB, status);
+  kvb_launch(decode_attention_split_kernel<T, D, GMAX>, grid, dim3(kDecThreads), smem, stream, (const T*)q,
+             q_row_stride, (const T*)k_pages, (const T*)v_pages, block_table, max_pages, page_size, num_pages,
+             q_start, ctx_len, part_o, part_ml, nq, nkv, nq / nkv, scale, window, KB, NB, status);
+  kvb_launch(decode_attention_combine_kernel<T, D>, dim3(R, nq), dim3(D >= 64 ? 64 : 32), 0, stream,
+             (const float*)part_o, (const float*)part_ml, q_start, ctx_len, (T*)out, nq, window, KB, NB, status);
   return kvb_launch_result();
 }
 

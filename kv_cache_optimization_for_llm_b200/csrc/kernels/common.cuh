@@ -49,6 +49,42 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Programmatic dependent launch: a kernel launched through kvb_launch may be set up
+// on the SMs while its predecessor in the stream still runs.  pdl_trigger() at the
+// top of a kernel lets the next one begin that early; pdl_wait() holds a kernel until
+// everything before it in the stream has finished and its writes are visible, so it
+// comes before the first read of data that an earlier kernel produced and before the
+// first write to global memory.  Both are no-ops for a kernel launched the plain way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <cstdlib>
+#include <utility>
+
+static inline bool kvb_pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("KVB200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kvb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = kvb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
 static inline int kvb_launch_result() {
   cudaError_t e = cudaPeekAtLastError();
   return (int)e;

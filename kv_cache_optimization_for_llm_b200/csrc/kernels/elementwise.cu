@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ resid, int H, int V, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= V) {
@@ -24,8 +26,8 @@ KVB_EXPORT int kvb_embed_gather(const void* table, int dtype, const int* ids, fl
                                 int H, int V, int* status, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
-  KVB_DISPATCH_DTYPE(dtype, T, (embed_gather_kernel<T><<<T_, threads, 0, stream>>>(
-                                   (const T*)table, ids, resid, H, V, status)));
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(embed_gather_kernel<T>, dim3(T_), dim3(threads), 0, stream,
+                                            (const T*)table, ids, resid, H, V, status)));
   return kvb_launch_result();
 }
 
@@ -40,6 +42,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    const int* __restrict__ rows, int H, float eps) {
   extern __shared__ float row_cache[];
   __shared__ float warp_part[32];
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   const size_t src = (size_t)(rows ? rows[b] : b) * H;
   float ss = 0.f;
@@ -79,8 +83,8 @@ KVB_EXPORT int kvb_add_rmsnorm(float* resid, const void* delta, const float* w, 
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
-    add_rmsnorm_kernel<T><<<n_out_rows, threads, smem, stream>>>(resid, (const T*)delta, w, (T*)out,
-                                                                  rows, H, eps);
+    kvb_launch(add_rmsnorm_kernel<T>, dim3(n_out_rows), dim3(threads), smem, stream, resid, (const T*)delta, w,
+               (T*)out, rows, H, eps);
   });
   return kvb_launch_result();
 }
@@ -90,6 +94,8 @@ KVB_EXPORT int kvb_add_rmsnorm(float* resid, const void* delta, const float* w, 
 // (upstream: base/src/kernels.cu:45-52)
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
@@ -106,7 +112,8 @@ KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int dtype,
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
                                                                       : 148 * 16);
-  KVB_DISPATCH_DTYPE(dtype, T, (silu_mul_kernel<T><<<blocks, threads, 0, stream>>>((const T*)gu, (T*)out, I, total)));
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu,
+                                            (T*)out, I, total)));
   return kvb_launch_result();
 }
 
@@ -125,6 +132,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
                                      int table_len, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      const int* __restrict__ block_table, int max_pages, int page_size,
                                      int num_pages, int nq, int nkv, int d, int rot, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rot >> 1;
@@ -193,9 +202,9 @@ KVB_EXPORT int kvb_rope_kv_write(void* qkv, const int* positions, const int* tok
   if (d % 2 || rot % 2 || rot > d) return KVB_ERR_BAD_SIZE;
   const int work = (nq + 2 * nkv) * (d / 2);
   const int threads = work >= 1024 ? 256 : 128;
-  KVB_DISPATCH_DTYPE(dtype, T, (rope_kv_write_kernel<T><<<T_, threads, 0, stream>>>(
-                                   (T*)qkv, positions, token_req, cos_t, sin_t, table_len, (T*)k_pages,
-                                   (T*)v_pages, block_table, max_pages, page_size, num_pages, nq, nkv, d,
-                                   rot, status)));
+  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(rope_kv_write_kernel<T>, dim3(T_), dim3(threads), 0, stream, (T*)qkv,
+                                            positions, token_req, cos_t, sin_t, table_len, (T*)k_pages,
+                                            (T*)v_pages, block_table, max_pages, page_size, num_pages, nq, nkv, d,
+                                            rot, status)));
   return kvb_launch_result();
 }

@@ -79,6 +79,8 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
   unsigned char* v_s = k_s + 2 * BN * D * 2;         // [2][BN][D]
   int* row_pos = reinterpret_cast<int*>(v_s + 2 * BN * D * 2);  // [BM] position of each row's token, -1 if none
 
+  pdl_trigger();
+  pdl_wait();
   const TileDesc tile = tiles[blockIdx.x];
   const int hk = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -275,10 +277,10 @@ int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_p
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(num_tiles, nkv);
-  paged_flash_attention_kernel<D><<<grid, kThreads, smem, stream>>>(
-      (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
-      block_table, max_pages, page_shift, num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq,
-      nkv, G, gp_shift, scale * 1.4426950408889634f, window, status);
+  kvb_launch(paged_flash_attention_kernel<D>, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q,
+             q_row_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, max_pages,
+             page_shift, num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq, nkv, G, gp_shift,
+             scale * 1.4426950408889634f, window, status);
   return kvb_launch_result();
 }
 

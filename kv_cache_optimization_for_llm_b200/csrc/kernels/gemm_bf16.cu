@@ -137,6 +137,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   unsigned* tmem_holder = reinterpret_cast<unsigned*>(accum + 1);
   int* flags = reinterpret_cast<int*>(tmem_holder + 1);  // [0]: abort, [1]: this block reduces the splits
 
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * TILE_N;
   const int per = (p.k_tiles + p.splits - 1) / p.splits;
@@ -159,11 +160,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const unsigned tmem_d = *tmem_holder;
 
   if (warp == 0 && lane == 0) {
-    // ---- TMA producer
-    for (int i = 0; i < my_tiles; ++i) {
+    // ---- TMA producer.  The weights do not depend on the kernel before this one: the
+    // first round of weight tiles is requested at once, the rows only after that kernel
+    // has finished.
+    const int first = min(p.stages, my_tiles);
+    for (int i = 0; i < first; ++i) {
+      mbar_expect_tx(&full[i], a_bytes + b_bytes);
+      tma_load_2d(a_s + (size_t)i * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[i]);
+    }
+    pdl_wait();
+    for (int i = 0; i < first; ++i)
+      tma_load_2d(b_s + (size_t)i * b_bytes, &map_x, (kt0 + i) * TILE_K, 0, &full[i]);
+    for (int i = first; i < my_tiles; ++i) {
       const int s = i % p.stages;
       const unsigned phase = (i / p.stages) & 1;
-      if (i >= p.stages && !mbar_wait(&empty[s], phase ^ 1)) { atomicExch(&flags[0], 1); break; }
+      if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(&flags[0], 1); break; }
       mbar_expect_tx(&full[s], a_bytes + b_bytes);
       tma_load_2d(a_s + (size_t)s * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[s]);
       tma_load_2d(b_s + (size_t)s * b_bytes, &map_x, (kt0 + i) * TILE_K, 0, &full[s]);
@@ -188,7 +199,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
   __syncwarp();
 
-  // ---- epilogue: all four warps
+  // ---- epilogue: all four warps (the accumulator depends on rows loaded after pdl_wait;
+  // the explicit wait also covers blocks that had no k tile)
+  pdl_wait();
   bool good = true;
   if (my_tiles > 0) good = mbar_wait(accum, 0);
   if (!good) atomicExch(&flags[0], 1);
@@ -388,13 +401,15 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = splits;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = kvb_pdl_enabled() ? 2 : 1;
   cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<0>, mw, mx, p);
   if (le != cudaSuccess) return (int)le;
   return kvb_launch_result();
