@@ -153,7 +153,9 @@ def run_decode(llm, batch, steps, warmup, end_to_end, seed):
             if ev.token is not None:
                 produced[ev.request_id] += 1
     lead = max(produced.values())
-    for _ in range(max(0, warmup - (lead - 1))):
+    # Warm-up: steps of single tokens only (the timed kind), at least three even when some
+    # requests already decoded while others still read their prompts.
+    for _ in range(max(3, warmup - (lead - 1))):
         eng.step()
         lead += 1
     if lead + steps > NEW_TOKENS:

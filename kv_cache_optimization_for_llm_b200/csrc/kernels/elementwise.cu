@@ -34,8 +34,82 @@ KVB_EXPORT int kvb_embed_gather(const void* table, int dtype, const int* ids, fl
 // ---------------------------------------------------------------- add + RMSNorm
 // v = resid[row] (+ delta[row]);  resid[row] = v (when delta is given and rows is null);
 // out[b] = v / sqrt(mean(v^2) + eps) * w          (upstream: base/src/kernels.cu:10-43)
-// The row is kept in shared memory between the two passes.  Sums run in a fixed
-// order that depends on H and the block size only, never on the batch.
+// Each thread keeps its share of the row in registers between the two passes (up to
+// kNormVec*4 elements per thread, 16-byte accesses).  Sums run in a fixed order that
+// depends on H and the block size only, never on the batch.
+constexpr int kNormThreads = 256;
+constexpr int kNormVec = 8;   // float4 groups per thread: rows up to 256*8*4 = 8192 wide stay in registers
+
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Pack4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&a);
+    u.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+__device__ __forceinline__ float block_sum(float v, float* warp_part) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+  const int nw = blockDim.x >> 5;
+  for (int i = 0; i < nw; ++i) t += warp_part[i];   // every thread adds the warps' sums in the same order
+  return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ w,
+                       T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+  __shared__ float warp_part[32];
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const size_t src = (size_t)(rows ? rows[b] : b) * H;
+  const int groups = H >> 2;
+  float4 v[kNormVec];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int g = i * kNormThreads + threadIdx.x;
+    if (g < groups) {
+      float4 x = *reinterpret_cast<const float4*>(resid + src + 4 * g);
+      if (delta) {
+        const float4 d = Pack4<T>::load(delta + src + 4 * g);
+        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+        if (!rows) *reinterpret_cast<float4*>(resid + src + 4 * g) = x;
+      }
+      v[i] = x;
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, warp_part) / (float)H + eps);
+  T* o = out + (size_t)b * H;
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int g = i * kNormThreads + threadIdx.x;
+    if (g < groups) {
+      const float4 ww = *reinterpret_cast<const float4*>(w + 4 * g);
+      Pack4<T>::store(o + 4 * g, make_float4(v[i].x * inv * ww.x, v[i].y * inv * ww.y, v[i].z * inv * ww.z,
+                                             v[i].w * inv * ww.w));
+    }
+  }
+}
+
+// General form: any H, the row is kept in shared memory between the two passes.
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                    const float* __restrict__ w, T* __restrict__ out,
@@ -56,16 +130,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
     row_cache[i] = v;
     ss += v * v;
   }
-  ss = warp_sum(ss);
-  if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    float v = threadIdx.x < (blockDim.x >> 5) ? warp_part[threadIdx.x] : 0.f;
-    v = warp_sum(v);
-    if (threadIdx.x == 0) warp_part[0] = 1.0f / sqrtf(v / (float)H + eps);
-  }
-  __syncthreads();
-  const float inv = warp_part[0];
+  const float inv = 1.0f / sqrtf(block_sum(ss, warp_part) / (float)H + eps);
   T* o = out + (size_t)b * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(row_cache[i] * inv * w[i]);
 }
@@ -74,6 +139,11 @@ KVB_EXPORT int kvb_add_rmsnorm(float* resid, const void* delta, const float* w, 
                                const int* rows, int n_out_rows, int H, float eps, int dtype,
                                cudaStream_t stream) {
   if (n_out_rows <= 0) return 0;
+  if (H % 4 == 0 && H <= kNormThreads * kNormVec * 4) {
+    KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(add_rmsnorm_vec_kernel<T>, dim3(n_out_rows), dim3(kNormThreads), 0,
+                                              stream, resid, (const T*)delta, w, (T*)out, rows, H, eps)));
+    return kvb_launch_result();
+  }
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return KVB_ERR_BAD_SIZE;  // widths above 51200 are refused
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
@@ -91,7 +161,25 @@ KVB_EXPORT int kvb_add_rmsnorm(float* resid, const void* delta, const float* w, 
 
 // ---------------------------------------------------------------- SiLU * up
 // out[t, i] = g * (1 / (1 + exp(-g))) * u with g = gu[t, i], u = gu[t, I + i]
-// (upstream: base/src/kernels.cu:45-52)
+// (upstream: base/src/kernels.cu:45-52).  Four elements per thread when I % 4 == 0.
+__device__ __forceinline__ float silu_mul_one(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
+
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t groups) {
+  pdl_trigger();
+  pdl_wait();
+  const int gpr = I >> 2;  // groups of four per row
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / gpr;
+    const int i = (int)(idx - t * gpr) << 2;
+    const float4 g = Pack4<T>::load(gu + t * 2 * I + i);
+    const float4 u = Pack4<T>::load(gu + t * 2 * I + I + i);
+    Pack4<T>::store(out + t * I + i, make_float4(silu_mul_one(g.x, u.x), silu_mul_one(g.y, u.y),
+                                                 silu_mul_one(g.z, u.z), silu_mul_one(g.w, u.w)));
+  }
+}
+
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
   pdl_trigger();
@@ -100,20 +188,24 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = to_f32(gu[t * 2 * I + i]);
-    const float u = to_f32(gu[t * 2 * I + I + i]);
-    out[idx] = from_f32<T>(g * (1.0f / (1.0f + expf(-g))) * u);
+    out[idx] = from_f32<T>(silu_mul_one(to_f32(gu[t * 2 * I + i]), to_f32(gu[t * 2 * I + I + i])));
   }
 }
 
 KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
-  const size_t total = (size_t)T_ * I;
   const int threads = 256;
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads
-                                                                      : 148 * 16);
-  KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu,
-                                            (T*)out, I, total)));
+  const bool vec = (I % 4 == 0);
+  const size_t work = vec ? (size_t)T_ * (I / 4) : (size_t)T_ * I;
+  size_t want = (work + threads - 1) / threads;
+  const int blocks = (int)(want < (size_t)148 * 16 ? want : (size_t)148 * 16);
+  if (vec) {
+    KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_vec_kernel<T>, dim3(blocks), dim3(threads), 0, stream,
+                                              (const T*)gu, (T*)out, I, work)));
+  } else {
+    KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream,
+                                              (const T*)gu, (T*)out, I, work)));
+  }
   return kvb_launch_result();
 }
 

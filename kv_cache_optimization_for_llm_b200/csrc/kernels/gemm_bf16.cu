@@ -12,11 +12,15 @@
 // to the TMA thread.  The four warps then read the accumulator with tcgen05.ld (warp
 // w owns features 32w..32w+31) and store C[row, feature].
 // When N gives too few blocks to pull the whole memory system, K is split over the
-// blocks of a thread-block cluster (gridDim.y = cluster size): each block parks its
-// float32 accumulator in its own shared memory, the cluster meets at its hardware
-// barrier, and block r adds up rows r, r + S, ... of all S blocks through distributed
-// shared memory, always in block order, so the sum has one fixed order.  No scratch in
-// global memory, no counters, no spinning.
+// blocks of a thread-block cluster (gridDim.y = cluster size): block s sends its
+// float32 partial of row m to slot s in the shared memory of block m mod S (distributed
+// shared memory), the cluster meets once at its hardware barrier, and every block adds
+// up the slots of its rows in block order, so the sum has one fixed order.  No scratch
+// in global memory, no counters, no spinning.
+// The weights do not depend on the step's data: a block asks for all its weight tiles
+// to be brought into L2 and requests the first ring of them before it waits for the
+// kernel in front of it (programmatic dependent launch), so weight traffic overlaps
+// the small kernels between the products.
 // Every wait on an mbarrier is bounded; a wait that runs out records
 // KVB_STATUS_WAIT_TIMEOUT, and the block frees its tensor memory and returns.
 #include "common.cuh"
@@ -97,12 +101,16 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_peer_f32(const void* my_smem_ptr, unsigned rank) {
+// Stores v at the place in block `rank`'s shared memory that `my_smem_ptr` names in ours.
+__device__ __forceinline__ void st_peer_f32(void* my_smem_ptr, unsigned rank, float v) {
   unsigned remote;
-  float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+// Asks for a tile to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void tma_prefetch_l2(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+               ::"l"((unsigned long long)map), "r"(x), "r"(y) : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
@@ -115,10 +123,21 @@ struct Params {
   int M, N, K, MP;            // MP: rows padded to the UMMA N extent
   int k_tiles, splits;        // k tiles in all, blocks along K
   int stages;
+  int red_bytes;              // shared memory set aside for the partials that peers send (splits > 1)
+  int prefetch_tiles;         // weight tiles beyond the first ring that are asked into L2 up front
   int out_f32;                // 1: C is float32, 0: bfloat16
   void* out;                  // [M, N]
   int* status;
+  unsigned long long* trace;  // optional [blocks, 8] nanosecond stamps of the phases of each block (profiling)
 };
+
+__device__ __forceinline__ void stamp(const Params& p, int slot) {
+  if (p.trace) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + slot] = t;
+  }
+}
 
 template <int kUnused = 0>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -131,7 +150,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int b_bytes = p.MP * TILE_K * 2;
   unsigned char* a_s = base;
   unsigned char* b_s = base + (size_t)p.stages * a_bytes;
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(b_s + (size_t)p.stages * b_bytes);
+  float* red = reinterpret_cast<float*>(b_s + (size_t)p.stages * b_bytes);  // never part of the stage ring:
+  // peers write here while this block may still be multiplying
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(red) + p.red_bytes);
   unsigned long long* empty = full + p.stages;
   unsigned long long* accum = empty + p.stages;
   unsigned* tmem_holder = reinterpret_cast<unsigned*>(accum + 1);
@@ -139,6 +160,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) stamp(p, 0);   // block started
   const int n0 = blockIdx.x * TILE_N;
   const int per = (p.k_tiles + p.splits - 1) / p.splits;
   const int kt0 = blockIdx.y * per;
@@ -168,7 +190,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       mbar_expect_tx(&full[i], a_bytes + b_bytes);
       tma_load_2d(a_s + (size_t)i * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[i]);
     }
+    for (int i = first; i < min(my_tiles, first + p.prefetch_tiles); ++i) tma_prefetch_l2(&map_w, (kt0 + i) * TILE_K, n0);
+    stamp(p, 1);                 // first round of weight tiles requested, the rest on their way to L2
     pdl_wait();
+    stamp(p, 2);                 // the kernel before this one has finished
     for (int i = 0; i < first; ++i)
       tma_load_2d(b_s + (size_t)i * b_bytes, &map_x, (kt0 + i) * TILE_K, 0, &full[i]);
     for (int i = first; i < my_tiles; ++i) {
@@ -187,6 +212,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const int s = i % p.stages;
       const unsigned phase = (i / p.stages) & 1;
       if (!mbar_wait(&full[s], phase)) { atomicExch(&flags[0], 1); ok = false; break; }
+      if (i == 0) stamp(p, 3);   // first tile arrived
       tc_fence_after();
       const unsigned long long ad = smem_desc_sw128(smem_u32(a_s + (size_t)s * a_bytes));
       const unsigned long long bd = smem_desc_sw128(smem_u32(b_s + (size_t)s * b_bytes));
@@ -195,6 +221,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
       umma_commit(&empty[s]);   // the stage is free once these products have read it
     }
+    stamp(p, 4);                // last product issued
     umma_commit(accum);         // everything issued so far has landed in tensor memory
   }
   __syncwarp();
@@ -209,6 +236,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   const bool aborted = flags[0] != 0;
   if (aborted && tid == 0) atomicCAS(p.status, 0, KVB_STATUS_WAIT_TIMEOUT);
+  if (tid == 0) stamp(p, 5);   // accumulator complete
 
   const int n = n0 + warp * 32 + lane;           // the feature this thread holds
   if (!aborted) {
@@ -232,9 +260,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
       }
     } else {
-      // park the accumulator as red[m][feature] in the (now idle) first stage buffers
-      float* red = reinterpret_cast<float*>(base);
-      for (int c = 0; c < p.MP; c += 16) {
+      // send row m of this block's partial to slot blockIdx.y of block (m mod S):
+      // red[(m / S) * S + slot][feature] there
+      for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
         if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
         else {
@@ -242,34 +270,34 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) red[(c + i) * TILE_N + tid] = v[i];
+        for (int i = 0; i < 16; ++i) {
+          const int m = c + i;
+          if (m < p.M)
+            st_peer_f32(red + ((m / p.splits) * p.splits + (int)blockIdx.y) * TILE_N + tid, (unsigned)(m % p.splits), v[i]);
+        }
       }
     }
   }
   if (p.splits > 1) {
     // Every block of the cluster comes here, aborted or not: the barrier is collective.
+    // After it all partials have arrived and nobody touches a peer's memory any more.
     cluster_sync_all();
     if (!aborted) {
-      const float* red = reinterpret_cast<const float*>(base);
-      for (int m = (int)blockIdx.y; m < p.M; m += p.splits) {
-        float t[16];   // all peers' values are requested before the first is used
-#pragma unroll
-        for (int s2 = 0; s2 < 16; ++s2) t[s2] = s2 < p.splits ? ld_peer_f32(red + m * TILE_N + tid, (unsigned)s2) : 0.f;
+      for (int m = (int)blockIdx.y, j = 0; m < p.M; m += p.splits, ++j) {
         float acc = 0.f;
-#pragma unroll
-        for (int s2 = 0; s2 < 16; ++s2) acc += t[s2];
+        for (int s2 = 0; s2 < p.splits; ++s2) acc += red[(j * p.splits + s2) * TILE_N + tid];
         if (n < p.N) {
           if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = acc;
           else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(acc);
         }
       }
     }
-    cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
   }
   if (aborted) {
     // give copies that may still be in flight time to land before the block ends
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
+  if (tid == 0) stamp(p, 6);   // result stored
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
@@ -345,7 +373,7 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
   const int k_tiles = (K + TILE_K - 1) / TILE_K;
   int s = (2 * 148) / tiles;                 // two blocks per SM in flight
   if (s > k_tiles / 2) s = k_tiles / 2;      // at least two k tiles per block
-  if (s > 16) s = 16;                        // the largest cluster
+  if (s > 8) s = 8;                          // the largest portable cluster
   if (s < 1) s = 1;
   while (s > 1 && (k_tiles + s - 1) / s * (s - 1) >= k_tiles) --s;  // no block without work
   *splits = s;
@@ -356,9 +384,11 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
 // C[M,N] = X[M,K] . W[N,K]^T, bfloat16 operands (ldx, ldw in elements, multiples of 8),
 // C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
 // address is stable (a captured graph), so its tensor map may be cached as the
-// weights' is.  Uses no memory beyond its operands.
+// weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
+// block (profiling only).  Uses no memory beyond its operands.
 KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
-                               int K, int x_is_static, int* status, cudaStream_t stream) {
+                               int K, int x_is_static, int* status, unsigned long long* trace,
+                               cudaStream_t stream) {
   int splits, tiles;
   const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &tiles);
   if (rc) return rc;
@@ -370,19 +400,26 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   p.M = M; p.N = N; p.K = K; p.MP = MP;
   p.k_tiles = (K + TILE_K - 1) / TILE_K;
   p.splits = splits;
-  p.out_f32 = out_f32; p.out = out; p.status = status;
+  p.out_f32 = out_f32; p.out = out; p.status = status; p.trace = trace;
   const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
   // two blocks per SM while the stages stay deep enough, one block otherwise
   const int budget = MP <= 64 ? 108 * 1024 : 200 * 1024;
-  int stages = budget / stage_bytes;
+  // room for the partials of this block's rows from every block of the cluster
+  int red_bytes = splits > 1 ? ((M + splits - 1) / splits) * splits * TILE_N * 4 : 0;
+  if (red_bytes > budget - 2 * stage_bytes) { splits = 1; red_bytes = 0; }   // no room: one block does all of K
+  p.splits = splits;
+  p.red_bytes = red_bytes;
+  int stages = (budget - red_bytes) / stage_bytes;
   if (stages > 8) stages = 8;
   const int per = (p.k_tiles + splits - 1) / splits;
   if (stages > per) stages = per;
   if (stages < 2) stages = 2;
-  // the split reduction parks MP x 128 floats in the stage buffers
-  while (splits > 1 && stages * stage_bytes < MP * TILE_N * 4) ++stages;
   p.stages = stages;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 1) * 8 + 16;
+  // Blocks that all run at once (one wave) may ask for more of their weights ahead of
+  // time; with several waves that would only push the first wave's loads back.
+  static const int prefetch_env = [] { const char* e = std::getenv("KVB200_GEMM_PREFETCH"); return e ? atoi(e) : 8; }();
+  p.prefetch_tiles = (tiles * splits <= 2 * 148) ? prefetch_env : 0;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + (2 * stages + 1) * 8 + 16;
   CUtensorMap mw, mx;
   int e = cached_map(&mw, w, N, K, ldw, TILE_N);
   if (e) return e;

@@ -175,7 +175,7 @@ def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token
 
 # ------------------------------------------------------------------ matrix products
 
-SKINNY_MAX_ROWS = 256
+SKINNY_MAX_ROWS = int(__import__('os').environ.get('KVB200_SKINNY_MAX_ROWS', '16'))
 _status_word: Dict[int, torch.Tensor] = {}
 
 
@@ -361,7 +361,7 @@ def gemm_skinny_plan(M: int, N: int, K: int):
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor,
-                x_is_static: bool = False) -> torch.Tensor:
+                x_is_static: bool = False, trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x . w^T`` for few rows (M <= 256) on tcgen05 tensor cores, weights streamed by TMA."""
     _need_cuda(x, w)
     M, K = x.shape
@@ -370,7 +370,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     rc = lib("gemm_bf16").kvb_gemm_skinny(
         _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(1 if out_dtype == torch.float32 else 0),
-        c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), _p(status), _stream())
+        c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), _p(status), _p(trace), _stream())
     if rc == -2:
         raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
     _check(rc, "gemm_skinny")
