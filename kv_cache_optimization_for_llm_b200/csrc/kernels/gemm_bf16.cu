@@ -107,6 +107,10 @@ __device__ __forceinline__ void st_peer_f32(void* my_smem_ptr, unsigned rank, fl
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
+// Asks for `bytes` (a multiple of 16, 16-byte aligned) to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* ptr, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+}
 // Asks for a tile to be brought into L2; nothing waits for it.
 __device__ __forceinline__ void tma_prefetch_l2(const CUtensorMap* map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
@@ -129,6 +133,8 @@ struct Params {
   void* out;                  // [M, N]
   int* status;
   unsigned long long* trace;  // optional [blocks, 8] nanosecond stamps of the phases of each block (profiling)
+  const unsigned char* next_w;  // optional: the weights the following product will read ...
+  long long next_bytes;         // ... and how many bytes of them to ask into L2 (a multiple of 4096)
 };
 
 __device__ __forceinline__ void stamp(const Params& p, int slot) {
@@ -204,6 +210,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       tma_load_2d(a_s + (size_t)s * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[s]);
       tma_load_2d(b_s + (size_t)s * b_bytes, &map_x, (kt0 + i) * TILE_K, 0, &full[s]);
     }
+  } else if (warp == 3 && p.next_w != nullptr) {
+    // ---- The weights of the product after this one start their way into L2 now, a slice
+    // per block, behind this block's own first tiles, so that the memory system stays busy
+    // through the small kernels that run between the two products.
+    if (my_tiles > 0) mbar_wait(&full[0], 0);
+    const long long blocks = (long long)gridDim.x * gridDim.y;
+    const long long me = (long long)blockIdx.y * gridDim.x + blockIdx.x;
+    const long long chunks = p.next_bytes / 4096;
+    for (long long c = me * 32 + lane; c < chunks; c += blocks * 32) bulk_prefetch_l2(p.next_w + c * 4096, 4096);
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer
     const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.MP >> 3) << 17) | ((unsigned)(TILE_N >> 4) << 24);
@@ -385,10 +400,12 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
 // C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
 // address is stable (a captured graph), so its tensor map may be cached as the
 // weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
-// block (profiling only).  Uses no memory beyond its operands.
+// block (profiling only).  next_w / next_bytes: nullptr, or the weights that the product
+// after this one will read; the kernel asks for them to be brought into L2 (a hint: it
+// changes no result).  Uses no memory beyond its operands.
 KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
                                int K, int x_is_static, int* status, unsigned long long* trace,
-                               cudaStream_t stream) {
+                               const void* next_w, long long next_bytes, cudaStream_t stream) {
   int splits, tiles;
   const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &tiles);
   if (rc) return rc;
@@ -401,6 +418,9 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   p.k_tiles = (K + TILE_K - 1) / TILE_K;
   p.splits = splits;
   p.out_f32 = out_f32; p.out = out; p.status = status; p.trace = trace;
+  p.next_w = reinterpret_cast<const unsigned char*>(next_w);
+  p.next_bytes = (next_w && !(reinterpret_cast<uintptr_t>(next_w) & 15)) ? (next_bytes / 4096) * 4096 : 0;
+  if (p.next_bytes == 0) p.next_w = nullptr;
   const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
   // two blocks per SM while the stages stay deep enough, one block otherwise
   const int budget = MP <= 64 ? 108 * 1024 : 200 * 1024;
