@@ -351,6 +351,262 @@ decode_attention_split_kernel(const T* __restrict__ q_base, int q_row_stride, co
   }
 }
 
+// ---------------------------------------------------------------------------
+// The whole attention of a decode step in one launch: rotary encoding of the query
+// and the new key, the write of the new key and value into their page, the split
+// attention over the key blocks, and the merge of the key blocks' partials.
+//
+// Block (kv head, request, slot) as above.  Every block rotates its own copy of the
+// group's queries (kept in float32).  The block that owns the key block holding the
+// token's own position rotates the new key, stores key and value into the cache, and
+// then reads them back like any other key.  After its last key block a block adds one
+// to the counter of its (request, kv head); the block that brings the counter to the
+// number of participating blocks merges all partials in ascending key-block order and
+// writes the output, then clears the counter.  Nobody waits for anybody.
+// qkv rows stay as the projection wrote them (unrotated).
+// ---------------------------------------------------------------------------
+template <typename T, int D, int GMAX>
+__global__ void __launch_bounds__(kDecThreads, 5)
+decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __restrict__ k_pages,
+                              T* __restrict__ v_pages, int write_kv, const int* __restrict__ block_table,
+                              int max_pages, int page_size, int num_pages, const int* __restrict__ q_start,
+                              const int* __restrict__ ctx_len, const float* __restrict__ cos_t,
+                              const float* __restrict__ sin_t, int table_len, int rot, T* __restrict__ out,
+                              float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                              int nq, int nkv, int G, float scale, int window, int KB, int NB, int* status) {
+  constexpr int DPL = D / 32;
+  constexpr int CPK = D * (int)sizeof(T) / 16;
+  __shared__ __align__(16) float q_s[GMAX][D];
+  __shared__ float red_s[4][GMAX];
+  __shared__ int last_s;
+  extern __shared__ __align__(16) unsigned char dec_smem[];
+  T (*v_s)[32][D] = reinterpret_cast<T (*)[32][D]>(dec_smem);
+
+  pdl_trigger();
+  pdl_wait();
+  const int hk = blockIdx.x, r = blockIdx.y;
+  const int pos = ctx_len[r] - 1;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (pos < 0 || pos / KB >= NB || (cos_t != nullptr && pos >= table_len)) {
+    if (tid == 0 && blockIdx.z == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
+    return;
+  }
+  if ((int)blockIdx.z * KB > pos) return;   // no key block for this slot; it is not counted either
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int* table = block_table + (size_t)r * max_pages;
+  const T* row = qkv + (size_t)q_start[r] * q_row_stride;
+  const int half = rot >> 1;
+  const bool rotary = cos_t != nullptr && rot > 0;
+
+  // the group's queries, rotated (pairs (j, j + rot/2) of the first rot dims), scaled
+  for (int i = tid; i < G * D; i += kDecThreads) {
+    const int g = i / D, dd = i % D;
+    const T* qh = row + (size_t)(hk * G + g) * D;
+    float val;
+    if (rotary && dd < rot) {
+      const int j = dd < half ? dd : dd - half;
+      const float c = cos_t[(size_t)pos * half + j], sn = sin_t[(size_t)pos * half + j];
+      const float x1 = to_f32(qh[j]), x2 = to_f32(qh[j + half]);
+      val = dd < half ? x1 * c - x2 * sn : x1 * sn + x2 * c;
+    } else {
+      val = to_f32(qh[dd]);
+    }
+    q_s[g][dd] = val * scale;
+  }
+  // the new key and value go to their page, written by the block that will read them
+  const int b_star = pos / KB;
+  if (write_kv && (b_star % (int)gridDim.z) == (int)blockIdx.z) {
+    const int lp = pos / page_size;
+    const int page = lp < max_pages ? table[lp] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (tid == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+    } else {
+      const size_t dst = (((size_t)page * nkv + hk) * page_size + (pos % page_size)) * D;
+      const T* kh = row + (size_t)(nq + hk) * D;
+      const T* vh = row + (size_t)(nq + nkv + hk) * D;
+      for (int dd = tid; dd < D; dd += kDecThreads) {
+        float val;
+        if (rotary && dd < rot) {
+          const int j = dd < half ? dd : dd - half;
+          const float c = cos_t[(size_t)pos * half + j], sn = sin_t[(size_t)pos * half + j];
+          const float x1 = to_f32(kh[j]), x2 = to_f32(kh[j + half]);
+          val = dd < half ? x1 * c - x2 * sn : x1 * sn + x2 * c;
+        } else {
+          val = to_f32(kh[dd]);
+        }
+        k_pages[dst + dd] = from_f32<T>(val);
+        v_pages[dst + dd] = vh[dd];
+      }
+    }
+    __threadfence();   // the cp.async reads below go to L2: the stores must have reached it
+  }
+  __syncthreads();
+
+  for (int b = blockIdx.z; b * KB <= pos && b < NB; b += gridDim.z) {
+    const int k0 = b * KB;
+    if (k0 + KB <= lo) continue;
+    float m_run[GMAX], l_run[GMAX], acc[GMAX][DPL];
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g) {
+      m_run[g] = -CUDART_INF_F; l_run[g] = 0.f;
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) acc[g][e] = 0.f;
+    }
+    const int k_end = min(k0 + KB, pos + 1);
+    for (int base = k0; base < k_end; base += kDecThreads) {
+      const int j = base + tid;
+      const bool valid = j < k_end && j >= lo;
+      long long off = -1;
+      if (valid) {
+        const int lp = j / page_size;
+        const int page = lp < max_pages ? table[lp] : -1;
+        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        else off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * D;
+      }
+#pragma unroll
+      for (int i = 0; i < CPK; ++i) {
+        const int c = i * 32 + lane;
+        const int key = c / CPK, part = c % CPK;
+        const long long oj = __shfl_sync(0xffffffffu, off, key);
+        if (oj >= 0)
+          cp_async_16(reinterpret_cast<char*>(&v_s[warp][key][0]) + part * 16,
+                      reinterpret_cast<const char*>(v_pages + oj) + part * 16);
+      }
+      float s[GMAX];
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) s[g] = -CUDART_INF_F;
+      if (off >= 0) {
+        const T* k = k_pages + off;
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g) s[g] = 0.f;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+          float kf[8];
+          Vec8<T>::load(k + c * 8, kf);
+#pragma unroll
+          for (int g = 0; g < GMAX; ++g) {
+            if (g < G) {
+              const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][c * 8]);
+              const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][c * 8 + 4]);
+              float t = s[g];
+              t = fmaf(qa.x, kf[0], t); t = fmaf(qa.y, kf[1], t); t = fmaf(qa.z, kf[2], t); t = fmaf(qa.w, kf[3], t);
+              t = fmaf(qb.x, kf[4], t); t = fmaf(qb.y, kf[5], t); t = fmaf(qb.z, kf[6], t); t = fmaf(qb.w, kf[7], t);
+              s[g] = t;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        const float wm = warp_max(g < G ? s[g] : -CUDART_INF_F);
+        if (lane == 0) red_s[warp][g] = wm;
+      }
+      __syncthreads();
+      float p[GMAX], corr[GMAX];
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        const float bm = fmaxf(fmaxf(red_s[0][g], red_s[1][g]), fmaxf(red_s[2][g], red_s[3][g]));
+        const float m_new = fmaxf(m_run[g], bm);
+        corr[g] = (m_run[g] == -CUDART_INF_F) ? 0.f : __expf(m_run[g] - m_new);
+        p[g] = (off >= 0 && g < G) ? __expf(s[g] - m_new) : 0.f;
+        m_run[g] = m_new;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        const float ws = warp_sum(p[g]);
+        if (lane == 0) red_s[warp][g] = ws;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        l_run[g] = l_run[g] * corr[g] + ((red_s[0][g] + red_s[1][g]) + (red_s[2][g] + red_s[3][g]));
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[g][e] *= corr[g];
+      }
+      cp_async_wait_all();
+      __syncwarp();
+      const int n_here = min(32, k_end - (base + warp * 32));
+      for (int jj = 0; jj < n_here; ++jj) {
+        const long long oj = __shfl_sync(0xffffffffu, off, jj);
+        float pj[GMAX];
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g) pj[g] = __shfl_sync(0xffffffffu, p[g], jj);
+        if (oj < 0) continue;
+        float vf[DPL];
+        const T* v = &v_s[warp][jj][lane * DPL];
+        if constexpr (sizeof(T) == 2 && DPL == 2) {
+          const unsigned w = *reinterpret_cast<const unsigned*>(v);
+          vf[0] = __uint_as_float(w << 16); vf[1] = __uint_as_float(w & 0xffff0000u);
+        } else if constexpr (sizeof(T) == 2 && DPL == 4) {
+          const uint2 w = *reinterpret_cast<const uint2*>(v);
+          vf[0] = __uint_as_float(w.x << 16); vf[1] = __uint_as_float(w.x & 0xffff0000u);
+          vf[2] = __uint_as_float(w.y << 16); vf[3] = __uint_as_float(w.y & 0xffff0000u);
+        } else {
+#pragma unroll
+          for (int e = 0; e < DPL; ++e) vf[e] = to_f32(v[e]);
+        }
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g)
+          if (g < G)
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(pj[g], vf[e], acc[g][e]);
+      }
+      __syncthreads();
+    }
+    float* red = reinterpret_cast<float*>(dec_smem);
+    static_assert(sizeof(T) * 32 >= sizeof(float) * GMAX, "the value stage must hold the warps' partial outputs");
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g)
+      if (g < G)
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) red[(warp * GMAX + g) * D + lane * DPL + e] = acc[g][e];
+    __syncthreads();
+    for (int i = tid; i < G * D; i += kDecThreads) {
+      const int g = i / D, dd = i % D;
+      const float o = (red[(0 * GMAX + g) * D + dd] + red[(1 * GMAX + g) * D + dd]) +
+                      (red[(2 * GMAX + g) * D + dd] + red[(3 * GMAX + g) * D + dd]);
+      part_o[(((size_t)r * nq + hk * G + g) * NB + b) * D + dd] = o;
+    }
+    if (tid < G) {
+      float mm = 0.f, ll = 0.f;
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) if (g == tid) { mm = m_run[g]; ll = l_run[g]; }
+      float* ml = part_ml + (((size_t)r * nq + hk * G + tid) * NB + b) * 2;
+      ml[0] = mm; ml[1] = ll;
+    }
+    __syncthreads();
+  }
+
+  // ---- who is last merges
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int expected = min((int)gridDim.z, pos / KB + 1);
+    const int old = atomicAdd(&counters[r * nkv + hk], 1);
+    last_s = (old == expected - 1);
+    if (last_s) counters[r * nkv + hk] = 0;   // ready for the next launch
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  const int b0 = lo / KB, b1 = pos / KB;
+  for (int i = tid; i < G * D; i += kDecThreads) {
+    const int g = i / D, dd = i % D;
+    const float* ml = part_ml + ((size_t)r * nq + hk * G + g) * NB * 2;
+    const float* po = part_o + ((size_t)r * nq + hk * G + g) * NB * D;
+    float M = -CUDART_INF_F;
+    for (int b = b0; b <= b1; ++b) M = fmaxf(M, __ldcg(ml + 2 * b));
+    float L = 0.f, a = 0.f;
+    for (int b = b0; b <= b1; ++b) {
+      const float f = __expf(__ldcg(ml + 2 * b) - M);
+      L += __ldcg(ml + 2 * b + 1) * f;
+      a += __ldcg(po + (size_t)b * D + dd) * f;
+    }
+    out[((size_t)q_start[r] * nq + hk * G + g) * D + dd] = from_f32<T>(L > 0.f ? a / L : 0.f);
+  }
+}
+
 template <typename T, int D>
 __global__ void decode_attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 const int* __restrict__ q_start, const int* __restrict__ ctx_len,
@@ -508,4 +764,58 @@ KVB_EXPORT int kvb_decode_attention_noalloc(const void* q, int q_row_stride, con
   return kvb_decode_attention(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_size, num_pages,
                               q_start, ctx_len, out, part_o, part_ml, R, nq, nkv, d, scale, window, KB, NB,
                               dtype, status, stream);
+}
+
+
+template <typename T, int D, int GMAX>
+static int launch_decode_fused(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv,
+                               const int* block_table, int max_pages, int page_size, int num_pages,
+                               const int* q_start, const int* ctx_len, const float* cos_t, const float* sin_t,
+                               int table_len, int rot, void* out, float* part_o, float* part_ml, int* counters,
+                               int R, int nq, int nkv, float scale, int window, int KB, int NB, int* status,
+                               cudaStream_t stream) {
+  int slots = (4 * 148 + nkv * R - 1) / (nkv * R);
+  slots = slots < 1 ? 1 : (slots > NB ? NB : slots);
+  dim3 grid(nkv, R, slots);
+  const size_t smem = (size_t)4 * 32 * D * sizeof(T);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_fused_kernel<T, D, GMAX>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kvb_launch(decode_attention_fused_kernel<T, D, GMAX>, grid, dim3(kDecThreads), smem, stream, (const T*)qkv,
+             q_row_stride, (T*)k_pages, (T*)v_pages, write_kv, block_table, max_pages, page_size, num_pages,
+             q_start, ctx_len, cos_t, sin_t, table_len, rot, (T*)out, part_o, part_ml, counters, nq, nkv, nq / nkv,
+             scale, window, KB, NB, status);
+  return kvb_launch_result();
+}
+
+// The attention of a decode step in one launch (see decode_attention_fused_kernel).
+// qkv: [T, (nq + 2 nkv) d] as the projection wrote it; request r's token is row q_start[r]
+// at position ctx_len[r]-1.  write_kv = 0: the layer reads another layer's cache and
+// writes nothing.  cos_t/sin_t: [table_len, rot/2] or nullptr for no rotation.
+// Scratch: part_o [R, nq, NB, d], part_ml [R, nq, NB, 2] float32; counters [R * nkv] int32,
+// zero on entry, left zero.  Same size rules as kvb_decode_attention.
+KVB_EXPORT int kvb_decode_attention_fused(const void* qkv, int q_row_stride, void* k_pages, void* v_pages,
+                                          int write_kv, const int* block_table, int max_pages, int page_size,
+                                          int num_pages, const int* q_start, const int* ctx_len,
+                                          const float* cos_t, const float* sin_t, int table_len, int rot, void* out,
+                                          float* part_o, float* part_ml, int* counters, int R, int nq, int nkv,
+                                          int d, float scale, int window, int KB, int NB, int dtype, int* status,
+                                          cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (nkv < 1 || nq % nkv || !kvb_decode_attention_supported(d, nq / nkv) || KB % kDecThreads || NB < 1 ||
+      R > 65535 || (rot & 1) || rot > d)
+    return KVB_ERR_BAD_SIZE;
+  const int G = nq / nkv;
+#define KVB_DECF(T, D, GM)                                                                                   \
+  return launch_decode_fused<T, D, GM>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, \
+                                       page_size, num_pages, q_start, ctx_len, cos_t, sin_t, table_len, rot,  \
+                                       out, part_o, part_ml, counters, R, nq, nkv, scale, window, KB, NB,     \
+                                       status, stream)
+#define KVB_DECF_D(T, D) do { if (G <= 2) KVB_DECF(T, D, 2); else if (G <= 4) KVB_DECF(T, D, 4); else KVB_DECF(T, D, 8); } while (0)
+#define KVB_DECF_T(T) do { if (d == 32) KVB_DECF_D(T, 32); else if (d == 64) KVB_DECF_D(T, 64); else KVB_DECF_D(T, 128); } while (0)
+  if (dtype == KVB_BF16) KVB_DECF_T(__nv_bfloat16);
+  if (dtype == KVB_F32) KVB_DECF_T(float);
+  return KVB_ERR_BAD_DTYPE;
 }

@@ -307,19 +307,50 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
     return out
 
 
-def attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window, max_positions) -> torch.Tensor:
-    """Attention of the step's tokens over their requests' pages; picks the kernel.
-    float32 always takes the general kernel, whose sums follow absolute positions in
-    one fixed order whatever the shape of the step.  bfloat16: single tokens only ->
-    the split decode kernel; runs of tokens -> the tensor-core kernel; sizes neither
-    takes -> the general kernel."""
-    if qkv.dtype == torch.bfloat16:
-        group, page_size = nq // nkv, k_pages.shape[2]
-        if batch.decode_only and decode_attention_supported(d, group):
-            return decode_attention(qkv, k_pages, v_pages, block_table, batch.q_start, batch.ctx_len, nq, nkv, d,
-                                    scale, window, max_positions, batch.status)
-        if not batch.decode_only and flash_attention_supported(d, group, page_size):
-            return flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window)
+def decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
+                           nq, nkv, d, scale, window, max_positions, status) -> torch.Tensor:
+    """The whole attention of a decode step in one launch: rotary encoding of query and
+    new key, the write of key and value into their page, split attention, merge."""
+    _need_cuda(qkv, k_pages)
+    R = ctx_len.numel()
+    T = qkv.shape[0]
+    kb, nb = decode_key_blocks(max_positions)
+    dev = qkv.device
+    part_o = scratch(("dec_o", dev.index, R, nq, nb, d), (R, nq, nb, d), torch.float32, dev)
+    part_ml = scratch(("dec_ml", dev.index, R, nq, nb), (R, nq, nb, 2), torch.float32, dev)
+    counters = _scratch.get(("dec_counters", dev.index))
+    if counters is None or counters.numel() < R * nkv:
+        counters = torch.zeros(max(R * nkv, 4096), dtype=torch.int32, device=dev)
+        _scratch[("dec_counters", dev.index)] = counters
+    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=dev)
+    rc = lib("attention").kvb_decode_attention_fused(
+        _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), c_int(1 if write_kv else 0), _p(block_table),
+        c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
+        _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rot), _p(out), _p(part_o), _p(part_ml),
+        _p(counters), c_int(R), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)),
+        c_int(kb), c_int(nb), c_int(dtype_code(qkv.dtype)), _p(status), _stream())
+    _check(rc, "decode_attention_fused")
+    return out
+
+
+def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv, d, scale, window, max_positions,
+                   cos, sin, rot) -> torch.Tensor:
+    """Everything between the q|k|v projection and the output projection: rotary
+    encoding, the write of keys and values into their pages, attention over the pages.
+    Picks the kernels:
+    * float32: rotary/write kernel, then the general kernel, whose sums follow absolute
+      positions in one fixed order whatever the shape of the step;
+    * bfloat16, single tokens only: one fused launch (split over key blocks);
+    * bfloat16, runs of tokens: rotary/write kernel, then the tensor-core kernel;
+    * sizes neither takes: rotary/write kernel, then the general kernel."""
+    group, page_size = nq // nkv, k_pages.shape[2]
+    if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_supported(d, group):
+        return decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
+                                      cos, sin, rot, nq, nkv, d, scale, window, max_positions, batch.status)
+    rope_kv_write(qkv, batch.positions, batch.token_req, cos, sin, k_pages if write_kv else None,
+                  v_pages if write_kv else None, block_table, page_size, nq, nkv, d, rot, batch.status)
+    if qkv.dtype == torch.bfloat16 and not batch.decode_only and flash_attention_supported(d, group, page_size):
+        return flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window)
     return paged_attention_generic(qkv, k_pages, v_pages, block_table, batch.positions, batch.token_req,
                                    nq, nkv, d, scale, window, batch.status)
 

@@ -68,9 +68,6 @@ class GroupedQueryAttention(Part):
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rot = self.position.rotary_dim if self.position is not None else 0
         table = batch.block_tables[cache.group]
-        ops.rope_kv_write(qkv, batch.positions, batch.token_req, cos, sin,
-                          cache.k if cache.write else None, cache.v if cache.write else None,
-                          table, cache.page_size, self.nq, self.nkv, self.d, rot, batch.status)
-        a = ops.attention(qkv, cache.k, cache.v, table, batch, self.nq, self.nkv, self.d, self.scale,
-                          self.window, self.ctx.max_positions)
+        a = ops.attention_step(qkv, cache.k, cache.v, cache.write, table, batch, self.nq, self.nkv, self.d,
+                               self.scale, self.window, self.ctx.max_positions, cos, sin, rot)
         return ops.linear(a, self.o)

@@ -364,3 +364,74 @@ def test_flash_attention_finds_a_far_key(spike):
     page, slot = int(c["table"][0, spike // 16]), spike % 16
     want = np.repeat(as64(c["vp"][page, :, slot]), nq // nkv, axis=0).reshape(-1)
     assert np.abs(as64(out)[-1] - want).max() < 0.08      # the last query sees that key's value
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,d,rot,page_size,window,write", [
+    (8, 2, 64, 64, 16, None, True), (32, 8, 64, 64, 16, None, True), (6, 1, 32, 32, 16, None, True),
+    (24, 8, 128, 128, 16, None, True), (8, 2, 64, 32, 8, None, True), (8, 2, 64, 64, 16, 100, True),
+    (4, 4, 32, 32, 4, 129, True), (8, 2, 64, 64, 16, None, False)])
+def test_fused_decode_attention(dtype, nq, nkv, d, rot, page_size, window, write):
+    """One launch does rotary encoding, the cache write, split attention and the merge:
+    against rotate-then-attend in float64.  The cache holds everything but the newest
+    key/value of each request, which the kernel has to put there itself."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    rng = np.random.default_rng(nq * d + rot)
+    ctxs = [1, 128, 129, 640, 300, 2, 1000]
+    R = len(ctxs)
+    max_pos = 1024
+    inv = P.rope_inv_freq(rot, 10000.0)
+    ang = np.arange(max_pos)[:, None] * inv[None, :]
+    cos_t, sin_t = dev(np.cos(ang), torch.float32), dev(np.sin(ang), torch.float32)
+    max_pages = max(-(-c // page_size) for c in ctxs) + 1
+    num_pages = sum(-(-c // page_size) for c in ctxs) + 2
+    kp = np.full((num_pages, nkv, page_size, d), 7.0)
+    vp = np.full((num_pages, nkv, page_size, d), -9.0)
+    free = list(rng.permutation(num_pages))
+    tables = np.full((R, max_pages), -1, dtype=np.int32)
+    rows, refs, new_kv = [], [], []
+    def rotate(x, pos):   # [heads, d] at one position
+        out = x.copy()
+        c, s = np.cos(ang[pos])[None, :], np.sin(ang[pos])[None, :]
+        out[:, :rot] = P.apply_rope(x[None, :, :rot], c, s)[0]
+        return out
+    for r, ctx in enumerate(ctxs):
+        k = as64(dev(rng.normal(size=(ctx, nkv, d)), DT[dtype]))      # keys as stored: already rotated
+        v = as64(dev(rng.normal(size=(ctx, nkv, d)), DT[dtype]))
+        q_raw = as64(dev(rng.normal(size=(nq, d)), DT[dtype]))
+        k_raw = as64(dev(rng.normal(size=(nkv, d)), DT[dtype]))
+        pos = ctx - 1
+        if write:
+            k[pos] = as64(dev(rotate(k_raw, pos), DT[dtype]))         # what the kernel must store
+            v_new = v[pos]
+        for j in range(ctx):
+            lp = j // page_size
+            if tables[r, lp] < 0:
+                tables[r, lp] = free.pop()
+            if j == pos and write:
+                continue                                                # left for the kernel to write
+            kp[tables[r, lp], :, j % page_size] = k[j]
+            vp[tables[r, lp], :, j % page_size] = v[j]
+        q_rot = rotate(q_raw, pos)
+        qfull = np.zeros((ctx, nq, d)); qfull[pos] = q_rot
+        refs.append(P.attention(qfull, k, v, window=window)[pos].reshape(-1))
+        rows.append(np.concatenate([q_raw.reshape(-1), k_raw.reshape(-1), v[pos].reshape(-1)]))
+        new_kv.append((tables[r, pos // page_size], pos % page_size, k[pos], v[pos]))
+    qkv = dev(np.array(rows), DT[dtype])
+    dkp, dvp = dev(kp, DT[dtype]), dev(vp, DT[dtype])
+    st = status()
+    out = ops.decode_attention_fused(qkv, dkp, dvp, write, dev(tables, torch.int32),
+                                     dev(np.arange(R + 1), torch.int32), dev(ctxs, torch.int32), cos_t, sin_t, rot,
+                                     nq, nkv, d, 1 / math.sqrt(d), window, max_pos, st)
+    assert int(st.item()) == 0
+    ref = np.array(refs)
+    assert rel_err(out, ref) < TOL[dtype] * (1 if dtype == "float32" else 1.5)
+    for page, slot, k_want, v_want in new_kv:
+        if write:
+            assert np.abs(as64(dkp[page, :, slot]) - k_want).max() < TOL[dtype] * 4
+            assert np.array_equal(as64(dvp[page, :, slot]), v_want)
+    # twice in a row: the counters were left at zero
+    out2 = ops.decode_attention_fused(qkv, dkp, dvp, write, dev(tables, torch.int32),
+                                      dev(np.arange(R + 1), torch.int32), dev(ctxs, torch.int32), cos_t, sin_t, rot,
+                                      nq, nkv, d, 1 / math.sqrt(d), window, max_pos, st)
+    assert torch.equal(out, out2)
