@@ -366,38 +366,86 @@ decode_attention_split_kernel(const T* __restrict__ q_base, int q_row_stride, co
 // qkv rows stay as the projection wrote them (unrotated).
 // ---------------------------------------------------------------------------
 template <typename T, int D, int GMAX>
-__global__ void __launch_bounds__(kDecThreads, 5)
+__global__ void __launch_bounds__(kDecThreads, 4)
 decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __restrict__ k_pages,
                               T* __restrict__ v_pages, int write_kv, const int* __restrict__ block_table,
                               int max_pages, int page_size, int num_pages, const int* __restrict__ q_start,
                               const int* __restrict__ ctx_len, const float* __restrict__ cos_t,
                               const float* __restrict__ sin_t, int table_len, int rot, T* __restrict__ out,
                               float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                              int nq, int nkv, int G, float scale, int window, int KB, int NB, int* status) {
+                              int nq, int nkv, int G, float scale, int window, int KB, int NB, int* status,
+                              unsigned long long* trace) {
   constexpr int DPL = D / 32;
-  constexpr int CPK = D * (int)sizeof(T) / 16;
+  constexpr int CPK = D * (int)sizeof(T) / 16;   // 16-byte chunks per key or value row
+  constexpr int EPC = 16 / (int)sizeof(T);       // elements per chunk
   __shared__ __align__(16) float q_s[GMAX][D];
   __shared__ float red_s[4][GMAX];
   __shared__ int last_s;
   extern __shared__ __align__(16) unsigned char dec_smem[];
-  T (*v_s)[32][D] = reinterpret_cast<T (*)[32][D]>(dec_smem);
-
+  T (*k_s)[32][D] = reinterpret_cast<T (*)[32][D]>(dec_smem);                                  // [4][32][D]
+  T (*v_s)[32][D] = reinterpret_cast<T (*)[32][D]>(dec_smem + (size_t)4 * 32 * D * sizeof(T)); // [4][32][D]
+  // optional profiling: nanosecond stamps of this block's phases, [blocks, 8]
+  auto stamp = [&](int slot) {
+    if (trace && threadIdx.x == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      trace[(((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + slot] = t;
+    }
+  };
+  stamp(0);
   pdl_trigger();
-  pdl_wait();
+  // Lengths, block tables and the keys and values of earlier tokens were all written
+  // before the kernel in front of this one started, so they may be read at once.
   const int hk = blockIdx.x, r = blockIdx.y;
   const int pos = ctx_len[r] - 1;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (pos < 0 || pos / KB >= NB || (cos_t != nullptr && pos >= table_len)) {
+    pdl_wait();
     if (tid == 0 && blockIdx.z == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
     return;
   }
   if ((int)blockIdx.z * KB > pos) return;   // no key block for this slot; it is not counted either
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int* table = block_table + (size_t)r * max_pages;
-  const T* row = qkv + (size_t)q_start[r] * q_row_stride;
   const int half = rot >> 1;
   const bool rotary = cos_t != nullptr && rot > 0;
 
+  // Requests the keys and values of the 128 positions from `base` on into shared memory;
+  // the token's own position is left out when this step writes it (it is filled in below).
+  // Returns this thread's own key's offset, -1 if it has none to read.
+  auto request_tile = [&](int base, int k_end, bool skip_pos) -> long long {
+    const int j = base + tid;
+    long long off = -1;
+    if (j < k_end && j >= lo && !(skip_pos && j == pos)) {
+      const int lp = j / page_size;
+      const int page = lp < max_pages ? table[lp] : -1;
+      if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      else off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * D;
+    }
+#pragma unroll
+    for (int i = 0; i < CPK; ++i) {
+      const int c = i * 32 + lane;
+      const int key = c / CPK, part = c % CPK;
+      const long long oj = __shfl_sync(0xffffffffu, off, key);
+      if (oj >= 0) {
+        cp_async_16(reinterpret_cast<char*>(&k_s[warp][key][0]) + part * 16,
+                    reinterpret_cast<const char*>(k_pages + oj) + part * 16);
+        cp_async_16(reinterpret_cast<char*>(&v_s[warp][key][0]) + part * 16,
+                    reinterpret_cast<const char*>(v_pages + oj) + part * 16);
+      }
+    }
+    return off;
+  };
+
+  const int b_first = blockIdx.z;
+  const int k_end_first = min(b_first * KB + KB, pos + 1);
+  long long off = -1;
+  const bool first_has_keys = b_first * KB + KB > lo;
+  if (first_has_keys) off = request_tile(b_first * KB, k_end_first, write_kv != 0);
+
+  pdl_wait();
+  stamp(1);   // the kernel before this one has finished: its q, k, v rows may be read
+  const T* row = qkv + (size_t)q_start[r] * q_row_stride;
   // the group's queries, rotated (pairs (j, j + rot/2) of the first rot dims), scaled
   for (int i = tid; i < G * D; i += kDecThreads) {
     const int g = i / D, dd = i % D;
@@ -413,17 +461,24 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
     }
     q_s[g][dd] = val * scale;
   }
-  // the new key and value go to their page, written by the block that will read them
+  // The new key and value: the block that owns the key block of `pos` rotates the key,
+  // stores both in the cache, and puts them into its shared-memory tile itself.
   const int b_star = pos / KB;
-  if (write_kv && (b_star % (int)gridDim.z) == (int)blockIdx.z) {
+  const bool owner = write_kv && (b_star % (int)gridDim.z) == (int)blockIdx.z;
+  // `pos` lies in the tile that was requested above: its key and value are put there directly
+  const bool place_direct = owner && b_star == b_first && (pos - b_star * KB) < kDecThreads;
+  bool own_ok = false;
+  if (owner) {
     const int lp = pos / page_size;
     const int page = lp < max_pages ? table[lp] : -1;
     if (page < 0 || page >= num_pages) {
       if (tid == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
     } else {
+      own_ok = true;
       const size_t dst = (((size_t)page * nkv + hk) * page_size + (pos % page_size)) * D;
       const T* kh = row + (size_t)(nq + hk) * D;
       const T* vh = row + (size_t)(nq + nkv + hk) * D;
+      const int slot = (pos - b_star * KB) % kDecThreads;  // place of `pos` inside its 128-key pass
       for (int dd = tid; dd < D; dd += kDecThreads) {
         float val;
         if (rotary && dd < rot) {
@@ -434,15 +489,18 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
         } else {
           val = to_f32(kh[dd]);
         }
-        k_pages[dst + dd] = from_f32<T>(val);
+        const T kr = from_f32<T>(val);
+        k_pages[dst + dd] = kr;
         v_pages[dst + dd] = vh[dd];
+        if (place_direct) { k_s[slot >> 5][slot & 31][dd] = kr; v_s[slot >> 5][slot & 31][dd] = vh[dd]; }
       }
+      if (!place_direct) __threadfence();  // it will be fetched from L2 by a later pass of this block
     }
-    __threadfence();   // the cp.async reads below go to L2: the stores must have reached it
   }
   __syncthreads();
+  stamp(2);   // queries rotated, new key/value stored
 
-  for (int b = blockIdx.z; b * KB <= pos && b < NB; b += gridDim.z) {
+  for (int b = b_first; b * KB <= pos && b < NB; b += gridDim.z) {
     const int k0 = b * KB;
     if (k0 + KB <= lo) continue;
     float m_run[GMAX], l_run[GMAX], acc[GMAX][DPL];
@@ -454,44 +512,48 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
     }
     const int k_end = min(k0 + KB, pos + 1);
     for (int base = k0; base < k_end; base += kDecThreads) {
-      const int j = base + tid;
-      const bool valid = j < k_end && j >= lo;
-      long long off = -1;
-      if (valid) {
-        const int lp = j / page_size;
-        const int page = lp < max_pages ? table[lp] : -1;
-        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
-        else off = (((long long)page * nkv + hk) * page_size + (j % page_size)) * D;
-      }
-#pragma unroll
-      for (int i = 0; i < CPK; ++i) {
-        const int c = i * 32 + lane;
-        const int key = c / CPK, part = c % CPK;
-        const long long oj = __shfl_sync(0xffffffffu, off, key);
-        if (oj >= 0)
-          cp_async_16(reinterpret_cast<char*>(&v_s[warp][key][0]) + part * 16,
-                      reinterpret_cast<const char*>(v_pages + oj) + part * 16);
-      }
+      const bool prefetched = (b == b_first && base == k0);
+      // Later tiles are requested here; by now the new key, if it falls into one of them,
+      // is in the cache and is read like any other.
+      if (!prefetched) off = request_tile(base, k_end, false);
+      const int j_mine = base + tid;
+      bool have = off >= 0;
+      if (prefetched && place_direct && own_ok && j_mine == pos) have = true;   // the key this block placed itself
+      cp_async_wait_all();
+      __syncwarp();
       float s[GMAX];
 #pragma unroll
-      for (int g = 0; g < GMAX; ++g) s[g] = -CUDART_INF_F;
-      if (off >= 0) {
-        const T* k = k_pages + off;
+      for (int g = 0; g < GMAX; ++g) s[g] = have ? 0.f : -CUDART_INF_F;
+      if (have) {
+        const T* k = &k_s[warp][lane][0];
 #pragma unroll
-        for (int g = 0; g < GMAX; ++g) s[g] = 0.f;
-#pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
+        for (int c = 0; c < CPK; ++c) {
+          const int cc = (c + lane) % CPK;                // each lane starts at another chunk: no bank conflicts
           float kf[8];
-          Vec8<T>::load(k + c * 8, kf);
+          if constexpr (sizeof(T) == 2) {
+            Vec8<T>::load(k + cc * 8, kf);
 #pragma unroll
-          for (int g = 0; g < GMAX; ++g) {
-            if (g < G) {
-              const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][c * 8]);
-              const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][c * 8 + 4]);
-              float t = s[g];
-              t = fmaf(qa.x, kf[0], t); t = fmaf(qa.y, kf[1], t); t = fmaf(qa.z, kf[2], t); t = fmaf(qa.w, kf[3], t);
-              t = fmaf(qb.x, kf[4], t); t = fmaf(qb.y, kf[5], t); t = fmaf(qb.z, kf[6], t); t = fmaf(qb.w, kf[7], t);
-              s[g] = t;
+            for (int g = 0; g < GMAX; ++g) {
+              if (g < G) {
+                const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][cc * 8]);
+                const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][cc * 8 + 4]);
+                float t = s[g];
+                t = fmaf(qa.x, kf[0], t); t = fmaf(qa.y, kf[1], t); t = fmaf(qa.z, kf[2], t); t = fmaf(qa.w, kf[3], t);
+                t = fmaf(qb.x, kf[4], t); t = fmaf(qb.y, kf[5], t); t = fmaf(qb.z, kf[6], t); t = fmaf(qb.w, kf[7], t);
+                s[g] = t;
+              }
+            }
+          } else {
+            const float4 ka = *reinterpret_cast<const float4*>(k + cc * EPC);
+#pragma unroll
+            for (int g = 0; g < GMAX; ++g) {
+              if (g < G) {
+                const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][cc * EPC]);
+                float t = s[g];
+                t = fmaf(qa.x, to_f32(ka.x), t); t = fmaf(qa.y, to_f32(ka.y), t);
+                t = fmaf(qa.z, to_f32(ka.z), t); t = fmaf(qa.w, to_f32(ka.w), t);
+                s[g] = t;
+              }
             }
           }
         }
@@ -508,7 +570,7 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
         const float bm = fmaxf(fmaxf(red_s[0][g], red_s[1][g]), fmaxf(red_s[2][g], red_s[3][g]));
         const float m_new = fmaxf(m_run[g], bm);
         corr[g] = (m_run[g] == -CUDART_INF_F) ? 0.f : __expf(m_run[g] - m_new);
-        p[g] = (off >= 0 && g < G) ? __expf(s[g] - m_new) : 0.f;
+        p[g] = (have && g < G) ? __expf(s[g] - m_new) : 0.f;
         m_run[g] = m_new;
       }
       __syncthreads();
@@ -524,15 +586,13 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
 #pragma unroll
         for (int e = 0; e < DPL; ++e) acc[g][e] *= corr[g];
       }
-      cp_async_wait_all();
-      __syncwarp();
       const int n_here = min(32, k_end - (base + warp * 32));
+      const unsigned have_mask = __ballot_sync(0xffffffffu, have);
       for (int jj = 0; jj < n_here; ++jj) {
-        const long long oj = __shfl_sync(0xffffffffu, off, jj);
         float pj[GMAX];
 #pragma unroll
         for (int g = 0; g < GMAX; ++g) pj[g] = __shfl_sync(0xffffffffu, p[g], jj);
-        if (oj < 0) continue;
+        if (!((have_mask >> jj) & 1u)) continue;
         float vf[DPL];
         const T* v = &v_s[warp][jj][lane * DPL];
         if constexpr (sizeof(T) == 2 && DPL == 2) {
@@ -552,10 +612,10 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
 #pragma unroll
             for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(pj[g], vf[e], acc[g][e]);
       }
-      __syncthreads();
+      __syncthreads();   // red_s and the tiles are rewritten by the next pass
     }
     float* red = reinterpret_cast<float*>(dec_smem);
-    static_assert(sizeof(T) * 32 >= sizeof(float) * GMAX, "the value stage must hold the warps' partial outputs");
+    static_assert(sizeof(T) * 32 >= sizeof(float) * GMAX, "the tiles must hold the warps' partial outputs");
 #pragma unroll
     for (int g = 0; g < GMAX; ++g)
       if (g < G)
@@ -577,6 +637,7 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
     }
     __syncthreads();
   }
+  stamp(3);   // key blocks done
 
   // ---- who is last merges
   __threadfence();
@@ -588,23 +649,40 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
     if (last_s) counters[r * nkv + hk] = 0;   // ready for the next launch
   }
   __syncthreads();
+  stamp(4);   // counted
   if (!last_s) return;
   __threadfence();
-  const int b0 = lo / KB, b1 = pos / KB;
+  // (max, sum) of every head and key block first, all requested at once; then the outputs
+  const int b0 = lo / KB, b1 = pos / KB, nbk = b1 - b0 + 1;
+  float* ml_s = reinterpret_cast<float*>(dec_smem);            // [G][nbk][2], nbk <= 64
+  for (int i = tid; i < G * nbk * 2; i += kDecThreads) {
+    const int g = i / (nbk * 2), rest = i % (nbk * 2);
+    ml_s[i] = __ldcg(part_ml + ((size_t)r * nq + hk * G + g) * NB * 2 + (size_t)b0 * 2 + rest);
+  }
+  __syncthreads();
   for (int i = tid; i < G * D; i += kDecThreads) {
     const int g = i / D, dd = i % D;
-    const float* ml = part_ml + ((size_t)r * nq + hk * G + g) * NB * 2;
-    const float* po = part_o + ((size_t)r * nq + hk * G + g) * NB * D;
+    const float* mlg = ml_s + (size_t)g * nbk * 2;
+    const float* po = part_o + (((size_t)r * nq + hk * G + g) * NB + b0) * D + dd;
     float M = -CUDART_INF_F;
-    for (int b = b0; b <= b1; ++b) M = fmaxf(M, __ldcg(ml + 2 * b));
+    for (int b = 0; b < nbk; ++b) M = fmaxf(M, mlg[2 * b]);
     float L = 0.f, a = 0.f;
-    for (int b = b0; b <= b1; ++b) {
-      const float f = __expf(__ldcg(ml + 2 * b) - M);
-      L += __ldcg(ml + 2 * b + 1) * f;
-      a += __ldcg(po + (size_t)b * D + dd) * f;
+    for (int bb = 0; bb < nbk; bb += 8) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) x[u] = (bb + u < nbk) ? __ldcg(po + (size_t)(bb + u) * D) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (bb + u < nbk) {
+          const float f = __expf(mlg[2 * (bb + u)] - M);
+          L += mlg[2 * (bb + u) + 1] * f;
+          a += x[u] * f;
+        }
+      }
     }
     out[((size_t)q_start[r] * nq + hk * G + g) * D + dd] = from_f32<T>(L > 0.f ? a / L : 0.f);
   }
+  stamp(5);   // merged
 }
 
 template <typename T, int D>
@@ -773,11 +851,11 @@ static int launch_decode_fused(const void* qkv, int q_row_stride, void* k_pages,
                                const int* q_start, const int* ctx_len, const float* cos_t, const float* sin_t,
                                int table_len, int rot, void* out, float* part_o, float* part_ml, int* counters,
                                int R, int nq, int nkv, float scale, int window, int KB, int NB, int* status,
-                               cudaStream_t stream) {
+                               unsigned long long* trace, cudaStream_t stream) {
   int slots = (4 * 148 + nkv * R - 1) / (nkv * R);
   slots = slots < 1 ? 1 : (slots > NB ? NB : slots);
   dim3 grid(nkv, R, slots);
-  const size_t smem = (size_t)4 * 32 * D * sizeof(T);
+  const size_t smem = (size_t)2 * 4 * 32 * D * sizeof(T);   // a key tile and a value tile of 128 positions
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(decode_attention_fused_kernel<T, D, GMAX>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -786,7 +864,7 @@ static int launch_decode_fused(const void* qkv, int q_row_stride, void* k_pages,
   kvb_launch(decode_attention_fused_kernel<T, D, GMAX>, grid, dim3(kDecThreads), smem, stream, (const T*)qkv,
              q_row_stride, (T*)k_pages, (T*)v_pages, write_kv, block_table, max_pages, page_size, num_pages,
              q_start, ctx_len, cos_t, sin_t, table_len, rot, (T*)out, part_o, part_ml, counters, nq, nkv, nq / nkv,
-             scale, window, KB, NB, status);
+             scale, window, KB, NB, status, trace);
   return kvb_launch_result();
 }
 
@@ -795,14 +873,15 @@ static int launch_decode_fused(const void* qkv, int q_row_stride, void* k_pages,
 // at position ctx_len[r]-1.  write_kv = 0: the layer reads another layer's cache and
 // writes nothing.  cos_t/sin_t: [table_len, rot/2] or nullptr for no rotation.
 // Scratch: part_o [R, nq, NB, d], part_ml [R, nq, NB, 2] float32; counters [R * nkv] int32,
-// zero on entry, left zero.  Same size rules as kvb_decode_attention.
+// zero on entry, left zero.  trace: nullptr, or [blocks, 8] uint64 phase stamps (profiling).
+// Same size rules as kvb_decode_attention.
 KVB_EXPORT int kvb_decode_attention_fused(const void* qkv, int q_row_stride, void* k_pages, void* v_pages,
                                           int write_kv, const int* block_table, int max_pages, int page_size,
                                           int num_pages, const int* q_start, const int* ctx_len,
                                           const float* cos_t, const float* sin_t, int table_len, int rot, void* out,
                                           float* part_o, float* part_ml, int* counters, int R, int nq, int nkv,
                                           int d, float scale, int window, int KB, int NB, int dtype, int* status,
-                                          cudaStream_t stream) {
+                                          unsigned long long* trace, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (nkv < 1 || nq % nkv || !kvb_decode_attention_supported(d, nq / nkv) || KB % kDecThreads || NB < 1 ||
       R > 65535 || (rot & 1) || rot > d)
@@ -812,7 +891,7 @@ KVB_EXPORT int kvb_decode_attention_fused(const void* qkv, int q_row_stride, voi
   return launch_decode_fused<T, D, GM>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, \
                                        page_size, num_pages, q_start, ctx_len, cos_t, sin_t, table_len, rot,  \
                                        out, part_o, part_ml, counters, R, nq, nkv, scale, window, KB, NB,     \
-                                       status, stream)
+                                       status, trace, stream)
 #define KVB_DECF_D(T, D) do { if (G <= 2) KVB_DECF(T, D, 2); else if (G <= 4) KVB_DECF(T, D, 4); else KVB_DECF(T, D, 8); } while (0)
 #define KVB_DECF_T(T) do { if (d == 32) KVB_DECF_D(T, 32); else if (d == 64) KVB_DECF_D(T, 64); else KVB_DECF_D(T, 128); } while (0)
   if (dtype == KVB_BF16) KVB_DECF_T(__nv_bfloat16);

@@ -308,7 +308,7 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
 
 
 def decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
-                           nq, nkv, d, scale, window, max_positions, status) -> torch.Tensor:
+                           nq, nkv, d, scale, window, max_positions, status, trace=None) -> torch.Tensor:
     """The whole attention of a decode step in one launch: rotary encoding of query and
     new key, the write of key and value into their page, split attention, merge."""
     _need_cuda(qkv, k_pages)
@@ -328,7 +328,7 @@ def decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, q_start
         c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
         _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rot), _p(out), _p(part_o), _p(part_ml),
         _p(counters), c_int(R), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)),
-        c_int(kb), c_int(nb), c_int(dtype_code(qkv.dtype)), _p(status), _stream())
+        c_int(kb), c_int(nb), c_int(dtype_code(qkv.dtype)), _p(status), _p(trace), _stream())
     _check(rc, "decode_attention_fused")
     return out
 
