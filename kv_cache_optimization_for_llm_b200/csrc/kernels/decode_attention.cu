@@ -1,0 +1,447 @@
+// The attention of a bfloat16 decode step in one launch, on tensor cores.
+//
+// Every request brings one query token.  A cluster of S = 8 blocks serves one
+// (request, key/value head): block z takes the 128-key tiles z, z + 8, ... of the
+// request's context, so the work of a token is cut at absolute positions and does not
+// depend on what else is in the batch.  The rows of the tensor-core tile are the query
+// heads that share the key/value head (padded to 16), so keys and values are fetched
+// once for the whole group (upstream fetches them once per query head:
+// paged_attention/src/kernels.cu:150-219).
+//
+// Per block: the keys and values of its first tile are requested (cp.async, 16-byte
+// chunks gathered through the block table into swizzled shared memory) before the
+// block waits for the projection kernel in front of it; then the group's queries are
+// rotated (rotary encoding, float32) and the block that owns the tile of the token's
+// own position rotates the new key, stores key and value in the cache and in its
+// tile.  Each warp multiplies the queries with its 32 keys (mma.sync m16n8k16,
+// float32 accumulate), keeps a running max and sum per head, and multiplies the
+// probabilities with its 32 values.  The four warps' partials are merged in warp
+// order, the block's tiles in ascending order, and each block sends one partial
+// (output, max, sum per head) into the shared memory of block 0 of its cluster
+// (distributed shared memory); after the cluster's hardware barrier block 0 merges the
+// eight partials in block order and writes the output.  No scratch in global memory,
+// no counters, no spinning.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kTile = 128;     // keys per tile (32 per warp)
+constexpr int kCluster = 8;    // blocks per (request, kv head)
+
+// 16 bytes into shared memory; `valid` false: zeros are written and nothing is read.
+__device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_peer_f32(void* my_smem_ptr, unsigned rank, float v) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(my_smem_ptr)), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+// Byte offset of 16-byte chunk `chunk` of row `row` in a [32][D] bfloat16 tile, chunks
+// XOR-swizzled with the row so that the 8 rows of an 8x8 matrix hit 8 bank groups.
+template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
+  return row * (D * 2) + ((chunk ^ (row & 7)) << 4);
+}
+
+// GP: the group of query heads padded to 4, 8 or 16 (rows that are kept).
+template <int D, int GP>
+__global__ void __launch_bounds__(kThreads)
+decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
+                            __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int write_kv,
+                            const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
+                            const int* __restrict__ q_start, const int* __restrict__ ctx_len,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len, int rot,
+                            __nv_bfloat16* __restrict__ out, int nq, int nkv, int G, float scale_log2, int window,
+                            int* status) {
+  constexpr int CPK = D / 8;      // 16-byte chunks per row
+  constexpr int KSTEPS = D / 16;
+  constexpr int DT = D / 8;       // n-tiles of the output
+  constexpr int PW = D + 2;       // floats per head in a partial: output dims, max, sum
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* k_s = smem;                                   // [4][32][D] bf16, swizzled
+  unsigned char* v_s = k_s + 4 * 32 * D * 2;                   // [4][32][D]
+  float* q_s = reinterpret_cast<float*>(v_s + 4 * 32 * D * 2); // [GP][D] rotated, scaled queries
+  float* run = q_s + GP * D;                                   // [GP][PW] this block's partial so far
+  float* recv = run + GP * PW;                                 // [kCluster][GP][PW], used in block 0 only
+  // the four warps' partials of one tile are merged in the tile memory: [4][GP][PW] floats
+  float* wpart = reinterpret_cast<float*>(smem);
+  static_assert(4 * GP * PW * 4 <= 2 * 4 * 32 * D * 2, "the warps' partials must fit into the tiles");
+
+  pdl_trigger();
+  const int hk = blockIdx.x, r = blockIdx.y, z = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int page_mask = (1 << page_shift) - 1;
+  const int pos = ctx_len[r] - 1;   // lengths and block tables were written before the step's kernels started
+  const bool bad = pos < 0 || (cos_t != nullptr && pos >= table_len);
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int* table = block_table + (size_t)r * max_pages;
+  const int half = rot >> 1;
+  const bool rotary = cos_t != nullptr && rot > 0;
+  const int n_tiles = bad ? 0 : pos / kTile + 1;
+  const int t_first = lo / kTile;               // tiles below it hold no key the window keeps
+  const int t_star = bad ? -1 : pos / kTile;    // the tile of the token's own position
+
+  for (int i = tid; i < GP * PW; i += kThreads) run[i] = ((i % PW) == D) ? -CUDART_INF_F : 0.f;
+
+  // Requests this warp's 32 keys and values of tile t; `skip_pos`: leave the token's own
+  // position out (it is placed by hand).  Returns the mask of this warp's keys that are there.
+  // Keys that are absent (beyond the context, outside the window) are filled with zeros, so
+  // that a probability of zero times whatever lay there before cannot turn into NaN.
+  auto request_tile = [&](int t, bool skip_pos) -> unsigned {
+    const int j = t * kTile + warp * 32 + lane;
+    long long off = -1;                      // -1: absent, zero-fill; -2: placed by hand, leave alone
+    if (skip_pos && j == pos) off = -2;
+    else if (j <= pos && j >= lo) {
+      const int lp = j >> page_shift;
+      const int page = lp < max_pages ? table[lp] : -1;
+      if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      else off = ((((long long)page * nkv + hk) << page_shift) + (j & page_mask)) * D;
+    }
+#pragma unroll
+    for (int i = 0; i < CPK; ++i) {
+      const int c = i * 32 + lane;
+      const int key = c / CPK, part = c % CPK;
+      const long long oj = __shfl_sync(0xffffffffu, off, key);
+      if (oj != -2) {
+        const long long src = oj >= 0 ? oj + part * 8 : 0;
+        cp_async_16_zfill(k_s + warp * 32 * D * 2 + swz<D>(key, part), k_pages + src, oj >= 0);
+        cp_async_16_zfill(v_s + warp * 32 * D * 2 + swz<D>(key, part), v_pages + src, oj >= 0);
+      }
+    }
+    return __ballot_sync(0xffffffffu, off >= 0);
+  };
+
+  // first tile of this block: on its way before the projection kernel has finished
+  int t = z;
+  while (t < t_first) t += kCluster;
+  const int my_first = t;
+  unsigned have = 0;
+  if (my_first < n_tiles) have = request_tile(my_first, write_kv != 0);
+
+  pdl_wait();
+  const __nv_bfloat16* row = qkv + (size_t)q_start[r] * q_row_stride;
+  if (!bad) {
+    // the group's queries, rotated (pairs (j, j + rot/2) of the first rot dims), scaled, float32
+    for (int i = tid; i < GP * D; i += kThreads) {
+      const int g = i / D, dd = i % D;
+      float val = 0.f;
+      if (g < G) {
+        const __nv_bfloat16* qh = row + (size_t)(hk * G + g) * D;
+        if (rotary && dd < rot) {
+          const int j = dd < half ? dd : dd - half;
+          const float c = cos_t[(size_t)pos * half + j], sn = sin_t[(size_t)pos * half + j];
+          const float x1 = to_f32(qh[j]), x2 = to_f32(qh[j + half]);
+          val = dd < half ? x1 * c - x2 * sn : x1 * sn + x2 * c;
+        } else {
+          val = to_f32(qh[dd]);
+        }
+      }
+      q_s[i] = val * scale_log2;
+    }
+    // the new key and value: stored by the block that owns their tile
+    const bool owner = write_kv && (t_star >= t_first) && ((t_star - z) % kCluster == 0);
+    if (owner) {
+      const int lp = pos >> page_shift;
+      const int page = lp < max_pages ? table[lp] : -1;
+      if (page < 0 || page >= num_pages) {
+        if (tid == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      } else {
+        const size_t dst = ((((size_t)page * nkv + hk) << page_shift) + (pos & page_mask)) * D;
+        const __nv_bfloat16* kh = row + (size_t)(nq + hk) * D;
+        const __nv_bfloat16* vh = row + (size_t)(nq + nkv + hk) * D;
+        const bool direct = (t_star == my_first);       // its tile is the one already requested
+        const int slot = pos - t_star * kTile;          // 0..127: warp slot>>5, key slot&31
+        for (int dd = tid; dd < D; dd += kThreads) {
+          float val;
+          if (rotary && dd < rot) {
+            const int j = dd < half ? dd : dd - half;
+            const float c = cos_t[(size_t)pos * half + j], sn = sin_t[(size_t)pos * half + j];
+            const float x1 = to_f32(kh[j]), x2 = to_f32(kh[j + half]);
+            val = dd < half ? x1 * c - x2 * sn : x1 * sn + x2 * c;
+          } else {
+            val = to_f32(kh[dd]);
+          }
+          const __nv_bfloat16 kr = __float2bfloat16_rn(val);
+          k_pages[dst + dd] = kr;
+          v_pages[dst + dd] = vh[dd];
+          if (direct) {
+            const int key = slot & 31, off_b = (slot >> 5) * 32 * D * 2 + swz<D>(key, dd >> 3) + (dd & 7) * 2;
+            *reinterpret_cast<__nv_bfloat16*>(k_s + off_b) = kr;
+            *reinterpret_cast<__nv_bfloat16*>(v_s + off_b) = vh[dd];
+          }
+        }
+        if (direct) { if (warp == (slot >> 5)) have |= 1u << (slot & 31); }
+        else __threadfence();   // a later tile of this block fetches it from L2
+      }
+    }
+  }
+  __syncthreads();
+
+  // query fragments (A operand, rows = heads): row lane/4 and lane/4 + 8, bfloat16
+  unsigned qf[KSTEPS][4];
+  {
+    const int r0 = lane >> 2, c0 = (lane & 3) << 1;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      const int c = kk * 16 + c0;
+      qf[kk][0] = r0 < GP ? pack_bf16(q_s[r0 * D + c], q_s[r0 * D + c + 1]) : 0u;
+      qf[kk][1] = r0 + 8 < GP ? pack_bf16(q_s[(r0 + 8) * D + c], q_s[(r0 + 8) * D + c + 1]) : 0u;
+      qf[kk][2] = r0 < GP ? pack_bf16(q_s[r0 * D + c + 8], q_s[r0 * D + c + 9]) : 0u;
+      qf[kk][3] = r0 + 8 < GP ? pack_bf16(q_s[(r0 + 8) * D + c + 8], q_s[(r0 + 8) * D + c + 9]) : 0u;
+    }
+  }
+
+  for (t = my_first; t < n_tiles; t += kCluster) {
+    if (t != my_first) have = request_tile(t, false);   // the new key, if here, is in the cache by now
+    cp_async_wait_all();
+    __syncwarp();
+    const unsigned char* kt = k_s + warp * 32 * D * 2;
+    const unsigned char* vt = v_s + warp * 32 * D * 2;
+    // scores of 16 rows x 32 keys
+    float s[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        unsigned b0, b1, b2, b3;
+        const int key = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int chunk = kk * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(b0, b1, b2, b3, kt + swz<D>(key, chunk));
+        mma_bf16(s[2 * np], qf[kk], b0, b1);
+        mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
+      }
+    }
+    float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = n * 8 + ((lane & 3) << 1) + (e & 1);
+        if (!((have >> key) & 1u)) s[n][e] = -CUDART_INF_F;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+      }
+    }
+    float m_use[2], l_add[2] = {0.f, 0.f};
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+      m_use[rr] = mx[rr] == -CUDART_INF_F ? 0.f : mx[rr];
+    }
+    unsigned pf[2][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
+      const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
+      l_add[0] += p0 + p1;
+      l_add[1] += p2 + p3;
+      pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      l_add[rr] += __shfl_xor_sync(0xffffffffu, l_add[rr], 1);
+      l_add[rr] += __shfl_xor_sync(0xffffffffu, l_add[rr], 2);
+    }
+    float o[DT][4];
+#pragma unroll
+    for (int n = 0; n < DT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int dp = 0; dp < DT / 2; ++dp) {
+        unsigned b0, b1, b2, b3;
+        const int key = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int chunk = dp * 2 + (lane >> 4);
+        ldmatrix_x4_trans(b0, b1, b2, b3, vt + swz<D>(key, chunk));
+        mma_bf16(o[2 * dp], pf[kk], b0, b1);
+        mma_bf16(o[2 * dp + 1], pf[kk], b2, b3);
+      }
+    }
+    __syncthreads();   // every warp is done with the tiles: they become the warps' partials
+    {
+      const int r0 = lane >> 2, c0 = (lane & 3) << 1;
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int rowi = r0 + rr * 8;
+        if (rowi < GP) {
+          float* dst = wpart + ((size_t)warp * GP + rowi) * PW;
+#pragma unroll
+          for (int n = 0; n < DT; ++n) { dst[n * 8 + c0] = o[n][rr * 2]; dst[n * 8 + c0 + 1] = o[n][rr * 2 + 1]; }
+          if ((lane & 3) == 0) { dst[D] = mx[rr]; dst[D + 1] = l_add[rr]; }
+        }
+      }
+    }
+    __syncthreads();
+    // fold the four warps' partials, in warp order, into the block's running partial
+    for (int i = tid; i < GP * D; i += kThreads) {
+      const int g = i / D, dd = i % D;
+      float M = run[g * PW + D];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, wpart[((size_t)w * GP + g) * PW + D]);
+      float a = 0.f;
+      if (M != -CUDART_INF_F) {
+        const float m0 = run[g * PW + D];
+        a = m0 == -CUDART_INF_F ? 0.f : run[g * PW + dd] * exp2f(m0 - M);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float mw = wpart[((size_t)w * GP + g) * PW + D];
+          if (mw != -CUDART_INF_F) a += wpart[((size_t)w * GP + g) * PW + dd] * exp2f(mw - M);
+        }
+      }
+      q_s[i] = a;   // the queries are in registers by now: their place holds the new outputs for a moment
+    }
+    __syncthreads();
+    if (tid < GP) {
+      const int g = tid;
+      float M = run[g * PW + D];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M = fmaxf(M, wpart[((size_t)w * GP + g) * PW + D]);
+      float L = 0.f;
+      if (M != -CUDART_INF_F) {
+        const float m0 = run[g * PW + D];
+        L = m0 == -CUDART_INF_F ? 0.f : run[g * PW + D + 1] * exp2f(m0 - M);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const float mw = wpart[((size_t)w * GP + g) * PW + D];
+          if (mw != -CUDART_INF_F) L += wpart[((size_t)w * GP + g) * PW + D + 1] * exp2f(mw - M);
+        }
+      }
+      run[g * PW + D] = M;
+      run[g * PW + D + 1] = L;
+    }
+    for (int i = tid; i < GP * D; i += kThreads) run[(i / D) * PW + (i % D)] = q_s[i];
+    __syncthreads();   // the tiles are free for the next request
+  }
+
+  // ---- one partial per block goes to block 0 of the cluster; block 0 merges in block order
+  for (int i = tid; i < GP * PW; i += kThreads) st_peer_f32(recv + (size_t)z * GP * PW + i, 0u, run[i]);
+  cluster_sync_all();
+  if (z != 0 || bad) {
+    if (bad && z == 0 && tid == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
+    return;
+  }
+  for (int i = tid; i < G * D; i += kThreads) {
+    const int g = i / D, dd = i % D;
+    float M = -CUDART_INF_F;
+#pragma unroll
+    for (int c = 0; c < kCluster; ++c) M = fmaxf(M, recv[((size_t)c * GP + g) * PW + D]);
+    float L = 0.f, a = 0.f;
+#pragma unroll
+    for (int c = 0; c < kCluster; ++c) {
+      const float mc = recv[((size_t)c * GP + g) * PW + D];
+      if (mc != -CUDART_INF_F) {
+        const float f = exp2f(mc - M);
+        L += recv[((size_t)c * GP + g) * PW + D + 1] * f;
+        a += recv[((size_t)c * GP + g) * PW + dd] * f;
+      }
+    }
+    out[((size_t)q_start[r] * nq + hk * G + g) * D + dd] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
+  }
+}
+
+int log2_exact(int x) {
+  int s = 0;
+  while ((1 << s) < x) ++s;
+  return (1 << s) == x ? s : -1;
+}
+
+template <int D, int GP>
+int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv, const int* block_table,
+           int max_pages, int page_shift, int num_pages, const int* q_start, const int* ctx_len, const float* cos_t,
+           const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv, float scale, int window,
+           int* status, cudaStream_t stream) {
+  constexpr int PW = D + 2;
+  const size_t smem = (size_t)2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
+                      (size_t)kCluster * GP * PW * 4;
+  static bool attr_set = false;
+  if (!attr_set && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nkv, R, kCluster);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = kCluster;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = kvb_pdl_enabled() ? 2 : 1;
+  cudaError_t le = cudaLaunchKernelEx(
+      &cfg, decode_attention_mma_kernel<D, GP>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
+      (__nv_bfloat16*)v_pages, write_kv, block_table, max_pages, page_shift, num_pages, q_start, ctx_len, cos_t, sin_t,
+      table_len, rot, (__nv_bfloat16*)out, nq, nkv, nq / nkv, scale * 1.4426950408889634f, window, status);
+  if (le != cudaSuccess) return (int)le;
+  return kvb_launch_result();
+}
+
+}  // namespace
+
+// 1 when the kernel takes these sizes: head size 64 or 128, a group of at most 16 query
+// heads per key/value head, a page size that is a power of two.
+KVB_EXPORT int kvb_decode_attention_mma_supported(int d, int group, int page_size) {
+  return (d == 64 || d == 128) && group >= 1 && group <= 16 && log2_exact(page_size) >= 0;
+}
+
+// qkv: [T, (nq + 2 nkv) d] bfloat16 as the projection wrote it; request r's token is row
+// q_start[r] at position ctx_len[r]-1.  write_kv = 0: the layer reads another layer's
+// cache and writes nothing.  cos_t/sin_t: [table_len, rot/2] or nullptr.  out: [T, nq d].
+// Uses no memory beyond its operands.  R <= 65535.
+KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv,
+                                        const int* block_table, int max_pages, int page_size, int num_pages,
+                                        const int* q_start, const int* ctx_len, const float* cos_t,
+                                        const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv,
+                                        int d, float scale, int window, int* status, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (nkv < 1 || nq % nkv || !kvb_decode_attention_mma_supported(d, nq / nkv, page_size) || R > 65535 || (rot & 1) ||
+      rot > d || nkv > 65535)
+    return KVB_ERR_BAD_SIZE;
+  const int G = nq / nkv;
+  const int ps = log2_exact(page_size);
+#define KVB_DM(D, GP)                                                                                             \
+  return launch<D, GP>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages,      \
+                       q_start, ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, stream)
+  if (d == 64) { if (G <= 4) KVB_DM(64, 4); if (G <= 8) KVB_DM(64, 8); KVB_DM(64, 16); }
+  if (G <= 4) KVB_DM(128, 4);
+  if (G <= 8) KVB_DM(128, 8);
+  KVB_DM(128, 16);
+}

@@ -333,6 +333,28 @@ def decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, q_start
     return out
 
 
+def decode_attention_mma_supported(d: int, group: int, page_size: int) -> bool:
+    return bool(lib("decode_attention").kvb_decode_attention_mma_supported(c_int(d), c_int(group), c_int(page_size)))
+
+
+def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
+                         nq, nkv, d, scale, window, status) -> torch.Tensor:
+    """The attention of a bfloat16 decode step in one launch on tensor cores: rotary
+    encoding of query and new key, cache write, attention over 128-key tiles spread over
+    a cluster of blocks, merge through distributed shared memory.  No scratch."""
+    _need_cuda(qkv, k_pages)
+    assert qkv.dtype == torch.bfloat16
+    R = ctx_len.numel()
+    out = torch.empty((qkv.shape[0], nq * d), dtype=qkv.dtype, device=qkv.device)
+    rc = lib("decode_attention").kvb_decode_attention_mma(
+        _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), c_int(1 if write_kv else 0), _p(block_table),
+        c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
+        _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rot), _p(out), c_int(R), c_int(nq),
+        c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), _p(status), _stream())
+    _check(rc, "decode_attention_mma")
+    return out
+
+
 def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv, d, scale, window, max_positions,
                    cos, sin, rot) -> torch.Tensor:
     """Everything between the q|k|v projection and the output projection: rotary
@@ -340,10 +362,14 @@ def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv,
     Picks the kernels:
     * float32: rotary/write kernel, then the general kernel, whose sums follow absolute
       positions in one fixed order whatever the shape of the step;
-    * bfloat16, single tokens only: one fused launch (split over key blocks);
+    * bfloat16, single tokens only: one fused launch, on tensor cores where the sizes allow
+      (head size 64/128), else the FMA form (head size 32);
     * bfloat16, runs of tokens: rotary/write kernel, then the tensor-core kernel;
     * sizes neither takes: rotary/write kernel, then the general kernel."""
     group, page_size = nq // nkv, k_pages.shape[2]
+    if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_mma_supported(d, group, page_size):
+        return decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
+                                    cos, sin, rot, nq, nkv, d, scale, window, batch.status)
     if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_supported(d, group):
         return decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
                                       cos, sin, rot, nq, nkv, d, scale, window, max_positions, batch.status)

@@ -36,7 +36,7 @@ class GroupedQueryAttention(Part):
     def kernel_modules(cls, params, dtype):
         mods = ["elementwise", "attention"]
         if dtype == torch.bfloat16 and params["head_dim"] in (64, 128):
-            mods.append("flash_attention")
+            mods += ["flash_attention", "decode_attention"]
         mods.append("gemm_f32" if dtype == torch.float32 else "gemm_bf16")
         return tuple(mods)
 

@@ -435,3 +435,74 @@ def test_fused_decode_attention(dtype, nq, nkv, d, rot, page_size, window, write
                                       dev(np.arange(R + 1), torch.int32), dev(ctxs, torch.int32), cos_t, sin_t, rot,
                                       nq, nkv, d, 1 / math.sqrt(d), window, max_pos, st)
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("nq,nkv,d,rot,page_size,window,write", [
+    (8, 2, 64, 64, 16, None, True), (32, 8, 64, 64, 16, None, True), (6, 2, 64, 64, 16, None, True),
+    (24, 8, 128, 128, 16, None, True), (8, 2, 64, 32, 8, None, True), (8, 2, 64, 64, 16, 100, True),
+    (4, 4, 128, 128, 4, 129, True), (16, 1, 64, 64, 32, None, True), (8, 2, 64, 64, 16, None, False),
+    (12, 2, 64, 64, 16, 1100, True)])
+def test_tensor_core_decode_attention(nq, nkv, d, rot, page_size, window, write):
+    """The cluster / tensor-core decode kernel against rotate-then-attend in float64;
+    contexts from one token to several tiles per block (more than 8 tiles of 128)."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    assert ops.decode_attention_mma_supported(d, nq // nkv, page_size)
+    dtype = "bfloat16"
+    rng = np.random.default_rng(nq * d + rot + page_size)
+    ctxs = [1, 128, 129, 640, 300, 2, 1000, 2500, 1025]
+    R = len(ctxs)
+    max_pos = 2560
+    inv = P.rope_inv_freq(rot, 10000.0)
+    ang = np.arange(max_pos)[:, None] * inv[None, :]
+    cos_t, sin_t = dev(np.cos(ang), torch.float32), dev(np.sin(ang), torch.float32)
+    max_pages = max(-(-c // page_size) for c in ctxs) + 1
+    num_pages = sum(-(-c // page_size) for c in ctxs) + 2
+    kp = np.full((num_pages, nkv, page_size, d), 7.0)
+    vp = np.full((num_pages, nkv, page_size, d), -9.0)
+    free = list(rng.permutation(num_pages))
+    tables = np.full((R, max_pages), -1, dtype=np.int32)
+    rows, refs, new_kv = [], [], []
+    def rotate(x, pos):
+        out = x.copy()
+        c, s = np.cos(ang[pos])[None, :], np.sin(ang[pos])[None, :]
+        out[:, :rot] = P.apply_rope(x[None, :, :rot], c, s)[0]
+        return out
+    for r, ctx in enumerate(ctxs):
+        k = as64(dev(rng.normal(size=(ctx, nkv, d)), DT[dtype]))
+        v = as64(dev(rng.normal(size=(ctx, nkv, d)), DT[dtype]))
+        q_raw = as64(dev(rng.normal(size=(nq, d)), DT[dtype]))
+        k_raw = as64(dev(rng.normal(size=(nkv, d)), DT[dtype]))
+        pos = ctx - 1
+        if write:
+            k[pos] = as64(dev(rotate(k_raw, pos), DT[dtype]))
+        for j in range(ctx):
+            lp = j // page_size
+            if tables[r, lp] < 0:
+                tables[r, lp] = free.pop()
+            if j == pos and write:
+                continue
+            kp[tables[r, lp], :, j % page_size] = k[j]
+            vp[tables[r, lp], :, j % page_size] = v[j]
+        q_rot = as64(dev(rotate(q_raw, pos), DT[dtype]))     # the kernel rounds the rotated query to bfloat16
+        qfull = np.zeros((ctx, nq, d)); qfull[pos] = q_rot
+        refs.append(P.attention(qfull, k, v, window=window)[pos].reshape(-1))
+        rows.append(np.concatenate([q_raw.reshape(-1), k_raw.reshape(-1), v[pos].reshape(-1)]))
+        new_kv.append((tables[r, pos // page_size], pos % page_size, k[pos], v[pos]))
+    qkv = dev(np.array(rows), DT[dtype])
+    dkp, dvp = dev(kp, DT[dtype]), dev(vp, DT[dtype])
+    st = status()
+    args = (qkv, dkp, dvp, write, dev(tables, torch.int32), dev(np.arange(R + 1), torch.int32),
+            dev(ctxs, torch.int32), cos_t, sin_t, rot, nq, nkv, d, 1 / math.sqrt(d), window, st)
+    out = ops.decode_attention_mma(*args)
+    assert int(st.item()) == 0
+    assert rel_err(out, np.array(refs)) < TOL[dtype] * 1.5
+    for page, slot, k_want, v_want in new_kv:
+        if write:
+            assert np.abs(as64(dkp[page, :, slot]) - k_want).max() < TOL[dtype] * 4
+            assert np.array_equal(as64(dvp[page, :, slot]), v_want)
+    assert torch.equal(out, ops.decode_attention_mma(*args))
+    # a request's result does not depend on its neighbours in the batch: bit for bit
+    one = ops.decode_attention_mma(qkv[3:4].contiguous(), dkp, dvp, write, dev(tables[3:4], torch.int32),
+                                   dev([0, 1], torch.int32), dev(ctxs[3:4], torch.int32), cos_t, sin_t, rot, nq, nkv, d,
+                                   1 / math.sqrt(d), window, st)
+    assert torch.equal(one[0], out[3])
