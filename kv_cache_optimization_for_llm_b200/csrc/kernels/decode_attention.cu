@@ -13,10 +13,11 @@
 // block waits for the projection kernel in front of it; then the group's queries are
 // rotated (rotary encoding, float32) and the block that owns the tile of the token's
 // own position rotates the new key, stores key and value in the cache and in its
-// tile.  Each warp multiplies the queries with its 32 keys (mma.sync m16n8k16,
-// float32 accumulate), keeps a running max and sum per head, and multiplies the
-// probabilities with its 32 values.  The four warps' partials are merged in warp
-// order, the block's tiles in ascending order, and each block sends one partial
+// tile.  Each warp walks its own 32-key slice of every tile of the block: it multiplies
+// the queries with the keys (mma.sync m16n8k16, float32 accumulate), keeps a running
+// max and sum per head and a running output, and multiplies the probabilities with its
+// 32 values; no block-wide barrier inside the walk.  The four warps' partials are
+// merged in warp order, and each block sends one partial
 // (output, max, sum per head) into the shared memory of block 0 of its cluster
 // (distributed shared memory); after the cluster's hardware barrier block 0 merges the
 // eight partials in block order and writes the output.  No scratch in global memory,
@@ -220,130 +221,122 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     }
   }
 
+  // Each warp walks its 32-key slices of this block's tiles on its own, with a running
+  // max and sum per head (rows lane/4 and lane/4 + 8) and a running output in registers;
+  // the slices of a warp are private to it, so the walk needs no block-wide barrier.
+  float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
+  float o[DT][4];
+#pragma unroll
+  for (int n = 0; n < DT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  const unsigned char* kt = k_s + warp * 32 * D * 2;
+  const unsigned char* vt = v_s + warp * 32 * D * 2;
   for (t = my_first; t < n_tiles; t += kCluster) {
     if (t != my_first) have = request_tile(t, false);   // the new key, if here, is in the cache by now
     cp_async_wait_all();
     __syncwarp();
-    const unsigned char* kt = k_s + warp * 32 * D * 2;
-    const unsigned char* vt = v_s + warp * 32 * D * 2;
-    // scores of 16 rows x 32 keys
-    float s[4][4];
+    if (have != 0u) {
+      float s[4][4];
 #pragma unroll
-    for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+      for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
 #pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk) {
+      for (int kk = 0; kk < KSTEPS; ++kk) {
 #pragma unroll
-      for (int np = 0; np < 2; ++np) {
-        unsigned b0, b1, b2, b3;
-        const int key = np * 16 + (lane & 7) + ((lane >> 4) << 3);
-        const int chunk = kk * 2 + ((lane >> 3) & 1);
-        ldmatrix_x4(b0, b1, b2, b3, kt + swz<D>(key, chunk));
-        mma_bf16(s[2 * np], qf[kk], b0, b1);
-        mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
+        for (int np = 0; np < 2; ++np) {
+          unsigned b0, b1, b2, b3;
+          const int key = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int chunk = kk * 2 + ((lane >> 3) & 1);
+          ldmatrix_x4(b0, b1, b2, b3, kt + swz<D>(key, chunk));
+          mma_bf16(s[2 * np], qf[kk], b0, b1);
+          mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
+        }
       }
-    }
-    float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+      float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
+      for (int n = 0; n < 4; ++n) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = n * 8 + ((lane & 3) << 1) + (e & 1);
-        if (!((have >> key) & 1u)) s[n][e] = -CUDART_INF_F;
-        mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        for (int e = 0; e < 4; ++e) {
+          const int key = n * 8 + ((lane & 3) << 1) + (e & 1);
+          if (!((have >> key) & 1u)) s[n][e] = -CUDART_INF_F;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        }
       }
-    }
-    float m_use[2], l_add[2] = {0.f, 0.f};
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
-      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
-      m_use[rr] = mx[rr] == -CUDART_INF_F ? 0.f : mx[rr];
-    }
-    unsigned pf[2][4];
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-      const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
-      const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
-      l_add[0] += p0 + p1;
-      l_add[1] += p2 + p3;
-      pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
-      pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
-    }
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      l_add[rr] += __shfl_xor_sync(0xffffffffu, l_add[rr], 1);
-      l_add[rr] += __shfl_xor_sync(0xffffffffu, l_add[rr], 2);
-    }
-    float o[DT][4];
-#pragma unroll
-    for (int n = 0; n < DT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
-#pragma unroll
-      for (int dp = 0; dp < DT / 2; ++dp) {
-        unsigned b0, b1, b2, b3;
-        const int key = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-        const int chunk = dp * 2 + (lane >> 4);
-        ldmatrix_x4_trans(b0, b1, b2, b3, vt + swz<D>(key, chunk));
-        mma_bf16(o[2 * dp], pf[kk], b0, b1);
-        mma_bf16(o[2 * dp + 1], pf[kk], b2, b3);
-      }
-    }
-    __syncthreads();   // every warp is done with the tiles: they become the warps' partials
-    {
-      const int r0 = lane >> 2, c0 = (lane & 3) << 1;
+      float corr[2], m_use[2];
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
-        const int rowi = r0 + rr * 8;
-        if (rowi < GP) {
-          float* dst = wpart + ((size_t)warp * GP + rowi) * PW;
+        mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+        mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+        const float m_new = fmaxf(m_run[rr], mx[rr]);       // finite: the slice holds at least one key
+        m_use[rr] = m_new;
+        corr[rr] = m_run[rr] == -CUDART_INF_F ? 0.f : exp2f(m_run[rr] - m_new);
+        m_run[rr] = m_new;
+        l_run[rr] *= corr[rr];
+      }
 #pragma unroll
-          for (int n = 0; n < DT; ++n) { dst[n * 8 + c0] = o[n][rr * 2]; dst[n * 8 + c0 + 1] = o[n][rr * 2 + 1]; }
-          if ((lane & 3) == 0) { dst[D] = mx[rr]; dst[D + 1] = l_add[rr]; }
+      for (int n = 0; n < DT; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+      unsigned pf[2][4];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
+        const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
+        l_run[0] += p0 + p1;     // each lane keeps the sum of its own columns; the four lanes of a row
+        l_run[1] += p2 + p3;     // are added up after the walk
+        pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+        for (int dp = 0; dp < DT / 2; ++dp) {
+          unsigned b0, b1, b2, b3;
+          const int key = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          const int chunk = dp * 2 + (lane >> 4);
+          ldmatrix_x4_trans(b0, b1, b2, b3, vt + swz<D>(key, chunk));
+          mma_bf16(o[2 * dp], pf[kk], b0, b1);
+          mma_bf16(o[2 * dp + 1], pf[kk], b2, b3);
         }
       }
     }
-    __syncthreads();
-    // fold the four warps' partials, in warp order, into the block's running partial
-    for (int i = tid; i < GP * D; i += kThreads) {
-      const int g = i / D, dd = i % D;
-      float M = run[g * PW + D];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) M = fmaxf(M, wpart[((size_t)w * GP + g) * PW + D]);
-      float a = 0.f;
-      if (M != -CUDART_INF_F) {
-        const float m0 = run[g * PW + D];
-        a = m0 == -CUDART_INF_F ? 0.f : run[g * PW + dd] * exp2f(m0 - M);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const float mw = wpart[((size_t)w * GP + g) * PW + D];
-          if (mw != -CUDART_INF_F) a += wpart[((size_t)w * GP + g) * PW + dd] * exp2f(mw - M);
-        }
-      }
-      q_s[i] = a;   // the queries are in registers by now: their place holds the new outputs for a moment
-    }
-    __syncthreads();
-    if (tid < GP) {
-      const int g = tid;
-      float M = run[g * PW + D];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) M = fmaxf(M, wpart[((size_t)w * GP + g) * PW + D]);
-      float L = 0.f;
-      if (M != -CUDART_INF_F) {
-        const float m0 = run[g * PW + D];
-        L = m0 == -CUDART_INF_F ? 0.f : run[g * PW + D + 1] * exp2f(m0 - M);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const float mw = wpart[((size_t)w * GP + g) * PW + D];
-          if (mw != -CUDART_INF_F) L += wpart[((size_t)w * GP + g) * PW + D + 1] * exp2f(mw - M);
-        }
-      }
-      run[g * PW + D] = M;
-      run[g * PW + D + 1] = L;
-    }
-    for (int i = tid; i < GP * D; i += kThreads) run[(i / D) * PW + (i % D)] = q_s[i];
-    __syncthreads();   // the tiles are free for the next request
+    __syncwarp();   // the slice is read; the next request may overwrite it
   }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 1);
+    l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
+  }
+  __syncthreads();   // every warp is done with the tiles: their memory takes the warps' partials
+  {
+    const int r0 = lane >> 2, c0 = (lane & 3) << 1;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int rowi = r0 + rr * 8;
+      if (rowi < GP) {
+        float* dst = wpart + ((size_t)warp * GP + rowi) * PW;
+#pragma unroll
+        for (int n = 0; n < DT; ++n) { dst[n * 8 + c0] = o[n][rr * 2]; dst[n * 8 + c0 + 1] = o[n][rr * 2 + 1]; }
+        if ((lane & 3) == 0) { dst[D] = m_run[rr]; dst[D + 1] = l_run[rr]; }
+      }
+    }
+  }
+  __syncthreads();
+  // the four warps' partials, merged in warp order, are this block's partial
+  for (int i = tid; i < GP * PW; i += kThreads) {
+    const int g = i / PW, dd = i % PW;
+    float M = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, wpart[((size_t)w * GP + g) * PW + D]);
+    float a = 0.f;
+    if (dd == D) a = M;
+    else if (M != -CUDART_INF_F) {
+      const int col = dd == D + 1 ? D + 1 : dd;   // the sum merges like an output dim
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = wpart[((size_t)w * GP + g) * PW + D];
+        if (mw != -CUDART_INF_F) a += wpart[((size_t)w * GP + g) * PW + col] * exp2f(mw - M);
+      }
+    }
+    run[i] = a;
+  }
+  __syncthreads();
 
   // ---- one partial per block goes to block 0 of the cluster; block 0 merges in block order
   for (int i = tid; i < GP * PW; i += kThreads) st_peer_f32(recv + (size_t)z * GP * PW + i, 0u, run[i]);

@@ -17,10 +17,9 @@
 // shared memory), the cluster meets once at its hardware barrier, and every block adds
 // up the slots of its rows in block order, so the sum has one fixed order.  No scratch
 // in global memory, no counters, no spinning.
-// The weights do not depend on the step's data: a block asks for all its weight tiles
-// to be brought into L2 and requests the first ring of them before it waits for the
-// kernel in front of it (programmatic dependent launch), so weight traffic overlaps
-// the small kernels between the products.
+// The weights do not depend on the step's data: a block requests its first ring of
+// weight tiles before it waits for the kernel in front of it (programmatic dependent
+// launch), so that the first tiles are under way while that kernel finishes.
 // Every wait on an mbarrier is bounded; a wait that runs out records
 // KVB_STATUS_WAIT_TIMEOUT, and the block frees its tensor memory and returns.
 #include "common.cuh"
@@ -107,15 +106,7 @@ __device__ __forceinline__ void st_peer_f32(void* my_smem_ptr, unsigned rank, fl
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
-// Asks for `bytes` (a multiple of 16, 16-byte aligned) to be brought into L2; nothing waits for it.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* ptr, unsigned bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
-}
-// Asks for a tile to be brought into L2; nothing waits for it.
-__device__ __forceinline__ void tma_prefetch_l2(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
-               ::"l"((unsigned long long)map), "r"(x), "r"(y) : "memory");
-}
+
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
 // 128 bytes, groups of 8 rows 1024 bytes apart, tile base aligned to 1024 bytes.
@@ -128,13 +119,10 @@ struct Params {
   int k_tiles, splits;        // k tiles in all, blocks along K
   int stages;
   int red_bytes;              // shared memory set aside for the partials that peers send (splits > 1)
-  int prefetch_tiles;         // weight tiles beyond the first ring that are asked into L2 up front
   int out_f32;                // 1: C is float32, 0: bfloat16
   void* out;                  // [M, N]
   int* status;
   unsigned long long* trace;  // optional [blocks, 8] nanosecond stamps of the phases of each block (profiling)
-  const unsigned char* next_w;  // optional: the weights the following product will read ...
-  long long next_bytes;         // ... and how many bytes of them to ask into L2 (a multiple of 4096)
 };
 
 __device__ __forceinline__ void stamp(const Params& p, int slot) {
@@ -196,8 +184,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       mbar_expect_tx(&full[i], a_bytes + b_bytes);
       tma_load_2d(a_s + (size_t)i * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[i]);
     }
-    for (int i = first; i < min(my_tiles, first + p.prefetch_tiles); ++i) tma_prefetch_l2(&map_w, (kt0 + i) * TILE_K, n0);
-    stamp(p, 1);                 // first round of weight tiles requested, the rest on their way to L2
+    stamp(p, 1);                 // first round of weight tiles requested
     pdl_wait();
     stamp(p, 2);                 // the kernel before this one has finished
     for (int i = 0; i < first; ++i)
@@ -210,15 +197,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       tma_load_2d(a_s + (size_t)s * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[s]);
       tma_load_2d(b_s + (size_t)s * b_bytes, &map_x, (kt0 + i) * TILE_K, 0, &full[s]);
     }
-  } else if (warp == 3 && p.next_w != nullptr) {
-    // ---- The weights of the product after this one start their way into L2 now, a slice
-    // per block, behind this block's own first tiles, so that the memory system stays busy
-    // through the small kernels that run between the two products.
-    if (my_tiles > 0) mbar_wait(&full[0], 0);
-    const long long blocks = (long long)gridDim.x * gridDim.y;
-    const long long me = (long long)blockIdx.y * gridDim.x + blockIdx.x;
-    const long long chunks = p.next_bytes / 4096;
-    for (long long c = me * 32 + lane; c < chunks; c += blocks * 32) bulk_prefetch_l2(p.next_w + c * 4096, 4096);
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer
     const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.MP >> 3) << 17) | ((unsigned)(TILE_N >> 4) << 24);
@@ -400,12 +378,10 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
 // C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
 // address is stable (a captured graph), so its tensor map may be cached as the
 // weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
-// block (profiling only).  next_w / next_bytes: nullptr, or the weights that the product
-// after this one will read; the kernel asks for them to be brought into L2 (a hint: it
-// changes no result).  Uses no memory beyond its operands.
+// block (profiling only).  Uses no memory beyond its operands.
 KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
                                int K, int x_is_static, int* status, unsigned long long* trace,
-                               const void* next_w, long long next_bytes, cudaStream_t stream) {
+                               cudaStream_t stream) {
   int splits, tiles;
   const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &tiles);
   if (rc) return rc;
@@ -418,9 +394,6 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   p.k_tiles = (K + TILE_K - 1) / TILE_K;
   p.splits = splits;
   p.out_f32 = out_f32; p.out = out; p.status = status; p.trace = trace;
-  p.next_w = reinterpret_cast<const unsigned char*>(next_w);
-  p.next_bytes = (next_w && !(reinterpret_cast<uintptr_t>(next_w) & 15)) ? (next_bytes / 4096) * 4096 : 0;
-  if (p.next_bytes == 0) p.next_w = nullptr;
   const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
   // two blocks per SM while the stages stay deep enough, one block otherwise
   const int budget = MP <= 64 ? 108 * 1024 : 200 * 1024;
@@ -435,10 +408,6 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   if (stages > per) stages = per;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  // Blocks that all run at once (one wave) may ask for more of their weights ahead of
-  // time; with several waves that would only push the first wave's loads back.
-  static const int prefetch_env = [] { const char* e = std::getenv("KVB200_GEMM_PREFETCH"); return e ? atoi(e) : 8; }();
-  p.prefetch_tiles = (tiles * splits <= 2 * 148) ? prefetch_env : 0;
   const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + (2 * stages + 1) * 8 + 16;
   CUtensorMap mw, mx;
   int e = cached_map(&mw, w, N, K, ldw, TILE_N);

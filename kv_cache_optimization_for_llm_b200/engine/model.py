@@ -40,15 +40,6 @@ class DecoderModel:
         self.final_norm = make("norm", spec.final_norm)
         self.head = make("head", spec.lm_head)
         self.schedule = list(spec.schedule)
-        # The order in which a step reads its weight matrices, for L2 prefetch between products.
-        from .. import ops
-        order = []
-        for e in self.schedule:
-            blk = self.layers[e.layer]
-            for part in (blk.mixer, blk.feed_forward):
-                order += list(getattr(part, "matrices_in_order", lambda: [])())
-        order += list(getattr(self.head, "matrices_in_order", lambda: [])())
-        ops.set_weight_order(order)
 
     def cache_specs(self):
         """Per schedule entry: what its mixer asks of the cache, and whose cache it reads."""

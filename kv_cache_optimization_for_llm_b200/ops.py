@@ -417,20 +417,6 @@ def gemm_skinny_plan(M: int, N: int, K: int):
     return splits.value, tiles.value
 
 
-_next_weight: Dict[int, torch.Tensor] = {}
-L2_PREFETCH_BYTES = int(__import__("os").environ.get("KVB200_L2_PREFETCH_BYTES", str(72 * 1024 * 1024)))
-
-
-def set_weight_order(weights) -> None:
-    """Tells the product kernels in which order a step reads its weight matrices (the
-    order wraps around to the next step), so that each product can ask for the next
-    one's weights to be brought into L2 while it runs."""
-    ws = [w for w in weights if w is not None and w.is_cuda and w.dtype == torch.bfloat16]
-    for a, b in zip(ws, ws[1:] + ws[:1]):
-        if a.data_ptr() != b.data_ptr():
-            _next_weight[a.data_ptr()] = b
-
-
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor,
                 x_is_static: bool = False, trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x . w^T`` for few rows (M <= 256) on tcgen05 tensor cores, weights streamed by TMA."""
@@ -439,11 +425,9 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    nxt = _next_weight.get(w.data_ptr()) if L2_PREFETCH_BYTES > 0 else None
     rc = lib("gemm_bf16").kvb_gemm_skinny(
         _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(1 if out_dtype == torch.float32 else 0),
-        c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), _p(status), _p(trace), _p(nxt),
-        c_longlong(0 if nxt is None else min(L2_PREFETCH_BYTES, nxt.numel() * nxt.element_size())), _stream())
+        c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), _p(status), _p(trace), _stream())
     if rc == -2:
         raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
     _check(rc, "gemm_skinny")

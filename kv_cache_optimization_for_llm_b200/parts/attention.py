@@ -59,10 +59,6 @@ class GroupedQueryAttention(Part):
     def cache_spec(self):
         return PagedKVSpec(self.nkv, self.d, self.window)
 
-    def matrices_in_order(self):
-        """The weight matrices in the order ``forward`` reads them."""
-        return [self.qkv, self.o]
-
     def forward(self, x, batch, cache):
         qkv = ops.linear(x, self.qkv)
         cos, sin = self.position.tables() if self.position is not None else (None, None)

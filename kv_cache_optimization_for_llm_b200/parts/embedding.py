@@ -48,9 +48,6 @@ class LinearHead(Part):
         super().__init__(params, weights, ctx)
         self.weight = weights["weight"]
 
-    def matrices_in_order(self):
-        return [self.weight]
-
     def forward(self, x):
         import torch
         return ops.linear(x, self.weight, out_dtype=torch.float32)

@@ -30,10 +30,6 @@ class SwiGLU(Part):
         self.gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
         self.down = weights["down"]
 
-    def matrices_in_order(self):
-        """The weight matrices in the order ``forward`` reads them."""
-        return [self.gate_up, self.down]
-
     def forward(self, x, batch):
         gu = ops.linear(x, self.gate_up)
         a = ops.silu_mul(gu)
