@@ -63,7 +63,7 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
 struct TileDesc { int req, t0, n_tok, pad; };
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, D == 64 ? 4 : 2)
 paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
                              const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                              const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
@@ -189,18 +189,33 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
         mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
       }
     }
-    // mask and running softmax; scores are kept in units of log2 (scale * log2 e folded in)
+    // mask and running softmax; scores are kept in units of log2 (scale * log2 e folded in).
+    // A tile that lies wholly at or below every row's position and wholly inside every row's
+    // window needs no per-element test; the tiles on the diagonal and at the window's edge do.
     const int kbase = t * BN + ((lane & 3) << 1);
     float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+    const bool full = (t * BN + BN - 1 <= min(pos_r[0], pos_r[1])) && (t * BN >= max(lo_r[0], lo_r[1])) &&
+                      pos_r[0] >= 0 && pos_r[1] >= 0;
+    if (__all_sync(0xffffffffu, full)) {
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) {
+      for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = kbase + n * 8 + (e & 1);
-        const int rr = e >> 1;
-        const bool ok = j <= pos_r[rr] && j >= lo_r[rr];
-        s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
-        mx[rr] = fmaxf(mx[rr], s[n][e]);
+        for (int e = 0; e < 4; ++e) {
+          s[n][e] *= scale_log2;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = kbase + n * 8 + (e & 1);
+          const int rr = e >> 1;
+          const bool ok = j <= pos_r[rr] && j >= lo_r[rr];
+          s[n][e] = ok ? s[n][e] * scale_log2 : -CUDART_INF_F;
+          mx[rr] = fmaxf(mx[rr], s[n][e]);
+        }
       }
     }
     float corr[2], m_use[2];
