@@ -160,12 +160,14 @@ KVB_EXPORT int kvb_add_rmsnorm(float* resid, const void* delta, const float* w, 
 }
 
 // ---------------------------------------------------------------- SiLU * up
-// out[t, i] = g * (1 / (1 + exp(-g))) * u with g = gu[t, i], u = gu[t, I + i]
-// (upstream: base/src/kernels.cu:45-52).  Four elements per thread when I % 4 == 0.
+// out[t, i] = g * (1 / (1 + exp(-g))) * u  (upstream: base/src/kernels.cu:45-52).
+// A row of gu holds gate and up in blocks of BL: [gate 0..BL) | up 0..BL) | gate BL..2BL) | ...],
+// so g = gu[t, (i / BL) * 2 BL + i % BL] and u = BL further.  BL = I is the plain [gate | up] row.
+// Four elements per thread when BL % 4 == 0.
 __device__ __forceinline__ float silu_mul_one(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
 template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t groups) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int BL, size_t groups) {
   pdl_trigger();
   pdl_wait();
   const int gpr = I >> 2;  // groups of four per row
@@ -173,38 +175,41 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / gpr;
     const int i = (int)(idx - t * gpr) << 2;
-    const float4 g = Pack4<T>::load(gu + t * 2 * I + i);
-    const float4 u = Pack4<T>::load(gu + t * 2 * I + I + i);
+    const size_t at = t * 2 * I + (size_t)(i / BL) * 2 * BL + (i % BL);
+    const float4 g = Pack4<T>::load(gu + at);
+    const float4 u = Pack4<T>::load(gu + at + BL);
     Pack4<T>::store(out + t * I + i, make_float4(silu_mul_one(g.x, u.x), silu_mul_one(g.y, u.y),
                                                  silu_mul_one(g.z, u.z), silu_mul_one(g.w, u.w)));
   }
 }
 
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int BL, size_t total) {
   pdl_trigger();
   pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    out[idx] = from_f32<T>(silu_mul_one(to_f32(gu[t * 2 * I + i]), to_f32(gu[t * 2 * I + I + i])));
+    const size_t at = t * 2 * I + (size_t)(i / BL) * 2 * BL + (i % BL);
+    out[idx] = from_f32<T>(silu_mul_one(to_f32(gu[at]), to_f32(gu[at + BL])));
   }
 }
 
-KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int dtype, cudaStream_t stream) {
+KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int BL, int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
+  if (BL < 1 || I % BL) return KVB_ERR_BAD_SIZE;
   const int threads = 256;
-  const bool vec = (I % 4 == 0);
+  const bool vec = (BL % 4 == 0);
   const size_t work = vec ? (size_t)T_ * (I / 4) : (size_t)T_ * I;
   size_t want = (work + threads - 1) / threads;
   const int blocks = (int)(want < (size_t)148 * 16 ? want : (size_t)148 * 16);
   if (vec) {
     KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_vec_kernel<T>, dim3(blocks), dim3(threads), 0, stream,
-                                              (const T*)gu, (T*)out, I, work)));
+                                              (const T*)gu, (T*)out, I, BL, work)));
   } else {
     KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, stream,
-                                              (const T*)gu, (T*)out, I, work)));
+                                              (const T*)gu, (T*)out, I, BL, work)));
   }
   return kvb_launch_result();
 }

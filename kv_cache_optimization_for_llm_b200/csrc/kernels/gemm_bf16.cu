@@ -114,13 +114,25 @@ __device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
   return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// What happens to the finished sums:
+//   EPI_STORE     C[m, n] = sum
+//   EPI_SWIGLU    the weight rows come in blocks of 128: 64 gate features, then the 64 up
+//                 features of the same indices; out[m, 64 t + j] = silu(gate) * up
+//                 (upstream: a kernel of its own after the product, base/src/kernels.cu:45-52)
+// (Adding into the residual and normalising in the block that finishes last was tried as a
+// third form and measured slower than the separate add+norm kernel: the serial tail of
+// one block costs more than the launch it saves.)
+enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+
 struct Params {
   int M, N, K, MP;            // MP: rows padded to the UMMA N extent
   int k_tiles, splits;        // k tiles in all, blocks along K
   int stages;
   int red_bytes;              // shared memory set aside for the partials that peers send (splits > 1)
   int out_f32;                // 1: C is float32, 0: bfloat16
-  void* out;                  // [M, N]
+  void* out;                  // [M, N]; EPI_SWIGLU: [M, N/2]
+  int epilogue;               // EPI_*
+  int fin_bytes;              // shared memory for the rows' final sums (EPI_SWIGLU)
   int* status;
   unsigned long long* trace;  // optional [blocks, 8] nanosecond stamps of the phases of each block (profiling)
 };
@@ -146,7 +158,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   unsigned char* b_s = base + (size_t)p.stages * a_bytes;
   float* red = reinterpret_cast<float*>(b_s + (size_t)p.stages * b_bytes);  // never part of the stage ring:
   // peers write here while this block may still be multiplying
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(red) + p.red_bytes);
+  float* fin = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(red) + p.red_bytes);   // [rows][128]
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(fin) + p.fin_bytes);
   unsigned long long* empty = full + p.stages;
   unsigned long long* accum = empty + p.stages;
   unsigned* tmem_holder = reinterpret_cast<unsigned*>(accum + 1);
@@ -232,25 +245,31 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (tid == 0) stamp(p, 5);   // accumulator complete
 
   const int n = n0 + warp * 32 + lane;           // the feature this thread holds
+  // What this block does with the final sum of (row m, its j-th own row, this thread's feature).
+  auto emit = [&](int m, int j, float val) {
+    if (p.epilogue == EPI_SWIGLU) {
+      fin[j * TILE_N + tid] = val;
+    } else if (n < p.N) {
+      if (p.out_f32) {
+        reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = val;
+      } else {
+        reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(val);
+      }
+    }
+  };
+  int own_first = 0, own_step = 1;               // the rows whose final sums this block holds
   if (!aborted) {
     if (p.splits == 1) {
-      for (int c = 0; c < p.MP; c += 16) {
+      for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
         if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
         else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
         }
-        if (n < p.N) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int m = c + i;
-            if (m < p.M) {
-              if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = v[i];
-              else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v[i]);
-            }
-          }
-        }
+        for (int i = 0; i < 16; ++i)
+          if (c + i < p.M) emit(c + i, c + i, v[i]);
       }
     } else {
       // send row m of this block's partial to slot blockIdx.y of block (m mod S):
@@ -275,13 +294,26 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // Every block of the cluster comes here, aborted or not: the barrier is collective.
     // After it all partials have arrived and nobody touches a peer's memory any more.
     cluster_sync_all();
+    own_first = (int)blockIdx.y;
+    own_step = p.splits;
     if (!aborted) {
-      for (int m = (int)blockIdx.y, j = 0; m < p.M; m += p.splits, ++j) {
+      for (int m = own_first, j = 0; m < p.M; m += own_step, ++j) {
         float acc = 0.f;
         for (int s2 = 0; s2 < p.splits; ++s2) acc += red[(j * p.splits + s2) * TILE_N + tid];
-        if (n < p.N) {
-          if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = acc;
-          else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(acc);
+        emit(m, j, acc);
+      }
+    }
+  }
+  if (p.epilogue == EPI_SWIGLU && !aborted) {
+    // gate and up of one feature sit 64 threads apart: pair them through shared memory
+    __syncthreads();
+    if (tid < TILE_N / 2) {
+      const int col = blockIdx.x * (TILE_N / 2) + tid;
+      if (col < p.N / 2) {
+        for (int m = own_first, j = 0; m < p.M; m += own_step, ++j) {
+          const float g = fin[j * TILE_N + tid], u = fin[j * TILE_N + TILE_N / 2 + tid];
+          const float a = g * (1.0f / (1.0f + expf(-g))) * u;
+          reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * (p.N / 2) + col] = __float2bfloat16_rn(a);
         }
       }
     }
@@ -378,9 +410,12 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
 // C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
 // address is stable (a captured graph), so its tensor map may be cached as the
 // weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
-// block (profiling only).  Uses no memory beyond its operands.
+// block (profiling only).
+// epilogue (see EPI_*): 0 store; 1 SwiGLU on row-interleaved weights, out is bfloat16
+// [M, N/2], N a multiple of 128, M <= 16.
+// Uses no memory beyond its operands.
 KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
-                               int K, int x_is_static, int* status, unsigned long long* trace,
+                               int K, int x_is_static, int epilogue, int* status, unsigned long long* trace,
                                cudaStream_t stream) {
   int splits, tiles;
   const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &tiles);
@@ -394,21 +429,26 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   p.k_tiles = (K + TILE_K - 1) / TILE_K;
   p.splits = splits;
   p.out_f32 = out_f32; p.out = out; p.status = status; p.trace = trace;
+  if (epilogue < EPI_STORE || epilogue > EPI_SWIGLU) return KVB_ERR_BAD_SIZE;
+  if (epilogue != EPI_STORE && (M > 16 || out_f32)) return KVB_ERR_BAD_SIZE;
+  if (epilogue == EPI_SWIGLU && (N % TILE_N)) return KVB_ERR_BAD_SIZE;
+  p.epilogue = epilogue;
+  p.fin_bytes = epilogue == EPI_SWIGLU ? MP * TILE_N * 4 : 0;
   const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
   // two blocks per SM while the stages stay deep enough, one block otherwise
   const int budget = MP <= 64 ? 108 * 1024 : 200 * 1024;
   // room for the partials of this block's rows from every block of the cluster
   int red_bytes = splits > 1 ? ((M + splits - 1) / splits) * splits * TILE_N * 4 : 0;
-  if (red_bytes > budget - 2 * stage_bytes) { splits = 1; red_bytes = 0; }   // no room: one block does all of K
+  if (red_bytes + p.fin_bytes > budget - 2 * stage_bytes) { splits = 1; red_bytes = 0; }   // no room: one block does all of K
   p.splits = splits;
   p.red_bytes = red_bytes;
-  int stages = (budget - red_bytes) / stage_bytes;
+  int stages = (budget - red_bytes - p.fin_bytes) / stage_bytes;
   if (stages > 8) stages = 8;
   const int per = (p.k_tiles + splits - 1) / splits;
   if (stages > per) stages = per;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + (2 * stages + 1) * 8 + 16;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 1) * 8 + 16;
   CUtensorMap mw, mx;
   int e = cached_map(&mw, w, N, K, ldw, TILE_N);
   if (e) return e;
@@ -416,7 +456,7 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   if (e) return e;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t ce = cudaFuncSetAttribute(gemm_skinny_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t ce = cudaFuncSetAttribute(gemm_skinny_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);  // the kernel also has a little static shared memory
     if (ce != cudaSuccess) return (int)ce;
     ce = cudaFuncSetAttribute(gemm_skinny_kernel<0>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (ce != cudaSuccess) return (int)ce;

@@ -122,14 +122,15 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     return out
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """``silu(gate) * up`` for rows laid out as [gate | up]."""
+def silu_mul(gate_up: torch.Tensor, block: Optional[int] = None) -> torch.Tensor:
+    """``silu(gate) * up`` for rows that hold gate and up in alternating blocks of
+    ``block`` features ([gate | up] as a whole when ``block`` is None)."""
     _need_cuda(gate_up)
     assert gate_up.is_contiguous()
     T, two_i = gate_up.shape
     I = two_i // 2
     out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
-    rc = lib("elementwise").kvb_silu_mul(_p(gate_up), _p(out), c_int(T), c_int(I),
+    rc = lib("elementwise").kvb_silu_mul(_p(gate_up), _p(out), c_int(T), c_int(I), c_int(block or I),
                                          c_int(dtype_code(gate_up.dtype)), _stream())
     _check(rc, "silu_mul")
     return out
@@ -213,6 +214,24 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w.t(), out_dtype=out_dtype)
     return torch.nn.functional.linear(x, w)
+
+
+def _skinny_ok(x: torch.Tensor, rows_limit: int) -> bool:
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= rows_limit and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+
+
+def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, block: int) -> torch.Tensor:
+    """``silu(x . gate^T) * (x . up^T)`` with gate and up stored as one matrix whose rows
+    alternate in blocks of ``block`` features.  Up to 16 bfloat16 rows with blocks of 64:
+    one kernel (the activation is the product's epilogue); otherwise product, then
+    activation kernel."""
+    I = gate_up.shape[0] // 2
+    if block == 64 and _skinny_ok(x, min(SKINNY_MAX_ROWS, FUSED_EPILOGUE_MAX_ROWS)) \
+            and gate_up.shape[0] % 128 == 0:
+        return gemm_skinny(x, gate_up, x.dtype, kernel_status(x.device),
+                           x_is_static=torch.cuda.is_current_stream_capturing(), epilogue="swiglu")
+    return silu_mul(linear(x, gate_up), block=block if block != I else None)
 
 
 _scratch: Dict[tuple, torch.Tensor] = {}
@@ -417,17 +436,25 @@ def gemm_skinny_plan(M: int, N: int, K: int):
     return splits.value, tiles.value
 
 
+FUSED_EPILOGUE_MAX_ROWS = 16
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor,
-                x_is_static: bool = False, trace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x . w^T`` for few rows (M <= 256) on tcgen05 tensor cores, weights streamed by TMA."""
+                x_is_static: bool = False, trace: Optional[torch.Tensor] = None, epilogue: str = "store") -> torch.Tensor:
+    """``x . w^T`` for few rows (M <= 256) on tcgen05 tensor cores, weights streamed by TMA.
+
+    ``epilogue``: "store", or "swiglu": ``w`` holds gate and up rows in alternating blocks
+    of 64 and ``silu(gate) * up`` [M, N/2] is returned (up to 16 rows)."""
     _need_cuda(x, w)
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    code = {"store": 0, "swiglu": 1}[epilogue]
+    out = torch.empty((M, N // 2 if code == 1 else N), dtype=out_dtype, device=x.device)
     rc = lib("gemm_bf16").kvb_gemm_skinny(
         _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(1 if out_dtype == torch.float32 else 0),
-        c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), _p(status), _p(trace), _stream())
+        c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), c_int(code), _p(status), _p(trace),
+        _stream())
     if rc == -2:
         raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
     _check(rc, "gemm_skinny")

@@ -27,10 +27,20 @@ class SwiGLU(Part):
 
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
-        self.gate_up = torch.cat([weights["gate"], weights["up"]], dim=0).contiguous()
+        inter = int(params["intermediate_size"])
+        # gate and up rows alternate in blocks, so that a 128-row tile of the product holds
+        # 64 gate features and the 64 up features of the same indices and the activation
+        # can be the product's epilogue; widths that are no multiple of 64 keep [gate | up]
+        self.block = 64 if inter % 64 == 0 else inter
+        g, u = weights["gate"], weights["up"]
+        if self.block == inter:
+            self.gate_up = torch.cat([g, u], dim=0).contiguous()
+        else:
+            nb, h = inter // self.block, g.shape[1]
+            self.gate_up = torch.stack([g.view(nb, self.block, h), u.view(nb, self.block, h)], dim=1) \
+                .reshape(2 * inter, h).contiguous()
         self.down = weights["down"]
 
     def forward(self, x, batch):
-        gu = ops.linear(x, self.gate_up)
-        a = ops.silu_mul(gu)
+        a = ops.linear_swiglu(x, self.gate_up, self.block)
         return ops.linear(a, self.down)

@@ -53,3 +53,29 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
     assert ops.gemm_skinny_plan(257, 128, 64) is None      # too many rows for the skinny form
     assert ops.gemm_skinny_plan(4, 128, 100) is None       # K * 2 bytes must be a multiple of 16
     assert ops.gemm_skinny_plan(4, 128, 104) is not None
+
+
+def _bf(t):
+    return t.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 128, 64), (8, 8192, 2048), (16, 512, 192), (5, 192, 520), (3, 64, 2048)])
+def test_swiglu_epilogue(M, I, K):
+    """Product with row-interleaved gate/up weights and silu(gate)*up as its epilogue,
+    against float64; and the same through the unfused pair of kernels."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(M + I + K)
+    x = _bf(torch.randn(M, K, generator=g, device="cuda"))
+    wg = _bf(torch.randn(I, K, generator=g, device="cuda") / K ** 0.5)
+    wu = _bf(torch.randn(I, K, generator=g, device="cuda") / K ** 0.5)
+    inter = torch.stack([wg.view(I // 64, 64, K), wu.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+    gate, up = x.double() @ wg.double().t(), x.double() @ wu.double().t()
+    ref = gate / (1 + torch.exp(-gate)) * up
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fused = ops.gemm_skinny(x, inter, torch.bfloat16, st, epilogue="swiglu")
+    assert fused.shape == (M, I) and int(st.item()) == 0
+    tol = 6e-3 * ref.abs().max().item()
+    assert (fused.double() - ref).abs().max().item() < tol
+    assert torch.equal(fused, ops.linear_swiglu(x, inter, 64))
+    unfused = ops.silu_mul(ops.gemm_skinny(x, inter, torch.bfloat16, st), block=64)
+    assert (unfused.double() - ref).abs().max().item() < 2 * tol   # gate and up rounded to bfloat16 in between
