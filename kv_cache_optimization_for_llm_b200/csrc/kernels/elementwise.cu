@@ -203,7 +203,7 @@ KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int BL, in
   const bool vec = (BL % 4 == 0);
   const size_t work = vec ? (size_t)T_ * (I / 4) : (size_t)T_ * I;
   size_t want = (work + threads - 1) / threads;
-  const int blocks = (int)(want < (size_t)148 * 16 ? want : (size_t)148 * 16);
+  const int blocks = (int)(want < (size_t)148 * 32 ? want : (size_t)148 * 32);
   if (vec) {
     KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_vec_kernel<T>, dim3(blocks), dim3(threads), 0, stream,
                                               (const T*)gu, (T*)out, I, BL, work)));
@@ -290,6 +290,105 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// The same for the common case of a full rotary dimension (rot == d): 16 bytes per
+// access.  A work item is VEC consecutive dims j..j+VEC-1 of a head's lower half together
+// with the matching dims of the upper half (q and k heads), or VEC dims of a v head.
+template <typename T> struct Vec16;
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+    unsigned w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<unsigned*>(&v);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                         const int* __restrict__ token_req, const float* __restrict__ cos_t,
+                                         const float* __restrict__ sin_t, int table_len, T* __restrict__ k_pages,
+                                         T* __restrict__ v_pages, const int* __restrict__ block_table,
+                                         int max_pages, int page_size, int num_pages, int nq, int nkv, int d,
+                                         int* status) {
+  constexpr int VEC = Vec16<T>::N;
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = d >> 1;
+  if (pos < 0 || pos >= table_len) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
+    return;
+  }
+  T* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
+  size_t dst = 0;
+  bool write = k_pages != nullptr;
+  if (write) {
+    const int lp = pos / page_size;
+    const int page = (lp < max_pages) ? block_table[(size_t)token_req[t] * max_pages + lp] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      write = false;
+    } else {
+      dst = ((size_t)page * nkv * page_size + (pos % page_size)) * d;
+    }
+  }
+  const int per_rot = half / VEC;            // items per rotated head
+  const int per_v = d / VEC;                 // items per v head
+  const int n_rot = (nq + nkv) * per_rot;
+  const int n_items = n_rot + nkv * per_v;
+  const float* cr = cos_t + (size_t)pos * half;
+  const float* sr = sin_t + (size_t)pos * half;
+  for (int w = threadIdx.x; w < n_items; w += blockDim.x) {
+    if (w < n_rot) {
+      const int head = w / per_rot, j = (w - head * per_rot) * VEC;
+      T* x = row + (size_t)head * d;
+      float x1[VEC], x2[VEC], a[VEC], b[VEC];
+      Vec16<T>::load(x + j, x1);
+      Vec16<T>::load(x + j + half, x2);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float c = cr[j + e], sn = sr[j + e];
+        a[e] = x1[e] * c - x2[e] * sn;
+        b[e] = x1[e] * sn + x2[e] * c;
+      }
+      if (head < nq) {
+        Vec16<T>::store(x + j, a);
+        Vec16<T>::store(x + j + half, b);
+      } else if (write) {
+        T* kd = k_pages + dst + (size_t)(head - nq) * page_size * d;
+        Vec16<T>::store(kd + j, a);
+        Vec16<T>::store(kd + j + half, b);
+      }
+    } else if (write) {
+      const int wv = w - n_rot;
+      const int head = wv / per_v, j = (wv - head * per_v) * VEC;
+      const uint4 val = *reinterpret_cast<const uint4*>(row + (size_t)(nq + nkv + head) * d + j);
+      *reinterpret_cast<uint4*>(v_pages + dst + (size_t)head * page_size * d + j) = val;
+    }
+  }
+}
+
 KVB_EXPORT int kvb_rope_kv_write(void* qkv, const int* positions, const int* token_req,
                                  const float* cos_t, const float* sin_t, int table_len,
                                  void* k_pages, void* v_pages, const int* block_table, int max_pages,
@@ -297,6 +396,16 @@ KVB_EXPORT int kvb_rope_kv_write(void* qkv, const int* positions, const int* tok
                                  int dtype, int* status, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (d % 2 || rot % 2 || rot > d) return KVB_ERR_BAD_SIZE;
+  const int esz = dtype == KVB_F32 ? 4 : 2;
+  if (cos_t != nullptr && rot == d && (d / 2) % (16 / esz) == 0 && dtype <= KVB_BF16) {
+    const int items = (nq + nkv) * (d / 2) / (16 / esz) + nkv * d / (16 / esz);
+    const int th = items >= 192 ? 256 : (items >= 96 ? 128 : 64);
+    KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(rope_kv_write_vec_kernel<T>, dim3(T_), dim3(th), 0, stream, (T*)qkv,
+                                              positions, token_req, cos_t, sin_t, table_len, (T*)k_pages,
+                                              (T*)v_pages, block_table, max_pages, page_size, num_pages, nq, nkv, d,
+                                              status)));
+    return kvb_launch_result();
+  }
   const int work = (nq + 2 * nkv) * (d / 2);
   const int threads = work >= 1024 ? 256 : 128;
   KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(rope_kv_write_kernel<T>, dim3(T_), dim3(threads), 0, stream, (T*)qkv,
