@@ -19,9 +19,9 @@
 
 namespace {
 
-constexpr int BM = 64;   // query rows per block
 constexpr int BN = 64;   // keys per tile
-constexpr int kThreads = 128;
+// Query rows per block: 16 per warp.  Eight warps (128 rows) when the step has enough
+// query tiles to fill the GPU with them, four warps (64 rows) otherwise.
 
 __device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
   const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -62,14 +62,16 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
 
 struct TileDesc { int req, t0, n_tok, pad; };
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, D == 64 ? 4 : 2)
+template <int D, int NW>
+__global__ void __launch_bounds__(NW * 32, (D == 64 ? 16 : 8) / NW)
 paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
                              const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                              const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
                              const int* __restrict__ positions, const TileDesc* __restrict__ tiles,
                              __nv_bfloat16* __restrict__ out, int nq, int nkv, int G, int gp_shift,
                              float scale_log2, int window, int* status) {
+  constexpr int BM = NW * 16;       // query rows of this block
+  constexpr int kThreads = NW * 32;
   constexpr int CPK = D / 8;        // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;    // k-steps of the score product
   constexpr int DT = D / 8;         // n-tiles of the output
@@ -111,28 +113,32 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
       cp_async_16_zfill(q_s + swz<D>(row, part), src, ok);
     }
   };
+  // A key's row is copied by kThreads / BN threads, so that its page is looked up once per
+  // thread and tile.
   auto load_kv = [&](int t, int buf) {
+    constexpr int TPK = kThreads / BN;          // threads per key
+    constexpr int CPT = CPK / TPK;              // chunks per thread
     unsigned char* kd = k_s + buf * BN * D * 2;
     unsigned char* vd = v_s + buf * BN * D * 2;
-#pragma unroll
-    for (int i = 0; i < BN * CPK / kThreads; ++i) {
-      const int c = i * kThreads + tid;
-      const int key = c / CPK, part = c % CPK;
-      const int j = t * BN + key;
-      bool ok = j < k_hi && j >= k_lo;
-      size_t off = 0;
-      if (ok) {
-        const int lp = j >> page_shift;
-        const int page = lp < max_pages ? __ldg(table + lp) : -1;
-        if (page < 0 || page >= num_pages) {
-          atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
-          ok = false;
-        } else {
-          off = ((((size_t)page * nkv + hk) << page_shift) + (j & page_mask)) * D + part * 8;
-        }
+    const int key = tid / TPK, part0 = (tid % TPK) * CPT;
+    const int j = t * BN + key;
+    bool ok = j < k_hi && j >= k_lo;
+    size_t off = 0;
+    if (ok) {
+      const int lp = j >> page_shift;
+      const int page = lp < max_pages ? __ldg(table + lp) : -1;
+      if (page < 0 || page >= num_pages) {
+        atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        ok = false;
+      } else {
+        off = ((((size_t)page * nkv + hk) << page_shift) + (j & page_mask)) * D;
       }
-      cp_async_16_zfill(kd + swz<D>(key, part), k_pages + off, ok);
-      cp_async_16_zfill(vd + swz<D>(key, part), v_pages + off, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      const int part = part0 + i;
+      cp_async_16_zfill(kd + swz<D>(key, part), k_pages + off + part * 8, ok);
+      cp_async_16_zfill(vd + swz<D>(key, part), v_pages + off + part * 8, ok);
     }
   };
 
@@ -280,19 +286,20 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
   }
 }
 
-template <int D>
+template <int D, int NW>
 int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_pages, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
            void* out, int nq, int nkv, int G, int gp_shift, float scale, int window, int* status,
            cudaStream_t stream) {
+  constexpr int BM = NW * 16;
   const size_t smem = (size_t)BM * D * 2 + 4 * (size_t)BN * D * 2 + BM * sizeof(int);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(paged_flash_attention_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(paged_flash_attention_kernel<D, NW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(num_tiles, nkv);
-  kvb_launch(paged_flash_attention_kernel<D>, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q,
+  kvb_launch(paged_flash_attention_kernel<D, NW>, grid, dim3(NW * 32), smem, stream, (const __nv_bfloat16*)q,
              q_row_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, max_pages,
              page_shift, num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq, nkv, G, gp_shift,
              scale * 1.4426950408889634f, window, status);
@@ -313,20 +320,23 @@ KVB_EXPORT int kvb_flash_attention_supported(int d, int group, int page_size) {
   return (d == 64 || d == 128) && group >= 1 && group <= 64 && log2_exact(page_size) >= 0;
 }
 
-// Query tokens per tile for a group size: 64 rows / the group padded to a power of two.
-KVB_EXPORT int kvb_flash_attention_tokens_per_tile(int group) {
+// Query tokens per tile for a group size: rows / the group padded to a power of two, with
+// rows = 128 (`wide` != 0) or 64.
+KVB_EXPORT int kvb_flash_attention_tokens_per_tile(int group, int wide) {
   int gp = 1;
   while (gp < group) gp <<= 1;
-  return BM / gp;
+  const int nt = (wide ? 128 : 64) / gp;
+  return nt < 1 ? 1 : nt;
 }
 
-// tiles: num_tiles x {request row, first token row, tokens (<= tokens_per_tile), 0}, int32.
-// The tokens of a tile are consecutive tokens of one request, positions ascending.
+// tiles: num_tiles x {request row, first token row, tokens (<= tokens_per_tile(group, wide)), 0},
+// int32.  The tokens of a tile are consecutive tokens of one request, positions ascending.
+// wide: the tiles were cut for 128 query rows per block, else for 64.
 // bfloat16 only.  out is [T, nq*d].
 KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                          const int* block_table, int max_pages, int page_size, int num_pages,
-                                         const int* positions, const void* tiles, int num_tiles, void* out, int nq,
-                                         int nkv, int d, float scale, int window, int* status,
+                                         const int* positions, const void* tiles, int num_tiles, int wide, void* out,
+                                         int nq, int nkv, int d, float scale, int window, int* status,
                                          cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nkv < 1 || nq % nkv) return KVB_ERR_BAD_SIZE;
@@ -335,9 +345,11 @@ KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const 
   int gp_shift = 0;
   while ((1 << gp_shift) < G) ++gp_shift;
   const int page_shift = log2_exact(page_size);
-  if (d == 64)
-    return launch<64>(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions,
-                      tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream);
-  return launch<128>(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions,
-                     tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream);
+  if (wide && (128 >> gp_shift) < 1) return KVB_ERR_BAD_SIZE;
+#define KVB_FA(D, NW)                                                                                           \
+  return launch<D, NW>(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions, \
+                       tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream)
+  if (d == 64) { if (wide) KVB_FA(64, 8); KVB_FA(64, 4); }
+  if (wide) KVB_FA(128, 8);
+  KVB_FA(128, 4);
 }

@@ -346,10 +346,12 @@ def test_flash_attention_mixed_runs(nq, nkv, d, page_size, window):
     assert ops.flash_attention_supported(d, nq // nkv, page_size)
     c = _attention_case("bfloat16", nq, nkv, d, ctxs=[1, 70, 130, 64, 400, 257, 2], q_lens=[1, 70, 2, 1, 150, 40, 2],
                         page_size=page_size, window=window, seed=d + nq + page_size)
-    fb = _FakeBatch(c)
-    out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), window)
-    assert int(fb.status.item()) == 0
-    assert rel_err(out, c["ref"]) < TOL["bfloat16"]
+    for wide in (False, True):      # 64 and 128 query rows per block
+        fb = _FakeBatch(c)
+        out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), window,
+                                  wide=wide)
+        assert int(fb.status.item()) == 0
+        assert rel_err(out, c["ref"]) < TOL["bfloat16"], wide
 
 
 @pytest.mark.parametrize("spike", [0, 63, 64, 511, 777])
