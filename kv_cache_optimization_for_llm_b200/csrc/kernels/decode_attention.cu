@@ -1,7 +1,8 @@
 // The attention of a bfloat16 decode step in one launch, on tensor cores.
 //
-// Every request brings one query token.  A cluster of S = 8 blocks serves one
-// (request, key/value head): block z takes the 128-key tiles z, z + 8, ... of the
+// Every request brings one query token.  A cluster of S blocks (4 or 8, chosen by the
+// caller from the longest context it allows, never from the batch) serves one
+// (request, key/value head): block z takes the 128-key tiles z, z + S, ... of the
 // request's context, so the work of a token is cut at absolute positions and does not
 // depend on what else is in the batch.  The rows of the tensor-core tile are the query
 // heads that share the key/value head (padded to 16), so keys and values are fetched
@@ -20,7 +21,7 @@
 // merged in warp order, and each block sends one partial
 // (output, max, sum per head) into the shared memory of block 0 of its cluster
 // (distributed shared memory); after the cluster's hardware barrier block 0 merges the
-// eight partials in block order and writes the output.  No scratch in global memory,
+// S partials in block order and writes the output.  No scratch in global memory,
 // no counters, no spinning.
 #include "common.cuh"
 
@@ -30,7 +31,6 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kTile = 128;     // keys per tile (32 per warp)
-constexpr int kCluster = 8;    // blocks per (request, kv head)
 
 // 16 bytes into shared memory; `valid` false: zeros are written and nothing is read.
 __device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
@@ -73,8 +73,9 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
   return row * (D * 2) + ((chunk ^ (row & 7)) << 4);
 }
 
-// GP: the group of query heads padded to 4, 8 or 16 (rows that are kept).
-template <int D, int GP>
+// GP: the group of query heads padded to 4, 8 or 16 (rows that are kept).  kCluster: blocks
+// per (request, kv head).
+template <int D, int GP, int kCluster>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int write_kv,
@@ -370,7 +371,7 @@ int log2_exact(int x) {
   return (1 << s) == x ? s : -1;
 }
 
-template <int D, int GP>
+template <int D, int GP, int kCluster>
 int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* q_start, const int* ctx_len, const float* cos_t,
            const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv, float scale, int window,
@@ -380,7 +381,7 @@ int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int 
                       (size_t)kCluster * GP * PW * 4;
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP>,
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kCluster>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
@@ -400,7 +401,7 @@ int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int 
   cfg.attrs = attr;
   cfg.numAttrs = kvb_pdl_enabled() ? 2 : 1;
   cudaError_t le = cudaLaunchKernelEx(
-      &cfg, decode_attention_mma_kernel<D, GP>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
+      &cfg, decode_attention_mma_kernel<D, GP, kCluster>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
       (__nv_bfloat16*)v_pages, write_kv, block_table, max_pages, page_shift, num_pages, q_start, ctx_len, cos_t, sin_t,
       table_len, rot, (__nv_bfloat16*)out, nq, nkv, nq / nkv, scale * 1.4426950408889634f, window, status);
   if (le != cudaSuccess) return (int)le;
@@ -418,21 +419,30 @@ KVB_EXPORT int kvb_decode_attention_mma_supported(int d, int group, int page_siz
 // qkv: [T, (nq + 2 nkv) d] bfloat16 as the projection wrote it; request r's token is row
 // q_start[r] at position ctx_len[r]-1.  write_kv = 0: the layer reads another layer's
 // cache and writes nothing.  cos_t/sin_t: [table_len, rot/2] or nullptr.  out: [T, nq d].
+// cluster: 4 or 8 blocks per (request, kv head); a function of the engine's limits only, so
+// that a token's sums are cut the same way in every batch.
 // Uses no memory beyond its operands.  R <= 65535.
 KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv,
                                         const int* block_table, int max_pages, int page_size, int num_pages,
                                         const int* q_start, const int* ctx_len, const float* cos_t,
                                         const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv,
-                                        int d, float scale, int window, int* status, cudaStream_t stream) {
+                                        int d, float scale, int window, int cluster, int* status,
+                                        cudaStream_t stream) {
   if (R <= 0) return 0;
+  if (cluster != 4 && cluster != 8) return KVB_ERR_BAD_SIZE;
   if (nkv < 1 || nq % nkv || !kvb_decode_attention_mma_supported(d, nq / nkv, page_size) || R > 65535 || (rot & 1) ||
       rot > d || nkv > 65535)
     return KVB_ERR_BAD_SIZE;
   const int G = nq / nkv;
   const int ps = log2_exact(page_size);
-#define KVB_DM(D, GP)                                                                                             \
-  return launch<D, GP>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages,      \
-                       q_start, ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, stream)
+#define KVB_DM(D, GP)                                                                                              \
+  do {                                                                                                             \
+    if (cluster == 4)                                                                                              \
+      return launch<D, GP, 4>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, \
+                              q_start, ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, stream); \
+    return launch<D, GP, 8>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages,   \
+                            q_start, ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, stream); \
+  } while (0)
   if (d == 64) { if (G <= 4) KVB_DM(64, 4); if (G <= 8) KVB_DM(64, 8); KVB_DM(64, 16); }
   if (G <= 4) KVB_DM(128, 4);
   if (G <= 8) KVB_DM(128, 8);

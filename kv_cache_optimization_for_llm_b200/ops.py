@@ -366,10 +366,11 @@ def decode_attention_mma_supported(d: int, group: int, page_size: int) -> bool:
 
 
 def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
-                         nq, nkv, d, scale, window, status) -> torch.Tensor:
+                         nq, nkv, d, scale, window, status, max_positions: int = 1 << 30) -> torch.Tensor:
     """The attention of a bfloat16 decode step in one launch on tensor cores: rotary
     encoding of query and new key, cache write, attention over 128-key tiles spread over
-    a cluster of blocks, merge through distributed shared memory.  No scratch."""
+    a cluster of blocks, merge through distributed shared memory.  No scratch.
+    The cluster has 4 blocks when the engine allows at most 4096 positions, else 8."""
     _need_cuda(qkv, k_pages)
     assert qkv.dtype == torch.bfloat16
     R = ctx_len.numel()
@@ -378,7 +379,8 @@ def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, 
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), c_int(1 if write_kv else 0), _p(block_table),
         c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
         _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rot), _p(out), c_int(R), c_int(nq),
-        c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), _p(status), _stream())
+        c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), c_int(4 if max_positions <= 4096 else 8),
+        _p(status), _stream())
     _check(rc, "decode_attention_mma")
     return out
 
@@ -397,7 +399,7 @@ def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv,
     group, page_size = nq // nkv, k_pages.shape[2]
     if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_mma_supported(d, group, page_size):
         return decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
-                                    cos, sin, rot, nq, nkv, d, scale, window, batch.status)
+                                    cos, sin, rot, nq, nkv, d, scale, window, batch.status, max_positions)
     if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_supported(d, group):
         return decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
                                       cos, sin, rot, nq, nkv, d, scale, window, max_positions, batch.status)

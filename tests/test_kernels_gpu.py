@@ -495,7 +495,9 @@ def test_tensor_core_decode_attention(nq, nkv, d, rot, page_size, window, write)
     st = status()
     args = (qkv, dkp, dvp, write, dev(tables, torch.int32), dev(np.arange(R + 1), torch.int32),
             dev(ctxs, torch.int32), cos_t, sin_t, rot, nq, nkv, d, 1 / math.sqrt(d), window, st)
-    out = ops.decode_attention_mma(*args)
+    out4 = ops.decode_attention_mma(*args, max_positions=4096)     # clusters of 4
+    assert rel_err(out4, np.array(refs)) < TOL[dtype] * 1.5
+    out = ops.decode_attention_mma(*args)                          # clusters of 8
     assert int(st.item()) == 0
     assert rel_err(out, np.array(refs)) < TOL[dtype] * 1.5
     for page, slot, k_want, v_want in new_kv:
