@@ -53,10 +53,25 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const float pen = penalty ? penalty[row] : 1.0f;
   unsigned char* mask = (mask_base != nullptr && pen != 1.0f) ? mask_base + (size_t)slots[row] * V : nullptr;
 
-  // pass 1: maximum and its lowest index
+  // pass 1: maximum and its lowest index.  Without a penalty the row is read 16 bytes at a
+  // time (the bulk of it; the ragged ends one by one).
   float bv = -CUDART_INF_F;
   int bi = 0x7fffffff;
-  for (int i = tid; i < V; i += kSampleThreads) better(bv, bi, penalised(l, mask, pen, i), i);
+  if (mask == nullptr) {
+    const int head = (int)((16 - (reinterpret_cast<uintptr_t>(l) & 15)) & 15) / 4;   // floats before alignment
+    const int lead = head < V ? head : V;
+    const int groups = (V - lead) / 4;
+    const float4* l4 = reinterpret_cast<const float4*>(l + lead);
+    for (int g = tid; g < groups; g += kSampleThreads) {
+      const float4 v = l4[g];
+      const int i = lead + 4 * g;
+      better(bv, bi, v.x, i); better(bv, bi, v.y, i + 1); better(bv, bi, v.z, i + 2); better(bv, bi, v.w, i + 3);
+    }
+    for (int i = tid; i < lead; i += kSampleThreads) better(bv, bi, l[i], i);
+    for (int i = lead + 4 * groups + tid; i < V; i += kSampleThreads) better(bv, bi, l[i], i);
+  } else {
+    for (int i = tid; i < V; i += kSampleThreads) better(bv, bi, penalised(l, mask, pen, i), i);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
