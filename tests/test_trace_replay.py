@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 # a few hundred long through a handful of layers, measured at ~1e-6.  bfloat16:
 # activations are rounded to 8 bits of mantissa (2^-9 relative) between kernels.
 TOL = {"float32": 2e-5, "bfloat16": 4e-2}
-LENGTHS = {"tiny_a": [70, 96, 45, 33], "tiny_b": [120, 81, 64, 39], "tiny_c": [77, 50, 101, 36]}
+LENGTHS = {"tiny_a": [70, 96, 45, 33], "tiny_b": [120, 81, 64, 39], "tiny_c": [77, 50, 101, 36],
+           "tiny_d": [300, 150, 129, 70], "tiny_e": [257, 140, 66, 200]}
 PORTIONS = [7, 2, 13, 3, 2, 5, 2, 31, 2, 4, 16, 2, 9]
 
 
@@ -40,7 +41,7 @@ def cut(n, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
 def test_replay_all_cuttings(name, dtype):
     cfg_dict, seed, _ = CONFIGS[name]
     storage = "float32" if dtype == "float32" else "bfloat16"
@@ -53,7 +54,7 @@ def test_replay_all_cuttings(name, dtype):
     # The mixed phase holds up to four requests; size the pool for exactly that, so
     # that the single-request phases before it already reuse pages again and again.
     max_tokens = sum(ceil64(len(s)) for s in seqs)
-    extra = ("--page-size", "4") if name == "tiny_a" else ()
+    extra = {"tiny_a": ("--page-size", "4"), "tiny_e": ("--page-size", "8")}.get(name, ())
     tr = TraceRun(mdir, dtype, max_tokens, extra)
     worst = 0.0
     try:

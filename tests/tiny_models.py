@@ -36,7 +36,29 @@ TINY_C = {
     "max_position_embeddings": 192, "tie_word_embeddings": False, "hidden_act": "silu",
 }
 
-CONFIGS = {"tiny_a": (TINY_A, 0, 0.02), "tiny_b": (TINY_B, 1, 0.05), "tiny_c": (TINY_C, 2, 0.08)}
+# head size 64, feed-forward width a multiple of 64: the sizes at which the bfloat16 engine
+# takes its tensor-core kernels (flash attention, cluster decode attention, tcgen05 products
+# with the SwiGLU epilogue)
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 515, "hidden_size": 256, "intermediate_size": 384, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
+    "max_position_embeddings": 320, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+# head size 128, groups of three query heads, width that is not heads * head size
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 300, "hidden_size": 160, "intermediate_size": 200, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128,
+    "rms_norm_eps": 2e-6, "rope_theta": 50000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 2.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "max_position_embeddings": 320, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+
+CONFIGS = {"tiny_a": (TINY_A, 0, 0.02), "tiny_b": (TINY_B, 1, 0.05), "tiny_c": (TINY_C, 2, 0.08),
+           "tiny_d": (TINY_D, 3, 0.05), "tiny_e": (TINY_E, 4, 0.06)}
 
 _made = {}
 
