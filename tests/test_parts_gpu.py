@@ -173,14 +173,15 @@ def _register_toy():
         ff = lambda p: PartSpec("swiglu", {"hidden_size": H, "intermediate_size": cfg["inter"]},
                                 {"gate": p + "ff.gate", "up": p + "ff.up", "down": p + "ff.down"})
         rope = PartSpec("rope", {"head_dim": cfg["head_dim"], "rotary_dim": cfg["head_dim"], "theta": 1000.0, "scaling": None})
-        def attn(p):
+        def attn(p, window):
             return PartSpec("attention", {"hidden_size": H, "num_heads": cfg["heads"], "num_kv_heads": cfg["kv_heads"],
-                                          "head_dim": cfg["head_dim"], "window": None, "position": rope},
+                                          "head_dim": cfg["head_dim"], "window": window, "position": rope},
                             {r: f"{p}attn.{r}" for r in "qkvo"})
         layers = []
+        windows = cfg.get("windows") or [None] * len(cfg["mixers"])
         for i, kind in enumerate(cfg["mixers"]):
             p = f"l{i}."
-            mixer = attn(p) if kind == "attention" else PartSpec("toy_decay", {"hidden_size": H, "decay": cfg["decay"]}, {"w": p + "decay.w"})
+            mixer = attn(p, windows[i]) if kind == "attention" else PartSpec("toy_decay", {"hidden_size": H, "decay": cfg["decay"]}, {"w": p + "decay.w"})
             layers.append(LayerSpec("prenorm", mixer, norm(p + "n1"), ff(p), norm(p + "n2")))
         return ModelSpec(architecture="ToyForCausalLM", hidden_size=H, vocab_size=V, max_position=cfg["max_pos"],
                          embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, {"table": "emb"}),
@@ -208,6 +209,7 @@ def _toy_plain(cfg, w, tokens):
     cos, sin = P.rope_tables(np.arange(T), inv)
     h = w["emb"][np.asarray(tokens)]
     kv_of = {}
+    windows = cfg.get("windows") or [None] * len(cfg["mixers"])
     for idx, (l, cache_of) in enumerate(cfg["schedule"]):
         p = f"l{l}."
         x = P.rms_norm(h, w[p + "n1"], cfg["eps"])
@@ -219,7 +221,7 @@ def _toy_plain(cfg, w, tokens):
                 kv_of[idx] = (k, v)
             else:
                 k, v = kv_of[cache_of]
-            a = P.linear(P.attention(q, k, v).reshape(T, nq * d), w[p + "attn.o"])
+            a = P.linear(P.attention(q, k, v, window=windows[l]).reshape(T, nq * d), w[p + "attn.o"])
         else:
             s = np.zeros(H)
             a = np.zeros((T, H))
@@ -274,3 +276,51 @@ def test_toy_architecture_with_a_state_mixer_registers_builds_and_steps():
     got = r.step([StepEntry(2, seqs[1][:9], 0, range(9))]).cpu().numpy()
     assert np.abs(got - refs[1][:9]).max() / np.abs(refs[1]).max() < 3e-5
     assert r.manager.check() == ""
+
+
+TOY_WINDOWED = {"architectures": ["ToyForCausalLM"], "hidden_size": 48, "vocab_size": 97, "inter": 80, "eps": 1e-5,
+                "heads": 4, "kv_heads": 2, "head_dim": 16, "max_pos": 96, "decay": 0.8,
+                # a layer that reads only its newest 9 keys beside a layer that reads them all:
+                # two cache groups, each with pages and block tables of its own
+                "mixers": ["attention", "attention", "attention"], "windows": [9, None, 9],
+                "schedule": [[0, None], [1, None], [2, None]]}
+
+
+def test_windowed_and_full_layers_have_page_groups_of_their_own():
+    """A model whose layers differ in what they keep: the window group gives pages back as
+    the window passes them while the full group keeps all; logits stay right through
+    portions, single tokens and the window's edge, in a pool far smaller than the sequence
+    for the window group."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+    _register_toy()
+    d = tempfile.mkdtemp(prefix="kvb200_toyw_")
+    write_random_model(d, TOY_WINDOWED, seed=6, std=0.2)
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    for dtype, tol in (("float32", 3e-5), ("bfloat16", 4e-2)):
+        r = ModelRunner(d, EngineConfig(dtype=dtype, page_size=4, num_pages=24, max_num_seqs=2,
+                                        max_num_batched_tokens=64, max_model_len=96, use_cuda_graphs=False))
+        m = r.manager
+        assert m.num_groups() == 2
+        groups = {m.group(g).window: g for g in range(2)}
+        gw, gf = groups[9], groups[0]
+        assert r.cache.group_entries[gw] == 2 and r.cache.group_entries[gf] == 1
+        seq = np.random.default_rng(8).integers(0, 97, 90).tolist()
+        ref = _toy_plain(TOY_WINDOWED, w, seq)
+        scale = np.abs(ref).max()
+        pos = 0
+        for n in (13, 2, 1, 1, 7, 1, 30, 1, 1, 1, 5, 2, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1):
+            got = r.step([StepEntry(0, seq[pos:pos + n], pos, range(n))]).cpu().numpy()
+            assert np.abs(got - ref[pos:pos + n]).max() / scale < tol, (dtype, pos, n)
+            pos += n
+            # the window group holds at most the window plus the current page; the full group everything
+            held_w = sum(p >= 0 for p in m.block_table(0, gw))
+            held_f = sum(p >= 0 for p in m.block_table(0, gf))
+            assert held_w <= (9 + 3) // 4 + 1 and held_f == -(-pos // 4), (pos, held_w, held_f)
+            assert m.check() == ""
+        assert pos == 87
+        r.check_status()
+        r.release(0)
+        assert m.free_pages(gw) == 24 and m.free_pages(gf) == 24
