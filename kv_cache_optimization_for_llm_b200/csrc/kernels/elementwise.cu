@@ -102,7 +102,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, c
   for (int i = 0; i < kNormVec; ++i) {
     const int g = i * kNormThreads + threadIdx.x;
     if (g < groups) {
-      const float4 ww = *reinterpret_cast<const float4*>(w + 4 * g);
+      const float4 ww = w ? *reinterpret_cast<const float4*>(w + 4 * g) : make_float4(1.f, 1.f, 1.f, 1.f);
       Pack4<T>::store(o + 4 * g, make_float4(v[i].x * inv * ww.x, v[i].y * inv * ww.y, v[i].z * inv * ww.z,
                                              v[i].w * inv * ww.w));
     }
@@ -132,7 +132,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   }
   const float inv = 1.0f / sqrtf(block_sum(ss, warp_part) / (float)H + eps);
   T* o = out + (size_t)b * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(row_cache[i] * inv * w[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(row_cache[i] * inv * (w ? w[i] : 1.0f));
 }
 
 KVB_EXPORT int kvb_add_rmsnorm(float* resid, const void* delta, const float* w, void* out,

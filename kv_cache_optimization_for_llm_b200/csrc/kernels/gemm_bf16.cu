@@ -119,10 +119,24 @@ __device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
 //   EPI_SWIGLU    the weight rows come in blocks of 128: 64 gate features, then the 64 up
 //                 features of the same indices; out[m, 64 t + j] = silu(gate) * up
 //                 (upstream: a kernel of its own after the product, base/src/kernels.cu:45-52)
-// (Adding into the residual and normalising in the block that finishes last was tried as a
-// third form and measured slower than the separate add+norm kernel: the serial tail of
-// one block costs more than the launch it saves.)
-enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+//   EPI_RESIDUAL  resid[m, n] += sum, in float32 and in place (every element has one owner);
+//                 xb[m, n] = bfloat16(new resid[m, n]), the rows of the product that reads the
+//                 residual next; and sumsq[m, tile] = the sum of the squares of the new
+//                 resid[m, n] over the tile's 128 features, added up in a fixed order.
+// Row scale (x_sumsq != nullptr), with any epilogue but EPI_RESIDUAL: the finished sum of
+// row m is multiplied by rsqrt(sum_p x_sumsq[m, p] / K + eps) first.  With the RMSNorm's
+// weight multiplied into the columns of W beforehand, a product over the bare residual
+// rows (xb) scaled so is the product over the normalised rows:
+//   sum_k (r[m,k] * rstd[m] * g[k]) * W[n,k]  =  rstd[m] * sum_k r[m,k] * (g[k] * W[n,k]),
+// so the add and the norm between two products need no kernel of their own (upstream: two
+// kernels, base/src/kernels.cu:10-43), and nothing of them lies on the path between the
+// end of one product and the first multiplication of the next: the partial sums are
+// read by the two warps that have no other work while the products run.
+// (Two other forms were tried and measured slower than the separate add+norm kernel:
+// adding and normalising in the block that finishes last, whose serial tail costs more
+// than the launch it saves, and normalising the float32 rows while loading them, which
+// puts two to three microseconds of loads in front of the first multiplication.)
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2 };
 
 struct Params {
   int M, N, K, MP;            // MP: rows padded to the UMMA N extent
@@ -133,6 +147,13 @@ struct Params {
   void* out;                  // [M, N]; EPI_SWIGLU: [M, N/2]
   int epilogue;               // EPI_*
   int fin_bytes;              // shared memory for the rows' final sums (EPI_SWIGLU)
+  float* resid;               // EPI_RESIDUAL: [M, ld_resid] float32, updated in place
+  int ld_resid;
+  __nv_bfloat16* xb_out;      // EPI_RESIDUAL: [M, N] bfloat16 copy of the new residual rows
+  float* sumsq_out;           // EPI_RESIDUAL: [M, tiles along N]
+  const float* x_sumsq;       // row scale: [M, x_parts] partial sums of squares of the rows' source, or nullptr
+  int x_parts;
+  float eps;
   int* status;
   unsigned long long* trace;  // optional [blocks, 8] nanosecond stamps of the phases of each block (profiling)
 };
@@ -164,6 +185,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   unsigned long long* accum = empty + p.stages;
   unsigned* tmem_holder = reinterpret_cast<unsigned*>(accum + 1);
   int* flags = reinterpret_cast<int*>(tmem_holder + 1);  // [0]: abort, [1]: this block reduces the splits
+  float* rstd = reinterpret_cast<float*>(flags + 2);     // [16] row scale
 
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -235,6 +257,30 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   // ---- epilogue: all four warps (the accumulator depends on rows loaded after pdl_wait;
   // the explicit wait also covers blocks that had no k tile)
   pdl_wait();
+  if (p.x_sumsq && warp >= 2) {
+    // Row scale: warps 2 and 3 have nothing else to do while the products run.  Lane pairs
+    // share a row; each thread adds up the parts in their order (both get the same sum).
+    const int r = (tid - 64) >> 2;
+    if (r < 16) {
+      float ss = 0.f;
+      if (r < p.M) {
+        const float* src = p.x_sumsq + (size_t)r * p.x_parts;
+        int q = 0;
+        for (; q + 4 <= p.x_parts; q += 4) {        // four loads in flight, added in order
+          const float a0 = src[q], a1 = src[q + 1], a2 = src[q + 2], a3 = src[q + 3];
+          ss = (((ss + a0) + a1) + a2) + a3;
+        }
+        for (; q < p.x_parts; ++q) ss += src[q];
+      }
+      if ((tid & 3) == 0) rstd[r] = rsqrtf(ss / (float)p.K + p.eps);
+    }
+  }
+  if (p.epilogue == EPI_RESIDUAL && n0 + tid < p.N) {
+    // the residual values this thread is going to add to: on their way while the products run
+    const int step = p.splits > 1 ? p.splits : 1;
+    for (int m = p.splits > 1 ? (int)blockIdx.y : 0; m < p.M; m += step)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(p.resid + (size_t)m * p.ld_resid + n0 + tid));
+  }
   bool good = true;
   if (my_tiles > 0) good = mbar_wait(accum, 0);
   if (!good) atomicExch(&flags[0], 1);
@@ -246,9 +292,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   const int n = n0 + warp * 32 + lane;           // the feature this thread holds
   // What this block does with the final sum of (row m, its j-th own row, this thread's feature).
+  const bool scaled = p.x_sumsq != nullptr;
   auto emit = [&](int m, int j, float val) {
+    if (scaled) val *= rstd[m];
     if (p.epilogue == EPI_SWIGLU) {
       fin[j * TILE_N + tid] = val;
+    } else if (p.epilogue == EPI_RESIDUAL) {
+      float nv = 0.f;
+      if (n < p.N) {
+        float* r = p.resid + (size_t)m * p.ld_resid + n;
+        nv = *r + val;
+        *r = nv;
+        p.xb_out[(size_t)m * p.N + n] = __float2bfloat16_rn(nv);
+      }
+      float sq = nv * nv;                           // lanes in a fixed tree, then the four warps in order
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (lane == 0) fin[j * 4 + warp] = sq;
     } else if (n < p.N) {
       if (p.out_f32) {
         reinterpret_cast<float*>(p.out)[(size_t)m * p.N + n] = val;
@@ -294,6 +354,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // Every block of the cluster comes here, aborted or not: the barrier is collective.
     // After it all partials have arrived and nobody touches a peer's memory any more.
     cluster_sync_all();
+    if (tid == 0) stamp(p, 7);   // the cluster has met
     own_first = (int)blockIdx.y;
     own_step = p.splits;
     if (!aborted) {
@@ -317,6 +378,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
       }
     }
+  }
+  if (p.epilogue == EPI_RESIDUAL && !aborted) {
+    __syncthreads();
+    const int m = own_first + tid * own_step;       // thread j finishes the block's j-th own row
+    if (tid < 16 && m < p.M)
+      p.sumsq_out[(size_t)m * gridDim.x + blockIdx.x] =
+          ((fin[tid * 4] + fin[tid * 4 + 1]) + fin[tid * 4 + 2]) + fin[tid * 4 + 3];
   }
   if (aborted) {
     // give copies that may still be in flight time to land before the block ends
@@ -406,17 +474,18 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
   return 0;
 }
 
-// C[M,N] = X[M,K] . W[N,K]^T, bfloat16 operands (ldx, ldw in elements, multiples of 8),
-// C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
-// address is stable (a captured graph), so its tensor map may be cached as the
-// weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
-// block (profiling only).
-// epilogue (see EPI_*): 0 store; 1 SwiGLU on row-interleaved weights, out is bfloat16
-// [M, N/2], N a multiple of 128, M <= 16.
-// Uses no memory beyond its operands.
-KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
-                               int K, int x_is_static, int epilogue, int* status, unsigned long long* trace,
-                               cudaStream_t stream) {
+namespace {
+
+struct Extras {
+  // row scale
+  const float* x_sumsq = nullptr; int x_parts = 0; float eps = 0.f;
+  // EPI_RESIDUAL
+  float* resid = nullptr; int ld_resid = 0; __nv_bfloat16* xb_out = nullptr; float* sumsq_out = nullptr;
+};
+
+int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N, int K,
+                       int x_is_static, int epilogue, const Extras& ex, int* status, unsigned long long* trace,
+                       cudaStream_t stream) {
   int splits, tiles;
   const int rc = kvb_gemm_skinny_plan(M, N, K, &splits, &tiles);
   if (rc) return rc;
@@ -429,11 +498,16 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   p.k_tiles = (K + TILE_K - 1) / TILE_K;
   p.splits = splits;
   p.out_f32 = out_f32; p.out = out; p.status = status; p.trace = trace;
-  if (epilogue < EPI_STORE || epilogue > EPI_SWIGLU) return KVB_ERR_BAD_SIZE;
+  if (epilogue < EPI_STORE || epilogue > EPI_RESIDUAL) return KVB_ERR_BAD_SIZE;
   if (epilogue != EPI_STORE && (M > 16 || out_f32)) return KVB_ERR_BAD_SIZE;
   if (epilogue == EPI_SWIGLU && (N % TILE_N)) return KVB_ERR_BAD_SIZE;
+  if (epilogue == EPI_RESIDUAL && (!ex.resid || !ex.sumsq_out || !ex.xb_out || ex.ld_resid < N || ex.x_sumsq))
+    return KVB_ERR_BAD_SIZE;
+  if (ex.x_sumsq && (M > 16 || ex.x_parts < 1)) return KVB_ERR_BAD_SIZE;
   p.epilogue = epilogue;
-  p.fin_bytes = epilogue == EPI_SWIGLU ? MP * TILE_N * 4 : 0;
+  p.resid = ex.resid; p.ld_resid = ex.ld_resid; p.xb_out = ex.xb_out; p.sumsq_out = ex.sumsq_out;
+  p.x_sumsq = ex.x_sumsq; p.x_parts = ex.x_parts; p.eps = ex.eps;
+  p.fin_bytes = epilogue == EPI_SWIGLU ? MP * TILE_N * 4 : epilogue == EPI_RESIDUAL ? 16 * 4 * 4 : 0;
   const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
   // two blocks per SM while the stages stay deep enough, one block otherwise
   const int budget = MP <= 64 ? 108 * 1024 : 200 * 1024;
@@ -448,7 +522,7 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   if (stages > per) stages = per;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 1) * 8 + 16;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 1) * 8 + 16 + 64;
   CUtensorMap mw, mx;
   int e = cached_map(&mw, w, N, K, ldw, TILE_N);
   if (e) return e;
@@ -479,4 +553,39 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
   cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<0>, mw, mx, p);
   if (le != cudaSuccess) return (int)le;
   return kvb_launch_result();
+}
+
+}  // namespace
+
+// C[M,N] = X[M,K] . W[N,K]^T, bfloat16 operands (ldx, ldw in elements, multiples of 8),
+// C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
+// address is stable (a captured graph), so its tensor map may be cached as the
+// weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
+// block (profiling only).
+// epilogue (see EPI_*): 0 store; 1 SwiGLU on row-interleaved weights, out is bfloat16
+// [M, N/2], N a multiple of 128, M <= 16.
+// Uses no memory beyond its operands.
+KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
+                               int K, int x_is_static, int epilogue, int* status, unsigned long long* trace,
+                               cudaStream_t stream) {
+  if (epilogue == EPI_RESIDUAL) return KVB_ERR_BAD_SIZE;
+  return gemm_skinny_launch(x, ldx, w, ldw, out, out_f32, M, N, K, x_is_static, epilogue, Extras(), status, trace,
+                            stream);
+}
+
+// The same product with the residual stream's add and RMSNorm folded around it, M <= 16.
+//  - x_sumsq != nullptr (row scale): row m of the result is multiplied by
+//    rsqrt(sum_p x_sumsq[m, p] / K + eps) before the epilogue (0 or 1) sees it; x holds the
+//    bare residual rows in bfloat16 and W has the norm's weight multiplied into its columns.
+//  - epilogue 2 (EPI_RESIDUAL): resid[M, ld_resid] += X . W^T in place, xb_out[M, N] gets the
+//    new rows in bfloat16 and sumsq_out[M, ceil(N/128)] their partial sums of squares; out unused.
+KVB_EXPORT int kvb_gemm_skinny_fused(const void* x, int ldx, const void* w, int ldw, void* out, int M, int N, int K,
+                                     int x_is_static, int epilogue, const float* x_sumsq, int x_parts, float eps,
+                                     float* resid, int ld_resid, void* xb_out, float* sumsq_out, int* status,
+                                     unsigned long long* trace, cudaStream_t stream) {
+  Extras ex;
+  ex.x_sumsq = x_sumsq; ex.x_parts = x_parts; ex.eps = eps;
+  ex.resid = resid; ex.ld_resid = ld_resid; ex.xb_out = reinterpret_cast<__nv_bfloat16*>(xb_out);
+  ex.sumsq_out = sumsq_out;
+  return gemm_skinny_launch(x, ldx, w, ldw, out, 0, M, N, K, x_is_static, epilogue, ex, status, trace, stream);
 }

@@ -107,10 +107,11 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``resid += delta`` (when given, in float32, in place unless ``rows`` selects),
-    then RMSNorm of the sum times ``weight``; ``rows`` (int32) picks the rows to
+    then RMSNorm of the sum times ``weight`` (no weight: ``None``); ``rows`` (int32) picks the rows to
     produce, in order, leaving ``resid`` untouched."""
-    _need_cuda(resid, weight)
-    assert resid.dtype == torch.float32 and weight.dtype == torch.float32 and resid.is_contiguous()
+    _need_cuda(resid)
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == resid.shape[1])
     T, H = resid.shape
     n = T if rows is None else rows.numel()
     out = torch.empty((n, H), dtype=out_dtype, device=resid.device)
@@ -191,16 +192,66 @@ def kernel_status(device) -> torch.Tensor:
     return t
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+class Folded:
+    """What a product hands on in place of its output once it has added that output into
+    the float32 residual itself: ``xb``, the new residual rows in bfloat16, and ``sumsq``
+    [rows, parts], partial sums of their squares, from which the next norm's 1/rms follows."""
+    __slots__ = ("xb", "sumsq")
+
+    def __init__(self, xb: torch.Tensor, sumsq: torch.Tensor):
+        self.xb, self.sumsq = xb, sumsq
+
+
+class PendingNorm:
+    """A weightless RMSNorm that has not been carried out (the norm's weight has been
+    multiplied into the matrices that read its result): the float32 rows, their bfloat16
+    copy and partial sums of squares, and eps.  ``linear`` and ``linear_swiglu`` take it in
+    place of a tensor: they multiply the bare rows and scale each row of the result by its
+    1/rms.  ``materialize`` runs the norm as a kernel of its own for everything else."""
+    __slots__ = ("resid", "xb", "sumsq", "eps", "dtype")
+
+    def __init__(self, resid, xb, sumsq, eps, dtype):
+        self.resid, self.xb, self.sumsq, self.eps, self.dtype = resid, xb, sumsq, eps, dtype
+
+    @property
+    def shape(self):
+        return self.resid.shape
+
+    def materialize(self) -> torch.Tensor:
+        return add_rmsnorm(self.resid, None, None, self.eps, self.dtype)
+
+
+FUSED_NORM = __import__('os').environ.get('KVB200_FUSED_NORM', '1') != '0'
+
+
+def fused_norm_rows(rows: int, dtype: torch.dtype) -> bool:
+    """Whether products over ``rows`` rows fold the residual add and the norm into themselves."""
+    return FUSED_NORM and dtype == torch.bfloat16 and rows <= min(SKINNY_MAX_ROWS, FUSED_EPILOGUE_MAX_ROWS)
+
+
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Optional[torch.Tensor] = None):
     """``x . w^T`` with ``w`` [out, in].
     float32: this package's FMA kernel (true 32-bit).
-    bfloat16, up to 256 rows (decode and short portions): this package's tcgen05/TMA
+    bfloat16, few rows (decode and short portions): this package's tcgen05/TMA
     kernel, which streams the weights.  bfloat16 with more rows (long prompt portions):
-    the library product, float32 accumulation, as upstream's cublasGemmEx."""
+    the library product, float32 accumulation, as upstream's cublasGemmEx.
+
+    ``x`` may be a :class:`PendingNorm`.  ``into``: a float32 residual [rows, out] the
+    caller is going to add the result to; where the tensor-core kernel can, it adds the
+    product there itself and a :class:`Folded` comes back instead of a tensor."""
+    if isinstance(x, PendingNorm):
+        if into is None and fused_norm_rows(x.xb.shape[0], x.dtype) and w.dtype == torch.bfloat16:
+            return gemm_skinny_fused(x.xb, w, kernel_status(w.device), row_scale=x,
+                                     x_is_static=torch.cuda.is_current_stream_capturing())
+        x = x.materialize()
     _need_cuda(x, w)
     M, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and x.dtype == w.dtype
+    if (into is not None and fused_norm_rows(M, x.dtype) and _skinny_ok(x, 16) and N % 8 == 0
+            and into.dtype == torch.float32 and into.shape == (M, N) and into.is_contiguous()):
+        return gemm_skinny_fused(x, w, kernel_status(w.device), into=into,
+                                 x_is_static=torch.cuda.is_current_stream_capturing())
     if x.dtype == torch.float32:
         assert x.stride(1) == 1 and w.stride(1) == 1
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
@@ -227,6 +278,14 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, block: int) -> torch.T
     one kernel (the activation is the product's epilogue); otherwise product, then
     activation kernel."""
     I = gate_up.shape[0] // 2
+    if isinstance(x, PendingNorm):
+        if fused_norm_rows(x.xb.shape[0], x.dtype) and gate_up.dtype == torch.bfloat16:
+            st, static = kernel_status(gate_up.device), torch.cuda.is_current_stream_capturing()
+            if block == 64 and gate_up.shape[0] % 128 == 0:
+                return gemm_skinny_fused(x.xb, gate_up, st, row_scale=x, epilogue="swiglu", x_is_static=static)
+            return silu_mul(gemm_skinny_fused(x.xb, gate_up, st, row_scale=x, x_is_static=static),
+                            block=block if block != I else None)
+        x = x.materialize()
     if block == 64 and _skinny_ok(x, min(SKINNY_MAX_ROWS, FUSED_EPILOGUE_MAX_ROWS)) \
             and gate_up.shape[0] % 128 == 0:
         return gemm_skinny(x, gate_up, x.dtype, kernel_status(x.device),
@@ -470,3 +529,43 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
         raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
     _check(rc, "gemm_skinny")
     return out
+
+
+def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, row_scale: Optional[PendingNorm] = None,
+                      into: Optional[torch.Tensor] = None, epilogue: str = "store", x_is_static: bool = False,
+                      trace: Optional[torch.Tensor] = None):
+    """The skinny product (up to 16 rows) with the residual stream's add and RMSNorm folded around it.
+
+    ``row_scale``: every row of ``x . w^T`` is multiplied by the 1/rms that follows from the
+    pending norm's partial sums (``x`` is then its bare bfloat16 rows, and ``w`` has the
+    norm's weight multiplied into its columns).  ``into``: the product is added into this
+    float32 residual in place and a :class:`Folded` is returned; otherwise the product
+    (``epilogue`` "store" or "swiglu") as a bfloat16 tensor."""
+    _need_cuda(x, w)
+    N, K = w.shape
+    M = x.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    assert x.shape[1] == K and M <= 16
+    ss, parts, eps = None, 0, 0.0
+    if row_scale is not None:
+        ss, eps = row_scale.sumsq, row_scale.eps
+        assert into is None and ss.dtype == torch.float32 and ss.is_contiguous() and ss.shape[0] == M
+        parts = ss.shape[1]
+    out = sumsq = xb = None
+    if into is not None:
+        assert epilogue == "store" and into.dtype == torch.float32 and into.shape == (M, N) and into.stride(1) == 1
+        code = 2
+        sumsq = torch.empty((M, -(-N // 128)), dtype=torch.float32, device=x.device)
+        xb = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        code = {"store": 0, "swiglu": 1}[epilogue]
+        out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.bfloat16, device=x.device)
+    rc = lib("gemm_bf16").kvb_gemm_skinny_fused(
+        _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(M), c_int(N), c_int(K),
+        c_int(1 if x_is_static else 0), c_int(code), _p(ss), c_int(parts), c_float(eps),
+        _p(into), c_int(into.stride(0) if into is not None else 0), _p(xb), _p(sumsq), _p(status), _p(trace),
+        _stream())
+    if rc == -2:
+        raise KernelError(f"gemm_skinny_fused refuses M={M}, N={N}, K={K}, epilogue {epilogue}")
+    _check(rc, "gemm_skinny_fused")
+    return Folded(xb, sumsq) if into is not None else out

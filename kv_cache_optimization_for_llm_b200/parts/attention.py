@@ -56,14 +56,21 @@ class GroupedQueryAttention(Part):
         if pos is not None:
             self.position = lookup("position", pos.kind)(pos.params, {}, ctx)
 
+    fuses_residual = True
+
+    def fold_input_scale(self, scale):
+        """Multiplies ``scale`` [hidden] (the weight of the norm in front) into the input
+        columns of the q, k, v matrix, so that the norm itself can go without."""
+        self.qkv = (self.qkv.float() * scale.float()[None, :]).to(self.qkv.dtype).contiguous()
+
     def cache_spec(self):
         return PagedKVSpec(self.nkv, self.d, self.window)
 
-    def forward(self, x, batch, cache):
+    def forward(self, x, batch, cache, into=None):
         qkv = ops.linear(x, self.qkv)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rot = self.position.rotary_dim if self.position is not None else 0
         table = batch.block_tables[cache.group]
         a = ops.attention_step(qkv, cache.k, cache.v, cache.write, table, batch, self.nq, self.nkv, self.d,
                                self.scale, self.window, self.ctx.max_positions, cos, sin, rot)
-        return ops.linear(a, self.o)
+        return ops.linear(a, self.o, into=into)

@@ -11,6 +11,9 @@ nothing of the model it sits in.  Interfaces by family:
 * feed_forward:  ``forward(x, batch) -> delta``
 * position:      whatever its mixer uses (rope: ``tables() -> (cos, sin)``)
 * block:         ``forward(residual, delta, batch, cache) -> (residual, delta)``
+* a mixer or feed-forward may set ``fuses_residual = True``; it then has
+  ``fold_input_scale(vector)``, and its ``forward`` also takes ``into=residual`` and may get
+  ``x`` as an ``ops.PendingNorm`` (see the prenorm block)
 * embedding:     ``forward(batch) -> residual``  (float32 [T, hidden])
 * head:          ``forward(x) -> logits``  (float32 [rows, vocab])
 """

@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import torch
+
 from .base import Part
 from .registry import register
 
@@ -12,15 +14,32 @@ class PreNormBlock(Part):
 
     The float32 residual travels with the branch output that has not been added
     yet: each norm adds the pending ``delta`` first, so add and norm are one kernel,
-    and the block hands its feed-forward output on as the next pending delta."""
+    and the block hands its feed-forward output on as the next pending delta.
+
+    A mixer or feed-forward with ``fuses_residual = True`` goes one step further (bfloat16
+    only; the 32-bit path keeps every formula as it stands).  When the block is built, the
+    part multiplies the weight of the norm in front of it into its own input matrices
+    (``fold_input_scale``) and the norm becomes weightless.  ``forward`` then may get ``x`` as
+    an ``ops.PendingNorm``, carried out by the part's first product, and gets the residual as
+    ``into=``, which its last product may add to itself, returning an ``ops.Folded``."""
 
     def __init__(self, mixer, mixer_norm, feed_forward, ff_norm):
         self.mixer, self.mixer_norm = mixer, mixer_norm
         self.feed_forward, self.ff_norm = feed_forward, ff_norm
+        for part, norm in ((mixer, mixer_norm), (feed_forward, ff_norm)):
+            if (getattr(part, "fuses_residual", False) and part.ctx.dtype == torch.bfloat16
+                    and hasattr(norm, "give_up_weight") and norm.weight is not None):
+                part.fold_input_scale(norm.give_up_weight())
 
     def forward(self, residual, delta, batch, cache):
-        x = self.mixer_norm.forward(residual, delta)
-        a = self.mixer.forward(x, batch, cache)
-        x = self.ff_norm.forward(residual, a)
-        f = self.feed_forward.forward(x, batch)
+        if getattr(self.mixer, "fuses_residual", False):
+            x = self.mixer_norm.forward(residual, delta, lazy=True)
+            a = self.mixer.forward(x, batch, cache, into=residual)
+        else:
+            a = self.mixer.forward(self.mixer_norm.forward(residual, delta), batch, cache)
+        if getattr(self.feed_forward, "fuses_residual", False):
+            x = self.ff_norm.forward(residual, a, lazy=True)
+            f = self.feed_forward.forward(x, batch, into=residual)
+        else:
+            f = self.feed_forward.forward(self.ff_norm.forward(residual, a), batch)
         return residual, f

@@ -41,6 +41,13 @@ class SwiGLU(Part):
                 .reshape(2 * inter, h).contiguous()
         self.down = weights["down"]
 
-    def forward(self, x, batch):
+    fuses_residual = True
+
+    def fold_input_scale(self, scale):
+        """Multiplies ``scale`` [hidden] (the weight of the norm in front) into the input
+        columns of the gate and up matrix, so that the norm itself can go without."""
+        self.gate_up = (self.gate_up.float() * scale.float()[None, :]).to(self.gate_up.dtype).contiguous()
+
+    def forward(self, x, batch, into=None):
         a = ops.linear_swiglu(x, self.gate_up, self.block)
-        return ops.linear(a, self.down)
+        return ops.linear(a, self.down, into=into)

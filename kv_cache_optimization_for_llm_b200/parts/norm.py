@@ -28,5 +28,16 @@ class RMSNorm(Part):
         self.eps = float(params["eps"])
         self.weight = weights["weight"]
 
-    def forward(self, residual, delta=None, rows=None):
+    def give_up_weight(self):
+        """Hands the weight to a part that multiplies it into its own matrices
+        (``fold_input_scale``); the norm is weightless from then on."""
+        w, self.weight = self.weight, None
+        return w
+
+    def forward(self, residual, delta=None, rows=None, lazy=False):
+        if isinstance(delta, ops.Folded):
+            # the branch before this norm has added its output itself and left the sums of squares
+            if lazy and rows is None and self.weight is None:
+                return ops.PendingNorm(residual, delta.xb, delta.sumsq, self.eps, self.ctx.dtype)
+            delta = None
         return ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.ctx.dtype, rows)

@@ -133,3 +133,43 @@ def test_long_decoding_and_first_tokens(dtype, tol):
         worst = max(worst, np.abs(got - ref[i:i + 1]).max() / scale)
     r.check_status()
     assert worst < tol, worst
+
+
+@pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
+def test_norm_weights_far_from_one(name):
+    """bfloat16: the layers' norm weights are multiplied into the matrices behind them and,
+    for steps of few tokens, the add and the norm happen inside the products.  With norm
+    weights spread over 0.25 .. 4 a weight that went missing, was applied twice or landed on
+    the wrong matrix shows at once: in one step of many tokens (separate norm kernel), in
+    steps of a few tokens and token by token, against the plain implementation."""
+    import json, os, shutil, tempfile
+    import torch
+    from kv_cache_optimization_for_llm_b200 import EngineConfig
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    from kv_cache_optimization_for_llm_b200.weights.safetensors_io import read_tensors, write_tensors
+    src = model_dir(name, "bfloat16")
+    d = tempfile.mkdtemp(prefix="kvb200_norms_")
+    try:
+        shutil.copy(os.path.join(src, "config.json"), d)
+        tensors = read_tensors(os.path.join(src, "model.safetensors"))
+        g = torch.Generator().manual_seed(5)
+        for k, t in tensors.items():
+            if "norm" in k:
+                tensors[k] = (2.0 ** (4 * torch.rand(t.shape, generator=g) - 2)).to(t.dtype)
+        write_tensors(os.path.join(d, "model.safetensors"), tensors)
+        cfg, w = P.read_model_dir(d)
+        seq = _prompts(cfg, [70], 23)[0]
+        ref = P.forward(cfg, w, seq)
+        scale = np.abs(ref).max()
+        r = ModelRunner(d, EngineConfig(dtype="bfloat16", page_size=16, num_pages=12, max_num_seqs=2,
+                                        max_num_batched_tokens=64, max_model_len=96))
+        got = [r.step([StepEntry(0, seq[:40], 0, list(range(40)))]).cpu().numpy()]      # many rows: library product
+        got.append(r.step([StepEntry(0, seq[40:52], 40, list(range(12)))]).cpu().numpy())  # few rows: folded
+        for i in range(52, 70):
+            got.append(r.step([StepEntry(0, [seq[i]], i, [0])]).cpu().numpy())
+        r.check_status()
+        got = np.concatenate(got)
+        assert np.abs(got - ref).max() / scale < 4e-2
+    finally:
+        shutil.rmtree(d)

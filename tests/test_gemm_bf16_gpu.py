@@ -79,3 +79,88 @@ def test_swiglu_epilogue(M, I, K):
     assert torch.equal(fused, ops.linear_swiglu(x, inter, 64))
     unfused = ops.silu_mul(ops.gemm_skinny(x, inter, torch.bfloat16, st), block=64)
     assert (unfused.double() - ref).abs().max().item() < 2 * tol   # gate and up rounded to bfloat16 in between
+
+
+# ---- the residual stream folded into the products: add in the epilogue, 1/rms as a row scale
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2048, 2048), (8, 2048, 8192), (5, 200, 72), (16, 1000, 520),
+                                   (3, 96, 1024)])
+def test_residual_epilogue(M, N, K):
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = _bf(torch.randn(M, K, generator=g, device="cuda"))
+    w = _bf(torch.randn(N, K, generator=g, device="cuda") / K ** 0.5)
+    resid0 = torch.randn(M, N, generator=g, device="cuda") * 3
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    resid = resid0.clone()
+    folded = ops.gemm_skinny_fused(x, w, st, into=resid)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and isinstance(folded, ops.Folded)
+    ref = resid0.double() + x.double() @ w.double().t()
+    scale = ref.abs().max().item()
+    assert (resid.double() - ref).abs().max().item() < 2e-5 * scale     # float32 sum, no bfloat16 rounding between
+    assert torch.equal(folded.xb, resid.to(torch.bfloat16))              # the bfloat16 copy is the new residual, rounded once
+    # the partial sums cover every feature once: together they are the squared norm of the new rows
+    assert folded.sumsq.shape == (M, -(-N // 128))
+    total = folded.sumsq.double().sum(dim=1)
+    want = (resid.double() ** 2).sum(dim=1)
+    assert ((total - want).abs() / want).max().item() < 1e-5
+    # each part is its own tile's sum
+    t = min(N, 128)
+    assert ((folded.sumsq[:, 0].double() - (resid[:, :t].double() ** 2).sum(dim=1)).abs() / want).max().item() < 1e-5
+    # a row's result does not depend on the rows beside it
+    if M > 1:
+        r2 = resid0[M - 1:].clone()
+        f2 = ops.gemm_skinny_fused(x[M - 1:].contiguous(), w, st, into=r2)
+        assert torch.equal(r2, resid[M - 1:]) and torch.equal(f2.sumsq, folded.sumsq[M - 1:])
+        assert torch.equal(f2.xb, folded.xb[M - 1:])
+
+
+@pytest.mark.parametrize("epilogue", ["store", "swiglu"])
+@pytest.mark.parametrize("M,N,K,parts,eps", [(1, 128, 64, 1, 1e-5), (8, 3072, 2048, 16, 1e-5), (8, 16384, 2048, 16, 1e-6),
+                                             (5, 256, 72, 3, 1e-3), (16, 1024, 520, 5, 1e-5), (16, 16384, 2048, 16, 1e-5),
+                                             (2, 384, 4096, 32, 1e-5), (7, 128, 8192, 64, 1e-5)])
+def test_row_scale(M, N, K, parts, eps, epilogue):
+    """x . w^T with every row scaled by the 1/rms that follows from partial sums of squares."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    resid = torch.randn(M, K, generator=g, device="cuda") * torch.linspace(0.5, 4.0, M, device="cuda")[:, None]
+    xb = _bf(resid)
+    w = _bf(torch.randn(N, K, generator=g, device="cuda") / K ** 0.5)
+    # the row's sum of squares, cut into parts in some uneven way
+    total = (resid.double() ** 2).sum(dim=1)
+    cut = torch.rand(M, parts, generator=g, device="cuda").double() + 0.1
+    sumsq = (cut / cut.sum(dim=1, keepdim=True) * total[:, None]).float().contiguous()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pn = ops.PendingNorm(resid, xb, sumsq, eps, torch.bfloat16)
+    out = ops.gemm_skinny_fused(xb, w, st, row_scale=pn, epilogue=epilogue)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    rstd = 1.0 / torch.sqrt(total / K + eps)
+    ref = (xb.double() @ w.double().t()) * rstd[:, None]
+    if epilogue == "swiglu":
+        ref = ref.view(M, N // 128, 2, 64)
+        gate, up = ref[:, :, 0], ref[:, :, 1]
+        ref = (gate * torch.sigmoid(gate) * up).reshape(M, N // 2)
+    scale = ref.abs().max().item()
+    assert (out.double() - ref).abs().max().item() < 5e-3 * scale      # the output's own bfloat16 rounding
+    # against the separate weightless norm kernel followed by the plain product: the rows are
+    # rounded to bfloat16 before the scale there and after it here
+    sep = ops.gemm_skinny(pn.materialize(), w, torch.bfloat16, st, epilogue=epilogue)
+    assert (out.double() - sep.double()).abs().max().item() < 1e-2 * scale
+    # rows alone give the same bits
+    if M > 1:
+        i = 2 % M
+        one = ops.gemm_skinny_fused(xb[i:i + 1].contiguous(), w, st, epilogue=epilogue,
+                                    row_scale=ops.PendingNorm(resid[i:i + 1], xb[i:i + 1], sumsq[i:i + 1].contiguous(),
+                                                              eps, torch.bfloat16))
+        assert torch.equal(one, out[i:i + 1])
+
+
+def test_weightless_norm_kernel():
+    from kv_cache_optimization_for_llm_b200 import ops
+    for H in (2048, 72, 1000):
+        resid = torch.randn(5, H, device="cuda") * 2
+        got = ops.add_rmsnorm(resid.clone(), None, None, 1e-5, torch.float32)
+        want = ops.add_rmsnorm(resid.clone(), None, torch.ones(H, device="cuda"), 1e-5, torch.float32)
+        assert torch.equal(got, want)
