@@ -59,6 +59,7 @@ PYBIND11_MODULE(_kvb_host, m) {
       .value("CACHE_EXHAUSTED", FinishReason::CacheExhausted)
       .value("ABORTED", FinishReason::Aborted);
   m.def("finish_reason_name", &finish_reason_name);
+  m.attr("PENDING_TOKEN") = kPendingToken;
 
   py::class_<PlanEntry>(m, "PlanEntry")
       .def_readonly("id", &PlanEntry::id)
@@ -87,6 +88,9 @@ PYBIND11_MODULE(_kvb_host, m) {
       .def("commit", &Scheduler::commit)
       .def("append_token", &Scheduler::append_token, py::arg("id"), py::arg("token"),
            py::arg("is_stop") = false)
+      .def("mark_pending", &Scheduler::mark_pending)
+      .def("resolve", &Scheduler::resolve, py::arg("id"), py::arg("token"), py::arg("is_stop") = false)
+      .def("has_pending", &Scheduler::has_pending)
       .def("abort", &Scheduler::abort)
       .def("has_unfinished", &Scheduler::has_unfinished)
       .def("num_running", &Scheduler::num_running)

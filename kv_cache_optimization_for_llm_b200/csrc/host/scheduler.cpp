@@ -73,6 +73,11 @@ void Scheduler::finish(Req* r, FinishReason why) {
   if (cache_->has(id)) cache_->release(id);
   running_.erase(std::remove(running_.begin(), running_.end(), id), running_.end());
   waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), id), waiting_.end());
+  if (r->pending) {   // ended before its newest tokens' values arrived: they are dropped
+    r->tokens.resize(r->tokens.size() - r->pending);
+    r->pending = 0;
+    r->closing = false;
+  }
   Req moved = std::move(*r);
   moved.reason = why;
   reqs_.erase(id);
@@ -107,8 +112,8 @@ Plan Scheduler::schedule() {
   size_t i = 0;
   while (i < running_.size()) {
     Req& r = reqs_.at(running_[i]);
-    const int want = portion(r, budget);
-    if (want <= 0) { ++i; continue; }  // budget spent: it waits for the next step
+    const int want = r.closing ? 0 : portion(r, budget);
+    if (want <= 0) { ++i; continue; }  // budget spent (or only waiting for its last token): not in this step
     bool scheduled = true;
     while (!cache_->extend(r.id, r.computed + want)) {
       // Pages ran out.  The latest arrival among the running gives way, this
@@ -143,6 +148,7 @@ Plan Scheduler::schedule() {
   while (!preempted_now && !waiting_.empty() && (int)running_.size() < cfg_.max_num_seqs &&
          budget > 0) {
     Req& r = reqs_.at(waiting_.front());
+    if (r.pending) break;                // its newest token is not known yet: next step
     if (cache_->admit(r.id) < 0) break;  // no state slot free
     const int want = portion(r, budget);
     if (!cache_->extend(r.id, want)) {
@@ -197,6 +203,55 @@ FinishReason Scheduler::append_token(int64_t id, int token, bool is_stop) {
   return FinishReason::None;
 }
 
+void Scheduler::mark_pending(const Plan& plan) {
+  for (const PlanEntry& e : plan.entries) {
+    if (!e.sample) continue;
+    auto it = reqs_.find(e.id);
+    if (it == reqs_.end()) continue;
+    Req& r = it->second;
+    if (r.pending > 1 || r.closing)
+      throw std::logic_error("Scheduler: request " + std::to_string(e.id) + " cannot take another pending token");
+    if (r.computed != (int)r.tokens.size())
+      throw std::logic_error("Scheduler: a token is pending for a request whose prompt is unread");
+    r.tokens.push_back(kPendingToken);
+    ++r.pending;
+    const int generated = (int)r.tokens.size() - r.prompt_len;
+    r.closing = generated >= r.max_tokens || (int)r.tokens.size() >= cfg_.max_model_len;
+  }
+}
+
+FinishReason Scheduler::resolve(int64_t id, int token, bool is_stop) {
+  auto it = reqs_.find(id);
+  if (it == reqs_.end()) return any(id).reason;   // ended meanwhile
+  Req& r = it->second;
+  if (!r.pending) throw std::logic_error("Scheduler: request " + std::to_string(id) + " has no pending token");
+  const size_t at = r.tokens.size() - r.pending;   // the oldest unknown token
+  if (is_stop) {
+    // neither the stop token nor anything sampled after it is kept
+    r.tokens.resize(at);
+    r.pending = 0;
+    r.closing = false;
+    finish(&r, FinishReason::Stop);
+    return FinishReason::Stop;
+  }
+  r.tokens[at] = token;
+  --r.pending;
+  if (r.pending) return FinishReason::None;
+  r.closing = false;
+  const int generated = (int)r.tokens.size() - r.prompt_len;
+  if (generated >= r.max_tokens) { finish(&r, FinishReason::Length); return FinishReason::Length; }
+  if ((int)r.tokens.size() >= cfg_.max_model_len) {
+    finish(&r, FinishReason::ModelLen);
+    return FinishReason::ModelLen;
+  }
+  return FinishReason::None;
+}
+
+bool Scheduler::has_pending(int64_t id) const {
+  auto it = reqs_.find(id);
+  return it != reqs_.end() && it->second.pending > 0;
+}
+
 void Scheduler::abort(int64_t id) {
   auto it = reqs_.find(id);
   if (it == reqs_.end()) return;
@@ -207,7 +262,7 @@ const std::vector<int>& Scheduler::tokens(int64_t id) const { return any(id).tok
 int Scheduler::prompt_len(int64_t id) const { return any(id).prompt_len; }
 std::vector<int> Scheduler::output(int64_t id) const {
   const Req& r = any(id);
-  return std::vector<int>(r.tokens.begin() + r.prompt_len, r.tokens.end());
+  return std::vector<int>(r.tokens.begin() + r.prompt_len, r.tokens.end() - r.pending);
 }
 FinishReason Scheduler::finish_reason(int64_t id) const { return any(id).reason; }
 int Scheduler::preemptions_of(int64_t id) const { return any(id).preemptions; }

@@ -30,9 +30,12 @@ const char* finish_reason_name(FinishReason r);
 struct PlanEntry {
   int64_t id = 0;
   int start = 0;            // position of the first token of this portion
-  std::vector<int> tokens;  // the tokens to run
+  std::vector<int> tokens;  // the tokens to run; kPendingToken stands for a token that was
+                            // sampled on the device and has not reached the host yet
   bool sample = false;      // the portion ends at the request's last known token
 };
+
+constexpr int kPendingToken = -1;
 
 struct Plan {
   std::vector<PlanEntry> entries;
@@ -62,6 +65,20 @@ class Scheduler {
   // Gives a sampled entry its new token.  A stop token ends the request and is not
   // kept.  Returns the reason if the request ended, None otherwise.
   FinishReason append_token(int64_t id, int token, bool is_stop);
+  // Running one step ahead of the host's knowledge of the tokens.  mark_pending: the
+  // committed plan's sampled entries each have a new token on the device whose value
+  // the host does not know yet; it takes its place in the sequence as kPendingToken, so
+  // that the next schedule() can plan the step that reads it.  A request whose pending
+  // token is its last by count (max_tokens, max_model_len) is not scheduled again.
+  // resolve: the value has arrived; same result as append_token.  A request that ended
+  // in between (abort, cache exhausted) ignores it and returns its own reason.  Values
+  // arrive in the order in which the tokens were marked.  schedule() wants at most one
+  // token per request pending (two are, for a moment, between mark_pending of one step and
+  // resolve of the step before it); a request with a pending token that went back to the
+  // queue is admitted again only once the token is known.
+  void mark_pending(const Plan& plan);
+  FinishReason resolve(int64_t id, int token, bool is_stop);
+  bool has_pending(int64_t id) const;
   void abort(int64_t id);
 
   bool has_unfinished() const { return !running_.empty() || !waiting_.empty(); }
@@ -90,6 +107,8 @@ class Scheduler {
     int max_tokens = 0;
     int computed = 0;
     int preemptions = 0;
+    int pending = 0;       // so many kPendingToken at the end of tokens
+    bool closing = false;  // the newest pending token is the last one by count
     FinishReason reason = FinishReason::None;
   };
   const Req& any(int64_t id) const;

@@ -6,13 +6,18 @@
 
 // ---------------------------------------------------------------- embedding
 // residual[t, :] = table[ids[t], :]   (upstream: base/src/kernels.cu:279-287)
+// An id below zero names a token that the sampling kernel of the step before left on the
+// device: -(1 + r) stands for sampled[r] (n_sampled entries), so that a step can be
+// launched before the host has seen the tokens it starts from.
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    const int* __restrict__ sampled, int n_sampled,
                                     float* __restrict__ resid, int H, int V, int* status) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (id < 0 && sampled && -(id + 1) < n_sampled) id = sampled[-(id + 1)];
   if (id < 0 || id >= V) {
     if (threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_BAD_TOKEN);
     for (int i = threadIdx.x; i < H; i += blockDim.x) resid[(size_t)t * H + i] = 0.f;
@@ -22,12 +27,12 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
   for (int i = threadIdx.x; i < H; i += blockDim.x) resid[(size_t)t * H + i] = to_f32(row[i]);
 }
 
-KVB_EXPORT int kvb_embed_gather(const void* table, int dtype, const int* ids, float* resid, int T_,
-                                int H, int V, int* status, cudaStream_t stream) {
+KVB_EXPORT int kvb_embed_gather(const void* table, int dtype, const int* ids, const int* sampled, int n_sampled,
+                                float* resid, int T_, int H, int V, int* status, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(embed_gather_kernel<T>, dim3(T_), dim3(threads), 0, stream,
-                                            (const T*)table, ids, resid, H, V, status)));
+                                            (const T*)table, ids, sampled, n_sampled, resid, H, V, status)));
   return kvb_launch_result();
 }
 

@@ -43,7 +43,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
               const unsigned* __restrict__ seed, const unsigned* __restrict__ key,
               const unsigned* __restrict__ pos, const float* __restrict__ penalty,
               unsigned char* __restrict__ mask_base, const int* __restrict__ slots,
-              int* __restrict__ out_ids) {
+              int* __restrict__ out_ids, const int* __restrict__ status_in, int status_at) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ float s_scan[kSampleThreads];
@@ -134,6 +134,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
     if (s_owner >= 0) chosen = s_idx[1];
   }
   if (tid == 0) {
+    if (row == 0 && status_in) out_ids[status_at] = *status_in;   // the kernels' error word rides along
     out_ids[row] = chosen;
     if (mask != nullptr) mask[chosen] = 1;  // the new token counts as seen from now on
   }
@@ -143,13 +144,16 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
 // temperature == nullptr means greedy for all rows, penalty == nullptr means none.
 // mask_base is [num_slots, V] bytes (1 = the request already produced this token),
 // indexed through slots[row]; it may be nullptr when no row uses a penalty.
+// status_in != nullptr: *status_in (the device word that kernels report errors into) is
+// copied to out_ids[status_at], so that one transfer brings the tokens and the word.
 KVB_EXPORT int kvb_sample(const float* logits, int R, int V, const float* temperature, const unsigned* seed,
                           const unsigned* key, const unsigned* pos, const float* penalty,
-                          unsigned char* mask_base, const int* slots, int* out_ids, cudaStream_t stream) {
+                          unsigned char* mask_base, const int* slots, int* out_ids, const int* status_in,
+                          int status_at, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V < 1) return KVB_ERR_BAD_SIZE;
   sample_kernel<<<R, kSampleThreads, 0, stream>>>(logits, V, temperature, seed, key, pos, penalty, mask_base,
-                                                  slots, out_ids);
+                                                  slots, out_ids, status_in, status_at);
   return kvb_launch_result();
 }
 

@@ -20,7 +20,8 @@ import torch
 class StepEntry:
     """One request's share of a step."""
     request_id: int
-    tokens: Sequence[int]        # the new tokens, in order
+    tokens: Sequence[int]        # the new tokens, in order; -(1 + r) names the token that the
+                                 # sampling kernel of the step before left in row r on the device
     start: int                   # position of tokens[0] in its sequence
     want: Sequence[int] = ()     # indices into ``tokens`` whose logits are asked for
 
@@ -44,6 +45,7 @@ class StepBatch:
     decode_only: bool            # every run is a single token
     status: torch.Tensor         # [1] int32 device word that kernels report into
     host: dict = field(default_factory=dict)  # numpy mirrors of the arrays above
+    sampled: Optional[torch.Tensor] = None    # [n] int32 on the device: what ids below zero refer to
 
 
 class BatchBuilder:
@@ -71,8 +73,14 @@ class BatchBuilder:
             off += (n + 3) // 4 * 4  # keep every array 16-byte aligned
         self.total = off
         use_cuda = self.device.type == "cuda"
-        self.host_buf = torch.zeros(self.total, dtype=torch.int32, pin_memory=use_cuda)
-        self.host_np = self.host_buf.numpy()
+        # Two pinned staging buffers, used in turn: the copy of one step may still be under
+        # way while the next step is written.  Each buffer's event tells when its copy is over.
+        self._staging = []
+        for _ in range(2):
+            buf = torch.zeros(self.total, dtype=torch.int32, pin_memory=use_cuda)
+            self._staging.append({"buf": buf, "np": buf.numpy(),
+                                  "event": torch.cuda.Event() if use_cuda else None, "busy": False})
+        self._turn = 0
         self.dev_buf = torch.zeros(self.total, dtype=torch.int32, device=self.device)
         self.last_h2d_bytes = 0
 
@@ -81,14 +89,18 @@ class BatchBuilder:
         return buf[off:off + (cap if n is None else n)]
 
     def build(self, entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None,
-              pad_reqs_to: int = 0, scratch_page: int = -1, scratch_slot: int = 0) -> StepBatch:
+              pad_reqs_to: int = 0, scratch_page: int = -1, scratch_slot: int = 0,
+              sampled: Optional[torch.Tensor] = None) -> StepBatch:
         """``cache`` is the CacheManager; every entry's pages must already cover
         ``start + len(tokens)``.
 
         ``pad_reqs_to`` > len(entries) appends single-token dummy requests (token 0 at
         position 0, writing to ``scratch_page`` and ``scratch_slot``, which no real
         request owns) so that a decode batch fills a captured graph's fixed shape;
-        their rows follow the real ones and their logits are never read."""
+        their rows follow the real ones and their logits are never read.
+
+        ``sampled``: the device buffer that token ids below zero refer to (see StepEntry);
+        without it such ids are refused."""
         n_real = len(entries)
         if pad_reqs_to > n_real:
             entries = list(entries) + [StepEntry(-1, (0,), 0, ()) for _ in range(pad_reqs_to - n_real)]
@@ -100,7 +112,12 @@ class BatchBuilder:
             raise ValueError(f"a step holds {R} requests, the engine was built for {self.max_reqs}")
         if T > self.max_tokens:
             raise ValueError(f"a step holds {T} tokens, the engine was built for {self.max_tokens}")
-        h = self.host_np
+        stage = self._staging[self._turn]
+        self._turn ^= 1
+        if stage["busy"]:
+            stage["event"].synchronize()
+            stage["busy"] = False
+        h = stage["np"]
         tok = self._view(h, "token_ids", T)
         pos = self._view(h, "positions", T)
         treq = self._view(h, "token_req", T)
@@ -127,7 +144,8 @@ class BatchBuilder:
                 rows.append(t + w)
             t += n
         qs[R] = T
-        if vocab_size is not None and (tok.min() < 0 or tok.max() >= vocab_size):
+        lowest = 0 if sampled is None else -int(sampled.numel())
+        if vocab_size is not None and (tok.min() < lowest or tok.max() >= vocab_size):
             raise ValueError(f"a token id is outside the vocabulary of {vocab_size}")
         lr = self._view(h, "logit_rows", len(rows))
         lr[:] = rows
@@ -147,7 +165,10 @@ class BatchBuilder:
             used = self.offsets[f"bt{g}"][0] + R * self.max_pages[g]
         else:
             used = self.total
-        self.dev_buf[:used].copy_(self.host_buf[:used], non_blocking=True)
+        self.dev_buf[:used].copy_(stage["buf"][:used], non_blocking=True)
+        if stage["event"] is not None:
+            stage["event"].record()
+            stage["busy"] = True
         self.last_h2d_bytes = 4 * used
         d = self.dev_buf
         batch = StepBatch(
@@ -163,5 +184,6 @@ class BatchBuilder:
             decode_only=all(len(e.tokens) == 1 for e in entries),
             status=self.status,
             host={"q_start": qs.copy(), "ctx_len": ctx.copy(), "req_start": rstart.copy()},
+            sampled=sampled,
         )
         return batch

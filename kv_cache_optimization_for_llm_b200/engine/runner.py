@@ -97,6 +97,10 @@ class ModelRunner:
         self.builder = BatchBuilder(self.config.max_num_batched_tokens, self.config.max_num_seqs,
                                     self.cache.max_pages, self.device, self.status)
         self.vocab_size = self.spec.vocab_size
+        # Where the sampling kernel leaves a step's tokens (one per sampled request, in the
+        # step's order; the last entry carries the kernels' error word).  A step whose entries
+        # name tokens as -(1 + row) reads them from here.
+        self.sampled = torch.zeros(self.config.max_num_seqs + 1, dtype=torch.int32, device=self.device)
         # Captured decode steps, by padded batch size.
         self._graphs = {}
         self._graph_pool = None
@@ -115,7 +119,7 @@ class ModelRunner:
         [wanted, vocab] on the device, in the order of the entries and their ``want``."""
         if self.graph_buckets and all(len(e.tokens) == 1 for e in entries):
             return self._run_decode_graph(entries)
-        batch = self.builder.build(entries, self.manager, self.vocab_size)
+        batch = self.builder.build(entries, self.manager, self.vocab_size, sampled=self.sampled[:-1])
         return self.model.forward(batch, self.cache)
 
     def _run_decode_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -127,7 +131,8 @@ class ModelRunner:
         wants = [bool(e.want) for e in entries]
         padded = [StepEntry(e.request_id, e.tokens, e.start, (0,)) for e in entries]
         batch = self.builder.build(padded, self.manager, self.vocab_size, pad_reqs_to=bucket,
-                                   scratch_page=self.cache.scratch_page, scratch_slot=self.cache.scratch_slot)
+                                   scratch_page=self.cache.scratch_page, scratch_slot=self.cache.scratch_slot,
+                                   sampled=self.sampled[:-1])
         got = self._graphs.get(bucket)
         if got is None:
             # Every row's logits are produced; rows are picked after the replay.
@@ -196,10 +201,12 @@ class ModelRunner:
         if self.manager.has(request_id):
             self.manager.release(request_id)
 
-    def check_status(self) -> None:
-        """Raises if a kernel reported an impossible index since the last check
-        (synchronises with the device)."""
-        code = int(self.status.item())
+    def check_status(self, code: Optional[int] = None) -> None:
+        """Raises if a kernel reported an impossible index since the last check.  ``code``:
+        the status word as it came back with a step's tokens; without it the word is read
+        from the device (which synchronises)."""
+        if code is None:
+            code = int(self.status.item())
         if code:
             self.status.zero_()
             raise ops.KernelError(ops.STATUS_TEXT.get(code, f"kernel status {code}"))

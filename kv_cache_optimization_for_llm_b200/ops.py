@@ -92,13 +92,17 @@ def _need_cuda(*ts):
 
 # ------------------------------------------------------------------ elementwise
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
-    """float32 residual rows ``table[ids]``."""
-    _need_cuda(table, ids)
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
+                 sampled: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 residual rows ``table[ids]``.  With ``sampled`` (int32), an id ``-(1 + r)``
+    stands for ``sampled[r]``: a token that is still on the device."""
+    _need_cuda(table, ids, sampled)
+    assert sampled is None or (sampled.dtype == torch.int32 and sampled.is_contiguous())
     V, H = table.shape
     T = ids.numel()
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
-    rc = lib("elementwise").kvb_embed_gather(_p(table), dtype_code(table.dtype), _p(ids), _p(out),
+    rc = lib("elementwise").kvb_embed_gather(_p(table), dtype_code(table.dtype), _p(ids), _p(sampled),
+                                             c_int(0 if sampled is None else sampled.numel()), _p(out),
                                              c_int(T), c_int(H), c_int(V), _p(status), _stream())
     _check(rc, "embed_gather")
     return out
@@ -472,16 +476,19 @@ def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv,
 
 # ------------------------------------------------------------------ sampling
 
-def sample(logits, temperature, seed, key, pos, penalty, mask, slots, out=None) -> torch.Tensor:
+def sample(logits, temperature, seed, key, pos, penalty, mask, slots, out=None, status=None,
+           status_at: int = 0) -> torch.Tensor:
     """One token id per row of float32 ``logits``.  ``temperature`` None: greedy for all
-    rows; ``penalty``/``mask`` None: no repetition penalty."""
+    rows; ``penalty``/``mask`` None: no repetition penalty.  ``status``: the kernels' error
+    word, copied to ``out[status_at]`` so that it travels with the tokens."""
     _need_cuda(logits)
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     R, V = logits.shape
     if out is None:
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
     rc = lib("sampling").kvb_sample(_p(logits), c_int(R), c_int(V), _p(temperature), _p(seed), _p(key),
-                                    _p(pos), _p(penalty), _p(mask), _p(slots), _p(out), _stream())
+                                    _p(pos), _p(penalty), _p(mask), _p(slots), _p(out), _p(status),
+                                    c_int(status_at), _stream())
     _check(rc, "sample")
     return out
 

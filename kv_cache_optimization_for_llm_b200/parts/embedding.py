@@ -26,7 +26,7 @@ class TokenEmbedding(Part):
         self.table = weights["table"]
 
     def forward(self, batch):
-        return ops.embed_gather(self.table, batch.token_ids, batch.status)
+        return ops.embed_gather(self.table, batch.token_ids, batch.status, batch.sampled)
 
 
 @register("head", "linear_head")

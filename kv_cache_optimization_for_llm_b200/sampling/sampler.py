@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -24,19 +24,32 @@ class Sampler:
     The record of tokens a request has produced (for the penalty) lives in the
     request's state slot: one row of bytes per slot, allocated at first use."""
 
-    def __init__(self, vocab_size: int, num_slots: int, device, default_seed: int = 0):
+    def __init__(self, vocab_size: int, num_slots: int, device, default_seed: int = 0,
+                 out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
+        """``out``: the device buffer [num_slots + 1] int32 that receives the tokens, row by row
+        (the step function reads tokens that the host has not seen yet from it); its last
+        entry carries ``status``, the kernels' error word, when one is given."""
         self.vocab_size, self.num_slots = int(vocab_size), int(num_slots)
         self.device = torch.device(device)
         self.default_seed = int(default_seed) & 0xFFFFFFFF
         self.mask = None
+        self.status = status
         cap = self.num_slots
-        # staging for the per-row parameters: temperature, penalty | seed, key, pos | slot
-        self._host_f = torch.zeros((2, cap), dtype=torch.float32, pin_memory=True)
-        self._host_u = torch.zeros((4, cap), dtype=torch.int32, pin_memory=True)
-        self._dev_f = torch.zeros((2, cap), dtype=torch.float32, device=self.device)
-        self._dev_u = torch.zeros((4, cap), dtype=torch.int32, device=self.device)
-        self._out = torch.zeros(cap, dtype=torch.int32, device=self.device)
-        self._out_host = torch.zeros(cap, dtype=torch.int32, pin_memory=True)
+        self._out = out if out is not None else torch.zeros(cap + 1, dtype=torch.int32, device=self.device)
+        assert self._out.numel() == cap + 1 and self._out.dtype == torch.int32
+        # Staging for the per-row parameters (temperature, penalty | seed, key, pos, slot) and
+        # for the tokens on their way back, twice: one set may still be in flight while the
+        # next step is prepared.  Each set's event tells when its transfers are over.
+        self._sets = []
+        for _ in range(2):
+            self._sets.append({
+                "host_f": torch.zeros((2, cap), dtype=torch.float32, pin_memory=True),
+                "host_u": torch.zeros((4, cap), dtype=torch.int32, pin_memory=True),
+                "dev_f": torch.zeros((2, cap), dtype=torch.float32, device=self.device),
+                "dev_u": torch.zeros((4, cap), dtype=torch.int32, device=self.device),
+                "out_host": torch.zeros(cap + 1, dtype=torch.int32, pin_memory=True),
+                "event": torch.cuda.Event(), "busy": False})
+        self._turn = 0
 
     def _ensure_mask(self):
         if self.mask is None:
@@ -51,17 +64,24 @@ class Sampler:
         toks = torch.tensor(list(produced), dtype=torch.int32, device=self.device) if len(produced) else None
         ops.reset_mask(self.mask, slot, toks)
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], keys: Sequence[int],
-               positions: Sequence[int], slots: Sequence[int]) -> List[int]:
-        """``logits`` [R, vocab] float32; row r belongs to the request with ``params[r]``,
-        random-stream key ``keys[r]``, whose new token will sit at ``positions[r]``."""
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], keys: Sequence[int],
+               positions: Sequence[int], slots: Sequence[int]):
+        """Starts the sampling of one step and the transfer of its tokens to the host;
+        returns a handle for :meth:`read`.  ``logits`` [R, vocab] float32; row r belongs to
+        the request with ``params[r]``, random-stream key ``keys[r]``, whose new token will
+        sit at ``positions[r]``.  Token r stays in ``out[r]`` on the device until the next
+        launch."""
         R = logits.shape[0]
-        assert R == len(params) == len(keys) == len(positions) == len(slots)
+        assert R == len(params) == len(keys) == len(positions) == len(slots) and R <= self.num_slots
+        st = self._sets[self._turn]
+        self._turn ^= 1
+        if st["busy"]:
+            st["event"].synchronize()       # the launch before last: long over, unless nobody read it
         if R == 0:
-            return []
+            return (st, 0)
         greedy = all(p.temperature <= 0 for p in params)
         no_pen = all(p.repetition_penalty == 1.0 for p in params)
-        hf, hu = self._host_f.numpy(), self._host_u.numpy().view(np.uint32)
+        hf, hu = st["host_f"].numpy(), st["host_u"].numpy().view(np.uint32)
         for r, p in enumerate(params):
             hf[0, r] = p.temperature
             hf[1, r] = p.repetition_penalty
@@ -69,15 +89,33 @@ class Sampler:
             hu[1, r] = int(keys[r]) & 0xFFFFFFFF
             hu[2, r] = int(positions[r]) & 0xFFFFFFFF
             hu[3, r] = int(slots[r])
-        self._dev_u[:, :R].copy_(self._host_u[:, :R], non_blocking=True)
+        dev_f, dev_u = st["dev_f"], st["dev_u"]
+        dev_u[:, :R].copy_(st["host_u"][:, :R], non_blocking=True)
         if not (greedy and no_pen):
-            self._dev_f[:, :R].copy_(self._host_f[:, :R], non_blocking=True)
+            dev_f[:, :R].copy_(st["host_f"][:, :R], non_blocking=True)
         if not no_pen:
             self._ensure_mask()
-        out = ops.sample(
+        ops.sample(
             logits,
-            None if greedy else self._dev_f[0], self._dev_u[0], self._dev_u[1], self._dev_u[2],
-            None if no_pen else self._dev_f[1], None if no_pen else self.mask, self._dev_u[3],
-            out=self._out)
-        self._out_host[:R].copy_(out[:R], non_blocking=False)
-        return self._out_host[:R].tolist()
+            None if greedy else dev_f[0], dev_u[0], dev_u[1], dev_u[2],
+            None if no_pen else dev_f[1], None if no_pen else self.mask, dev_u[3],
+            out=self._out, status=self.status, status_at=self.num_slots)
+        st["out_host"].copy_(self._out, non_blocking=True)
+        st["event"].record()
+        st["busy"] = True
+        return (st, R)
+
+    def read(self, handle):
+        """Waits for a launch's tokens.  Returns (token ids, kernel status word)."""
+        st, R = handle
+        if R == 0:
+            return [], 0
+        st["event"].synchronize()
+        st["busy"] = False
+        vals = st["out_host"].tolist()
+        return vals[:R], (vals[self.num_slots] if self.status is not None else 0)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], keys: Sequence[int],
+               positions: Sequence[int], slots: Sequence[int]) -> List[int]:
+        """:meth:`launch` and :meth:`read` in one; the tokens only."""
+        return self.read(self.launch(logits, params, keys, positions, slots))[0]

@@ -191,3 +191,97 @@ def test_random_workloads_finish_with_exact_token_counts():
         for i, n in want.items():
             assert len(s.output(i)) == n and s.finish_reason(i) == H.FinishReason.LENGTH
         assert cache.free_pages(0) == pages and cache.free_slots() == 4
+
+
+# ---- running one step ahead: tokens that are on the device but not yet known to the host
+
+def run_ahead(sched, arrivals, token_of, stop, rng):
+    """Drives the scheduler the way the engine does when it runs ahead: the next step is
+    planned (with the placeholder in place of each token that was just sampled) before the
+    values of the previous step's tokens are handed over."""
+    in_flight = None          # sampled entries of the step whose tokens are not known yet
+    steps = 0
+    while arrivals or sched.has_unfinished() or in_flight is not None:
+        if arrivals and rng.random() < 0.5:
+            sched.add(*arrivals.pop(0))
+        plan = sched.schedule()
+        sched.commit(plan)
+        for e in plan.entries:
+            for t in e.tokens[:-1]:
+                assert t != H.PENDING_TOKEN          # only the newest token may be unknown
+        sched.mark_pending(plan)
+        launched = [(e.id, e.start + len(e.tokens)) for e in plan.entries if e.sample]
+        if in_flight is not None:
+            for rid, pos in in_flight:
+                if sched.is_live(rid):
+                    tok = token_of(rid, pos)
+                    sched.resolve(rid, tok, stop is not None and tok == stop)
+        in_flight = launched or None
+        steps += 1
+        assert steps < 5000, "the scheduler stopped making progress"
+    return steps
+
+
+def test_running_ahead_gives_the_same_tokens():
+    """Planning a step before the last step's tokens are known changes no request's output:
+    with stop tokens, a token budget, chunked prompts and a pool so small that requests are
+    dropped and recomputed, every request ends with the same tokens and the same reason as
+    when every token is handed over at once."""
+    token_of = lambda rid, pos: (rid * 31 + pos * 7) % 23
+    for trial in range(40):
+        rng = random.Random(100 + trial)
+        pages = rng.randint(6, 20)
+        kw = dict(pages=pages, page_size=4, slots=4, seqs=rng.randint(1, 4), budget=rng.randint(2, 24),
+                  model_len=rng.choice([80, 24]), chunk=rng.choice([0, 0, 2, 5]))
+        stop = rng.choice([None, 5, 11])
+        reqs = []
+        for i in range(rng.randint(3, 10)):
+            n_prompt = rng.randint(1, min(4 * pages - 8, 20))
+            n_out = rng.randint(1, max(1, min(20, 4 * pages - n_prompt - 1)))
+            reqs.append((i, [rng.randrange(97) for _ in range(n_prompt)], n_out))
+        # every token at once
+        cache_a, a = make(**kw)
+        arrivals, r2 = list(reqs), random.Random(trial)
+        while arrivals or a.has_unfinished():
+            if arrivals and r2.random() < 0.5:
+                a.add(*arrivals.pop(0))
+            run_step(a, token_of, stop)
+        # one step ahead
+        cache_b, b = make(**kw)
+        run_ahead(b, list(reqs), token_of, stop, random.Random(trial))
+        for i, _, _ in reqs:
+            assert a.output(i) == b.output(i), (trial, i)
+            assert a.finish_reason(i) == b.finish_reason(i), (trial, i)
+            assert H.PENDING_TOKEN not in b.output(i)
+        assert cache_b.check() == "" and cache_b.free_pages(0) == pages and cache_b.free_slots() == 4
+
+
+def test_pending_token_protocol():
+    cache, s = make(pages=8, budget=16)
+    s.add(0, [1, 2, 3], 3)
+    plan = s.schedule(); s.commit(plan); s.mark_pending(plan)
+    assert s.has_pending(0) and s.output(0) == []            # the placeholder is not output
+    plan2 = s.schedule(); s.commit(plan2)
+    assert [(e.id, e.start, list(e.tokens), e.sample) for e in plan2.entries] == [(0, 3, [H.PENDING_TOKEN], True)]
+    s.mark_pending(plan2)                                     # two on the way for a moment
+    with pytest.raises(Exception):
+        s.mark_pending(plan2)                                 # never three
+    assert s.resolve(0, 42) == H.FinishReason.NONE and s.output(0) == [42]   # the older one first
+    plan3 = s.schedule(); s.commit(plan3); s.mark_pending(plan3)             # its third token is the last by count
+    assert s.resolve(0, 43) == H.FinishReason.NONE and s.output(0) == [42, 43]
+    assert s.schedule().entries == []                         # nothing more to run for it
+    assert s.has_unfinished()
+    assert s.resolve(0, 44) == H.FinishReason.LENGTH and s.output(0) == [42, 43, 44]
+    assert not s.has_unfinished() and cache.free_pages(0) == 8
+    # a stop token drops what was sampled after it
+    s.add(2, [7], 9)
+    p1 = s.schedule(); s.commit(p1); s.mark_pending(p1)
+    p2 = s.schedule(); s.commit(p2); s.mark_pending(p2)
+    assert s.resolve(2, 5, True) == H.FinishReason.STOP and s.output(2) == []
+    assert s.resolve(2, 6) == H.FinishReason.STOP            # the later value finds the request ended
+    # a request that ends while its token is on the way drops that token
+    s.add(1, [4, 5], 5)
+    plan = s.schedule(); s.commit(plan); s.mark_pending(plan)
+    s.abort(1)
+    assert s.resolve(1, 9) == H.FinishReason.ABORTED and s.output(1) == []
+    assert cache.check() == "" and cache.free_pages(0) == 8
