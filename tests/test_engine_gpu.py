@@ -173,3 +173,53 @@ def test_norm_weights_far_from_one(name):
         assert np.abs(got - ref).max() / scale < 4e-2
     finally:
         shutil.rmtree(d)
+
+
+def test_running_ahead_changes_no_token():
+    """The engine launches a step before the tokens of the step before it have reached the
+    host.  With stop tokens (whose request has one more token computed for nothing), a pool
+    that forces requests out and back in, and a request withdrawn while a step with it is on
+    the device: the same tokens as when it waits after every step, and as the plain
+    implementation; no page lost."""
+    import json, os, shutil, tempfile
+    from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
+    mdir = model_dir("tiny_a", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    prompts = _prompts(cfg, [5, 30, 17, 9], 31)
+    free = [P.generate(cfg, w, p, 24) for p in prompts]
+    d = tempfile.mkdtemp(prefix="kvb200_ahead_")
+    try:
+        shutil.copy(os.path.join(mdir, "model.safetensors"), d)
+        c = dict(cfg)
+        c["eos_token_id"] = [int(free[0][6]), int(free[2][15])]       # both stop somewhere in the middle
+        json.dump(c, open(os.path.join(d, "config.json"), "w"))
+        _, w2 = P.read_model_dir(d)
+        ref = [P.generate(c, w2, p, 24, eos=c["eos_token_id"]) for p in prompts]
+        assert any(len(r) < 24 for r in ref)
+        outs = {}
+        for ahead in (False, True):
+            llm = LLM(d, dtype="float32", page_size=4, num_pages=16, max_num_seqs=4, max_num_batched_tokens=16,
+                      run_ahead=ahead)
+            outs[ahead] = llm.generate(prompts, SamplingParams(max_tokens=24))
+            assert llm.engine.stats()["preemptions"] > 0
+            assert llm.engine.runner.manager.check() == "" and llm.engine.runner.manager.free_pages(0) == 16
+        assert outs[True] == outs[False] == ref
+        # withdrawn in flight
+        llm = LLM(d, dtype="float32", page_size=4, num_pages=40, max_num_seqs=4, run_ahead=True)
+        eng = llm.engine
+        ids = [eng.add_request(p, SamplingParams(max_tokens=24)) for p in prompts[:2]]
+        got = {i: [] for i in ids}
+        for _ in range(4):
+            for ev in eng.step():
+                if ev.token is not None:
+                    got[ev.request_id].append(ev.token)
+        eng.abort(ids[0])
+        while eng.has_unfinished():
+            for ev in eng.step():
+                assert ev.request_id != ids[0]
+                if ev.token is not None:
+                    got[ev.request_id].append(ev.token)
+        assert got[ids[1]] == ref[1] and got[ids[0]] == ref[0][:len(got[ids[0]])]
+        assert eng.runner.manager.check() == "" and eng.runner.manager.free_pages(0) == 40
+    finally:
+        shutil.rmtree(d)
