@@ -9,12 +9,13 @@
 // once for the whole group (upstream fetches them once per query head:
 // paged_attention/src/kernels.cu:150-219).
 //
-// Per block: the keys and values of its first tile are requested (cp.async, 16-byte
-// chunks gathered through the block table into swizzled shared memory) before the
-// block waits for the projection kernel in front of it; then the group's queries are
+// Per block: the keys and values of its first two tiles are requested (cp.async, 16-byte
+// chunks gathered through the block table into two swizzled shared-memory stages) before
+// the block waits for the projection kernel in front of it; then the group's queries are
 // rotated (rotary encoding, float32) and the block that owns the tile of the token's
-// own position rotates the new key, stores key and value in the cache and in its
-// tile.  Each warp walks its own 32-key slice of every tile of the block: it multiplies
+// own position rotates the new key, stores key and value in the cache and, when that
+// tile is one of the two under way, in its stage by hand (a later tile fetches them from
+// the cache).  While a tile is multiplied the tile after the next is requested.  Each warp walks its own 32-key slice of every tile of the block: it multiplies
 // the queries with the keys (mma.sync m16n8k16, float32 accumulate), keeps a running
 // max and sum per head and a running output, and multiplies the probabilities with its
 // 32 values; no block-wide barrier inside the walk.  The four warps' partials are
@@ -38,7 +39,9 @@ __device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gm
   const int n = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(n) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+// Waits until at most N of this thread's committed groups are still under way.
+template <int N> __device__ __forceinline__ void cp_async_wait_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -74,8 +77,11 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
 }
 
 // GP: the group of query heads padded to 4, 8 or 16 (rows that are kept).  kCluster: blocks
-// per (request, kv head).
-template <int D, int GP, int kCluster>
+// per (request, kv head).  kStages: tiles in shared memory at a time, 2 when the whole grid
+// is resident at once anyway (small batches: the second tile is under way before the
+// projection has finished), 1 when more blocks per SM matter more (large batches).  The
+// order of the sums is the same for both.
+template <int D, int GP, int kCluster, int kStages>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int write_kv,
@@ -83,24 +89,34 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
                             const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len, int rot,
                             __nv_bfloat16* __restrict__ out, int nq, int nkv, int G, float scale_log2, int window,
-                            int* status) {
+                            int* status, unsigned long long* trace) {
   constexpr int CPK = D / 8;      // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;
   constexpr int DT = D / 8;       // n-tiles of the output
   constexpr int PW = D + 2;       // floats per head in a partial: output dims, max, sum
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* k_s = smem;                                   // [4][32][D] bf16, swizzled
-  unsigned char* v_s = k_s + 4 * 32 * D * 2;                   // [4][32][D]
-  float* q_s = reinterpret_cast<float*>(v_s + 4 * 32 * D * 2); // [GP][D] rotated, scaled queries
+  constexpr int kTileBytes = 4 * 32 * D * 2;                   // keys (or values) of one tile
+  unsigned char* k_s = smem;                                   // [kStages][4][32][D] bf16, swizzled
+  unsigned char* v_s = k_s + kStages * kTileBytes;             // [kStages][4][32][D]
+  float* q_s = reinterpret_cast<float*>(v_s + kStages * kTileBytes); // [GP][D] rotated, scaled queries
   float* run = q_s + GP * D;                                   // [GP][PW] this block's partial so far
   float* recv = run + GP * PW;                                 // [kCluster][GP][PW], used in block 0 only
   // the four warps' partials of one tile are merged in the tile memory: [4][GP][PW] floats
   float* wpart = reinterpret_cast<float*>(smem);
-  static_assert(4 * GP * PW * 4 <= 2 * 4 * 32 * D * 2, "the warps' partials must fit into the tiles");
+  static_assert(4 * GP * PW * 4 <= 2 * kStages * kTileBytes, "the warps' partials must fit into the tiles");
 
   pdl_trigger();
   const int hk = blockIdx.x, r = blockIdx.y, z = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // profiling only: nanosecond stamps of this block's phases, [blocks][8]
+  auto stamp = [&](int slot) {
+    if (trace && tid == 0) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      trace[(((size_t)r * gridDim.x + hk) * kCluster + z) * 8 + slot] = now;
+    }
+  };
+  stamp(0);   // block started
   const int page_mask = (1 << page_shift) - 1;
   const int pos = ctx_len[r] - 1;   // lengths and block tables were written before the step's kernels started
   const bool bad = pos < 0 || (cos_t != nullptr && pos >= table_len);
@@ -114,11 +130,13 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
 
   for (int i = tid; i < GP * PW; i += kThreads) run[i] = ((i % PW) == D) ? -CUDART_INF_F : 0.f;
 
-  // Requests this warp's 32 keys and values of tile t; `skip_pos`: leave the token's own
+  // Requests this warp's 32 keys and values of tile t into a stage; `skip_pos`: leave the token's own
   // position out (it is placed by hand).  Returns the mask of this warp's keys that are there.
   // Keys that are absent (beyond the context, outside the window) are filled with zeros, so
   // that a probability of zero times whatever lay there before cannot turn into NaN.
-  auto request_tile = [&](int t, bool skip_pos) -> unsigned {
+  auto request_tile = [&](int t, int stage, bool skip_pos) -> unsigned {
+    unsigned char* kd = k_s + stage * kTileBytes + warp * 32 * D * 2;
+    unsigned char* vd = v_s + stage * kTileBytes + warp * 32 * D * 2;
     const int j = t * kTile + warp * 32 + lane;
     long long off = -1;                      // -1: absent, zero-fill; -2: placed by hand, leave alone
     if (skip_pos && j == pos) off = -2;
@@ -135,21 +153,30 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       const long long oj = __shfl_sync(0xffffffffu, off, key);
       if (oj != -2) {
         const long long src = oj >= 0 ? oj + part * 8 : 0;
-        cp_async_16_zfill(k_s + warp * 32 * D * 2 + swz<D>(key, part), k_pages + src, oj >= 0);
-        cp_async_16_zfill(v_s + warp * 32 * D * 2 + swz<D>(key, part), v_pages + src, oj >= 0);
+        cp_async_16_zfill(kd + swz<D>(key, part), k_pages + src, oj >= 0);
+        cp_async_16_zfill(vd + swz<D>(key, part), v_pages + src, oj >= 0);
       }
     }
     return __ballot_sync(0xffffffffu, off >= 0);
   };
 
-  // first tile of this block: on its way before the projection kernel has finished
+  // the first tiles of this block: on their way before the projection kernel has finished.
+  // Every thread commits one group per stage here and one per tile walked, requests or not,
+  // so that "all but the newest group" always means "the tile that is multiplied next".
   int t = z;
   while (t < t_first) t += kCluster;
   const int my_first = t;
-  unsigned have = 0;
-  if (my_first < n_tiles) have = request_tile(my_first, write_kv != 0);
+  const int n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / kCluster + 1 : 0;
+  unsigned have0 = 0, have1 = 0;
+  if (n_mine > 0) have0 = request_tile(my_first, 0, write_kv != 0);
+  cp_async_commit();
+  if (kStages > 1) {
+    if (n_mine > 1) have1 = request_tile(my_first + kCluster, 1, write_kv != 0);
+    cp_async_commit();
+  }
 
   pdl_wait();
+  stamp(1);   // the projection in front has finished
   const __nv_bfloat16* row = qkv + (size_t)q_start[r] * q_row_stride;
   if (!bad) {
     // the group's queries, rotated (pairs (j, j + rot/2) of the first rot dims), scaled, float32
@@ -180,7 +207,8 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         const size_t dst = ((((size_t)page * nkv + hk) << page_shift) + (pos & page_mask)) * D;
         const __nv_bfloat16* kh = row + (size_t)(nq + hk) * D;
         const __nv_bfloat16* vh = row + (size_t)(nq + nkv + hk) * D;
-        const bool direct = (t_star == my_first);       // its tile is the one already requested
+        const int star_i = (t_star - my_first) / kCluster;   // which of this block's tiles it is
+        const bool direct = star_i < kStages;           // its tile is one of those already requested
         const int slot = pos - t_star * kTile;          // 0..127: warp slot>>5, key slot&31
         for (int dd = tid; dd < D; dd += kThreads) {
           float val;
@@ -196,17 +224,21 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
           k_pages[dst + dd] = kr;
           v_pages[dst + dd] = vh[dd];
           if (direct) {
-            const int key = slot & 31, off_b = (slot >> 5) * 32 * D * 2 + swz<D>(key, dd >> 3) + (dd & 7) * 2;
+            const int key = slot & 31;
+            const int off_b = star_i * kTileBytes + (slot >> 5) * 32 * D * 2 + swz<D>(key, dd >> 3) + (dd & 7) * 2;
             *reinterpret_cast<__nv_bfloat16*>(k_s + off_b) = kr;
             *reinterpret_cast<__nv_bfloat16*>(v_s + off_b) = vh[dd];
           }
         }
-        if (direct) { if (warp == (slot >> 5)) have |= 1u << (slot & 31); }
+        if (direct) {
+          if (warp == (slot >> 5)) { if (star_i == 0) have0 |= 1u << (slot & 31); else have1 |= 1u << (slot & 31); }
+        }
         else __threadfence();   // a later tile of this block fetches it from L2
       }
     }
   }
   __syncthreads();
+  stamp(2);   // queries rotated, new key and value stored
 
   // query fragments (A operand, rows = heads): row lane/4 and lane/4 + 8, bfloat16
   unsigned qf[KSTEPS][4];
@@ -229,11 +261,12 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   float o[DT][4];
 #pragma unroll
   for (int n = 0; n < DT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
-  const unsigned char* kt = k_s + warp * 32 * D * 2;
-  const unsigned char* vt = v_s + warp * 32 * D * 2;
-  for (t = my_first; t < n_tiles; t += kCluster) {
-    if (t != my_first) have = request_tile(t, false);   // the new key, if here, is in the cache by now
-    cp_async_wait_all();
+  for (int i = 0; i < n_mine; ++i) {
+    const int stage = i % kStages;
+    const unsigned char* kt = k_s + stage * kTileBytes + warp * 32 * D * 2;
+    const unsigned char* vt = v_s + stage * kTileBytes + warp * 32 * D * 2;
+    const unsigned have = stage ? have1 : have0;
+    cp_async_wait_but<kStages - 1>();
     __syncwarp();
     if (have != 0u) {
       float s[4][4];
@@ -298,6 +331,12 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       }
     }
     __syncwarp();   // the slice is read; the next request may overwrite it
+    if (i + kStages < n_mine) {
+      // the new key, if in that tile, is in the cache by now
+      const unsigned h = request_tile(my_first + (i + kStages) * kCluster, stage, false);
+      if (stage) have1 = h; else have0 = h;
+    }
+    cp_async_commit();
   }
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
@@ -305,6 +344,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
   }
   __syncthreads();   // every warp is done with the tiles: their memory takes the warps' partials
+  stamp(3);   // tiles walked
   {
     const int r0 = lane >> 2, c0 = (lane & 3) << 1;
 #pragma unroll
@@ -340,8 +380,10 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   __syncthreads();
 
   // ---- one partial per block goes to block 0 of the cluster; block 0 merges in block order
+  stamp(4);   // the block's partial is complete
   for (int i = tid; i < GP * PW; i += kThreads) st_peer_f32(recv + (size_t)z * GP * PW + i, 0u, run[i]);
   cluster_sync_all();
+  stamp(5);   // the cluster has met
   if (z != 0 || bad) {
     if (bad && z == 0 && tid == 0) atomicCAS(status, 0, KVB_STATUS_BAD_POSITION);
     return;
@@ -363,6 +405,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     }
     out[((size_t)q_start[r] * nq + hk * G + g) * D + dd] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
   }
+  stamp(6);   // output stored
 }
 
 int log2_exact(int x) {
@@ -371,17 +414,17 @@ int log2_exact(int x) {
   return (1 << s) == x ? s : -1;
 }
 
-template <int D, int GP, int kCluster>
+template <int D, int GP, int kCluster, int kStages>
 int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* q_start, const int* ctx_len, const float* cos_t,
            const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv, float scale, int window,
-           int* status, cudaStream_t stream) {
+           int* status, unsigned long long* trace, cudaStream_t stream) {
   constexpr int PW = D + 2;
-  const size_t smem = (size_t)2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
+  const size_t smem = (size_t)kStages * 2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
                       (size_t)kCluster * GP * PW * 4;
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kCluster>,
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kCluster, kStages>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
@@ -401,9 +444,9 @@ int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int 
   cfg.attrs = attr;
   cfg.numAttrs = kvb_pdl_enabled() ? 2 : 1;
   cudaError_t le = cudaLaunchKernelEx(
-      &cfg, decode_attention_mma_kernel<D, GP, kCluster>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
+      &cfg, decode_attention_mma_kernel<D, GP, kCluster, kStages>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
       (__nv_bfloat16*)v_pages, write_kv, block_table, max_pages, page_shift, num_pages, q_start, ctx_len, cos_t, sin_t,
-      table_len, rot, (__nv_bfloat16*)out, nq, nkv, nq / nkv, scale * 1.4426950408889634f, window, status);
+      table_len, rot, (__nv_bfloat16*)out, nq, nkv, nq / nkv, scale * 1.4426950408889634f, window, status, trace);
   if (le != cudaSuccess) return (int)le;
   return kvb_launch_result();
 }
@@ -421,13 +464,14 @@ KVB_EXPORT int kvb_decode_attention_mma_supported(int d, int group, int page_siz
 // cache and writes nothing.  cos_t/sin_t: [table_len, rot/2] or nullptr.  out: [T, nq d].
 // cluster: 4 or 8 blocks per (request, kv head); a function of the engine's limits only, so
 // that a token's sums are cut the same way in every batch.
+// trace: nullptr, or [R * nkv * cluster, 8] uint64 for the phase stamps of every block (profiling only).
 // Uses no memory beyond its operands.  R <= 65535.
 KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv,
                                         const int* block_table, int max_pages, int page_size, int num_pages,
                                         const int* q_start, const int* ctx_len, const float* cos_t,
                                         const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv,
                                         int d, float scale, int window, int cluster, int* status,
-                                        cudaStream_t stream) {
+                                        unsigned long long* trace, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (cluster != 4 && cluster != 8) return KVB_ERR_BAD_SIZE;
   if (nkv < 1 || nq % nkv || !kvb_decode_attention_mma_supported(d, nq / nkv, page_size) || R > 65535 || (rot & 1) ||
@@ -435,13 +479,16 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
     return KVB_ERR_BAD_SIZE;
   const int G = nq / nkv;
   const int ps = log2_exact(page_size);
-#define KVB_DM(D, GP)                                                                                              \
-  do {                                                                                                             \
-    if (cluster == 4)                                                                                              \
-      return launch<D, GP, 4>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, \
-                              q_start, ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, stream); \
-    return launch<D, GP, 8>(qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages,   \
-                            q_start, ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, stream); \
+  // two stages while every block of the grid fits on the GPU at once
+  const bool deep = (long long)R * nkv * cluster <= 2 * 148;
+#define KVB_DM_ARGS qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, q_start, \
+                    ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, trace, stream
+#define KVB_DM(D, GP)                                                       \
+  do {                                                                      \
+    if (cluster == 4 && deep) return launch<D, GP, 4, 2>(KVB_DM_ARGS);      \
+    if (cluster == 4) return launch<D, GP, 4, 1>(KVB_DM_ARGS);              \
+    if (deep) return launch<D, GP, 8, 2>(KVB_DM_ARGS);                      \
+    return launch<D, GP, 8, 1>(KVB_DM_ARGS);                                \
   } while (0)
   if (d == 64) { if (G <= 4) KVB_DM(64, 4); if (G <= 8) KVB_DM(64, 8); KVB_DM(64, 16); }
   if (G <= 4) KVB_DM(128, 4);

@@ -429,7 +429,8 @@ def decode_attention_mma_supported(d: int, group: int, page_size: int) -> bool:
 
 
 def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
-                         nq, nkv, d, scale, window, status, max_positions: int = 1 << 30) -> torch.Tensor:
+                         nq, nkv, d, scale, window, status, max_positions: int = 1 << 30,
+                         trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The attention of a bfloat16 decode step in one launch on tensor cores: rotary
     encoding of query and new key, cache write, attention over 128-key tiles spread over
     a cluster of blocks, merge through distributed shared memory.  No scratch.
@@ -443,7 +444,7 @@ def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, 
         c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
         _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rot), _p(out), c_int(R), c_int(nq),
         c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), c_int(4 if max_positions <= 4096 else 8),
-        _p(status), _stream())
+        _p(status), _p(trace), _stream())
     _check(rc, "decode_attention_mma")
     return out
 
