@@ -83,7 +83,9 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
 
   pdl_trigger();
   pdl_wait();
-  const TileDesc tile = tiles[blockIdx.x];
+  // the last tiles of a request read the most keys: they start first, so that the grid's
+  // last blocks to start are short ones
+  const TileDesc tile = tiles[gridDim.x - 1 - blockIdx.x];
   const int hk = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gp = 1 << gp_shift;
@@ -286,6 +288,368 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention on the 5th-generation tensor cores, for tiles of 128 query rows and head
+// size 64.  A block of 256 threads owns one query tile; threads r and r + 128 share row r:
+// each takes half of a tile's keys in the softmax and half of the output dims.  Per tile of
+// 128 keys:
+//   S = Q K^T     one thread issues tcgen05.mma (M 128, N 128, K 16 x 4) from shared memory
+//                 into tensor memory; keys and values were gathered through the block table by
+//                 16-byte cp.async copies, in the 128-byte-swizzled layout the tensor cores read
+//   softmax       every thread reads its half row of S from tensor memory (tcgen05.ld), masks
+//                 (only where a warp's rows meet the diagonal or the window's edge), keeps the
+//                 running max and sum in float32, and writes its probabilities in bfloat16 to
+//                 shared memory, again in the swizzled K-major layout
+//   O' = P V      tcgen05.mma (M 128, N 64, K 16 x 8); V is read as the MN-major operand, so
+//                 the same [key][dim] tile serves
+//   O = O corr + O'   in registers: a thread holds 32 of its row's 64 outputs.
+// The next tile's keys are requested as soon as S has been computed, its values as soon as
+// P V has been, so loads run under the softmax and the products; two blocks share an SM and
+// fill each other's gaps.  mbarrier waits are bounded: a wait that runs out records
+// KVB_STATUS_WAIT_TIMEOUT and the block frees its tensor memory and returns.
+namespace tc5 {
+
+constexpr unsigned kSpinLimit = 20u * 1000u * 1000u;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {   // false: the limit ran out
+  for (unsigned i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tmem_alloc(void* holder, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// 32 consecutive columns of this thread's lane of tensor memory
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024
+// bytes apart, base aligned to 1024 bytes.  The same image is a K-major operand (rows are
+// M or N, the 64 elements of a row run along K) or, with the major bit of the instruction
+// descriptor set, an MN-major one (rows run along K, the 64 elements of a row along N).
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+constexpr int BM = 128, BNK = 64, D = 64;
+constexpr int kThreads = 256;                // two threads per query row: each takes half of the keys of a tile
+constexpr int kQBytes = BM * D * 2;          // [128 rows][64] bfloat16
+constexpr int kKVBytes = BNK * D * 2;        // [64 keys][64]
+constexpr int kPBytes = BM * BNK * 2;        // [128 rows][64 keys]
+constexpr unsigned kTmemCols = 256;          // S: columns 0..63 and 64..127 in turn, P V: columns 128..191
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
+                                const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                                const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
+                                const int* __restrict__ positions, const TileDesc* __restrict__ tiles,
+                                __nv_bfloat16* __restrict__ out, int nq, int nkv, int G, int gp_shift,
+                                float scale_log2, int window, int* status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* q_s = base;                       // [128 rows][64]
+  unsigned char* k_s = q_s + kQBytes;              // [2][64 keys][64]
+  unsigned char* v_s = k_s + 2 * kKVBytes;         // [2][64 keys][64]
+  unsigned char* p_s = v_s + 2 * kKVBytes;         // [128 rows][64 keys]
+  float* mx_s = reinterpret_cast<float*>(p_s + kPBytes);   // [2][128] the halves' row maxima of a tile
+  unsigned long long* bar_s = reinterpret_cast<unsigned long long*>(mx_s + 2 * BM);   // [2]: one per S buffer
+  unsigned long long* bar_o = bar_s + 2;
+  unsigned* tmem_holder = reinterpret_cast<unsigned*>(bar_o + 1);
+  int* abort_flag = reinterpret_cast<int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int r = tid & (BM - 1);      // this thread's query row (= its lane of tensor memory)
+  const int h = tid >> 7;            // which half of a tile's keys, and of the output dims, it takes
+  if (tid == 0) {
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(tmem_holder, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = *tmem_holder;
+  // only now may the kernel behind this one start: its resident, waiting blocks must not be
+  // able to take tensor memory that a block of this grid still needs
+  pdl_trigger();
+  pdl_wait();
+
+  // the last tiles of a request read the most keys: they start first, so that the grid's
+  // last blocks to start are short ones
+  const TileDesc tile = tiles[gridDim.x - 1 - blockIdx.x];
+  const int hk = blockIdx.y;
+  const int gp = 1 << gp_shift;
+  const int page_mask = (1 << page_shift) - 1;
+  const int* table = block_table + (size_t)tile.req * max_pages;
+  const int ti = r >> gp_shift, hi = r & (gp - 1);
+  const bool row_ok = ti < tile.n_tok && hi < G;
+  const int pos = row_ok ? positions[tile.t0 + ti] : -1;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int pos_first = positions[tile.t0];
+  const int pos_last = positions[tile.t0 + tile.n_tok - 1];
+  const int k_hi = pos_last + 1;
+  const int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int first_tile = k_lo / BNK, last_tile = (k_hi - 1) / BNK;
+  const int n_tiles = last_tile - first_tile + 1;
+
+  // Loaders.  Query: thread (r, h) brings the 16-byte pieces 4h..4h+3 of row r.  Keys and
+  // values: thread j brings pieces 2 (j mod 4), +1 of key j / 4 of a tile; a key's page is
+  // looked up when the tile is requested (the tile is not needed before the next tile's turn).
+  {
+    const __nv_bfloat16* src = q_base + (size_t)(tile.t0 + (row_ok ? ti : 0)) * q_row_stride +
+                               (size_t)(hk * G + (row_ok ? hi : 0)) * D;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cp_async_16_zfill(q_s + swz<D>(r, 4 * h + i), src + (4 * h + i) * 8, row_ok);
+  }
+  const int lkey = tid >> 2, lpart = (tid & 3) * 2;
+  auto load_tile = [&](int i, unsigned char* dst, const __nv_bfloat16* pages) {   // i-th tile of this block
+    const int j = (first_tile + i) * BNK + lkey;
+    bool ok = i < n_tiles && j < k_hi && j >= k_lo;
+    size_t off = 0;
+    if (ok) {
+      const int lp = j >> page_shift;
+      const int page = lp < max_pages ? __ldg(table + lp) : -1;
+      if (page < 0 || page >= num_pages) {
+        atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        ok = false;
+      } else {
+        off = ((((size_t)page * nkv + hk) << page_shift) + (j & page_mask)) * D;
+      }
+    }
+    cp_async_16_zfill(dst + swz<D>(lkey, lpart), pages + off + lpart * 8, ok);
+    cp_async_16_zfill(dst + swz<D>(lkey, lpart + 1), pages + off + (lpart + 1) * 8, ok);
+  };
+  // Every thread commits the same groups in the same order, requests or not:
+  //   prologue: [Q, K0] [K1] [V0];  tile i: [K(i+2)] after S(i) has been read, [V(i+1)] after P V(i-1) has been.
+  load_tile(0, k_s, k_pages);
+  cp_async_commit();
+  if (n_tiles > 1) load_tile(1, k_s + kKVBytes, k_pages);
+  cp_async_commit();
+  load_tile(0, v_s, v_pages);
+  cp_async_commit();
+
+  // instruction descriptors: float32 accumulator, bfloat16 operands, N >> 3 at bit 17, M >> 4 at bit 24
+  const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BNK >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+  const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
+                           ((unsigned)(D >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+  const unsigned lane_base = tmem + ((unsigned)((warp & 3) * 32) << 16);
+  const unsigned o_cols = lane_base + 128 + 32 * h;    // this thread's 32 output dims
+  const unsigned long long qd = smem_desc_sw128(smem_u32(q_s));
+  auto issue_s = [&](int i) {   // S(i) = Q K(i)^T into S buffer i mod 2   (one thread)
+    const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i & 1) * kKVBytes));
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+      umma_bf16(tmem + (i & 1) * BNK, qd + 2 * kk, kd + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+    umma_commit(&bar_s[i & 1]);
+  };
+
+  float o[D / 2];
+#pragma unroll
+  for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
+  float m_run = -CUDART_INF_F, l_run = 0.f;   // l_run: the sum over this thread's half of the keys
+  bool failed = false;
+
+  cp_async_wait<2>();                      // Q and K0
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) { tc_fence_after(); issue_s(0); }
+
+  for (int i = 0; i < n_tiles; ++i) {
+    const int t = first_tile + i;
+    // ---- the next tile's scores are started before this tile's are looked at
+    cp_async_wait<1>();                    // K(i+1) is here
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();                       // ... for everybody; and everybody has read S(i-1) out of its buffer
+    if (*abort_flag) { failed = true; break; }
+    if (tid == 0 && i + 1 < n_tiles) { tc_fence_after(); issue_s(i + 1); }
+
+    // ---- S(i): this thread's 32 scores, kept in registers
+    if (!failed && !mbar_wait(&bar_s[i & 1], (unsigned)(i >> 1) & 1u)) { failed = true; *abort_flag = 1; }
+    tc_fence_after();
+    float v[32];
+    tmem_ld32(lane_base + (i & 1) * BNK + 32 * h, v);
+    load_tile(i + 2, k_s + (i & 1) * kKVBytes, k_pages);   // K(i) has been read: its buffer takes K(i+2)
+    cp_async_commit();
+
+    const int kb = t * BNK + 32 * h;       // first key of this thread's half
+    const bool full = pos >= 0 && t * BNK + BNK - 1 <= pos && t * BNK >= lo;
+    const bool plain = __all_sync(0xffffffffu, full);   // no key of the tile is masked for any row of the warp
+    float mx = -CUDART_INF_F;
+    if (plain) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int key = kb + j;
+        if (!(key <= pos && key >= lo)) v[j] = -CUDART_INF_F;
+        mx = fmaxf(mx, v[j]);
+      }
+    }
+    mx_s[h * BM + r] = mx * scale_log2;    // the scale is positive: the maximum commutes with it
+    __syncthreads();
+    if (*abort_flag) { failed = true; break; }
+    const float m_new = fmaxf(m_run, fmaxf(mx_s[r], mx_s[BM + r]));
+    const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;   // a row with no key yet: everything stays zero
+    const float corr = (m_run == -CUDART_INF_F) ? 0.f : ex2(m_run - m_use);
+    m_run = m_new;
+    l_run *= corr;
+
+    // ---- O += P V(i-1), which ran while this tile's scores were read; then O is rescaled
+    if (i > 0) {
+      if (!failed && !mbar_wait(bar_o, (unsigned)(i - 1) & 1u)) { failed = true; *abort_flag = 1; }
+      tc_fence_after();
+      float pv[32];
+      tmem_ld32(o_cols, pv);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] += pv[j];
+    }
+    load_tile(i + 1, v_s + ((i + 1) & 1) * kKVBytes, v_pages);   // V(i-1) has been read: its buffer takes V(i+1)
+    cp_async_commit();
+#pragma unroll
+    for (int j = 0; j < D / 2; ++j) o[j] *= corr;
+
+    // ---- P(i): probabilities of this thread's 32 keys, bfloat16, pieces 4h..4h+3 of row r
+    unsigned pk[16];
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      // a masked score is -inf: its probability comes out as zero
+      const float p0 = ex2(fmaf(v[j], scale_log2, -m_use)), p1 = ex2(fmaf(v[j + 1], scale_log2, -m_use));
+      l_run += p0 + p1;
+      pk[j >> 1] = pack_bf16(p0, p1);
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4)
+      *reinterpret_cast<uint4*>(p_s + swz<D>(r, 4 * h + q4)) =
+          make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+
+    // ---- P V(i) is started and left to run
+    cp_async_wait<2>();                    // V(i) is here (newer: K(i+2), V(i+1))
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) { failed = true; break; }
+    if (tid == 0) {
+      tc_fence_after();
+      const unsigned long long pd = smem_desc_sw128(smem_u32(p_s));
+      const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (i & 1) * kKVBytes));
+#pragma unroll
+      for (int kk = 0; kk < BNK / 16; ++kk)   // 16 keys per step: 32 bytes along a row of P, 16 rows of V
+        umma_bf16(tmem + 128, pd + 2 * kk, vd + 128 * kk, idesc_o, kk > 0 ? 1u : 0u);
+      umma_commit(bar_o);
+    }
+  }
+  if (!failed && n_tiles > 0) {
+    if (!mbar_wait(bar_o, (unsigned)(n_tiles - 1) & 1u)) { failed = true; *abort_flag = 1; }
+    tc_fence_after();
+    float pv[32];
+    tmem_ld32(o_cols, pv);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[j] += pv[j];
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  if (*abort_flag) failed = true;
+
+  if (failed) {
+    if (tid == 0) atomicCAS(status, 0, KVB_STATUS_WAIT_TIMEOUT);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let products that may still run finish
+  } else {
+    // the row's sum is the sum of its two halves
+    mx_s[h * BM + r] = l_run;
+    __syncthreads();
+    const float l = mx_s[r] + mx_s[BM + r];
+    if (row_ok) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = out + ((size_t)(tile.t0 + ti) * nq + hk * G + hi) * D + 32 * h;
+#pragma unroll
+      for (int j = 0; j < D / 2; j += 8)
+        *reinterpret_cast<uint4*>(dst + j) =
+            make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
+                       pack_bf16(o[j + 4] * inv, o[j + 5] * inv), pack_bf16(o[j + 6] * inv, o[j + 7] * inv));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_pages, const int* block_table,
+           int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
+           void* out, int nq, int nkv, int G, int gp_shift, float scale, int window, int* status,
+           cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)kQBytes + 4 * (size_t)kKVBytes + kPBytes + 2 * BM * 4 + 64;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(paged_flash_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid(num_tiles, nkv);
+  kvb_launch(paged_flash_attention_tc_kernel, grid, dim3(kThreads), smem, stream, (const __nv_bfloat16*)q, q_row_stride,
+             (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, max_pages, page_shift,
+             num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq, nkv, G, gp_shift,
+             scale * 1.4426950408889634f, window, status);
+  return kvb_launch_result();
+}
+
+}  // namespace tc5
+
 template <int D, int NW>
 int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_pages, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
@@ -331,7 +695,8 @@ KVB_EXPORT int kvb_flash_attention_tokens_per_tile(int group, int wide) {
 
 // tiles: num_tiles x {request row, first token row, tokens (<= tokens_per_tile(group, wide)), 0},
 // int32.  The tokens of a tile are consecutive tokens of one request, positions ascending.
-// wide: the tiles were cut for 128 query rows per block, else for 64.
+// wide: 0: the tiles were cut for 64 query rows per block; 1: for 128; 2: for 128, and the
+// kernel is the tcgen05 form (head size 64 only).
 // bfloat16 only.  out is [T, nq*d].
 KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                          const int* block_table, int max_pages, int page_size, int num_pages,
@@ -346,6 +711,11 @@ KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const 
   while ((1 << gp_shift) < G) ++gp_shift;
   const int page_shift = log2_exact(page_size);
   if (wide && (128 >> gp_shift) < 1) return KVB_ERR_BAD_SIZE;
+  if (wide == 2) {   // tcgen05 form
+    if (d != 64 || (reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7)) return KVB_ERR_BAD_SIZE;
+    return tc5::launch(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions,
+                       tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream);
+  }
 #define KVB_FA(D, NW)                                                                                           \
   return launch<D, NW>(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions, \
                        tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream)

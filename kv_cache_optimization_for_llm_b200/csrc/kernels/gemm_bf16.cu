@@ -187,7 +187,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   int* flags = reinterpret_cast<int*>(tmem_holder + 1);  // [0]: abort, [1]: this block reduces the splits
   float* rstd = reinterpret_cast<float*>(flags + 2);     // [16] row scale
 
-  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) stamp(p, 0);   // block started
   const int n0 = blockIdx.x * TILE_N;
@@ -209,6 +208,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_d = *tmem_holder;
+  // The kernel behind this one may start only now that this block holds its tensor memory:
+  // blocks of that kernel which wait, resident, for this grid to finish must not be able to
+  // take the columns that a block of this grid still needs.
+  pdl_trigger();
 
   if (warp == 0 && lane == 0) {
     // ---- TMA producer.  The weights do not depend on the kernel before this one: the

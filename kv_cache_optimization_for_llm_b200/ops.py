@@ -345,6 +345,7 @@ def decode_attention(qkv, k_pages, v_pages, block_table, q_start, ctx_len, nq, n
 
 
 FLASH_WIDE = __import__('os').environ.get('KVB200_FLASH_WIDE', '1') != '0'
+FLASH_TC = __import__('os').environ.get('KVB200_FLASH_TC', '1') != '0'
 
 
 def flash_attention_supported(d: int, group: int, page_size: int) -> bool:
@@ -380,19 +381,23 @@ def flash_tiles(batch, group: int, wide: bool) -> torch.Tensor:
 def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window,
                     wide: Optional[bool] = None) -> torch.Tensor:
     """Tensor-core attention for steps with runs of query tokens (bfloat16).  ``wide``:
-    128 query rows per block instead of 64 (None: chosen from the step's size)."""
+    False: 64 query rows per block (mma.sync); True: 128 rows (mma.sync); 2: 128 rows on
+    tcgen05 with the scores in tensor memory (head size 64); None: chosen from the step's
+    size and the head size."""
     _need_cuda(qkv, k_pages)
     T = qkv.shape[0]
     # 128-row tiles when there are enough of them to keep every SM busy, else 64-row tiles
     nt128 = int(lib("flash_attention").kvb_flash_attention_tokens_per_tile(c_int(nq // nkv), c_int(1)))
     if wide is None:
         wide = FLASH_WIDE and (T // nt128) * nkv >= 2 * 148
+        if wide and FLASH_TC and d == 64:
+            wide = 2
     tiles = flash_tiles(batch, nq // nkv, wide)
     out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
     rc = lib("flash_attention").kvb_paged_flash_attention(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
         c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]),
-        c_int(1 if wide else 0), _p(out), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), _p(batch.status),
+        c_int(int(wide)), _p(out), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), _p(batch.status),
         _stream())
     _check(rc, "paged_flash_attention")
     return out

@@ -346,7 +346,7 @@ def test_flash_attention_mixed_runs(nq, nkv, d, page_size, window):
     assert ops.flash_attention_supported(d, nq // nkv, page_size)
     c = _attention_case("bfloat16", nq, nkv, d, ctxs=[1, 70, 130, 64, 400, 257, 2], q_lens=[1, 70, 2, 1, 150, 40, 2],
                         page_size=page_size, window=window, seed=d + nq + page_size)
-    for wide in (False, True):      # 64 and 128 query rows per block
+    for wide in (False, True) + ((2,) if d == 64 else ()):   # 64 and 128 query rows per block (mma.sync), 128 on tcgen05
         fb = _FakeBatch(c)
         out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), window,
                                   wide=wide)
@@ -360,12 +360,15 @@ def test_flash_attention_finds_a_far_key(spike):
     nq, nkv, d = 8, 2, 64
     c = _attention_case("bfloat16", nq, nkv, d, ctxs=[900], q_lens=[37], page_size=16, window=None, seed=spike,
                         spike=spike)
-    fb = _FakeBatch(c)
-    out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), None)
-    assert rel_err(out, c["ref"]) < TOL["bfloat16"]
-    page, slot = int(c["table"][0, spike // 16]), spike % 16
-    want = np.repeat(as64(c["vp"][page, :, slot]), nq // nkv, axis=0).reshape(-1)
-    assert np.abs(as64(out)[-1] - want).max() < 0.08      # the last query sees that key's value
+    for wide in (None, 2):
+        fb = _FakeBatch(c)
+        out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), None,
+                                  wide=wide)
+        assert int(fb.status.item()) == 0
+        assert rel_err(out, c["ref"]) < TOL["bfloat16"], wide
+        page, slot = int(c["table"][0, spike // 16]), spike % 16
+        want = np.repeat(as64(c["vp"][page, :, slot]), nq // nkv, axis=0).reshape(-1)
+        assert np.abs(as64(out)[-1] - want).max() < 0.08, wide      # the last query sees that key's value
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
