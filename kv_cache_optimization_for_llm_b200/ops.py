@@ -349,6 +349,8 @@ FLASH_TC = __import__('os').environ.get('KVB200_FLASH_TC', '1') != '0'
 
 
 def flash_attention_supported(d: int, group: int, page_size: int) -> bool:
+    if d not in (64, 128):      # answered here, so that a model of another head size never builds the module
+        return False
     return bool(lib("flash_attention").kvb_flash_attention_supported(c_int(d), c_int(group), c_int(page_size)))
 
 
@@ -430,6 +432,8 @@ def decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, q_start
 
 
 def decode_attention_mma_supported(d: int, group: int, page_size: int) -> bool:
+    if d not in (64, 128):      # answered here, so that a model of another head size never builds the module
+        return False
     return bool(lib("decode_attention").kvb_decode_attention_mma_supported(c_int(d), c_int(group), c_int(page_size)))
 
 
