@@ -1,10 +1,13 @@
 // The attention of a bfloat16 decode step in one launch, on tensor cores.
 //
-// Every request brings one query token.  A cluster of S blocks (4 or 8, chosen by the
-// caller from the longest context it allows, never from the batch) serves one
-// (request, key/value head): block z takes the 128-key tiles z, z + S, ... of the
-// request's context, so the work of a token is cut at absolute positions and does not
-// depend on what else is in the batch.  The rows of the tensor-core tile are the query
+// Every request brings one query token.  The 128-key tiles of a request's context fall into
+// C classes (tile t belongs to class t mod C; C is 4 or 8, chosen by the caller from the
+// longest context it allows, never from the batch).  A class is one running softmax over
+// its tiles; the C class results are merged in class order.  So the sums of a token are
+// cut at absolute positions and added in one fixed order, whatever else is in the batch.
+// A cluster of S blocks (S divides C; the caller takes a smaller S for a larger batch)
+// serves one (request, key/value head): block z walks the classes z, z + S, ... one after
+// the other.  S changes who computes a class, not what is computed.  The rows of the tensor-core tile are the query
 // heads that share the key/value head (padded to 16), so keys and values are fetched
 // once for the whole group (upstream fetches them once per query head:
 // paged_attention/src/kernels.cu:150-219).
@@ -76,12 +79,12 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
   return row * (D * 2) + ((chunk ^ (row & 7)) << 4);
 }
 
-// GP: the group of query heads padded to 4, 8 or 16 (rows that are kept).  kCluster: blocks
-// per (request, kv head).  kStages: tiles in shared memory at a time, 2 when the whole grid
+// GP: the group of query heads padded to 4, 8 or 16 (rows that are kept).  kClasses: classes
+// of tiles per (request, kv head); gridDim.z = cluster size = blocks that share them.  kStages: tiles in shared memory at a time, 2 when the whole grid
 // is resident at once anyway (small batches: the second tile is under way before the
 // projection has finished), 1 when more blocks per SM matter more (large batches).  The
 // order of the sums is the same for both.
-template <int D, int GP, int kCluster, int kStages>
+template <int D, int GP, int kClasses, int kStages>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int write_kv,
@@ -100,10 +103,8 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   unsigned char* v_s = k_s + kStages * kTileBytes;             // [kStages][4][32][D]
   float* q_s = reinterpret_cast<float*>(v_s + kStages * kTileBytes); // [GP][D] rotated, scaled queries
   float* run = q_s + GP * D;                                   // [GP][PW] this block's partial so far
-  float* recv = run + GP * PW;                                 // [kCluster][GP][PW], used in block 0 only
-  // the four warps' partials of one tile are merged in the tile memory: [4][GP][PW] floats
-  float* wpart = reinterpret_cast<float*>(smem);
-  static_assert(4 * GP * PW * 4 <= 2 * kStages * kTileBytes, "the warps' partials must fit into the tiles");
+  float* recv = run + GP * PW;                                 // [kClasses][GP][PW], used in block 0 only
+  float* wpart = recv + kClasses * GP * PW;                    // [4][GP][PW] the four warps' partials of a class
 
   pdl_trigger();
   const int hk = blockIdx.x, r = blockIdx.y, z = blockIdx.z;
@@ -113,7 +114,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     if (trace && tid == 0) {
       unsigned long long now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-      trace[(((size_t)r * gridDim.x + hk) * kCluster + z) * 8 + slot] = now;
+      trace[(((size_t)r * gridDim.x + hk) * gridDim.z + z) * 8 + slot] = now;
     }
   };
   stamp(0);   // block started
@@ -160,18 +161,19 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     return __ballot_sync(0xffffffffu, off >= 0);
   };
 
-  // the first tiles of this block: on their way before the projection kernel has finished.
-  // Every thread commits one group per stage here and one per tile walked, requests or not,
-  // so that "all but the newest group" always means "the tile that is multiplied next".
-  int t = z;
-  while (t < t_first) t += kCluster;
-  const int my_first = t;
-  const int n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / kCluster + 1 : 0;
+  // The first tiles of this block's first class: on their way before the projection kernel
+  // has finished.  Every thread commits one group per stage at the start of a class and one
+  // per tile walked, requests or not, so that "all but the newest group(s)" always means
+  // "the tile that is multiplied next".
+  const int S = (int)gridDim.z;
+  int my_first = z;                              // first tile of the class that is being walked
+  while (my_first < t_first) my_first += kClasses;
+  int n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / kClasses + 1 : 0;
   unsigned have0 = 0, have1 = 0;
   if (n_mine > 0) have0 = request_tile(my_first, 0, write_kv != 0);
   cp_async_commit();
   if (kStages > 1) {
-    if (n_mine > 1) have1 = request_tile(my_first + kCluster, 1, write_kv != 0);
+    if (n_mine > 1) have1 = request_tile(my_first + kClasses, 1, write_kv != 0);
     cp_async_commit();
   }
 
@@ -197,7 +199,8 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       q_s[i] = val * scale_log2;
     }
     // the new key and value: stored by the block that owns their tile
-    const bool owner = write_kv && (t_star >= t_first) && ((t_star - z) % kCluster == 0);
+    const int c_star = t_star % kClasses;                          // the class of the new key's tile
+    const bool owner = write_kv && (t_star >= t_first) && (c_star % S == z);
     if (owner) {
       const int lp = pos >> page_shift;
       const int page = lp < max_pages ? table[lp] : -1;
@@ -207,8 +210,8 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         const size_t dst = ((((size_t)page * nkv + hk) << page_shift) + (pos & page_mask)) * D;
         const __nv_bfloat16* kh = row + (size_t)(nq + hk) * D;
         const __nv_bfloat16* vh = row + (size_t)(nq + nkv + hk) * D;
-        const int star_i = (t_star - my_first) / kCluster;   // which of this block's tiles it is
-        const bool direct = star_i < kStages;           // its tile is one of those already requested
+        const int star_i = (t_star - my_first) / kClasses;   // which tile of its class it is
+        const bool direct = c_star == z && star_i < kStages;   // its tile is one of those already requested
         const int slot = pos - t_star * kTile;          // 0..127: warp slot>>5, key slot&31
         for (int dd = tid; dd < D; dd += kThreads) {
           float val;
@@ -254,9 +257,23 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     }
   }
 
-  // Each warp walks its 32-key slices of this block's tiles on its own, with a running
-  // max and sum per head (rows lane/4 and lane/4 + 8) and a running output in registers;
-  // the slices of a warp are private to it, so the walk needs no block-wide barrier.
+  // Class after class.  Each warp walks its 32-key slices of the class's tiles on its own, with
+  // a running max and sum per head (rows lane/4 and lane/4 + 8) and a running output in
+  // registers; the slices of a warp are private to it, so the walk needs no block-wide barrier.
+  for (int cls = z; cls < kClasses; cls += S) {
+  if (cls != z) {
+    // the new key, if in this class, is in the cache by now
+    my_first = cls;
+    while (my_first < t_first) my_first += kClasses;
+    n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / kClasses + 1 : 0;
+    have0 = have1 = 0;
+    if (n_mine > 0) have0 = request_tile(my_first, 0, false);
+    cp_async_commit();
+    if (kStages > 1) {
+      if (n_mine > 1) have1 = request_tile(my_first + kClasses, 1, false);
+      cp_async_commit();
+    }
+  }
   float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
   float o[DT][4];
 #pragma unroll
@@ -333,7 +350,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     __syncwarp();   // the slice is read; the next request may overwrite it
     if (i + kStages < n_mine) {
       // the new key, if in that tile, is in the cache by now
-      const unsigned h = request_tile(my_first + (i + kStages) * kCluster, stage, false);
+      const unsigned h = request_tile(my_first + (i + kStages) * kClasses, stage, false);
       if (stage) have1 = h; else have0 = h;
     }
     cp_async_commit();
@@ -343,8 +360,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 1);
     l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
   }
-  __syncthreads();   // every warp is done with the tiles: their memory takes the warps' partials
-  stamp(3);   // tiles walked
+  if (cls == z) stamp(3);   // first class walked
   {
     const int r0 = lane >> 2, c0 = (lane & 3) << 1;
 #pragma unroll
@@ -379,9 +395,11 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   }
   __syncthreads();
 
-  // ---- one partial per block goes to block 0 of the cluster; block 0 merges in block order
-  stamp(4);   // the block's partial is complete
-  for (int i = tid; i < GP * PW; i += kThreads) st_peer_f32(recv + (size_t)z * GP * PW + i, 0u, run[i]);
+  // ---- the class's partial goes to block 0 of the cluster
+  for (int i = tid; i < GP * PW; i += kThreads) st_peer_f32(recv + (size_t)cls * GP * PW + i, 0u, run[i]);
+  }   // classes
+  stamp(4);   // the block's partials are complete
+  // ---- block 0 merges the classes in class order
   cluster_sync_all();
   stamp(5);   // the cluster has met
   if (z != 0 || bad) {
@@ -392,10 +410,10 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     const int g = i / D, dd = i % D;
     float M = -CUDART_INF_F;
 #pragma unroll
-    for (int c = 0; c < kCluster; ++c) M = fmaxf(M, recv[((size_t)c * GP + g) * PW + D]);
+    for (int c = 0; c < kClasses; ++c) M = fmaxf(M, recv[((size_t)c * GP + g) * PW + D]);
     float L = 0.f, a = 0.f;
 #pragma unroll
-    for (int c = 0; c < kCluster; ++c) {
+    for (int c = 0; c < kClasses; ++c) {
       const float mc = recv[((size_t)c * GP + g) * PW + D];
       if (mc != -CUDART_INF_F) {
         const float f = exp2f(mc - M);
@@ -414,23 +432,23 @@ int log2_exact(int x) {
   return (1 << s) == x ? s : -1;
 }
 
-template <int D, int GP, int kCluster, int kStages>
+template <int D, int GP, int kClasses, int kStages>
 int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* q_start, const int* ctx_len, const float* cos_t,
            const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv, float scale, int window,
-           int* status, unsigned long long* trace, cudaStream_t stream) {
+           int blocks_per_cluster, int* status, unsigned long long* trace, cudaStream_t stream) {
   constexpr int PW = D + 2;
   const size_t smem = (size_t)kStages * 2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
-                      (size_t)kCluster * GP * PW * 4;
+                      (size_t)kClasses * GP * PW * 4 + (size_t)4 * GP * PW * 4;
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kCluster, kStages>,
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(nkv, R, kCluster);
+  cfg.gridDim = dim3(nkv, R, blocks_per_cluster);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -438,13 +456,13 @@ int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int 
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = kCluster;
+  attr[0].val.clusterDim.z = blocks_per_cluster;
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = kvb_pdl_enabled() ? 2 : 1;
   cudaError_t le = cudaLaunchKernelEx(
-      &cfg, decode_attention_mma_kernel<D, GP, kCluster, kStages>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
+      &cfg, decode_attention_mma_kernel<D, GP, kClasses, kStages>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
       (__nv_bfloat16*)v_pages, write_kv, block_table, max_pages, page_shift, num_pages, q_start, ctx_len, cos_t, sin_t,
       table_len, rot, (__nv_bfloat16*)out, nq, nkv, nq / nkv, scale * 1.4426950408889634f, window, status, trace);
   if (le != cudaSuccess) return (int)le;
@@ -462,8 +480,9 @@ KVB_EXPORT int kvb_decode_attention_mma_supported(int d, int group, int page_siz
 // qkv: [T, (nq + 2 nkv) d] bfloat16 as the projection wrote it; request r's token is row
 // q_start[r] at position ctx_len[r]-1.  write_kv = 0: the layer reads another layer's
 // cache and writes nothing.  cos_t/sin_t: [table_len, rot/2] or nullptr.  out: [T, nq d].
-// cluster: 4 or 8 blocks per (request, kv head); a function of the engine's limits only, so
-// that a token's sums are cut the same way in every batch.
+// cluster: 4 or 8 classes of tiles per (request, kv head); a function of the engine's limits
+// only, so that a token's sums are cut the same way in every batch.  How many blocks share
+// the classes is chosen here from the size of the grid.
 // trace: nullptr, or [R * nkv * cluster, 8] uint64 for the phase stamps of every block (profiling only).
 // Uses no memory beyond its operands.  R <= 65535.
 KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv,
@@ -479,10 +498,14 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
     return KVB_ERR_BAD_SIZE;
   const int G = nq / nkv;
   const int ps = log2_exact(page_size);
+  // blocks per cluster: as many as there are classes while the grid stays small, fewer for
+  // larger batches (every block then walks several classes and pays its fixed cost once)
+  int S = cluster;
+  while (S > 1 && (long long)R * nkv * S > 4 * 148) S >>= 1;
   // two stages while every block of the grid fits on the GPU at once
-  const bool deep = (long long)R * nkv * cluster <= 2 * 148;
+  const bool deep = (long long)R * nkv * S <= 2 * 148;
 #define KVB_DM_ARGS qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, q_start, \
-                    ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, status, trace, stream
+                    ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, S, status, trace, stream
 #define KVB_DM(D, GP)                                                       \
   do {                                                                      \
     if (cluster == 4 && deep) return launch<D, GP, 4, 2>(KVB_DM_ARGS);      \

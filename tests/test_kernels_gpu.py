@@ -513,3 +513,12 @@ def test_tensor_core_decode_attention(nq, nkv, d, rot, page_size, window, write)
                                    dev([0, 1], torch.int32), dev(ctxs[3:4], torch.int32), cos_t, sin_t, rot, nq, nkv, d,
                                    1 / math.sqrt(d), window, st)
     assert torch.equal(one[0], out[3])
+    # ... nor on the size of the batch, which decides how many blocks share a request's classes
+    # of tiles: the same requests many times over (a large grid, clusters of 1 or 2 blocks)
+    reps = 12
+    big = (qkv.repeat(reps, 1), dkp, dvp, write, dev(np.tile(tables, (reps, 1)), torch.int32),
+           dev(np.arange(R * reps + 1), torch.int32), dev(ctxs * reps, torch.int32), cos_t, sin_t, rot, nq, nkv, d,
+           1 / math.sqrt(d), window, st)
+    assert torch.equal(ops.decode_attention_mma(*big), out.repeat(reps, 1))
+    assert torch.equal(ops.decode_attention_mma(*big, max_positions=4096), out4.repeat(reps, 1))
+    assert int(st.item()) == 0
