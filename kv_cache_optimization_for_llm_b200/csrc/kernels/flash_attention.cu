@@ -300,9 +300,10 @@ paged_flash_attention_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row
 //                 (only where a warp's rows meet the diagonal or the window's edge), keeps the
 //                 running max and sum in float32, and writes its probabilities in bfloat16 to
 //                 shared memory, again in the swizzled K-major layout
-//   O' = P V      tcgen05.mma (M 128, N 64, K 16 x 8); V is read as the MN-major operand, so
+//   P V           tcgen05.mma (M 128, N 64, K 16 x 4); V is read as the MN-major operand, so
 //                 the same [key][dim] tile serves
-//   O = O corr + O'   in registers: a thread holds 32 of its row's 64 outputs.
+//   O += P V      accumulates in tensor memory; the rows are rescaled there only when the running
+//                 maximum has grown by more than a threshold since the last time.
 // The next tile's keys are requested as soon as S has been computed, its values as soon as
 // P V has been, so loads run under the softmax and the products; two blocks share an SM and
 // fill each other's gaps.  mbarrier waits are bounded: a wait that runs out records
@@ -365,6 +366,24 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 32 consecutive columns of this thread's lane of tensor memory, written
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024
 // bytes apart, base aligned to 1024 bytes.  The same image is a K-major operand (rows are
@@ -495,10 +514,13 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
     umma_commit(&bar_s[i & 1]);
   };
 
-  float o[D / 2];
-#pragma unroll
-  for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
-  float m_run = -CUDART_INF_F, l_run = 0.f;   // l_run: the sum over this thread's half of the keys
+  // The output accumulates in tensor memory over the tiles.  Probabilities are taken against a
+  // reference maximum m_ref that follows the running maximum only when that has grown by more
+  // than kRescale (in log2 units): any reference gives the same softmax as long as nothing
+  // overflows (probabilities stay below 2^kRescale), and the rows of the output then need
+  // rescaling (read, multiply, write back) only a few times per sequence.
+  constexpr float kRescale = 8.0f;
+  float m_ref = -CUDART_INF_F, l_run = 0.f;   // l_run: the sum over this thread's half of the keys
   bool failed = false;
 
   cp_async_wait<2>();                      // Q and K0
@@ -543,25 +565,30 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
     mx_s[h * BM + r] = mx * scale_log2;    // the scale is positive: the maximum commutes with it
     __syncthreads();
     if (*abort_flag) { failed = true; break; }
-    const float m_new = fmaxf(m_run, fmaxf(mx_s[r], mx_s[BM + r]));
-    const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;   // a row with no key yet: everything stays zero
-    const float corr = (m_run == -CUDART_INF_F) ? 0.f : ex2(m_run - m_use);
-    m_run = m_new;
-    l_run *= corr;
+    const float m_new = fmaxf(m_ref, fmaxf(mx_s[r], mx_s[BM + r]));
+    const bool grow = m_new > m_ref + kRescale;     // also: the row's first key (m_ref is -inf)
 
-    // ---- O += P V(i-1), which ran while this tile's scores were read; then O is rescaled
+    // ---- P V(i-1), which ran while this tile's scores were read, has to be over before the
+    // output may be rescaled and before P is written again
     if (i > 0) {
       if (!failed && !mbar_wait(bar_o, (unsigned)(i - 1) & 1u)) { failed = true; *abort_flag = 1; }
       tc_fence_after();
-      float pv[32];
-      tmem_ld32(o_cols, pv);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) o[j] += pv[j];
     }
     load_tile(i + 1, v_s + ((i + 1) & 1) * kKVBytes, v_pages);   // V(i-1) has been read: its buffer takes V(i+1)
     cp_async_commit();
+    if (__any_sync(0xffffffffu, grow)) {
+      const float corr = !grow ? 1.0f : (m_ref == -CUDART_INF_F ? 0.f : ex2(m_ref - m_new));
+      if (i > 0) {                                  // before the first product the output holds nothing yet
+        float ov[32];
+        tmem_ld32(o_cols, ov);
 #pragma unroll
-    for (int j = 0; j < D / 2; ++j) o[j] *= corr;
+        for (int j = 0; j < 32; ++j) ov[j] *= corr;
+        tmem_st32(o_cols, ov);
+      }
+      l_run *= corr;
+      if (grow) m_ref = m_new;
+    }
+    const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;   // a row with no key yet: everything stays zero
 
     // ---- P(i): probabilities of this thread's 32 keys, bfloat16, pieces 4h..4h+3 of row r
     unsigned pk[16];
@@ -589,17 +616,17 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
       const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (i & 1) * kKVBytes));
 #pragma unroll
       for (int kk = 0; kk < BNK / 16; ++kk)   // 16 keys per step: 32 bytes along a row of P, 16 rows of V
-        umma_bf16(tmem + 128, pd + 2 * kk, vd + 128 * kk, idesc_o, kk > 0 ? 1u : 0u);
+        umma_bf16(tmem + 128, pd + 2 * kk, vd + 128 * kk, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
       umma_commit(bar_o);
     }
   }
+  float o[D / 2];
+#pragma unroll
+  for (int j = 0; j < D / 2; ++j) o[j] = 0.f;
   if (!failed && n_tiles > 0) {
     if (!mbar_wait(bar_o, (unsigned)(n_tiles - 1) & 1u)) { failed = true; *abort_flag = 1; }
     tc_fence_after();
-    float pv[32];
-    tmem_ld32(o_cols, pv);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) o[j] += pv[j];
+    tmem_ld32(o_cols, o);
   }
   cp_async_wait<0>();
   __syncthreads();
