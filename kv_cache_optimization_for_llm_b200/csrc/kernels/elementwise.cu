@@ -188,6 +188,32 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
   }
 }
 
+// bfloat16 with blocks that are multiples of 8: eight elements per thread, 16-byte accesses.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I,
+                                       int BL, size_t groups) {
+  pdl_trigger();
+  pdl_wait();
+  const int gpr = I >> 3;  // groups of eight per row
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / gpr;
+    const int i = (int)(idx - t * gpr) << 3;
+    const size_t at = t * 2 * I + (size_t)(i / BL) * 2 * BL + (i % BL);
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + at);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + at + BL);
+    const unsigned gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    unsigned ow[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float a = silu_mul_one(__uint_as_float(gw[k] << 16), __uint_as_float(uw[k] << 16));
+      const float b = silu_mul_one(__uint_as_float(gw[k] & 0xffff0000u), __uint_as_float(uw[k] & 0xffff0000u));
+      __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+      ow[k] = *reinterpret_cast<unsigned*>(&v);
+    }
+    *reinterpret_cast<uint4*>(out + t * I + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int BL, size_t total) {
   pdl_trigger();
@@ -205,6 +231,15 @@ KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int BL, in
   if (T_ <= 0) return 0;
   if (BL < 1 || I % BL) return KVB_ERR_BAD_SIZE;
   const int threads = 256;
+  if (dtype == KVB_BF16 && BL % 8 == 0 && (reinterpret_cast<uintptr_t>(gu) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    const size_t work8 = (size_t)T_ * (I / 8);
+    const size_t want8 = (work8 + threads - 1) / threads;
+    const int blocks8 = (int)(want8 < (size_t)148 * 32 ? want8 : (size_t)148 * 32);
+    kvb_launch(silu_mul_bf16x8_kernel, dim3(blocks8), dim3(threads), 0, stream, (const __nv_bfloat16*)gu,
+               (__nv_bfloat16*)out, I, BL, work8);
+    return kvb_launch_result();
+  }
   const bool vec = (BL % 4 == 0);
   const size_t work = vec ? (size_t)T_ * (I / 4) : (size_t)T_ * I;
   size_t want = (work + threads - 1) / threads;

@@ -69,6 +69,14 @@ def test_silu_mul_and_embedding(dtype):
     out = ops.silu_mul(dev(gu, DT[dtype]))
     g, u = gu[:, :333], gu[:, 333:]
     assert rel_err(out, g / (1 + np.exp(-g)) * u) < TOL[dtype]
+    # rows that hold gate and up in alternating blocks, at widths that take the 4-wide, the 8-wide
+    # (bfloat16) and the one-by-one form
+    for inter, block in ((384, 64), (200, 8), (100, 4), (99, 3)):
+        gu = as64(dev(rng.normal(size=(5, 2 * inter)) * 4, DT[dtype]))
+        out = ops.silu_mul(dev(gu, DT[dtype]), block=block)
+        v = gu.reshape(5, inter // block, 2, block)
+        g, u = v[:, :, 0].reshape(5, inter), v[:, :, 1].reshape(5, inter)
+        assert rel_err(out, g / (1 + np.exp(-g)) * u) < TOL[dtype], (inter, block)
     table = as64(dev(rng.normal(size=(777, 100)), DT[dtype]))
     ids = [0, 776, 5, 5, 300]
     st = status()
