@@ -14,9 +14,12 @@
 // When N gives too few blocks to pull the whole memory system, K is split over the
 // blocks of a thread-block cluster (gridDim.y = cluster size): block s sends its
 // float32 partial of row m to slot s in the shared memory of block m mod S (distributed
-// shared memory), the cluster meets once at its hardware barrier, and every block adds
-// up the slots of its rows in block order, so the sum has one fixed order.  No scratch
-// in global memory, no counters, no spinning.
+// shared memory) with st.async, which counts the bytes on an mbarrier of the receiving
+// block; a block goes on as soon as the partials of its own rows are there (it does not
+// wait for the whole cluster) and adds up the slots in block order, so the sum has one
+// fixed order.  The cluster meets once, at the start, while the first weights are already
+// on their way, so that no block writes to a peer whose barrier is not set up.  No
+// scratch in global memory, no counters.
 // The weights do not depend on the step's data: a block requests its first ring of
 // weight tiles before it waits for the kernel in front of it (programmatic dependent
 // launch), so that the first tiles are under way while that kernel finishes.
@@ -100,11 +103,15 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Stores v at the place in block `rank`'s shared memory that `my_smem_ptr` names in ours.
-__device__ __forceinline__ void st_peer_f32(void* my_smem_ptr, unsigned rank, float v) {
-  unsigned remote;
+// Stores v at the place in block `rank`'s shared memory that `my_smem_ptr` names in ours and
+// counts its four bytes on that block's mbarrier `my_bar` (asynchronous: the store is
+// complete for the receiver when its barrier says so).
+__device__ __forceinline__ void st_async_peer_f32(void* my_smem_ptr, void* my_bar, unsigned rank, float v) {
+  unsigned remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(my_bar)), "r"(rank));
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(remote), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
 }
 
 
@@ -183,7 +190,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   unsigned long long* full = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(fin) + p.fin_bytes);
   unsigned long long* empty = full + p.stages;
   unsigned long long* accum = empty + p.stages;
-  unsigned* tmem_holder = reinterpret_cast<unsigned*>(accum + 1);
+  unsigned long long* red_bar = accum + 1;       // counts the bytes of the partials that peers send
+  unsigned* tmem_holder = reinterpret_cast<unsigned*>(red_bar + 1);
   int* flags = reinterpret_cast<int*>(tmem_holder + 1);  // [0]: abort, [1]: this block reduces the splits
   float* rstd = reinterpret_cast<float*>(flags + 2);     // [16] row scale
 
@@ -196,33 +204,41 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int my_tiles = max(0, kt1 - kt0);
   const unsigned tmem_cols = p.MP < 32 ? 32u : (unsigned)p.MP;
 
+  // the rows whose final sums this block holds when K is split: blockIdx.y, + splits, ...
+  const int rows_own = (p.splits > 1 && p.M > (int)blockIdx.y) ? (p.M - 1 - (int)blockIdx.y) / p.splits + 1 : 0;
+  const int first = min(p.stages, my_tiles);
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(accum, 1);
+    mbar_init(red_bar, 1);
     flags[0] = 0; flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // every block of the cluster sends 128 floats for each of this block's rows
+    if (p.splits > 1) mbar_expect_tx(red_bar, (unsigned)(rows_own * p.splits * TILE_N * 4));
+    // The weights do not depend on the kernel before this one: the first round of weight
+    // tiles is requested at once, before anything else.
+    for (int i = 0; i < first; ++i) {
+      mbar_expect_tx(&full[i], a_bytes + b_bytes);
+      tma_load_2d(a_s + (size_t)i * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[i]);
+    }
+    stamp(p, 1);                 // first round of weight tiles requested
   }
   if (warp == 1) tmem_alloc(tmem_holder, tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_d = *tmem_holder;
+  // From here on peers may write into this block's shared memory: every block's barrier is set up.
+  if (p.splits > 1) cluster_sync_all();
   // The kernel behind this one may start only now that this block holds its tensor memory:
   // blocks of that kernel which wait, resident, for this grid to finish must not be able to
   // take the columns that a block of this grid still needs.
   pdl_trigger();
 
   if (warp == 0 && lane == 0) {
-    // ---- TMA producer.  The weights do not depend on the kernel before this one: the
-    // first round of weight tiles is requested at once, the rows only after that kernel
-    // has finished.
-    const int first = min(p.stages, my_tiles);
-    for (int i = 0; i < first; ++i) {
-      mbar_expect_tx(&full[i], a_bytes + b_bytes);
-      tma_load_2d(a_s + (size_t)i * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[i]);
-    }
-    stamp(p, 1);                 // first round of weight tiles requested
+    // ---- TMA producer.  The rows are requested only after the kernel before this one has
+    // finished.
     pdl_wait();
     stamp(p, 2);                 // the kernel before this one has finished
     for (int i = 0; i < first; ++i)
@@ -321,7 +337,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
   };
   int own_first = 0, own_step = 1;               // the rows whose final sums this block holds
-  if (!aborted) {
+  if (p.splits > 1 || !aborted) {
     if (p.splits == 1) {
       for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
@@ -336,10 +352,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     } else {
       // send row m of this block's partial to slot blockIdx.y of block (m mod S):
-      // red[(m / S) * S + slot][feature] there
+      // red[(m / S) * S + slot][feature] there.  A block that gave up sends zeros, so that the
+      // byte counts of its peers still come out.
       for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
-        if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
+        if (my_tiles > 0 && !aborted) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
         else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
@@ -348,19 +365,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int i = 0; i < 16; ++i) {
           const int m = c + i;
           if (m < p.M)
-            st_peer_f32(red + ((m / p.splits) * p.splits + (int)blockIdx.y) * TILE_N + tid, (unsigned)(m % p.splits), v[i]);
+            st_async_peer_f32(red + ((m / p.splits) * p.splits + (int)blockIdx.y) * TILE_N + tid, red_bar,
+                              (unsigned)(m % p.splits), v[i]);
         }
       }
     }
   }
+  bool red_ok = true;
   if (p.splits > 1) {
-    // Every block of the cluster comes here, aborted or not: the barrier is collective.
-    // After it all partials have arrived and nobody touches a peer's memory any more.
-    cluster_sync_all();
-    if (tid == 0) stamp(p, 7);   // the cluster has met
+    // The partials of this block's rows: complete when the barrier has counted all their bytes.
+    // Nobody leaves before that, so no block writes into the memory of a peer that is gone.
+    if (rows_own > 0) red_ok = mbar_wait(red_bar, 0);
+    red_ok = __syncthreads_and(red_ok) != 0;        // one answer for the whole block
+    if (!red_ok && tid == 0) atomicCAS(p.status, 0, KVB_STATUS_WAIT_TIMEOUT);
+    if (tid == 0) stamp(p, 7);   // this block's partials are here
     own_first = (int)blockIdx.y;
     own_step = p.splits;
-    if (!aborted) {
+    if (!aborted && red_ok) {
       for (int m = own_first, j = 0; m < p.M; m += own_step, ++j) {
         float acc = 0.f;
         for (int s2 = 0; s2 < p.splits; ++s2) acc += red[(j * p.splits + s2) * TILE_N + tid];
@@ -368,7 +389,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
   }
-  if (p.epilogue == EPI_SWIGLU && !aborted) {
+  if (p.epilogue == EPI_SWIGLU && !aborted && red_ok) {
     // gate and up of one feature sit 64 threads apart: pair them through shared memory
     __syncthreads();
     if (tid < TILE_N / 2) {
@@ -382,7 +403,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
   }
-  if (p.epilogue == EPI_RESIDUAL && !aborted) {
+  if (p.epilogue == EPI_RESIDUAL && !aborted && red_ok) {
     __syncthreads();
     const int m = own_first + tid * own_step;       // thread j finishes the block's j-th own row
     if (tid < 16 && m < p.M)
@@ -525,7 +546,7 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
   if (stages > per) stages = per;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 1) * 8 + 16 + 64;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 2) * 8 + 16 + 64;
   CUtensorMap mw, mx;
   int e = cached_map(&mw, w, N, K, ldw, TILE_N);
   if (e) return e;
