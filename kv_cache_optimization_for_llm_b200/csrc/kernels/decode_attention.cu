@@ -1,13 +1,15 @@
 // The attention of a bfloat16 decode step in one launch, on tensor cores.
 //
 // Every request brings one query token.  The 128-key tiles of a request's context fall into
-// C classes (tile t belongs to class t mod C; C is 4 or 8, chosen by the caller from the
-// longest context it allows, never from the batch).  A class is one running softmax over
+// C classes (tile t belongs to class t mod C; C is 4, 8 or 16 by the token's own position,
+// never by the batch: more classes for longer contexts, up to the kernel's capacity, which
+// the caller chooses from the longest context it allows).  A class is one running softmax over
 // its tiles; the C class results are merged in class order.  So the sums of a token are
 // cut at absolute positions and added in one fixed order, whatever else is in the batch.
-// A cluster of S blocks (S divides C; the caller takes a smaller S for a larger batch)
-// serves one (request, key/value head): block z walks the classes z, z + S, ... one after
-// the other.  S changes who computes a class, not what is computed.  The rows of the tensor-core tile are the query
+// A cluster of S blocks (a power of two up to the capacity; the launcher takes a smaller S
+// for a larger batch) serves one (request, key/value head): block z walks the classes z,
+// z + S, ... below C one after the other (a block beyond C has nothing to do).  S changes
+// who computes a class, not what is computed.  The rows of the tensor-core tile are the query
 // heads that share the key/value head (padded to 16), so keys and values are fetched
 // once for the whole group (upstream fetches them once per query head:
 // paged_attention/src/kernels.cu:150-219).
@@ -79,6 +81,10 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
   return row * (D * 2) + ((chunk ^ (row & 7)) << 4);
 }
 
+// How many classes the tiles of a token at position pos fall into: 4 below 2048, 8 below 8192,
+// 16 beyond (32 tiles of 128 keys per class at most up to 65536 positions).
+__host__ __device__ __forceinline__ int classes_at(int pos) { return pos < 2048 ? 4 : (pos < 8192 ? 8 : 16); }
+
 // GP: the group of query heads padded to 4, 8 or 16 (rows that are kept).  kClasses: classes
 // of tiles per (request, kv head); gridDim.z = cluster size = blocks that share them.  kStages: tiles in shared memory at a time, 2 when the whole grid
 // is resident at once anyway (small batches: the second tile is under way before the
@@ -128,6 +134,9 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   const int n_tiles = bad ? 0 : pos / kTile + 1;
   const int t_first = lo / kTile;               // tiles below it hold no key the window keeps
   const int t_star = bad ? -1 : pos / kTile;    // the tile of the token's own position
+  // Classes of tiles for this token: a function of its own position only (and of the kernel's
+  // capacity kClasses, which the launcher takes from the longest context of the step).
+  const int C = min(kClasses, classes_at(pos));
 
   for (int i = tid; i < GP * PW; i += kThreads) run[i] = ((i % PW) == D) ? -CUDART_INF_F : 0.f;
 
@@ -167,13 +176,13 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   // "the tile that is multiplied next".
   const int S = (int)gridDim.z;
   int my_first = z;                              // first tile of the class that is being walked
-  while (my_first < t_first) my_first += kClasses;
-  int n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / kClasses + 1 : 0;
+  while (my_first < t_first) my_first += C;
+  int n_mine = (z < C && my_first < n_tiles) ? (n_tiles - 1 - my_first) / C + 1 : 0;   // a block beyond the classes has no tile
   unsigned have0 = 0, have1 = 0;
   if (n_mine > 0) have0 = request_tile(my_first, 0, write_kv != 0);
   cp_async_commit();
   if (kStages > 1) {
-    if (n_mine > 1) have1 = request_tile(my_first + kClasses, 1, write_kv != 0);
+    if (n_mine > 1) have1 = request_tile(my_first + C, 1, write_kv != 0);
     cp_async_commit();
   }
 
@@ -199,7 +208,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       q_s[i] = val * scale_log2;
     }
     // the new key and value: stored by the block that owns their tile
-    const int c_star = t_star % kClasses;                          // the class of the new key's tile
+    const int c_star = t_star % C;                          // the class of the new key's tile
     const bool owner = write_kv && (t_star >= t_first) && (c_star % S == z);
     if (owner) {
       const int lp = pos >> page_shift;
@@ -210,7 +219,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         const size_t dst = ((((size_t)page * nkv + hk) << page_shift) + (pos & page_mask)) * D;
         const __nv_bfloat16* kh = row + (size_t)(nq + hk) * D;
         const __nv_bfloat16* vh = row + (size_t)(nq + nkv + hk) * D;
-        const int star_i = (t_star - my_first) / kClasses;   // which tile of its class it is
+        const int star_i = (t_star - my_first) / C;   // which tile of its class it is
         const bool direct = c_star == z && star_i < kStages;   // its tile is one of those already requested
         const int slot = pos - t_star * kTile;          // 0..127: warp slot>>5, key slot&31
         for (int dd = tid; dd < D; dd += kThreads) {
@@ -260,17 +269,17 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   // Class after class.  Each warp walks its 32-key slices of the class's tiles on its own, with
   // a running max and sum per head (rows lane/4 and lane/4 + 8) and a running output in
   // registers; the slices of a warp are private to it, so the walk needs no block-wide barrier.
-  for (int cls = z; cls < kClasses; cls += S) {
+  for (int cls = z; cls < C; cls += S) {
   if (cls != z) {
     // the new key, if in this class, is in the cache by now
     my_first = cls;
-    while (my_first < t_first) my_first += kClasses;
-    n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / kClasses + 1 : 0;
+    while (my_first < t_first) my_first += C;
+    n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / C + 1 : 0;
     have0 = have1 = 0;
     if (n_mine > 0) have0 = request_tile(my_first, 0, false);
     cp_async_commit();
     if (kStages > 1) {
-      if (n_mine > 1) have1 = request_tile(my_first + kClasses, 1, false);
+      if (n_mine > 1) have1 = request_tile(my_first + C, 1, false);
       cp_async_commit();
     }
   }
@@ -350,7 +359,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     __syncwarp();   // the slice is read; the next request may overwrite it
     if (i + kStages < n_mine) {
       // the new key, if in that tile, is in the cache by now
-      const unsigned h = request_tile(my_first + (i + kStages) * kClasses, stage, false);
+      const unsigned h = request_tile(my_first + (i + kStages) * C, stage, false);
       if (stage) have1 = h; else have0 = h;
     }
     cp_async_commit();
@@ -410,10 +419,10 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     const int g = i / D, dd = i % D;
     float M = -CUDART_INF_F;
 #pragma unroll
-    for (int c = 0; c < kClasses; ++c) M = fmaxf(M, recv[((size_t)c * GP + g) * PW + D]);
+    for (int c = 0; c < C; ++c) M = fmaxf(M, recv[((size_t)c * GP + g) * PW + D]);
     float L = 0.f, a = 0.f;
 #pragma unroll
-    for (int c = 0; c < kClasses; ++c) {
+    for (int c = 0; c < C; ++c) {
       const float mc = recv[((size_t)c * GP + g) * PW + D];
       if (mc != -CUDART_INF_F) {
         const float f = exp2f(mc - M);
@@ -441,10 +450,17 @@ int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int 
   const size_t smem = (size_t)kStages * 2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
                       (size_t)kClasses * GP * PW * 4 + (size_t)4 * GP * PW * 4;
   static bool attr_set = false;
-  if (!attr_set && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+  if (!attr_set) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    if (kClasses > 8) {   // clusters of 16 are beyond the portable size
+      cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages>,
+                                           cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (e != cudaSuccess) return (int)e;
+    }
     attr_set = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -480,19 +496,22 @@ KVB_EXPORT int kvb_decode_attention_mma_supported(int d, int group, int page_siz
 // qkv: [T, (nq + 2 nkv) d] bfloat16 as the projection wrote it; request r's token is row
 // q_start[r] at position ctx_len[r]-1.  write_kv = 0: the layer reads another layer's
 // cache and writes nothing.  cos_t/sin_t: [table_len, rot/2] or nullptr.  out: [T, nq d].
-// cluster: 4 or 8 classes of tiles per (request, kv head); a function of the engine's limits
-// only, so that a token's sums are cut the same way in every batch.  How many blocks share
-// the classes is chosen here from the size of the grid.
+// max_ctx: the longest context of the step (a hint from the host, 0: unknown): it decides how
+// many classes the kernel has room for and how many blocks share a (request, kv head), not
+// the sums, which are cut by each token's own position.
 // trace: nullptr, or [R * nkv * cluster, 8] uint64 for the phase stamps of every block (profiling only).
 // Uses no memory beyond its operands.  R <= 65535.
 KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv,
                                         const int* block_table, int max_pages, int page_size, int num_pages,
                                         const int* q_start, const int* ctx_len, const float* cos_t,
                                         const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv,
-                                        int d, float scale, int window, int cluster, int* status,
+                                        int d, float scale, int window, int max_ctx, int* status,
                                         unsigned long long* trace, cudaStream_t stream) {
   if (R <= 0) return 0;
-  if (cluster != 4 && cluster != 8) return KVB_ERR_BAD_SIZE;
+  // the kernel is built for as many classes as the longest context of the step needs
+  // (head size 128: 8 at most, for the shared memory the partials take)
+  int cluster = max_ctx > 0 ? classes_at(max_ctx - 1) : 16;
+  if (d != 64 && cluster > 8) cluster = 8;
   if (nkv < 1 || nq % nkv || !kvb_decode_attention_mma_supported(d, nq / nkv, page_size) || R > 65535 || (rot & 1) ||
       rot > d || nkv > 65535)
     return KVB_ERR_BAD_SIZE;
@@ -506,6 +525,11 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
   const bool deep = (long long)R * nkv * S <= 2 * 148;
 #define KVB_DM_ARGS qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, q_start, \
                     ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, S, status, trace, stream
+#define KVB_DM16(GP)                                                        \
+  do {                                                                      \
+    if (cluster == 16 && deep) return launch<64, GP, 16, 2>(KVB_DM_ARGS);   \
+    if (cluster == 16) return launch<64, GP, 16, 1>(KVB_DM_ARGS);           \
+  } while (0)
 #define KVB_DM(D, GP)                                                       \
   do {                                                                      \
     if (cluster == 4 && deep) return launch<D, GP, 4, 2>(KVB_DM_ARGS);      \
@@ -513,6 +537,7 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
     if (deep) return launch<D, GP, 8, 2>(KVB_DM_ARGS);                      \
     return launch<D, GP, 8, 1>(KVB_DM_ARGS);                                \
   } while (0)
+  if (d == 64 && cluster == 16) { if (G <= 4) KVB_DM16(4); if (G <= 8) KVB_DM16(8); KVB_DM16(16); }
   if (d == 64) { if (G <= 4) KVB_DM(64, 4); if (G <= 8) KVB_DM(64, 8); KVB_DM(64, 16); }
   if (G <= 4) KVB_DM(128, 4);
   if (G <= 8) KVB_DM(128, 8);

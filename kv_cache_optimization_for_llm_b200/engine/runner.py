@@ -133,7 +133,9 @@ class ModelRunner:
         batch = self.builder.build(padded, self.manager, self.vocab_size, pad_reqs_to=bucket,
                                    scratch_page=self.cache.scratch_page, scratch_slot=self.cache.scratch_slot,
                                    sampled=self.sampled[:-1])
-        got = self._graphs.get(bucket)
+        # one graph per padded batch size and class of context length (launches are sized by both)
+        key = (bucket, ops.decode_context_class(batch.max_ctx_len))
+        got = self._graphs.get(key)
         if got is None:
             # Every row's logits are produced; rows are picked after the replay.
             rows = torch.arange(bucket, dtype=torch.int32, device=self.device)
@@ -150,7 +152,7 @@ class ModelRunner:
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
             got = (graph, out, ops.launch_count - before, rows)
-            self._graphs[bucket] = got
+            self._graphs[key] = got
             ops.launch_count = before                       # captured, not launched
         graph, out, launches, _rows = got
         graph.replay()

@@ -437,13 +437,31 @@ def decode_attention_mma_supported(d: int, group: int, page_size: int) -> bool:
     return bool(lib("decode_attention").kvb_decode_attention_mma_supported(c_int(d), c_int(group), c_int(page_size)))
 
 
+def decode_context_class(max_ctx: int) -> int:
+    """The classes of 128-key tiles (4, 8 or 16) that the longest context of a decode step
+    needs in the tensor-core decode attention.  The launch (kernel variant, blocks per request)
+    depends on it, the results do not; steps are replayed from graphs captured per class."""
+    return 4 if max_ctx <= 2048 else (8 if max_ctx <= 8192 else 16)
+
+
+def decode_launch_context(batch) -> int:
+    """The context length a decode step's launches are sized for: the upper end of the class
+    of the step's longest context, so that every step of a class launches alike (a captured
+    graph is replayed for all of them)."""
+    c = decode_context_class(int(batch.max_ctx_len))
+    return 2048 if c == 4 else (8192 if c == 8 else 1 << 30)
+
+
 def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
-                         nq, nkv, d, scale, window, status, max_positions: int = 1 << 30,
+                         nq, nkv, d, scale, window, status, max_ctx: int = 0,
                          trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The attention of a bfloat16 decode step in one launch on tensor cores: rotary
     encoding of query and new key, cache write, attention over 128-key tiles spread over
     a cluster of blocks, merge through distributed shared memory.  No scratch.
-    The cluster has 4 blocks when the engine allows at most 4096 positions, else 8."""
+    A token's tiles fall into 4 classes below position 2048, 8 below 8192, 16 beyond (head
+    size 64), whatever the batch; up to that many blocks share a (request, kv head).
+    ``max_ctx``: the longest context of the step if the host knows it (the launch is sized
+    for it), 0 otherwise."""
     _need_cuda(qkv, k_pages)
     assert qkv.dtype == torch.bfloat16
     R = ctx_len.numel()
@@ -452,7 +470,7 @@ def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, 
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), c_int(1 if write_kv else 0), _p(block_table),
         c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
         _p(cos), _p(sin), c_int(0 if cos is None else cos.shape[0]), c_int(rot), _p(out), c_int(R), c_int(nq),
-        c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), c_int(4 if max_positions <= 4096 else 8),
+        c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), c_int(int(max_ctx)),
         _p(status), _p(trace), _stream())
     _check(rc, "decode_attention_mma")
     return out
@@ -472,7 +490,8 @@ def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv,
     group, page_size = nq // nkv, k_pages.shape[2]
     if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_mma_supported(d, group, page_size):
         return decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
-                                    cos, sin, rot, nq, nkv, d, scale, window, batch.status, max_positions)
+                                    cos, sin, rot, nq, nkv, d, scale, window, batch.status,
+                                    max_ctx=decode_launch_context(batch))
     if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_supported(d, group):
         return decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
                                       cos, sin, rot, nq, nkv, d, scale, window, max_positions, batch.status)

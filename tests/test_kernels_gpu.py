@@ -506,9 +506,11 @@ def test_tensor_core_decode_attention(nq, nkv, d, rot, page_size, window, write)
     st = status()
     args = (qkv, dkp, dvp, write, dev(tables, torch.int32), dev(np.arange(R + 1), torch.int32),
             dev(ctxs, torch.int32), cos_t, sin_t, rot, nq, nkv, d, 1 / math.sqrt(d), window, st)
-    out4 = ops.decode_attention_mma(*args, max_positions=4096)     # clusters of 4
+    out4 = ops.decode_attention_mma(*args, max_ctx=max(ctxs))      # the launch sized for the longest context here
     assert rel_err(out4, np.array(refs)) < TOL[dtype] * 1.5
-    out = ops.decode_attention_mma(*args)                          # clusters of 8
+    out = ops.decode_attention_mma(*args)                          # sized for any context
+    # the classes a token's tiles fall into follow from its own position, not from the launch
+    assert torch.equal(out, out4)
     assert int(st.item()) == 0
     assert rel_err(out, np.array(refs)) < TOL[dtype] * 1.5
     for page, slot, k_want, v_want in new_kv:
@@ -528,5 +530,5 @@ def test_tensor_core_decode_attention(nq, nkv, d, rot, page_size, window, write)
            dev(np.arange(R * reps + 1), torch.int32), dev(ctxs * reps, torch.int32), cos_t, sin_t, rot, nq, nkv, d,
            1 / math.sqrt(d), window, st)
     assert torch.equal(ops.decode_attention_mma(*big), out.repeat(reps, 1))
-    assert torch.equal(ops.decode_attention_mma(*big, max_positions=4096), out4.repeat(reps, 1))
+    assert torch.equal(ops.decode_attention_mma(*big, max_ctx=max(ctxs)), out4.repeat(reps, 1))
     assert int(st.item()) == 0
