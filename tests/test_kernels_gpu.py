@@ -532,3 +532,55 @@ def test_tensor_core_decode_attention(nq, nkv, d, rot, page_size, window, write)
     assert torch.equal(ops.decode_attention_mma(*big), out.repeat(reps, 1))
     assert torch.equal(ops.decode_attention_mma(*big, max_ctx=max(ctxs)), out4.repeat(reps, 1))
     assert int(st.item()) == 0
+
+
+def test_tensor_core_decode_attention_long_contexts():
+    """Contexts beyond 8192 tokens: 16 classes of tiles and clusters of 16 blocks.  No rotary
+    encoding here, the cache already holds every key; one key far back is made to stand out."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    nq, nkv, d, page_size = 8, 2, 64, 16
+    rng = np.random.default_rng(5)
+    ctxs = [8200, 12001, 70, 2049, 16500]
+    R = len(ctxs)
+    max_pages = max(-(-c // page_size) for c in ctxs) + 1
+    num_pages = sum(-(-c // page_size) for c in ctxs) + 2
+    kp = np.zeros((num_pages, nkv, page_size, d))
+    vp = np.zeros((num_pages, nkv, page_size, d))
+    free = list(rng.permutation(num_pages))
+    tables = np.full((R, max_pages), -1, dtype=np.int32)
+    rows, refs = [], []
+    for r, ctx in enumerate(ctxs):
+        k = as64(dev(rng.normal(size=(ctx, nkv, d)), torch.bfloat16))
+        v = as64(dev(rng.normal(size=(ctx, nkv, d)), torch.bfloat16))
+        q = as64(dev(rng.normal(size=(nq, d)), torch.bfloat16))
+        far = ctx // 3                                     # this key gets a large score for head 0
+        k[far, 0] = as64(dev(q[0] * 1.5, torch.bfloat16))
+        for j in range(ctx):
+            lp = j // page_size
+            if tables[r, lp] < 0:
+                tables[r, lp] = free.pop()
+        idx = np.arange(ctx)
+        kp[tables[r, idx // page_size], :, idx % page_size] = k
+        vp[tables[r, idx // page_size], :, idx % page_size] = v
+        out = np.zeros((nq, d))
+        for h in range(nq):
+            s_ = k[:, h // (nq // nkv)] @ q[h] / math.sqrt(d)
+            p = np.exp(s_ - s_.max()); p /= p.sum()
+            out[h] = p @ v[:, h // (nq // nkv)]
+        refs.append(out.reshape(-1))
+        # the row brings the newest key and value again; write_kv is off, so they are not used
+        rows.append(np.concatenate([q.reshape(-1), k[ctx - 1].reshape(-1), v[ctx - 1].reshape(-1)]))
+    qkv = dev(np.array(rows), torch.bfloat16)
+    dkp, dvp = dev(kp, torch.bfloat16), dev(vp, torch.bfloat16)
+    st = status()
+    args = (qkv, dkp, dvp, False, dev(tables, torch.int32), dev(np.arange(R + 1), torch.int32), dev(ctxs, torch.int32),
+            None, None, 0, nq, nkv, d, 1 / math.sqrt(d), None, st)
+    out = ops.decode_attention_mma(*args, max_ctx=max(ctxs))
+    assert int(st.item()) == 0
+    assert rel_err(out, np.array(refs)) < TOL["bfloat16"] * 1.5
+    # a launch sized for any context, and one request alone: the same bits
+    assert torch.equal(out, ops.decode_attention_mma(*args))
+    one = ops.decode_attention_mma(qkv[1:2].contiguous(), dkp, dvp, False, dev(tables[1:2], torch.int32),
+                                   dev([0, 1], torch.int32), dev(ctxs[1:2], torch.int32), None, None, 0, nq, nkv, d,
+                                   1 / math.sqrt(d), None, st, max_ctx=ctxs[1])
+    assert torch.equal(one[0], out[1])
