@@ -186,9 +186,41 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     cp_async_commit();
   }
 
+  // The new key and value are stored by the block that owns their tile; where they go does
+  // not depend on the projection in front, so the page is looked up before the wait.
+  const int c_star = bad ? 0 : t_star % C;                  // the class of the new key's tile
+  const bool owner = !bad && write_kv && (t_star >= t_first) && (c_star % S == z);
+  int own_page = -1;
+  if (owner) {
+    const int lp = pos >> page_shift;
+    own_page = lp < max_pages ? table[lp] : -1;
+    if (own_page < 0 || own_page >= num_pages) {
+      if (tid == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+      own_page = -1;
+    }
+  }
+  const bool own_t = own_page >= 0 && tid < D;              // this thread carries dim `tid` of the new key and value
+
   pdl_wait();
   stamp(1);   // the projection in front has finished
   const __nv_bfloat16* row = qkv + (size_t)q_start[r] * q_row_stride;
+  // the owner's loads go out first, so that they are under way while the queries are rotated
+  float nk1 = 0.f, nk2 = 0.f, nc = 1.f, ns = 0.f;
+  __nv_bfloat16 nv = __float2bfloat16_rn(0.f);
+  if (own_t) {
+    const __nv_bfloat16* kh = row + (size_t)(nq + hk) * D;
+    const int dd = tid;
+    if (rotary && dd < rot) {
+      const int j = dd < half ? dd : dd - half;
+      nc = cos_t[(size_t)pos * half + j];
+      ns = sin_t[(size_t)pos * half + j];
+      nk1 = to_f32(kh[j]);
+      nk2 = to_f32(kh[j + half]);
+    } else {
+      nk1 = to_f32(kh[dd]);
+    }
+    nv = row[(size_t)(nq + nkv + hk) * D + dd];
+  }
   if (!bad) {
     // the group's queries, rotated (pairs (j, j + rot/2) of the first rot dims), scaled, float32
     for (int i = tid; i < GP * D; i += kThreads) {
@@ -207,39 +239,24 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       }
       q_s[i] = val * scale_log2;
     }
-    // the new key and value: stored by the block that owns their tile
-    const int c_star = t_star % C;                          // the class of the new key's tile
-    const bool owner = write_kv && (t_star >= t_first) && (c_star % S == z);
-    if (owner) {
-      const int lp = pos >> page_shift;
-      const int page = lp < max_pages ? table[lp] : -1;
-      if (page < 0 || page >= num_pages) {
-        if (tid == 0) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
-      } else {
-        const size_t dst = ((((size_t)page * nkv + hk) << page_shift) + (pos & page_mask)) * D;
-        const __nv_bfloat16* kh = row + (size_t)(nq + hk) * D;
-        const __nv_bfloat16* vh = row + (size_t)(nq + nkv + hk) * D;
+    // the new key and value
+    if (owner && own_page >= 0) {
+      {
+        const size_t dst = ((((size_t)own_page * nkv + hk) << page_shift) + (pos & page_mask)) * D;
         const int star_i = (t_star - my_first) / C;   // which tile of its class it is
         const bool direct = c_star == z && star_i < kStages;   // its tile is one of those already requested
         const int slot = pos - t_star * kTile;          // 0..127: warp slot>>5, key slot&31
-        for (int dd = tid; dd < D; dd += kThreads) {
-          float val;
-          if (rotary && dd < rot) {
-            const int j = dd < half ? dd : dd - half;
-            const float c = cos_t[(size_t)pos * half + j], sn = sin_t[(size_t)pos * half + j];
-            const float x1 = to_f32(kh[j]), x2 = to_f32(kh[j + half]);
-            val = dd < half ? x1 * c - x2 * sn : x1 * sn + x2 * c;
-          } else {
-            val = to_f32(kh[dd]);
-          }
+        if (own_t) {
+          const int dd = tid;
+          const float val = (rotary && dd < rot) ? (dd < half ? nk1 * nc - nk2 * ns : nk1 * ns + nk2 * nc) : nk1;
           const __nv_bfloat16 kr = __float2bfloat16_rn(val);
           k_pages[dst + dd] = kr;
-          v_pages[dst + dd] = vh[dd];
+          v_pages[dst + dd] = nv;
           if (direct) {
             const int key = slot & 31;
             const int off_b = star_i * kTileBytes + (slot >> 5) * 32 * D * 2 + swz<D>(key, dd >> 3) + (dd & 7) * 2;
             *reinterpret_cast<__nv_bfloat16*>(k_s + off_b) = kr;
-            *reinterpret_cast<__nv_bfloat16*>(v_s + off_b) = vh[dd];
+            *reinterpret_cast<__nv_bfloat16*>(v_s + off_b) = nv;
           }
         }
         if (direct) {
