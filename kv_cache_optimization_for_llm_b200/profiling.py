@@ -4,6 +4,11 @@ random-weights model, with the CUDA profiler range switched on around them only.
     python -m kv_cache_optimization_for_llm_b200.profiling decode  --batch 8 --layers 4 --steps 2
     python -m kv_cache_optimization_for_llm_b200.profiling prefill --tokens 2048 --layers 4
     python -m kv_cache_optimization_for_llm_b200.profiling attention --batch 8 --context 16000
+    python -m kv_cache_optimization_for_llm_b200.profiling timeline --batch 8 --layers 16
+
+``timeline`` prints, for the kernels of one captured decode step, the medians over their blocks
+of the phase stamps that the product kernel and the decode attention kernel write themselves
+(globaltimer), relative to the moment the kernel in front of each had finished.
 
 ``attention`` times the decode attention kernel alone (CUDA events around a graph of 16
 launches over 16 layers' caches, so that the keys and values do not come from L2) and prints
@@ -35,7 +40,7 @@ LLAMA_3_2_1B = {
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["decode", "prefill", "attention"])
+    ap.add_argument("what", choices=["decode", "prefill", "attention", "timeline"])
     ap.add_argument("--config-json", help="a config.json; default: the Llama-3.2-1B shape")
     ap.add_argument("--layers", type=int, default=None, help="override num_hidden_layers")
     ap.add_argument("--batch", type=int, default=8)
@@ -58,6 +63,8 @@ def main(argv=None) -> int:
         cfg["num_hidden_layers"] = a.layers
     if a.what == "attention":
         return _attention_alone(cfg, a.batch, a.context)
+    if a.what == "timeline":
+        return _timeline(cfg, a.batch, a.prompt)
     page = 16
     need = a.batch * (a.prompt + 64 + a.steps) if a.what == "decode" else a.tokens
     llm = LLM.from_random(cfg, dtype=a.dtype, page_size=page, num_pages=need // page + 64,
@@ -99,6 +106,84 @@ def main(argv=None) -> int:
     ms = (time.perf_counter() - t0) * 1e3 / a.steps
     prof.cudaProfilerStop()
     print(f"decode, batch {a.batch}, {cfg['num_hidden_layers']} layers: {ms:.3f} ms per step")
+    return 0
+
+
+def _timeline(cfg, batch: int, prompt: int) -> int:
+    """Phase stamps of the product and attention kernels inside a captured decode step."""
+    import numpy as np
+    import torch
+
+    from . import LLM, SamplingParams, ops
+    pool = [torch.zeros(4096, 8, dtype=torch.int64, device="cuda") for _ in range(8 * cfg["num_hidden_layers"] + 8)]
+    calls = []          # (kind, trace buffer) in launch order
+
+    def buffer_for(kind):
+        t = pool[len(calls) % len(pool)]
+        calls.append((kind, t))
+        return t
+    names = {}
+    plain, fused, attn = ops.gemm_skinny, ops.gemm_skinny_fused, ops.decode_attention_mma
+
+    def kind_of(w, extra=""):
+        return names.setdefault((w.shape[0], w.shape[1], extra), f"product {w.shape[0]}x{w.shape[1]}{extra}")
+    ops.gemm_skinny = lambda x, w, dt, st, x_is_static=False, trace=None, **kw: plain(
+        x, w, dt, st, x_is_static, buffer_for(kind_of(w)), **kw)
+    ops.gemm_skinny_fused = lambda x, w, st, **kw: fused(
+        x, w, st, **{**kw, "trace": buffer_for(kind_of(w, " +residual" if kw.get("into") is not None else
+                                                         (" +silu" if kw.get("epilogue") == "swiglu" else "")))})
+    ops.decode_attention_mma = lambda *args, **kw: attn(*args, **{**kw, "trace": buffer_for("decode attention")})
+
+    llm = LLM.from_random(cfg, dtype="bfloat16", page_size=16, num_pages=batch * (prompt + 128) // 16 + 64,
+                          max_num_seqs=batch, max_num_batched_tokens=2048, max_model_len=4096)
+    eng = llm.engine
+    rng = np.random.default_rng(0)
+    sp = SamplingParams(max_tokens=64, ignore_eos=True)
+    ids = [eng.add_request(rng.integers(0, eng.runner.vocab_size, prompt).tolist(), sp) for _ in range(batch)]
+    produced = {i: 0 for i in ids}
+    while min(produced.values()) < 1:
+        for ev in eng.step():
+            if ev.token is not None:
+                produced[ev.request_id] += 1
+    for _ in range(4):
+        eng.step()
+    torch.cuda.synchronize()
+    # the graph was captured by the last forward pass that went through the hooks: its calls are the tail of the list
+    n = 5 * cfg["num_hidden_layers"] + 1
+    captured = calls[-n:]
+    for t in pool:
+        t.zero_()
+    for _ in range(4):
+        eng.step()
+    torch.cuda.synchronize()
+    gemm_cols = [("first tile", 3), ("last product issued", 4), ("accumulator complete", 5), ("partials here", 7), ("stored", 6)]
+    attn_cols = [("queries ready", 2), ("first class walked", 3), ("partials sent", 4), ("cluster met", 5), ("stored", 6)]
+    rows, t_first = {}, None
+    for kind, t in captured:
+        a = t.cpu().numpy().astype(np.float64)
+        a = a[a[:, 0] > 0]
+        if len(a) == 0:
+            continue
+        is_attn = kind == "decode attention"
+        dep = np.median(a[:, 1 if is_attn else 2])
+        if t_first is None:
+            t_first = a[:, 0].min()
+        vals = [(np.median(a[:, 0]) - dep) / 1e3]
+        for _, col in (attn_cols if is_attn else gemm_cols):
+            c = a[:, col]
+            c = c[c > 0]
+            vals.append((np.median(c) - dep) / 1e3 if len(c) else float("nan"))
+        vals.append((a[:, 6].max() - dep) / 1e3)
+        rows.setdefault(kind, []).append(vals)
+        t_last = a[:, 6].max()
+    print(f"decode step, batch {batch}: {(t_last - t_first) / 1e3:.1f} us from the first product's first block to the LM head's last store")
+    print("microseconds relative to the end of each kernel's wait for the kernel in front (medians over blocks, mean over layers)")
+    for kind, v in rows.items():
+        arr = np.array(v)
+        m = np.array([np.nanmean(c) if np.isfinite(c).any() else float("nan") for c in arr.T])
+        cols = attn_cols if kind == "decode attention" else gemm_cols
+        txt = "  ".join(f"{nm} {x:5.1f}" for (nm, _), x in zip(cols, m[1:-1]))
+        print(f"  {kind:32s} x{len(v):3d}  blocks start {m[0]:6.1f}  {txt}  last block done {m[-1]:5.1f}")
     return 0
 
 
