@@ -58,11 +58,12 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
   return ok != 0;
 }
 // Bounded wait.  false: the limit ran out.
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
-  for (unsigned i = 0; i < kSpinLimit; ++i)
+__device__ __forceinline__ bool mbar_wait_limited(void* bar, unsigned parity, unsigned limit) {
+  for (unsigned i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) { return mbar_wait_limited(bar, parity, kSpinLimit); }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -420,6 +421,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
 }
 
+// One warp waits, with a limit of `polls`, on a barrier that nothing ever completes, and
+// reports what the product kernel reports when one of its waits runs out.
+__global__ void wait_selftest_kernel(unsigned polls, int* status) {
+  __shared__ unsigned long long bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (!mbar_wait_limited(&bar, 0, polls) && threadIdx.x == 0) atomicCAS(status, 0, KVB_STATUS_WAIT_TIMEOUT);
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -612,4 +625,12 @@ KVB_EXPORT int kvb_gemm_skinny_fused(const void* x, int ldx, const void* w, int 
   ex.resid = resid; ex.ld_resid = ld_resid; ex.xb_out = reinterpret_cast<__nv_bfloat16*>(xb_out);
   ex.sumsq_out = sumsq_out;
   return gemm_skinny_launch(x, ldx, w, ldw, out, 0, M, N, K, x_is_static, epilogue, ex, status, trace, stream);
+}
+
+// Runs the bounded wait of this file's kernels against a barrier that is never completed: after
+// `polls` polls the kernel gives up, records KVB_STATUS_WAIT_TIMEOUT in *status and returns; the
+// context stays usable.  For tests of the give-up path.
+KVB_EXPORT int kvb_wait_selftest(unsigned polls, int* status, cudaStream_t stream) {
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(polls, status);
+  return kvb_launch_result();
 }

@@ -605,3 +605,10 @@ def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, ro
         raise KernelError(f"gemm_skinny_fused refuses M={M}, N={N}, K={K}, epilogue {epilogue}")
     _check(rc, "gemm_skinny_fused")
     return Folded(xb, sumsq) if into is not None else out
+
+
+def wait_selftest(polls: int, status: torch.Tensor) -> None:
+    """Lets the product kernels' bounded barrier wait run out on a barrier that nothing
+    completes: ``status`` receives the wait-timeout code, the kernel returns."""
+    rc = lib("gemm_bf16").kvb_wait_selftest(ctypes.c_uint(int(polls)), _p(status), _stream())
+    _check(rc, "wait_selftest")

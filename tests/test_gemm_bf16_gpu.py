@@ -164,3 +164,20 @@ def test_weightless_norm_kernel():
         got = ops.add_rmsnorm(resid.clone(), None, None, 1e-5, torch.float32)
         want = ops.add_rmsnorm(resid.clone(), None, torch.ones(H, device="cuda"), 1e-5, torch.float32)
         assert torch.equal(got, want)
+
+
+def test_a_wait_that_runs_out_reports_and_returns():
+    """Every barrier wait of the tensor-core kernels has a limit; when it runs out the kernel
+    records a status the host can read and returns.  Here the limit is short and the barrier
+    is one that nothing completes; afterwards the device works as before."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.wait_selftest(2000, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 4 and "wait" in ops.STATUS_TEXT[4].lower()
+    st.zero_()
+    x = _bf(torch.randn(4, 256, device="cuda"))
+    w = _bf(torch.randn(128, 256, device="cuda") / 16)
+    out = ops.gemm_skinny(x, w, torch.float32, st)
+    assert int(st.item()) == 0
+    assert (out.double() - x.double() @ w.double().t()).abs().max().item() < 1e-3
