@@ -12,14 +12,15 @@
 // to the TMA thread.  The four warps then read the accumulator with tcgen05.ld (warp
 // w owns features 32w..32w+31) and store C[row, feature].
 // When N gives too few blocks to pull the whole memory system, K is split over the
-// blocks of a thread-block cluster (gridDim.y = cluster size): block s sends its
-// float32 partial of row m to slot s in the shared memory of block m mod S (distributed
-// shared memory) with st.async, which counts the bytes on an mbarrier of the receiving
-// block; a block goes on as soon as the partials of its own rows are there (it does not
-// wait for the whole cluster) and adds up the slots in block order, so the sum has one
-// fixed order.  The cluster meets once, at the start, while the first weights are already
-// on their way, so that no block writes to a peer whose barrier is not set up.  No
-// scratch in global memory, no counters.
+// blocks of a thread-block cluster (gridDim.y = cluster size).  Groups of four consecutive
+// rows have an owner block (group g: block g mod S); block s sends its float32 partials of a
+// group, four rows of a feature in one 16-byte st.async, to slot s in the shared memory of
+// the owner (distributed shared memory), which counts the bytes on an mbarrier; an owner
+// goes on as soon as the partials of its own rows are there (it does not wait for the whole
+// cluster) and adds up the slots in block order, so the sum has one fixed order.  The
+// cluster meets once, at the start, while the first weights are already on their way, so
+// that no block writes to a peer whose barrier is not set up.  No scratch in global
+// memory, no counters.
 // The weights do not depend on the step's data: a block requests its first ring of
 // weight tiles before it waits for the kernel in front of it (programmatic dependent
 // launch), so that the first tiles are under way while that kernel finishes.
@@ -104,17 +105,18 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Stores v at the place in block `rank`'s shared memory that `my_smem_ptr` names in ours and
-// counts its four bytes on that block's mbarrier `my_bar` (asynchronous: the store is
-// complete for the receiver when its barrier says so).
-__device__ __forceinline__ void st_async_peer_f32(void* my_smem_ptr, void* my_bar, unsigned rank, float v) {
+// Stores four floats (16 bytes, 16-byte aligned) at the place in block `rank`'s shared memory
+// that `my_smem_ptr` names in ours and counts their bytes on that block's mbarrier `my_bar`
+// (asynchronous: the store is complete for the receiver when its barrier says so).
+__device__ __forceinline__ void st_async_peer_f32x4(void* my_smem_ptr, void* my_bar, unsigned rank, float a, float b,
+                                                    float c, float d) {
   unsigned remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_u32(my_bar)), "r"(rank));
-  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
-               ::"r"(remote), "r"(__float_as_uint(v)), "r"(remote_bar) : "memory");
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(remote), "r"(__float_as_uint(a)), "r"(__float_as_uint(b)), "r"(__float_as_uint(c)),
+                 "r"(__float_as_uint(d)), "r"(remote_bar) : "memory");
 }
-
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of
 // 128 bytes, groups of 8 rows 1024 bytes apart, tile base aligned to 1024 bytes.
@@ -194,7 +196,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   unsigned long long* red_bar = accum + 1;       // counts the bytes of the partials that peers send
   unsigned* tmem_holder = reinterpret_cast<unsigned*>(red_bar + 1);
   int* flags = reinterpret_cast<int*>(tmem_holder + 1);  // [0]: abort, [1]: this block reduces the splits
-  float* rstd = reinterpret_cast<float*>(flags + 2);     // [16] row scale
+  float* rstd = reinterpret_cast<float*>(flags + 2);     // [64] row scale
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) stamp(p, 0);   // block started
@@ -205,8 +207,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int my_tiles = max(0, kt1 - kt0);
   const unsigned tmem_cols = p.MP < 32 ? 32u : (unsigned)p.MP;
 
-  // the rows whose final sums this block holds when K is split: blockIdx.y, + splits, ...
-  const int rows_own = (p.splits > 1 && p.M > (int)blockIdx.y) ? (p.M - 1 - (int)blockIdx.y) / p.splits + 1 : 0;
+  // Which rows' final sums this block holds.  K not split: all.  K split: groups of four
+  // consecutive rows go round the blocks, group g to block g mod splits, so that a sender hands
+  // over four rows of a feature in one 16-byte store (measured faster than single rows spread
+  // over all blocks, at every number of rows).
+  const int S = p.splits, y = (int)blockIdx.y;
+  const int groups_all = (p.M + 3) >> 2;
+  const int groups_own = (S > 1 && groups_all > y) ? (groups_all - 1 - y) / S + 1 : 0;
+  // own rows are numbered j = 0 .. own_slots-1 (the last group may reach beyond M)
+  const int own_slots = S == 1 ? p.M : 4 * groups_own;
+  auto own_row = [&](int j) -> int { return S == 1 ? j : 4 * (y + (j >> 2) * S) + (j & 3); };
+  const unsigned red_expect = (unsigned)(groups_own * S * TILE_N * 16);
   const int first = min(p.stages, my_tiles);
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -216,7 +227,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // every block of the cluster sends 128 floats for each of this block's rows
-    if (p.splits > 1) mbar_expect_tx(red_bar, (unsigned)(rows_own * p.splits * TILE_N * 4));
+    if (S > 1) mbar_expect_tx(red_bar, red_expect);
     // The weights do not depend on the kernel before this one: the first round of weight
     // tiles is requested at once, before anything else.
     for (int i = 0; i < first; ++i) {
@@ -278,28 +289,27 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   // the explicit wait also covers blocks that had no k tile)
   pdl_wait();
   if (p.x_sumsq && warp >= 2) {
-    // Row scale: warps 2 and 3 have nothing else to do while the products run.  Lane pairs
-    // share a row; each thread adds up the parts in their order (both get the same sum).
-    const int r = (tid - 64) >> 2;
-    if (r < 16) {
+    // Row scale: warps 2 and 3 have nothing else to do while the products run.  A thread takes
+    // a row and adds up its parts in their order.
+    const int r = tid - 64;
+    if (r < p.M) {
       float ss = 0.f;
-      if (r < p.M) {
-        const float* src = p.x_sumsq + (size_t)r * p.x_parts;
-        int q = 0;
-        for (; q + 4 <= p.x_parts; q += 4) {        // four loads in flight, added in order
-          const float a0 = src[q], a1 = src[q + 1], a2 = src[q + 2], a3 = src[q + 3];
-          ss = (((ss + a0) + a1) + a2) + a3;
-        }
-        for (; q < p.x_parts; ++q) ss += src[q];
+      const float* src = p.x_sumsq + (size_t)r * p.x_parts;
+      int q = 0;
+      for (; q + 4 <= p.x_parts; q += 4) {        // four loads in flight, added in order
+        const float a0 = src[q], a1 = src[q + 1], a2 = src[q + 2], a3 = src[q + 3];
+        ss = (((ss + a0) + a1) + a2) + a3;
       }
-      if ((tid & 3) == 0) rstd[r] = rsqrtf(ss / (float)p.K + p.eps);
+      for (; q < p.x_parts; ++q) ss += src[q];
+      rstd[r] = rsqrtf(ss / (float)p.K + p.eps);
     }
   }
   if (p.epilogue == EPI_RESIDUAL && n0 + tid < p.N) {
     // the residual values this thread is going to add to: on their way while the products run
-    const int step = p.splits > 1 ? p.splits : 1;
-    for (int m = p.splits > 1 ? (int)blockIdx.y : 0; m < p.M; m += step)
-      asm volatile("prefetch.global.L1 [%0];" ::"l"(p.resid + (size_t)m * p.ld_resid + n0 + tid));
+    for (int j = 0; j < own_slots; ++j) {
+      const int m = own_row(j);
+      if (m < p.M) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.resid + (size_t)m * p.ld_resid + n0 + tid));
+    }
   }
   bool good = true;
   if (my_tiles > 0) good = mbar_wait(accum, 0);
@@ -337,9 +347,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
   };
-  int own_first = 0, own_step = 1;               // the rows whose final sums this block holds
-  if (p.splits > 1 || !aborted) {
-    if (p.splits == 1) {
+  if (S > 1 || !aborted) {
+    if (S == 1) {
       for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
         if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
@@ -352,9 +361,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (c + i < p.M) emit(c + i, c + i, v[i]);
       }
     } else {
-      // send row m of this block's partial to slot blockIdx.y of block (m mod S):
-      // red[(m / S) * S + slot][feature] there.  A block that gave up sends zeros, so that the
-      // byte counts of its peers still come out.
+      // Send this block's partials to the rows' owners, slot blockIdx.y there.  A block that gave
+      // up sends zeros, so that the byte counts of its peers still come out.
       for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
         if (my_tiles > 0 && !aborted) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
@@ -362,54 +370,94 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
         }
+        // rows c+4k .. c+4k+3 are group c/4 + k: red4[(group / S) * S + slot][feature] in block group mod S
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int m = c + i;
-          if (m < p.M)
-            st_async_peer_f32(red + ((m / p.splits) * p.splits + (int)blockIdx.y) * TILE_N + tid, red_bar,
-                              (unsigned)(m % p.splits), v[i]);
+        for (int k = 0; k < 4; ++k) {
+          const int g4 = (c >> 2) + k;
+          if (g4 < groups_all)
+            st_async_peer_f32x4(reinterpret_cast<float4*>(red) + ((g4 / S) * S + y) * TILE_N + tid, red_bar,
+                                (unsigned)(g4 % S), v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
         }
       }
     }
   }
   bool red_ok = true;
-  if (p.splits > 1) {
+  if (S > 1) {
     // The partials of this block's rows: complete when the barrier has counted all their bytes.
     // Nobody leaves before that, so no block writes into the memory of a peer that is gone.
-    if (rows_own > 0) red_ok = mbar_wait(red_bar, 0);
+    if (own_slots > 0) red_ok = mbar_wait(red_bar, 0);
     red_ok = __syncthreads_and(red_ok) != 0;        // one answer for the whole block
     if (!red_ok && tid == 0) atomicCAS(p.status, 0, KVB_STATUS_WAIT_TIMEOUT);
     if (tid == 0) stamp(p, 7);   // this block's partials are here
-    own_first = (int)blockIdx.y;
-    own_step = p.splits;
     if (!aborted && red_ok) {
-      for (int m = own_first, j = 0; m < p.M; m += own_step, ++j) {
-        float acc = 0.f;
-        for (int s2 = 0; s2 < p.splits; ++s2) acc += red[(j * p.splits + s2) * TILE_N + tid];
-        emit(m, j, acc);
+      {
+        for (int gi = 0; gi < groups_own; ++gi) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s2 = 0; s2 < S; ++s2) {          // the blocks' partials in block order
+            const float4 part = reinterpret_cast<const float4*>(red)[(gi * S + s2) * TILE_N + tid];
+            acc.x += part.x; acc.y += part.y; acc.z += part.z; acc.w += part.w;
+          }
+          const int m0 = own_row(4 * gi);
+          if (p.epilogue == EPI_RESIDUAL) {
+            // the group's four rows side by side, so that their loads and their reductions overlap
+            float a4[4] = {acc.x, acc.y, acc.z, acc.w}, nv[4], sq[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              nv[k] = 0.f;
+              if (m0 + k < p.M && n < p.N)
+                nv[k] = p.resid[(size_t)(m0 + k) * p.ld_resid + n] + (scaled ? a4[k] * rstd[m0 + k] : a4[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (m0 + k < p.M && n < p.N) {
+                p.resid[(size_t)(m0 + k) * p.ld_resid + n] = nv[k];
+                p.xb_out[(size_t)(m0 + k) * p.N + n] = __float2bfloat16_rn(nv[k]);
+              }
+              sq[k] = nv[k] * nv[k];
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) sq[k] += __shfl_xor_sync(0xffffffffu, sq[k], o);
+            }
+            if (lane == 0) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) fin[(4 * gi + k) * 4 + warp] = sq[k];
+            }
+          } else {
+            if (m0 < p.M) emit(m0, 4 * gi, acc.x);
+            if (m0 + 1 < p.M) emit(m0 + 1, 4 * gi + 1, acc.y);
+            if (m0 + 2 < p.M) emit(m0 + 2, 4 * gi + 2, acc.z);
+            if (m0 + 3 < p.M) emit(m0 + 3, 4 * gi + 3, acc.w);
+          }
+        }
       }
     }
   }
   if (p.epilogue == EPI_SWIGLU && !aborted && red_ok) {
     // gate and up of one feature sit 64 threads apart: pair them through shared memory
     __syncthreads();
-    if (tid < TILE_N / 2) {
-      const int col = blockIdx.x * (TILE_N / 2) + tid;
-      if (col < p.N / 2) {
-        for (int m = own_first, j = 0; m < p.M; m += own_step, ++j) {
-          const float g = fin[j * TILE_N + tid], u = fin[j * TILE_N + TILE_N / 2 + tid];
-          const float a = g * (1.0f / (1.0f + expf(-g))) * u;
-          reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * (p.N / 2) + col] = __float2bfloat16_rn(a);
-        }
+    // 64 columns per row; the block's threads take (row, column) pairs in turn
+    const int c = tid & (TILE_N / 2 - 1);
+    const int col = blockIdx.x * (TILE_N / 2) + c;
+    if (col < p.N / 2) {
+      for (int j = tid >> 6; j < own_slots; j += kThreads / (TILE_N / 2)) {
+        const int m = own_row(j);
+        if (m >= p.M) continue;
+        const float g = fin[j * TILE_N + c], u = fin[j * TILE_N + TILE_N / 2 + c];
+        const float a = g * (1.0f / (1.0f + expf(-g))) * u;
+        reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * (p.N / 2) + col] = __float2bfloat16_rn(a);
       }
     }
   }
   if (p.epilogue == EPI_RESIDUAL && !aborted && red_ok) {
     __syncthreads();
-    const int m = own_first + tid * own_step;       // thread j finishes the block's j-th own row
-    if (tid < 16 && m < p.M)
-      p.sumsq_out[(size_t)m * gridDim.x + blockIdx.x] =
-          ((fin[tid * 4] + fin[tid * 4 + 1]) + fin[tid * 4 + 2]) + fin[tid * 4 + 3];
+    if (tid < own_slots) {                          // thread j finishes the block's j-th own row
+      const int m = own_row(tid);
+      if (m < p.M)
+        p.sumsq_out[(size_t)m * gridDim.x + blockIdx.x] =
+            ((fin[tid * 4] + fin[tid * 4 + 1]) + fin[tid * 4 + 2]) + fin[tid * 4 + 3];
+    }
   }
   if (aborted) {
     // give copies that may still be in flight time to land before the block ends
@@ -536,21 +584,31 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
   p.splits = splits;
   p.out_f32 = out_f32; p.out = out; p.status = status; p.trace = trace;
   if (epilogue < EPI_STORE || epilogue > EPI_RESIDUAL) return KVB_ERR_BAD_SIZE;
-  if (epilogue != EPI_STORE && (M > 16 || out_f32)) return KVB_ERR_BAD_SIZE;
+  if (epilogue != EPI_STORE && (M > 64 || out_f32)) return KVB_ERR_BAD_SIZE;
   if (epilogue == EPI_SWIGLU && (N % TILE_N)) return KVB_ERR_BAD_SIZE;
   if (epilogue == EPI_RESIDUAL && (!ex.resid || !ex.sumsq_out || !ex.xb_out || ex.ld_resid < N || ex.x_sumsq))
     return KVB_ERR_BAD_SIZE;
-  if (ex.x_sumsq && (M > 16 || ex.x_parts < 1)) return KVB_ERR_BAD_SIZE;
+  if (ex.x_sumsq && (M > 64 || ex.x_parts < 1)) return KVB_ERR_BAD_SIZE;
   p.epilogue = epilogue;
   p.resid = ex.resid; p.ld_resid = ex.ld_resid; p.xb_out = ex.xb_out; p.sumsq_out = ex.sumsq_out;
   p.x_sumsq = ex.x_sumsq; p.x_parts = ex.x_parts; p.eps = ex.eps;
-  p.fin_bytes = epilogue == EPI_SWIGLU ? MP * TILE_N * 4 : epilogue == EPI_RESIDUAL ? 16 * 4 * 4 : 0;
   const int stage_bytes = TILE_N * TILE_K * 2 + MP * TILE_K * 2;
   // two blocks per SM while the stages stay deep enough, one block otherwise
   const int budget = MP <= 64 ? 108 * 1024 : 200 * 1024;
-  // room for the partials of this block's rows from every block of the cluster
-  int red_bytes = splits > 1 ? ((M + splits - 1) / splits) * splits * TILE_N * 4 : 0;
-  if (red_bytes + p.fin_bytes > budget - 2 * stage_bytes) { splits = 1; red_bytes = 0; }   // no room: one block does all of K
+  // Room for the partials of this block's rows from every block of the cluster, and for the
+  // finished sums that an epilogue passes between threads (one slot per own row; see the kernel
+  // for which rows a block owns).
+  auto own_slots = [&](int s) {
+    if (s == 1) return M;
+    return 4 * ((((M + 3) >> 2) + s - 1) / s);
+  };
+  auto fin_bytes = [&](int s) {
+    return epilogue == EPI_SWIGLU ? own_slots(s) * TILE_N * 4 : epilogue == EPI_RESIDUAL ? own_slots(s) * 4 * 4 : 0;
+  };
+  int red_bytes = splits > 1 ? own_slots(splits) * splits * TILE_N * 4 : 0;
+  if (red_bytes + fin_bytes(splits) > budget - 2 * stage_bytes) { splits = 1; red_bytes = 0; }   // no room: one block does all of K
+  p.fin_bytes = fin_bytes(splits);
+  if (p.fin_bytes > budget - 2 * stage_bytes) return KVB_ERR_BAD_SIZE;
   p.splits = splits;
   p.red_bytes = red_bytes;
   int stages = (budget - red_bytes - p.fin_bytes) / stage_bytes;
@@ -559,7 +617,7 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
   if (stages > per) stages = per;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 2) * 8 + 16 + 64;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 2) * 8 + 16 + 256;
   CUtensorMap mw, mx;
   int e = cached_map(&mw, w, N, K, ldw, TILE_N);
   if (e) return e;
@@ -600,7 +658,7 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
 // weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
 // block (profiling only).
 // epilogue (see EPI_*): 0 store; 1 SwiGLU on row-interleaved weights, out is bfloat16
-// [M, N/2], N a multiple of 128, M <= 16.
+// [M, N/2], N a multiple of 128, M <= 64.
 // Uses no memory beyond its operands.
 KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, void* out, int out_f32, int M, int N,
                                int K, int x_is_static, int epilogue, int* status, unsigned long long* trace,
@@ -610,7 +668,7 @@ KVB_EXPORT int kvb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, v
                             stream);
 }
 
-// The same product with the residual stream's add and RMSNorm folded around it, M <= 16.
+// The same product with the residual stream's add and RMSNorm folded around it, M <= 64.
 //  - x_sumsq != nullptr (row scale): row m of the result is multiplied by
 //    rsqrt(sum_p x_sumsq[m, p] / K + eps) before the epilogue (0 or 1) sees it; x holds the
 //    bare residual rows in bfloat16 and W has the norm's weight multiplied into its columns.

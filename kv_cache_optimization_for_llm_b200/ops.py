@@ -181,7 +181,7 @@ def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token
 
 # ------------------------------------------------------------------ matrix products
 
-SKINNY_MAX_ROWS = int(__import__('os').environ.get('KVB200_SKINNY_MAX_ROWS', '16'))
+SKINNY_MAX_ROWS = int(__import__('os').environ.get('KVB200_SKINNY_MAX_ROWS', '32'))   # measured: the library product wins beyond
 _status_word: Dict[int, torch.Tensor] = {}
 
 
@@ -252,7 +252,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
     M, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and x.dtype == w.dtype
-    if (into is not None and fused_norm_rows(M, x.dtype) and _skinny_ok(x, 16) and N % 8 == 0
+    if (into is not None and fused_norm_rows(M, x.dtype) and _skinny_ok(x, FUSED_EPILOGUE_MAX_ROWS) and N % 8 == 0
             and into.dtype == torch.float32 and into.shape == (M, N) and into.is_contiguous()):
         return gemm_skinny_fused(x, w, kernel_status(w.device), into=into,
                                  x_is_static=torch.cuda.is_current_stream_capturing())
@@ -278,7 +278,7 @@ def _skinny_ok(x: torch.Tensor, rows_limit: int) -> bool:
 
 def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, block: int) -> torch.Tensor:
     """``silu(x . gate^T) * (x . up^T)`` with gate and up stored as one matrix whose rows
-    alternate in blocks of ``block`` features.  Up to 16 bfloat16 rows with blocks of 64:
+    alternate in blocks of ``block`` features.  Few bfloat16 rows (SKINNY_MAX_ROWS) with blocks of 64:
     one kernel (the activation is the product's epilogue); otherwise product, then
     activation kernel."""
     I = gate_up.shape[0] // 2
@@ -542,7 +542,7 @@ def gemm_skinny_plan(M: int, N: int, K: int):
     return splits.value, tiles.value
 
 
-FUSED_EPILOGUE_MAX_ROWS = 16
+FUSED_EPILOGUE_MAX_ROWS = int(__import__('os').environ.get('KVB200_FUSED_MAX_ROWS', '32'))   # the kernel takes up to 64
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor,
@@ -550,7 +550,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
     """``x . w^T`` for few rows (M <= 256) on tcgen05 tensor cores, weights streamed by TMA.
 
     ``epilogue``: "store", or "swiglu": ``w`` holds gate and up rows in alternating blocks
-    of 64 and ``silu(gate) * up`` [M, N/2] is returned (up to 16 rows)."""
+    of 64 and ``silu(gate) * up`` [M, N/2] is returned (up to 64 rows)."""
     _need_cuda(x, w)
     M, K = x.shape
     N = w.shape[0]
@@ -570,7 +570,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
 def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, row_scale: Optional[PendingNorm] = None,
                       into: Optional[torch.Tensor] = None, epilogue: str = "store", x_is_static: bool = False,
                       trace: Optional[torch.Tensor] = None):
-    """The skinny product (up to 16 rows) with the residual stream's add and RMSNorm folded around it.
+    """The skinny product (up to 64 rows) with the residual stream's add and RMSNorm folded around it.
 
     ``row_scale``: every row of ``x . w^T`` is multiplied by the 1/rms that follows from the
     pending norm's partial sums (``x`` is then its bare bfloat16 rows, and ``w`` has the
@@ -581,7 +581,7 @@ def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, ro
     N, K = w.shape
     M = x.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
-    assert x.shape[1] == K and M <= 16
+    assert x.shape[1] == K and M <= 64
     ss, parts, eps = None, 0, 0.0
     if row_scale is not None:
         ss, eps = row_scale.sumsq, row_scale.eps
