@@ -164,9 +164,10 @@ def test_norm_weights_far_from_one(name):
         scale = np.abs(ref).max()
         r = ModelRunner(d, EngineConfig(dtype="bfloat16", page_size=16, num_pages=12, max_num_seqs=2,
                                         max_num_batched_tokens=64, max_model_len=96))
-        got = [r.step([StepEntry(0, seq[:40], 0, list(range(40)))]).cpu().numpy()]      # many rows: library product
-        got.append(r.step([StepEntry(0, seq[40:52], 40, list(range(12)))]).cpu().numpy())  # few rows: folded
-        for i in range(52, 70):
+        got = [r.step([StepEntry(0, seq[:34], 0, list(range(34)))]).cpu().numpy()]      # many rows: library product
+        got.append(r.step([StepEntry(0, seq[34:58], 34, list(range(24)))]).cpu().numpy())  # 24 rows: folded
+        got.append(r.step([StepEntry(0, seq[58:64], 58, list(range(6)))]).cpu().numpy())   # 6 rows: folded
+        for i in range(64, 70):
             got.append(r.step([StepEntry(0, [seq[i]], i, [0])]).cpu().numpy())
         r.check_status()
         got = np.concatenate(got)
