@@ -398,7 +398,7 @@ constexpr int kThreads = 256;                // two threads per query row: each 
 constexpr int kQBytes = BM * D * 2;          // [128 rows][64] bfloat16
 constexpr int kKVBytes = BNK * D * 2;        // [64 keys][64]
 constexpr int kPBytes = BM * BNK * 2;        // [128 rows][64 keys]
-constexpr unsigned kTmemCols = 256;          // S: columns 0..63 and 64..127 in turn, P V: columns 128..191
+constexpr unsigned kTmemCols = 128;          // S: columns 0..63, the output: columns 64..127
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -406,7 +406,7 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 3)
 paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
                                 const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                                 const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
@@ -416,8 +416,8 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* q_s = base;                       // [128 rows][64]
-  unsigned char* k_s = q_s + kQBytes;              // [3][64 keys][64]
-  unsigned char* v_s = k_s + 3 * kKVBytes;         // [2][64 keys][64]
+  unsigned char* k_s = q_s + kQBytes;              // [2][64 keys][64]
+  unsigned char* v_s = k_s + 2 * kKVBytes;         // [2][64 keys][64]
   unsigned char* p_s = v_s + 2 * kKVBytes;         // [128 rows][64 keys]
   float* mx_s = reinterpret_cast<float*>(p_s + kPBytes);   // [2][128] the halves' row maxima of a tile
   unsigned long long* bar_s = reinterpret_cast<unsigned long long*>(mx_s + 2 * BM);   // [2]: one per S buffer
@@ -491,12 +491,10 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
     cp_async_16_zfill(dst + swz<D>(lkey, lpart + 1), pages + off + (lpart + 1) * 8, ok);
   };
   // Every thread commits the same groups in the same order, requests or not:
-  //   prologue: [Q, K0] [K1] [K2] [V0];  tile i: [K(i+3)] after S(i) has been read, [V(i+1)] after P V(i-1) has been.
+  //   prologue: [Q, K0] [K1] [V0];  tile i: [K(i+2)] after S(i) has been read, [V(i+1)] after P V(i-1) has been.
   load_tile(0, k_s, k_pages);
   cp_async_commit();
   load_tile(1, k_s + kKVBytes, k_pages);
-  cp_async_commit();
-  load_tile(2, k_s + 2 * kKVBytes, k_pages);
   cp_async_commit();
   load_tile(0, v_s, v_pages);
   cp_async_commit();
@@ -506,14 +504,13 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
   const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
                            ((unsigned)(D >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
   const unsigned lane_base = tmem + ((unsigned)((warp & 3) * 32) << 16);
-  const unsigned o_cols = lane_base + 128 + 32 * h;    // this thread's 32 output dims
+  const unsigned o_cols = lane_base + 64 + 32 * h;     // this thread's 32 output dims
   const unsigned long long qd = smem_desc_sw128(smem_u32(q_s));
-  auto issue_s = [&](int i) {   // S(i) = Q K(i)^T into S buffer i mod 2, keys from buffer i mod 3   (one thread)
-    const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i % 3) * kKVBytes));
+  auto issue_s = [&](int i) {   // S(i) = Q K(i)^T, keys from buffer i mod 2   (one thread)
+    const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i & 1) * kKVBytes));
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk)
-      umma_bf16(tmem + (i & 1) * BNK, qd + 2 * kk, kd + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
-    umma_commit(&bar_s[i & 1]);
+    for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem, qd + 2 * kk, kd + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+    umma_commit(&bar_s[0]);
   };
 
   // The output accumulates in tensor memory over the tiles.  Probabilities are taken against a
@@ -525,26 +522,22 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
   float m_ref = -CUDART_INF_F, l_run = 0.f;   // l_run: the sum over this thread's half of the keys
   bool failed = false;
 
-  // The scores run two tiles ahead of the softmax: S(0) and S(1) are started here, S(i+2) when
-  // tile i's probabilities are handed to the tensor cores.
-  cp_async_wait<2>();                      // Q, K0 and K1
+  // S(0) is started here; S(i+1) as soon as every thread has read S(i) out of tensor memory,
+  // so that it runs under tile i's exponentials.
+  cp_async_wait<2>();                      // Q and K0
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) {
-    tc_fence_after();
-    issue_s(0);
-    if (n_tiles > 1) issue_s(1);
-  }
+  if (tid == 0) { tc_fence_after(); issue_s(0); }
 
   for (int i = 0; i < n_tiles; ++i) {
     const int t = first_tile + i;
     // ---- S(i): this thread's 32 scores, kept in registers
-    if (!failed && !mbar_wait(&bar_s[i & 1], (unsigned)(i >> 1) & 1u)) { failed = true; *abort_flag = 1; }
+    if (!failed && !mbar_wait(&bar_s[0], (unsigned)i & 1u)) { failed = true; *abort_flag = 1; }
     tc_fence_after();
     float v[32];
-    tmem_ld32(lane_base + (i & 1) * BNK + 32 * h, v);
-    load_tile(i + 3, k_s + (i % 3) * kKVBytes, k_pages);   // K(i) has been read: its buffer takes K(i+3)
+    tmem_ld32(lane_base + 32 * h, v);
+    load_tile(i + 2, k_s + (i & 1) * kKVBytes, k_pages);   // K(i) has been read: its buffer takes K(i+2)
     cp_async_commit();
 
     const int kb = t * BNK + 32 * h;       // first key of this thread's half
@@ -563,8 +556,12 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
       }
     }
     mx_s[h * BM + r] = mx * scale_log2;    // the scale is positive: the maximum commutes with it
-    __syncthreads();
+    cp_async_wait<2>();                    // K(i+1) is here (newer: V(i), or V(i) and ... see the group list above)
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();                       // everybody has read S(i): the next tile's scores may overwrite it
     if (*abort_flag) { failed = true; break; }
+    if (tid == 0 && i + 1 < n_tiles) { tc_fence_after(); issue_s(i + 1); }
     const float m_new = fmaxf(m_ref, fmaxf(mx_s[r], mx_s[BM + r]));
     const bool grow = m_new > m_ref + kRescale;     // also: the row's first key (m_ref is -inf)
 
@@ -604,8 +601,8 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
       *reinterpret_cast<uint4*>(p_s + swz<D>(r, 4 * h + q4)) =
           make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
 
-    // ---- P V(i) is started and left to run, and so are the scores of the tile after the next
-    cp_async_wait<2>();                    // V(i) and K(i+2) are here (newer: K(i+3), V(i+1))
+    // ---- P V(i) is started and left to run
+    cp_async_wait<2>();                    // V(i) is here (newer: K(i+2), V(i+1))
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -616,9 +613,8 @@ paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_
       const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (i & 1) * kKVBytes));
 #pragma unroll
       for (int kk = 0; kk < BNK / 16; ++kk)   // 16 keys per step: 32 bytes along a row of P, 16 rows of V
-        umma_bf16(tmem + 128, pd + 2 * kk, vd + 128 * kk, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+        umma_bf16(tmem + 64, pd + 2 * kk, vd + 128 * kk, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
       umma_commit(bar_o);
-      if (i + 2 < n_tiles) issue_s(i + 2);   // everybody has read S(i) out of its buffer
     }
   }
   float o[D / 2];
@@ -660,7 +656,7 @@ int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_p
            int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
            void* out, int nq, int nkv, int G, int gp_shift, float scale, int window, int* status,
            cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)kQBytes + 5 * (size_t)kKVBytes + kPBytes + 2 * BM * 4 + 64;
+  const size_t smem = 1024 + (size_t)kQBytes + 4 * (size_t)kKVBytes + kPBytes + 2 * BM * 4 + 64;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(paged_flash_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
