@@ -188,3 +188,34 @@ def test_a_wait_that_runs_out_reports_and_returns():
     out = ops.gemm_skinny(x, w, torch.float32, st)
     assert int(st.item()) == 0
     assert (out.double() - x.double() @ w.double().t()).abs().max().item() < 1e-3
+
+
+def test_every_number_of_rows_up_to_64():
+    """The split-K partials travel in groups of four rows to their owner blocks; the last group
+    may be partly filled and, with few rows, most blocks own nothing.  Every row count from 1
+    to 64, with K split eight ways: store, add-into-residual with its sums of squares, and the
+    row scale."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    N, K = 256, 1024                       # two tiles of 128 features, eight blocks along K
+    assert ops.gemm_skinny_plan(8, N, K)[0] == 8
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w = _bf(torch.randn(N, K, generator=g, device="cuda") / K ** 0.5)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for M in range(1, 65):
+        x = _bf(torch.randn(M, K, generator=g, device="cuda"))
+        ref = x.double() @ w.double().t()
+        scale = ref.abs().max().item()
+        out = ops.gemm_skinny(x, w, torch.float32, st)
+        assert (out.double() - ref).abs().max().item() < 2e-5 * scale, M
+        resid0 = torch.randn(M, N, generator=g, device="cuda")
+        resid = resid0.clone()
+        folded = ops.gemm_skinny_fused(x, w, st, into=resid)
+        assert (resid.double() - (resid0.double() + ref)).abs().max().item() < 2e-5 * (scale + 4), M
+        want = (resid.double() ** 2).sum(dim=1)
+        assert ((folded.sumsq.double().sum(dim=1) - want).abs() / want).max().item() < 1e-5, M
+        sumsq = (x.float() ** 2).sum(dim=1, keepdim=True).contiguous()
+        pn = ops.PendingNorm(x.float(), x, sumsq, 1e-5, torch.bfloat16)
+        scaled = ops.gemm_skinny_fused(x, w, st, row_scale=pn)
+        rstd = 1.0 / torch.sqrt(sumsq.double() / K + 1e-5)
+        assert (scaled.double() - ref * rstd).abs().max().item() < 5e-3 * (ref * rstd).abs().max().item(), M
+    assert int(st.item()) == 0
