@@ -224,3 +224,48 @@ def test_running_ahead_changes_no_token():
         assert eng.runner.manager.check() == "" and eng.runner.manager.free_pages(0) == 40
     finally:
         shutil.rmtree(d)
+
+
+def test_random_workload_ahead_and_waiting_agree():
+    """120 requests with random prompt lengths, budgets, temperatures, seeds, penalties and
+    arrival gaps, in a pool small enough to drop and recompute some: the engine one step
+    ahead produces the tokens of the engine that waits after every step, and every tenth
+    request's are those of the plain implementation (float32)."""
+    import random
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, SamplingParams
+    from kv_cache_optimization_for_llm_b200.engine.llm_engine import LLMEngine
+    mdir = model_dir("tiny_b", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    rng = random.Random(7)
+    reqs = []
+    for i in range(120):
+        prompt = [rng.randrange(cfg["vocab_size"] - 2) for _ in range(rng.choice([1, 2, 3, 5, 8, 13, 21, 34, 55, 80]))]
+        sp = SamplingParams(max_tokens=rng.choice([1, 2, 4, 9, 17, 30]), temperature=rng.choice([0.0, 0.0, 0.7, 1.3]),
+                            seed=rng.randrange(1000), ignore_eos=True, repetition_penalty=rng.choice([1.0, 1.0, 1.15]))
+        reqs.append((prompt, sp, rng.randrange(0, 3)))        # tokens, sampling, steps until the next arrival
+
+    def run(run_ahead):
+        eng = LLMEngine(mdir, EngineConfig(dtype="float32", page_size=4, num_pages=70, max_num_seqs=6,
+                                           max_num_batched_tokens=24, max_model_len=128, run_ahead=run_ahead))
+        out, waiting, gap, steps = {}, list(enumerate(reqs)), 0, 0
+        while waiting or eng.has_unfinished():
+            while waiting and gap <= 0:
+                i, (prompt, sp, gap) = waiting.pop(0)
+                eng.add_request(prompt, sp, request_id=i)
+                out[i] = []
+            gap -= 1
+            for ev in eng.step():
+                if ev.token is not None:
+                    out[ev.request_id].append(ev.token)
+            steps += 1
+            assert steps < 20000
+        assert eng.stats()["preemptions"] > 0
+        assert eng.runner.manager.check() == "" and eng.runner.manager.free_pages(0) == 70
+        return out
+
+    ahead, waited = run(True), run(False)
+    assert ahead == waited
+    for i in range(0, len(reqs), 10):
+        prompt, sp, _ = reqs[i]
+        assert ahead[i] == P.generate(cfg, w, prompt, sp.max_tokens, temperature=sp.temperature, seed=sp.seed, key=i,
+                                      penalty=sp.repetition_penalty), i
