@@ -1,0 +1,218 @@
+"""Parts that no model of the package has, defined and registered in this file and stepped
+through the engine without any change to the package: a feed-forward that routes every
+token to one of several experts, a position encoding with frequencies of its own over a
+part of the head, and a block that runs its mixer and its feed-forward side by side.
+They are toys that show what the interfaces of the part families carry; none of them is
+a model of anyone's.  Torch operations inside them stand for kernels a real part would
+bring."""
+
+import os
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+
+def _register():
+    from kv_cache_optimization_for_llm_b200.models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from kv_cache_optimization_for_llm_b200.parts import Part, register
+    from kv_cache_optimization_for_llm_b200.registry import register_architecture
+    from kv_cache_optimization_for_llm_b200.weights.loader import WeightSpec
+
+    @register("feed_forward", "toy_top1_experts")
+    class Top1Experts(Part):
+        """Router logits in 32-bit from a router kept in 32-bit; each token goes to the expert
+        with the largest logit, and that expert's output (down . relu(up . x)) is scaled by
+        the softmax probability of the choice.  params: hidden_size, num_experts, expert_size."""
+
+        @classmethod
+        def weight_specs(cls, params):
+            h, e, i = params["hidden_size"], params["num_experts"], params["expert_size"]
+            return {"router": WeightSpec((e, h), "vector"), "up": WeightSpec((e, i, h)),
+                    "down": WeightSpec((e, h, i))}
+
+        def __init__(self, params, weights, ctx):
+            super().__init__(params, weights, ctx)
+            self.router, self.up, self.down = weights["router"], weights["up"], weights["down"]
+            assert self.router.dtype == torch.float32      # a tensor of kind 'vector' stays 32-bit
+
+        def forward(self, x, batch):
+            logits = x.float() @ self.router.t()
+            choice = logits.argmax(-1)
+            gate = torch.softmax(logits, -1).gather(1, choice[:, None])
+            out = torch.zeros_like(x)
+            for e in range(self.up.shape[0]):
+                rows = (choice == e).nonzero()[:, 0]
+                if rows.numel():
+                    hidden = torch.relu(x[rows] @ self.up[e].t())
+                    out[rows] = ((hidden @ self.down[e].t()).float() * gate[rows]).to(x.dtype)
+            return out
+
+    @register("position", "toy_harmonic")
+    class HarmonicRotation(Part):
+        """Rotation of the first ``rotary_dim`` dims of each head by angles
+        ``pos * base / (i + 1)``: the attention mixer asks a position part for
+        ``rotary_dim`` and ``tables()`` only.  params: rotary_dim, base."""
+
+        def __init__(self, params, weights, ctx):
+            super().__init__(params, weights, ctx)
+            self.rotary_dim = int(params["rotary_dim"])
+            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            ang = torch.arange(ctx.max_positions, dtype=torch.float64)[:, None] * (float(params["base"]) / (i + 1))[None, :]
+            self.cos = ang.cos().to(torch.float32).to(ctx.device).contiguous()
+            self.sin = ang.sin().to(torch.float32).to(ctx.device).contiguous()
+
+        def tables(self):
+            return self.cos, self.sin
+
+    @register("block", "toy_parallel")
+    class ParallelBlock:
+        """``h += mixer(norm1(h)) + ff(norm2(h))``: both branches read the same residual."""
+
+        def __init__(self, mixer, mixer_norm, feed_forward, ff_norm):
+            self.mixer, self.mixer_norm, self.feed_forward, self.ff_norm = mixer, mixer_norm, feed_forward, ff_norm
+
+        def forward(self, residual, delta, batch, cache):
+            x1 = self.mixer_norm.forward(residual, delta)      # adds what the layer before left pending
+            x2 = self.ff_norm.forward(residual, None)
+            a = self.mixer.forward(x1, batch, cache)
+            f = self.feed_forward.forward(x2, batch)
+            return residual, (a.float() + f.float()).to(a.dtype)
+
+    def build(cfg):
+        H, V, d = cfg["hidden_size"], cfg["vocab_size"], cfg["head_dim"]
+        norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": cfg["eps"]}, {"weight": name})
+        layers = []
+        for i, lc in enumerate(cfg["layers"]):
+            p = f"l{i}."
+            if lc["position"] == "harmonic":
+                pos = PartSpec("toy_harmonic", {"rotary_dim": lc["rotary_dim"], "base": cfg["harmonic_base"]})
+            else:
+                pos = PartSpec("rope", {"head_dim": d, "rotary_dim": d, "theta": 500.0, "scaling": None})
+            mixer = PartSpec("attention", {"hidden_size": H, "num_heads": cfg["heads"], "num_kv_heads": cfg["kv_heads"],
+                                           "head_dim": d, "window": None, "position": pos},
+                             {r: f"{p}attn.{r}" for r in "qkvo"})
+            if lc["experts"]:
+                ff = PartSpec("toy_top1_experts", {"hidden_size": H, "num_experts": lc["experts"], "expert_size": lc["inter"]},
+                              {"router": p + "ff.router", "up": p + "ff.up", "down": p + "ff.down"})
+            else:
+                ff = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": lc["inter"]},
+                              {"gate": p + "ff.gate", "up": p + "ff.up", "down": p + "ff.down"})
+            layers.append(LayerSpec(lc["block"], mixer, norm(p + "n1"), ff, norm(p + "n2")))
+        return ModelSpec(architecture="ToyRoutedForCausalLM", hidden_size=H, vocab_size=V, max_position=cfg["max_pos"],
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, {"table": "emb"}),
+                         layers=layers, schedule=[ScheduleEntry(i) for i in range(len(layers))],
+                         final_norm=norm("nf"),
+                         lm_head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": H}, {"weight": "head"}))
+
+    register_architecture("ToyRoutedForCausalLM", lambda d: d, build)
+
+
+TOY = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 56, "vocab_size": 101, "eps": 1e-5,
+       "heads": 3, "kv_heads": 1, "head_dim": 16, "max_pos": 64, "harmonic_base": 0.7,
+       "layers": [
+           {"block": "prenorm", "position": "harmonic", "rotary_dim": 8, "experts": 3, "inter": 40},
+           {"block": "toy_parallel", "position": "rope", "experts": 0, "inter": 72},
+           {"block": "prenorm", "position": "harmonic", "rotary_dim": 12, "experts": 5, "inter": 24}]}
+
+
+def _rotate_part(x, cos, sin, rot):
+    """Rotation of the first ``rot`` dims, pairs (j, j + rot/2); the rest passes through."""
+    return np.concatenate([P.apply_rope(x[..., :rot], cos, sin), x[..., rot:]], axis=-1)
+
+
+def _plain(cfg, w, tokens):
+    """The toy model on a whole sequence, no cache, numpy float64.  Returns the logits and the
+    smallest gap between the two largest router logits of any token in any routed layer."""
+    T, d, nq, nkv = len(tokens), cfg["head_dim"], cfg["heads"], cfg["kv_heads"]
+    pos = np.arange(T)
+    h = w["emb"][np.asarray(tokens)]
+    gap = np.inf
+    for i, lc in enumerate(cfg["layers"]):
+        p = f"l{i}."
+        if lc["position"] == "harmonic":
+            rot = lc["rotary_dim"]
+            ang = pos[:, None] * (cfg["harmonic_base"] / (np.arange(rot // 2) + 1.0))[None, :]
+            cos, sin = np.cos(ang), np.sin(ang)
+        else:
+            rot = d
+            cos, sin = P.rope_tables(pos, P.rope_inv_freq(d, 500.0))
+
+        def mixer(x):
+            q = _rotate_part(P.linear(x, w[p + "attn.q"]).reshape(T, nq, d), cos, sin, rot)
+            k = _rotate_part(P.linear(x, w[p + "attn.k"]).reshape(T, nkv, d), cos, sin, rot)
+            v = P.linear(x, w[p + "attn.v"]).reshape(T, nkv, d)
+            return P.linear(P.attention(q, k, v).reshape(T, nq * d), w[p + "attn.o"])
+
+        def feed_forward(x):
+            nonlocal gap
+            if not lc["experts"]:
+                return P.swiglu_part(x, {"gate_proj.weight": w[p + "ff.gate"], "up_proj.weight": w[p + "ff.up"],
+                                         "down_proj.weight": w[p + "ff.down"]}, "")
+            logits = x @ w[p + "ff.router"].T
+            order = np.sort(logits, -1)
+            gap = min(gap, float((order[:, -1] - order[:, -2]).min()))
+            prob = np.exp(logits - logits.max(-1, keepdims=True))
+            prob /= prob.sum(-1, keepdims=True)
+            out = np.zeros_like(x)
+            for t in range(T):
+                e = int(logits[t].argmax())
+                out[t] = prob[t, e] * (w[p + "ff.down"][e] @ np.maximum(w[p + "ff.up"][e] @ x[t], 0.0))
+            return out
+
+        if lc["block"] == "prenorm":
+            h = h + mixer(P.rms_norm(h, w[p + "n1"], cfg["eps"]))
+            h = h + feed_forward(P.rms_norm(h, w[p + "n2"], cfg["eps"]))
+        else:
+            h = h + mixer(P.rms_norm(h, w[p + "n1"], cfg["eps"])) + feed_forward(P.rms_norm(h, w[p + "n2"], cfg["eps"]))
+    return P.linear(P.rms_norm(h, w["nf"], cfg["eps"]), w["head"]), gap
+
+
+SEED, SEQ_SEED = 31, 5
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 4e-2)])
+def test_routed_feed_forward_other_position_and_parallel_block(dtype, tol):
+    from kv_cache_optimization_for_llm_b200 import EngineConfig
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    from kv_cache_optimization_for_llm_b200.parts import known
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+    _register()
+    assert "toy_top1_experts" in known("feed_forward") and "toy_harmonic" in known("position") \
+        and "toy_parallel" in known("block")
+    d = tempfile.mkdtemp(prefix="kvb200_toyr_")
+    write_random_model(d, TOY, seed=SEED, std=0.2)
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    assert w["l0.ff.up"].shape == (3, 40, 56) and w["l2.ff.down"].shape == (5, 56, 24) and "l1.ff.gate" in w
+    rng = np.random.default_rng(SEQ_SEED)
+    seqs = [rng.integers(0, 101, n).tolist() for n in (21, 30)]
+    refs, gaps = zip(*(_plain(TOY, w, s) for s in seqs))
+    # A choice between two experts whose logits nearly tie is decided by rounding, and the
+    # outputs then differ by an expert: the weights and sequences of this test keep every
+    # choice clear of that.  If this fails, the generator changed; pick other seeds.
+    assert min(gaps) > 0.08, gaps
+    r = ModelRunner(d, EngineConfig(dtype=dtype, page_size=4, num_pages=20, max_num_seqs=2,
+                                    max_num_batched_tokens=64, max_model_len=64, use_cuda_graphs=False))
+    scale = max(np.abs(x).max() for x in refs)
+    got0 = r.step([StepEntry(0, seqs[0][:14], 0, range(14))]).cpu().numpy()
+    assert np.abs(got0 - refs[0][:14]).max() / scale < tol
+    pos0, pos1 = 14, 0
+    for n1 in (9, 2, 1, 1, 11, 1, 5):
+        entries = [StepEntry(1, seqs[1][pos1:pos1 + n1], pos1, range(n1))]
+        expect = [refs[1][pos1:pos1 + n1]]
+        if pos0 < len(seqs[0]):
+            entries.append(StepEntry(0, [seqs[0][pos0]], pos0, [0]))
+            expect.append(refs[0][pos0:pos0 + 1])
+            pos0 += 1
+        got = r.step(entries).cpu().numpy()
+        assert np.abs(got - np.concatenate(expect)).max() / scale < tol, (dtype, pos0, pos1)
+        pos1 += n1
+    assert pos1 == 30 and pos0 == 21
+    r.check_status()
+    assert r.manager.check() == ""
