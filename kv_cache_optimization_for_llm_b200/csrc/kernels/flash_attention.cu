@@ -15,7 +15,11 @@
 // key > position - window.
 #include "common.cuh"
 
+#include <cuda.h>
 #include <math_constants.h>
+
+#include <mutex>
+#include <unordered_map>
 
 namespace {
 
@@ -388,6 +392,29 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// 16 consecutive columns of this thread's lane of tensor memory, read and written
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st16(unsigned taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024
 // bytes apart, base aligned to 1024 bytes.  The same image is a K-major operand (rows are
 // M or N, the 64 elements of a row run along K) or, with the major bit of the instruction
@@ -675,6 +702,444 @@ int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_p
   return kvb_launch_result();
 }
 
+
+// ---------------------------------------------------------------- the same, with roles
+// Warp-specialised form (224 threads, two blocks per SM):
+//   warp 0        the loader: finds the pages of a 64-key tile through the block table and
+//                 requests them as TMA boxes (cp.async.bulk.tensor, 128-byte swizzle) into rings
+//                 of three key and three value stages; the copies count their bytes on the
+//                 stage's mbarrier, so nobody waits on the loader itself;
+//   warps 1, 2    one thread each issues tcgen05.mma: warp 1 the scores S(i) = Q K(i)^T into the
+//                 score buffer that the softmax warps have read already (two tiles ahead),
+//                 warp 2 the products O += P(i) V(i) as soon as the probabilities of tile i are
+//                 in shared memory; tcgen05.commit hands stages and buffers back;
+//   warps 3..6    the softmax: a thread owns one query row (its lane of tensor memory) and all
+//                 64 keys of a tile, so the row's maximum and sum need no exchange; scores out
+//                 of tensor memory in halves of 32, mask on the diagonal and at the window's
+//                 edge only, probabilities in bfloat16 to one of two swizzled buffers, the
+//                 output rescaled in tensor memory only when the running maximum has grown by
+//                 2^8.
+// Tensor memory: scores in columns 0..63 and 64..127 (double-buffered), the output in 128..191;
+// 256 columns per block, two blocks per SM.  The roles meet on mbarriers only; every wait is
+// bounded and gives up early when another role has given up.  Needs pages of at least 8 rows
+// (a TMA box of 8 x 64 bfloat16 is the smallest that the 128-byte swizzle repeats over) and
+// 16-byte aligned page pools.
+constexpr int kWsThreads = 224;
+constexpr int kStages = 3;
+constexpr unsigned kWsTmemCols = 256;
+
+struct WsBars {
+  unsigned long long q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  unsigned long long s_full[2], s_free[2], p_full[2], o_done[2];
+};
+
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait that also ends when another role of the block has given up.  false: gave up.
+__device__ __forceinline__ bool mbar_test_wait(void* bar, unsigned parity) {   // a look, no suspension
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool wait_or_abort(void* bar, unsigned parity, volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  for (unsigned i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__global__ void __launch_bounds__(kWsThreads, 2)
+paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                int box_rows, const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
+                                const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
+                                const int* __restrict__ positions, const TileDesc* __restrict__ tiles,
+                                __nv_bfloat16* __restrict__ out, int nq, int nkv, int G, int gp_shift,
+                                float scale_log2, int window, int* status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* q_s = base;                           // [128 rows][64]
+  unsigned char* k_s = q_s + kQBytes;                  // [3][64 keys][64]
+  unsigned char* v_s = k_s + kStages * kKVBytes;       // [3][64 keys][64]
+  unsigned char* p_s = v_s + kStages * kKVBytes;       // [2][128 rows][64 keys]
+  WsBars* bars = reinterpret_cast<WsBars*>(p_s + 2 * kPBytes);
+  unsigned* tmem_holder = reinterpret_cast<unsigned*>(bars + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(&bars->q_full, 4);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->s_full[b], 1); mbar_init(&bars->s_free[b], 4);
+      mbar_init(&bars->p_full[b], 4); mbar_init(&bars->o_done[b], 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(tmem_holder, kWsTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = *tmem_holder;
+  // only now may the kernel behind this one start: its resident, waiting blocks must not be
+  // able to take tensor memory that a block of this grid still needs
+  pdl_trigger();
+  pdl_wait();
+
+  // Blocks start in the order of their linear index.  The last tiles of a request read the most
+  // keys: they come first, for every key/value head, so that the blocks that start last are
+  // short ones.
+  const int lin = blockIdx.y * gridDim.x + blockIdx.x;
+  const TileDesc tile = tiles[gridDim.x - 1 - lin / nkv];
+  const int hk = lin % nkv;
+  const int gp = 1 << gp_shift;
+  const int page_mask = (1 << page_shift) - 1;
+  const int* table = block_table + (size_t)tile.req * max_pages;
+  const int pos_first = positions[tile.t0];
+  const int pos_last = positions[tile.t0 + tile.n_tok - 1];
+  const int k_hi = pos_last + 1;
+  const int k_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int first_tile = k_lo / BNK, last_tile = (k_hi - 1) / BNK;
+  const int n_tiles = last_tile - first_tile + 1;
+  bool failed = false;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- loader
+    // A tile of 64 keys is 64 / box_rows boxes of the tensor map over the pages
+    // ([pages x kv heads x page_size rows][64]; box_rows = min(page size, 64)), each found
+    // through the block table and copied by TMA with the 128-byte swizzle the products read;
+    // the copies count their bytes on the tile's barrier.  Lane 0 waits and issues; the warp
+    // reads the block table 32 boxes at a time, one entry per lane, and hands lane 0 the pages
+    // by shuffle, so that no copy waits for a load of its own.  A box that no row may see and
+    // that has no page is requested beyond the end of the map, where TMA delivers zeros.  Keys
+    // run two tiles ahead of values: a key stage is free again when the scores of its tile are
+    // done, a value stage only when the tile's P V is.
+    const int total_rows = (num_pages * nkv) << page_shift;
+    const int n_box = BNK / box_rows;                 // 1, 2, 4 or 8: a tile never straddles 32 boxes
+    const int first_box = first_tile * n_box;
+    auto pages_of = [&](int chunk) -> int {           // this lane's entry of boxes 32 chunk .. 32 chunk + 31 of the block
+      const int lp = (int)(((long long)(first_box + chunk * 32 + lane) * box_rows) >> page_shift);
+      return lp < max_pages ? __ldg(table + lp) : -1;
+    };
+    auto request = [&](int i, int pg, unsigned char* dst, const CUtensorMap* map, void* bar) {
+      if (lane == 0) mbar_expect_tx(bar, kKVBytes);
+      __syncwarp();                                              // the bytes are expected before any copy can report
+      const int page = __shfl_sync(0xffffffffu, pg, (i * n_box + lane) & 31);
+      if (lane < n_box) {                                        // lane c requests box c of the tile
+        const int kj = (first_tile + i) * BNK + lane * box_rows;
+        int row = total_rows;                                    // zeros
+        if (page >= 0 && page < num_pages) {
+          row = (((page * nkv) + hk) << page_shift) + (kj & page_mask);
+        } else if (kj < k_hi && kj + box_rows > k_lo) {
+          atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);        // keys that a row reads
+        }
+        tma_load_2d(dst + lane * box_rows * (D * 2), map, 0, row, bar);
+      }
+    };
+    int pg_k = -1, pg_v = -1, chunk_k = -1, chunk_v = -1;
+    for (int it = 0; it < n_tiles + 2; ++it) {
+      const int kt = it, vt = it - 2;
+      if (kt < n_tiles) {
+        const int chunk = (kt * n_box) >> 5;
+        if (chunk != chunk_k) { pg_k = pages_of(chunk); chunk_k = chunk; }
+        if (lane == 0 && kt >= kStages &&
+            !wait_or_abort(&bars->k_empty[kt % kStages], (unsigned)(kt / kStages - 1) & 1u, abort_flag))
+          failed = true;
+        failed = __shfl_sync(0xffffffffu, (int)failed, 0) != 0;
+        if (failed) break;
+        request(kt, pg_k, k_s + (kt % kStages) * kKVBytes, &map_k, &bars->k_full[kt % kStages]);
+      }
+      if (vt >= 0) {
+        const int chunk = (vt * n_box) >> 5;
+        if (chunk != chunk_v) { pg_v = pages_of(chunk); chunk_v = chunk; }
+        if (lane == 0 && vt >= kStages &&
+            !wait_or_abort(&bars->v_empty[vt % kStages], (unsigned)(vt / kStages - 1) & 1u, abort_flag))
+          failed = true;
+        failed = __shfl_sync(0xffffffffu, (int)failed, 0) != 0;
+        if (failed) break;
+        request(vt, pg_v, v_s + (vt % kStages) * kKVBytes, &map_v, &bars->v_full[vt % kStages]);
+      }
+    }
+  } else if (warp <= 2) {
+    // ---------------------------------------------------------------- tcgen05.mma issuers
+    // Two threads, so that neither product waits behind the other's barriers: lane 0 issues the
+    // scores, lane 1 the P V products (in order: the output accumulates).
+    const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BNK >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+    const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
+                             ((unsigned)(D >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+    if (warp == 1 && lane == 0) {
+      const unsigned long long qd = smem_desc_sw128(smem_u32(q_s));
+      if (!wait_or_abort(&bars->q_full, 0, abort_flag)) failed = true;
+      for (int i = 0; i < n_tiles && !failed; ++i) {
+        // S(i) = Q K(i)^T into score buffer i mod 2, which the softmax has read (tile i - 2)
+        if (!wait_or_abort(&bars->k_full[i % kStages], (unsigned)(i / kStages) & 1u, abort_flag)) { failed = true; break; }
+        if (i >= 2 && !wait_or_abort(&bars->s_free[i & 1], (unsigned)((i - 2) >> 1) & 1u, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i % kStages) * kKVBytes));
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem + 64 * (i & 1), qd + 2 * kk, kd + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+        umma_commit(&bars->k_empty[i % kStages]);
+        umma_commit(&bars->s_full[i & 1]);
+      }
+    } else if (warp == 2 && lane == 0) {
+      for (int j = 0; j < n_tiles && !failed; ++j) {
+        // O += P(j) V(j)
+        if (!wait_or_abort(&bars->p_full[j & 1], (unsigned)(j >> 1) & 1u, abort_flag)) { failed = true; break; }
+        if (!wait_or_abort(&bars->v_full[j % kStages], (unsigned)(j / kStages) & 1u, abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        const unsigned long long pd = smem_desc_sw128(smem_u32(p_s + (j & 1) * kPBytes));
+        const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (j % kStages) * kKVBytes));
+#pragma unroll
+        for (int kk = 0; kk < BNK / 16; ++kk)   // 16 keys per step: 32 bytes along a row of P, 16 rows of V
+          umma_bf16(tmem + 128, pd + 2 * kk, vd + 128 * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bars->v_empty[j % kStages]);
+        umma_commit(&bars->o_done[j & 1]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax
+    const int quarter = warp & 3;                   // the lanes of tensor memory this warp may read
+    const int r = quarter * 32 + lane;              // query row
+    const int ti = r >> gp_shift, hi = r & (gp - 1);
+    const bool row_ok = ti < tile.n_tok && hi < G;
+    const int pos = row_ok ? positions[tile.t0 + ti] : -1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    {
+      const __nv_bfloat16* src = q_base + (size_t)(tile.t0 + (row_ok ? ti : 0)) * q_row_stride +
+                                 (size_t)(hk * G + (row_ok ? hi : 0)) * D;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) cp_async_16_zfill(q_s + swz<D>(r, i), src + i * 8, row_ok);
+      cp_async_commit();
+      cp_async_wait<0>();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->q_full);
+    }
+    const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
+    const unsigned o_cols = lane_base + 128;
+    constexpr float kRescale = 8.0f;
+    float m_ref = -CUDART_INF_F, l_run = 0.f;
+    for (int i = 0; i < n_tiles; ++i) {
+      const int b = i & 1;
+      const int t = first_tile + i;
+      if (!wait_or_abort(&bars->s_full[b], (unsigned)(i >> 1) & 1u, abort_flag)) { failed = true; break; }
+      tc_fence_after();
+      // The row's 64 scores are read in two halves of 32, the first half twice (once for the
+      // maximum, once for the probabilities): a thread holds 32 scores at a time, so that the
+      // block's eight warps fit two blocks per SM without spills.
+      const int kb = t * BNK;
+      const bool full = pos >= 0 && kb + BNK - 1 <= pos && kb >= lo;
+      const bool plain = __all_sync(0xffffffffu, full);
+      float v[32];
+      auto read_half = [&](int hh) {           // scores of keys kb + 32 hh .. + 31, masked ones -inf
+        tmem_ld32(lane_base + 64 * b + 32 * hh, v);
+        if (!plain) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = kb + 32 * hh + j;
+            if (!(key <= pos && key >= lo)) v[j] = -CUDART_INF_F;
+          }
+        }
+      };
+      auto max_of_half = [&]() -> float {      // four chains, not one of 32
+        float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) m4[c] = fmaxf(m4[c], v[j + c]);
+        }
+        return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      };
+      read_half(0);
+      const float mx_a = max_of_half();
+      read_half(1);
+      const float mx = fmaxf(mx_a, max_of_half());
+      const float m_new = fmaxf(m_ref, mx * scale_log2);   // the scale is positive: the maximum commutes with it
+      const bool grow = m_new > m_ref + kRescale;          // also: the row's first key (m_ref is -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        const float corr = !grow ? 1.0f : (m_ref == -CUDART_INF_F ? 0.f : ex2(m_ref - m_new));
+        if (i > 0) {
+          // every product into the output so far has to be over; P V(i) is not issued before this
+          // thread's probabilities of tile i are written
+          if (!wait_or_abort(&bars->o_done[(i - 1) & 1], (unsigned)((i - 1) >> 1) & 1u, abort_flag)) { failed = true; break; }
+          tc_fence_after();
+          // the second half of the scores is kept across the rescaling: it goes through the
+          // same 32 registers in two parts
+#pragma unroll
+          for (int part = 0; part < 4; ++part) {
+            float ov[16];
+            tmem_ld16(o_cols + 16 * part, ov);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ov[j] *= corr;
+            tmem_st16(o_cols + 16 * part, ov);
+          }
+        }
+        l_run *= corr;
+        if (grow) m_ref = m_new;
+      }
+      const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;   // a row with no key yet: everything stays zero
+      // the buffer of P(i) was read by P V(i - 2)
+      if (i >= 2 && !wait_or_abort(&bars->o_done[b], (unsigned)((i - 2) >> 1) & 1u, abort_flag)) { failed = true; break; }
+      unsigned char* pb = p_s + b * kPBytes;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};    // the tile's sum in four chains, added up in a fixed order
+      auto probabilities = [&](int hh) {     // of the half in v: pieces 4 hh .. 4 hh + 3 of row r of P
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          unsigned pk[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // a masked score is -inf: its probability comes out as zero
+            const float p0 = ex2(fmaf(v[8 * q4 + 2 * j], scale_log2, -m_use));
+            const float p1 = ex2(fmaf(v[8 * q4 + 2 * j + 1], scale_log2, -m_use));
+            l4[j] += p0 + p1;
+            pk[j] = pack_bf16(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(pb + swz<D>(r, 4 * hh + q4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      };
+      probabilities(1);
+      read_half(0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_free[b]);    // this warp has read its rows of S(i) for the last time
+      probabilities(0);
+      l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      fence_async_smem();
+      tc_fence_before();     // orders the rescaled output before the product that the arrival lets go
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full[b]);
+    }
+    if (!failed) {
+      if (!wait_or_abort(&bars->o_done[(n_tiles - 1) & 1], (unsigned)((n_tiles - 1) >> 1) & 1u, abort_flag)) failed = true;
+    }
+    if (!failed) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* dst = out + ((size_t)(tile.t0 + ti) * nq + hk * G + hi) * D;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float o[32];
+        tmem_ld32(o_cols + 32 * half, o);
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8)
+            *reinterpret_cast<uint4*>(dst + 32 * half + j) =
+                make_uint4(pack_bf16(o[j] * inv, o[j + 1] * inv), pack_bf16(o[j + 2] * inv, o[j + 3] * inv),
+                           pack_bf16(o[j + 4] * inv, o[j + 5] * inv), pack_bf16(o[j + 6] * inv, o[j + 7] * inv));
+        }
+      }
+    }
+  }
+  if (failed) *abort_flag = 1;
+  cp_async_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (tid == 0) atomicCAS(status, 0, KVB_STATUS_WAIT_TIMEOUT);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let products that may still run finish
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem, kWsTmemCols);
+}
+
+// The pages of one layer, [num_pages x nkv x page_size rows][64] bfloat16, as a 2-D tensor map
+// with boxes of box_rows x 64 and the 128-byte swizzle.  Encoded once per address and shape.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+struct MapKey {
+  const void* ptr; long long rows; int box;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && box == o.box; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 2654435761u ^ (size_t)k.box; }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows) {
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return KVB_ERR_BAD_SIZE;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  MapKey key{ptr, rows, box_rows};
+  auto it = g_maps.find(key);
+  if (it == g_maps.end()) {
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    if (g_maps.size() > 4096) g_maps.clear();
+    it = g_maps.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
+int launch_ws(const void* q, int q_row_stride, const void* k_pages, const void* v_pages, const int* block_table,
+              int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
+              void* out, int nq, int nkv, int G, int gp_shift, float scale, int window, int* status,
+              cudaStream_t stream) {
+  const int page_size = 1 << page_shift;
+  const int box_rows = page_size < BNK ? page_size : BNK;
+  const long long rows = (long long)num_pages * nkv * page_size;
+  if (rows >= (1ll << 31)) return KVB_ERR_BAD_SIZE;
+  CUtensorMap mk, mv;
+  int e = pages_map(&mk, k_pages, rows, box_rows);
+  if (e) return e;
+  e = pages_map(&mv, v_pages, rows, box_rows);
+  if (e) return e;
+  const size_t smem = 1024 + (size_t)kQBytes + 2 * kStages * (size_t)kKVBytes + 2 * kPBytes + sizeof(WsBars) + 64;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem);
+    if (ce != cudaSuccess) return (int)ce;
+    // two blocks per SM need the largest shared-memory configuration
+    ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                              (int)cudaSharedmemCarveoutMaxShared);
+    if (ce != cudaSuccess) return (int)ce;
+    attr_set = true;
+  }
+  dim3 grid(num_tiles, nkv);
+  kvb_launch(paged_flash_attention_ws_kernel, grid, dim3(kWsThreads), smem, stream, mk, mv, box_rows,
+             (const __nv_bfloat16*)q, q_row_stride, block_table, max_pages, page_shift,
+             num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq, nkv, G, gp_shift,
+             scale * 1.4426950408889634f, window, status);
+  return kvb_launch_result();
+}
+
 }  // namespace tc5
 
 template <int D, int NW>
@@ -705,6 +1170,7 @@ int log2_exact(int x) {
 
 }  // namespace
 
+
 // 1 when the tensor-core kernel takes these sizes: head size 64 or 128, a group of at
 // most 64 query heads per key/value head, a page size that is a power of two.
 KVB_EXPORT int kvb_flash_attention_supported(int d, int group, int page_size) {
@@ -723,7 +1189,8 @@ KVB_EXPORT int kvb_flash_attention_tokens_per_tile(int group, int wide) {
 // tiles: num_tiles x {request row, first token row, tokens (<= tokens_per_tile(group, wide)), 0},
 // int32.  The tokens of a tile are consecutive tokens of one request, positions ascending.
 // wide: 0: the tiles were cut for 64 query rows per block; 1: for 128; 2: for 128, and the
-// kernel is the tcgen05 form (head size 64 only).
+// kernel is the tcgen05 form (head size 64 only); 3: for 128, the tcgen05 form with roles
+// (head size 64, pages of at least 8 rows, page pools aligned to 16 bytes).
 // bfloat16 only.  out is [T, nq*d].
 KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                          const int* block_table, int max_pages, int page_size, int num_pages,
@@ -738,6 +1205,13 @@ KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const 
   while ((1 << gp_shift) < G) ++gp_shift;
   const int page_shift = log2_exact(page_size);
   if (wide && (128 >> gp_shift) < 1) return KVB_ERR_BAD_SIZE;
+  if (wide == 3) {   // tcgen05 form with roles
+    if (d != 64 || (reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7) || page_size < 8 ||
+        (reinterpret_cast<uintptr_t>(k_pages) & 15) || (reinterpret_cast<uintptr_t>(v_pages) & 15))
+      return KVB_ERR_BAD_SIZE;
+    return tc5::launch_ws(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions,
+                          tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream);
+  }
   if (wide == 2) {   // tcgen05 form
     if (d != 64 || (reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7)) return KVB_ERR_BAD_SIZE;
     return tc5::launch(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions,

@@ -346,6 +346,7 @@ def decode_attention(qkv, k_pages, v_pages, block_table, q_start, ctx_len, nq, n
 
 FLASH_WIDE = __import__('os').environ.get('KVB200_FLASH_WIDE', '1') != '0'
 FLASH_TC = __import__('os').environ.get('KVB200_FLASH_TC', '1') != '0'
+FLASH_TC_ROLES = __import__('os').environ.get('KVB200_FLASH_TC_ROLES', '1') != '0'
 
 
 def flash_attention_supported(d: int, group: int, page_size: int) -> bool:
@@ -384,8 +385,9 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
                     wide: Optional[bool] = None) -> torch.Tensor:
     """Tensor-core attention for steps with runs of query tokens (bfloat16).  ``wide``:
     False: 64 query rows per block (mma.sync); True: 128 rows (mma.sync); 2: 128 rows on
-    tcgen05 with the scores in tensor memory (head size 64); None: chosen from the step's
-    size and the head size."""
+    tcgen05 with the scores in tensor memory (head size 64); 3: the same with roles (a TMA
+    loader warp, two issuing warps, four softmax warps; pages of at least 8 rows); None:
+    chosen from the step's size, the head size and the page size."""
     _need_cuda(qkv, k_pages)
     T = qkv.shape[0]
     # 128-row tiles when there are enough of them to keep every SM busy, else 64-row tiles
@@ -393,7 +395,9 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
     if wide is None:
         wide = FLASH_WIDE and (T // nt128) * nkv >= 2 * 148
         if wide and FLASH_TC and d == 64:
-            wide = 2
+            roles = (FLASH_TC_ROLES and k_pages.shape[2] >= 8 and k_pages.data_ptr() % 16 == 0
+                     and v_pages.data_ptr() % 16 == 0)
+            wide = 3 if roles else 2
     tiles = flash_tiles(batch, nq // nkv, wide)
     out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
     rc = lib("flash_attention").kvb_paged_flash_attention(

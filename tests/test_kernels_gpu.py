@@ -354,7 +354,7 @@ def test_flash_attention_mixed_runs(nq, nkv, d, page_size, window):
     assert ops.flash_attention_supported(d, nq // nkv, page_size)
     c = _attention_case("bfloat16", nq, nkv, d, ctxs=[1, 70, 130, 64, 400, 257, 2], q_lens=[1, 70, 2, 1, 150, 40, 2],
                         page_size=page_size, window=window, seed=d + nq + page_size)
-    for wide in (False, True) + ((2,) if d == 64 else ()):   # 64 and 128 query rows per block (mma.sync), 128 on tcgen05
+    for wide in (False, True) + ((2,) if d == 64 else ()) + ((3,) if d == 64 and page_size >= 8 else ()):   # 64 and 128 query rows per block (mma.sync), 128 on tcgen05 (two forms)
         fb = _FakeBatch(c)
         out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), window,
                                   wide=wide)
@@ -368,7 +368,7 @@ def test_flash_attention_finds_a_far_key(spike):
     nq, nkv, d = 8, 2, 64
     c = _attention_case("bfloat16", nq, nkv, d, ctxs=[900], q_lens=[37], page_size=16, window=None, seed=spike,
                         spike=spike)
-    for wide in (None, 2):
+    for wide in (None, 2, 3):
         fb = _FakeBatch(c)
         out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), None,
                                   wide=wide)
