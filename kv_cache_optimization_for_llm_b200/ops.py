@@ -266,9 +266,28 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
     if M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
         return gemm_skinny(x, w, out_dtype or x.dtype, kernel_status(x.device),
                            x_is_static=torch.cuda.is_current_stream_capturing())
+    if WIDE == "all" and _wide_ok(x, w, 8) and (out_dtype is None or out_dtype == x.dtype):
+        return gemm_wide(x, w, kernel_status(x.device))
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w.t(), out_dtype=out_dtype)
     return torch.nn.functional.linear(x, w)
+
+
+# Which products of steps with many rows run on this package's tcgen05 kernel (gemm_bf16_wide.cu):
+#   "auto"  those it is faster for on a B200 at every number of rows: the gate|up product, whose
+#           SiLU * up it does as its epilogue (at 2048 rows it is level with the library for the
+#           others, at 512 rows the library's split of K wins for the down product)
+#   "all"   every one (no library product in a bfloat16 step)
+#   "off"   none (the library product, then the activation kernel)
+WIDE = __import__('os').environ.get('KVB200_WIDE', 'auto')
+WIDE_MIN_ROWS = 128
+
+
+def _wide_ok(x: torch.Tensor, w: torch.Tensor, n_multiple: int) -> bool:
+    """Whether the tcgen05 kernel for steps of many rows takes this product."""
+    return (x.shape[0] >= WIDE_MIN_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.shape[1] % 8 == 0 and w.shape[0] % n_multiple == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def _skinny_ok(x: torch.Tensor, rows_limit: int) -> bool:
@@ -294,6 +313,8 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, block: int) -> torch.T
             and gate_up.shape[0] % 128 == 0:
         return gemm_skinny(x, gate_up, x.dtype, kernel_status(x.device),
                            x_is_static=torch.cuda.is_current_stream_capturing(), epilogue="swiglu")
+    if WIDE != "off" and block == 64 and _wide_ok(x, gate_up, 128):
+        return gemm_wide(x, gate_up, kernel_status(x.device), epilogue="swiglu")
     return silu_mul(linear(x, gate_up), block=block if block != I else None)
 
 
@@ -609,6 +630,33 @@ def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, ro
         raise KernelError(f"gemm_skinny_fused refuses M={M}, N={N}, K={K}, epilogue {epilogue}")
     _check(rc, "gemm_skinny_fused")
     return Folded(xb, sumsq) if into is not None else out
+
+
+def gemm_wide(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, epilogue: str = "store",
+              tile=(0, 0)) -> torch.Tensor:
+    """``x . w^T`` for steps of many rows on tcgen05 tensor cores: a persistent kernel with a TMA
+    loader warp, an issuing warp and four epilogue warps, two accumulators in tensor memory.
+
+    ``epilogue``: "store", or "swiglu": ``w`` holds gate and up rows in alternating blocks
+    of 64 and ``silu(gate) * up`` [M, N/2] is returned.  ``tile``: (rows of x, features) per
+    tile, one of (128, 64), (128, 128), (128, 256), (256, 256); (256, 256, 1): such a tile shared
+    by the two blocks of a cluster; (0, 0) for the kernel's own choice."""
+    _need_cuda(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    assert w.shape[1] == K
+    code = {"store": 0, "swiglu": 1}[epilogue]
+    out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.bfloat16, device=x.device)
+    rc = lib("gemm_bf16_wide").kvb_gemm_wide(
+        _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(out.stride(0)), c_int(M), c_int(N),
+        c_int(K), c_int(code), c_int(tile[0]), c_int(tile[1]), c_int(tile[2] if len(tile) > 2 else 0), _p(status),
+        _stream())
+    if rc in (-2, -3):
+        raise KernelError(f"gemm_wide refuses M={M}, N={N}, K={K}, epilogue {epilogue}, tile {tile} (K and N "
+                          "multiples of 8, N a multiple of 128 for swiglu, 16-byte aligned rows are required)")
+    _check(rc, "gemm_wide")
+    return out
 
 
 def wait_selftest(polls: int, status: torch.Tensor) -> None:

@@ -37,7 +37,7 @@ class GroupedQueryAttention(Part):
         mods = ["elementwise", "attention"]
         if dtype == torch.bfloat16 and params["head_dim"] in (64, 128):
             mods += ["flash_attention", "decode_attention"]
-        mods.append("gemm_f32" if dtype == torch.float32 else "gemm_bf16")
+        mods += ["gemm_f32"] if dtype == torch.float32 else ["gemm_bf16", "gemm_bf16_wide"]
         return tuple(mods)
 
     def __init__(self, params, weights, ctx):

@@ -42,7 +42,7 @@ class LinearHead(Part):
     @classmethod
     def kernel_modules(cls, params, dtype):
         import torch
-        return ("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16",)
+        return ("gemm_f32",) if dtype == torch.float32 else ("gemm_bf16", "gemm_bf16_wide")
 
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)

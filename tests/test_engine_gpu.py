@@ -269,3 +269,32 @@ def test_random_workload_ahead_and_waiting_agree():
         prompt, sp, _ = reqs[i]
         assert ahead[i] == P.generate(cfg, w, prompt, sp.max_tokens, temperature=sp.temperature, seed=sp.seed, key=i,
                                       penalty=sp.repetition_penalty), i
+
+
+@pytest.mark.parametrize("mode", ["off", "auto", "all"])
+def test_long_portion_through_the_products_for_many_rows(mode, monkeypatch):
+    """bfloat16, a portion of 200 tokens in one step (tiny_b): with the library products, with
+    this package's tcgen05 kernel for the gate|up product only, and with it for every product,
+    the logits at the first, the 128th, the 129th and the last place against the plain implementation."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, ops
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    monkeypatch.setattr(ops, "WIDE", mode)
+    mdir = model_dir("tiny_b", "bfloat16")
+    cfg, w = P.read_model_dir(mdir)
+    seq = _prompts(cfg, [203], 23)[0]
+    ref = P.forward(cfg, w, seq)
+    r = ModelRunner(mdir, EngineConfig(dtype="bfloat16", page_size=16, num_pages=13, max_num_seqs=2,
+                                       max_num_batched_tokens=256, max_model_len=208))
+    before = ops.launch_count
+    want = [0, 127, 128, 199]
+    got = r.step([StepEntry(0, seq[:200], 0, want)]).cpu().numpy()
+    r.check_status()
+    assert np.abs(got - ref[want]).max() / np.abs(ref).max() < 4e-2
+    if mode != "off":
+        assert "gemm_bf16_wide" in ops.loaded_libraries()
+    # the rest one by one, from the cache that the long portion left
+    for i in range(200, 203):
+        got = r.step([StepEntry(0, [seq[i]], i, [0])]).cpu().numpy()
+        assert np.abs(got - ref[i:i + 1]).max() / np.abs(ref).max() < 4e-2
+    assert ops.launch_count > before

@@ -219,3 +219,92 @@ def test_every_number_of_rows_up_to_64():
         rstd = 1.0 / torch.sqrt(sumsq.double() / K + 1e-5)
         assert (scaled.double() - ref * rstd).abs().max().item() < 5e-3 * (ref * rstd).abs().max().item(), M
     assert int(st.item()) == 0
+
+
+# ------------------------------------------------------------------ the kernel for steps of many rows
+
+WIDE_SHAPES = [(128, 256, 64), (130, 264, 72), (1, 8, 8), (300, 1000, 200), (2048, 3072, 2048), (517, 2048, 8192),
+               (1000, 777 * 8, 520), (129, 16384, 256)]
+
+
+@pytest.mark.parametrize("tile", [(0, 0), (128, 64), (128, 128), (128, 256), (256, 256), (256, 256, 1)])
+@pytest.mark.parametrize("M,N,K", WIDE_SHAPES)
+def test_gemm_wide_matches_float64(M, N, K, tile):
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.gemm_wide(x, w, st, tile=tile)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    ref = x.double() @ w.double().t()
+    err = (out.double() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err < 5e-3 * scale, (err, scale)     # float32 accumulation, one bfloat16 rounding of 2^-9
+    assert torch.equal(out, ops.gemm_wide(x, w, st, tile=tile))
+
+
+def test_gemm_wide_finds_one_large_product_anywhere():
+    """One element of x and one of w made large: exactly one output stands out, wherever the
+    pair lies (a tile's last row, the last feature, the last element of K)."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    M, N, K = 391, 1544, 1096
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for (m, n, k) in [(0, 0, 0), (127, 255, 63), (128, 256, 64), (390, 1543, 1095), (255, 1300, 1087)]:
+        x = torch.zeros(M, K, dtype=torch.bfloat16, device="cuda")
+        w = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+        x[m, k] = 3.0
+        w[n, k] = 5.0
+        out = ops.gemm_wide(x, w, st).float()
+        assert torch.equal(out, ops.gemm_wide(x, w, st, tile=(256, 256)).float())
+        assert torch.equal(out, ops.gemm_wide(x, w, st, tile=(256, 256, 1)).float())
+        assert out[m, n].item() == 15.0
+        out[m, n] = 0
+        assert out.abs().max().item() == 0.0
+    assert int(st.item()) == 0
+
+
+@pytest.mark.parametrize("tile", [(0, 0), (128, 128), (128, 256), (256, 256), (256, 256, 1)])
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (333, 704, 200), (2048, 8192, 2048)])
+def test_gemm_wide_swiglu_epilogue(M, I, K, tile):
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(M + I + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    gate = (torch.randn(I, K, generator=g, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    up = (torch.randn(I, K, generator=g, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    # rows in blocks of 128: 64 gate features, then the 64 up features of the same indices
+    gu = torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.gemm_wide(x, gu, st, epilogue="swiglu", tile=tile)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and out.shape == (M, I)
+    gd, ud = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    ref = gd / (1 + torch.exp(-gd)) * ud
+    err = (out.double() - ref).abs().max().item()
+    assert err < 5e-3 * ref.abs().max().item() + 1e-6
+
+
+def test_gemm_wide_rows_do_not_depend_on_their_neighbours():
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(400, 2048, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(3072, 2048, generator=g, device="cuda") / 45).to(torch.bfloat16)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    full = ops.gemm_wide(x, w, st)
+    for rows in (slice(0, 1), slice(399, 400), slice(100, 329)):
+        assert torch.equal(ops.gemm_wide(x[rows].contiguous(), w, st), full[rows])
+    assert int(st.item()) == 0
+
+
+def test_gemm_wide_refuses_what_it_cannot_do():
+    from kv_cache_optimization_for_llm_b200 import ops
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = torch.zeros(128, 100, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError):
+        ops.gemm_wide(x, torch.zeros(64, 100, dtype=torch.bfloat16, device="cuda"), st)     # K no multiple of 8
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError):
+        ops.gemm_wide(x, torch.zeros(60, 64, dtype=torch.bfloat16, device="cuda"), st)      # N no multiple of 8
+    with pytest.raises(ops.KernelError):
+        ops.gemm_wide(x, torch.zeros(192, 64, dtype=torch.bfloat16, device="cuda"), st, epilogue="swiglu")
