@@ -148,6 +148,11 @@ struct Bars {
   unsigned long long full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
 };
 
+// g / (1 + e^-g) with the hardware's exponential and reciprocal (a few units in the last place of
+// float32, far below the bfloat16 rounding that follows): the activation of a tile's last round
+// is not hidden under products.
+__device__ __forceinline__ float silu_fast(float g) { return g * __fdividef(1.0f, 1.0f + __expf(-g)); }
+
 // The epilogue of one row: BN finished sums of row m, features n0.., out of this thread's lane of
 // tensor memory (columns `cols`..), 32 at a time.  Every lane of the warp takes part in the
 // reads, whatever its row.
@@ -198,8 +203,7 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, unsigned cols, in
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const float g0 = g[j + 2 * q], g1 = g[j + 2 * q + 1];
-              pk[q] = pack_bf16(g0 * (1.0f / (1.0f + expf(-g0))) * u[j + 2 * q],
-                                g1 * (1.0f / (1.0f + expf(-g1))) * u[j + 2 * q + 1]);
+              pk[q] = pack_bf16(silu_fast(g0) * u[j + 2 * q], silu_fast(g1) * u[j + 2 * q + 1]);
             }
             if (p.store32) {
               st_global_32(dst + c / 2 + h + j, pk);
@@ -339,8 +343,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 // of them).  The tensor cores of both SMs read both halves of W, so each SM's shared memory
 // delivers a half of what a tile of its own would ask of it; that is what bounds the single form.
 // Measured on a B200 (2048 rows): 0.35 us per 64 of K and pair, the tensor pipe of both SMs busy
-// throughout; gate|up with its SiLU * up 103 us against 114 us single and 117 us for the library
-// product followed by the activation kernel.
+// throughout; gate|up with its SiLU * up 95 us against 108 us single and 117 us for the library
+// product followed by the activation kernel (97 us for the library product alone).
 //   warp 0       of either block loads the block's own operands;
 //   warp 1       of the first block (the leader) issues the products for both and hands stages
 //                and accumulators back to both blocks (tcgen05.commit with multicast); warp 1 of
@@ -393,15 +397,19 @@ __device__ __forceinline__ void umma_commit_pair(void* bar) {
                ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
-constexpr int kPairBN = 256;       // features per tile; each block loads 128 of the rows of W
-constexpr int kPairStages = 6;
+// PBN: features per tile (each block loads a half of these rows of W).  Only 256 is built: tiles
+// of 192 features, which would cut 3072 features into rounds of three quarters the length, took
+// 0.69 us per stage against 0.35 us for 256 when they were measured.
+constexpr int pair_stages(int pbn) { return pbn == 256 ? 6 : 7; }
 
-template <int EPI>
+template <int PBN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_wide_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p) {
   constexpr unsigned kHalfBytes = BM * BK * 2;           // 128 rows of 128 bytes
-  constexpr unsigned kStageBytes = 2 * kHalfBytes;       // this block's rows of X and of W
-  constexpr unsigned kTmemCols = 512;
+  constexpr unsigned kStageBytes = kHalfBytes + (PBN / 2) * BK * 2;   // this block's rows of X and of W
+  constexpr unsigned kTmemCols = 512;                    // two accumulators, 256 columns apart
+  constexpr int kPairStages = pair_stages(PBN);
+  constexpr int kPairBN = PBN;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Bars* bars = reinterpret_cast<Bars*>(base + (size_t)kPairStages * kStageBytes);
@@ -466,7 +474,7 @@ gemm_wide_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           break;
         }
         tc_fence_after();
-        const unsigned d = tmem + (unsigned)(acc * kPairBN);
+        const unsigned d = tmem + (unsigned)(acc * 256);
         for (int k = 0; k < p.k_tiles; ++k, ++it) {
           const int s = it % kPairStages;
           KVB_STAMP(0);
@@ -506,8 +514,8 @@ gemm_wide_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       const int m = (tile % p.m_tiles) * (2 * BM) + r, n0 = (tile / p.m_tiles) * kPairBN;
       if (!wait_or_abort(&bars->acc_full[acc], (unsigned)(n_local >> 1) & 1u, abort_flag)) { failed = true; break; }
       tc_fence_after();
-      const unsigned cols = lane_base + (unsigned)(acc * kPairBN);
-      epilogue_rows<kPairBN, EPI>(p, cols, m, n0);
+      const unsigned cols = lane_base + (unsigned)(acc * 256);
+      epilogue_rows<PBN, EPI>(p, cols, m, n0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&bars->acc_empty[acc], 0);
@@ -618,9 +626,9 @@ int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, Params p, cudaStre
 // the ones left over would run after the others, each with a full share of tiles.
 unsigned long long* g_trace = nullptr;   // set by kvb_gemm_wide_trace
 
-template <int EPI>
+template <int PBN, int EPI>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, Params p, cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)kPairStages * 2 * BM * BK * 2 + sizeof(Bars) + 64;
+  const size_t smem = 1024 + (size_t)pair_stages(PBN) * (BM + PBN / 2) * BK * 2 + sizeof(Bars) + 64;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = smem;
@@ -635,22 +643,22 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, Params p, cudaStre
   cfg.attrs = attr;
   static int max_pairs = 0;
   if (!max_pairs) {
-    cudaError_t ce = cudaFuncSetAttribute(gemm_wide_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t ce = cudaFuncSetAttribute(gemm_wide_pair_kernel<PBN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
     cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
     cfg.numAttrs = 1;
     int n = 0;
-    ce = cudaOccupancyMaxActiveClusters(&n, gemm_wide_pair_kernel<EPI>, &cfg);
+    ce = cudaOccupancyMaxActiveClusters(&n, gemm_wide_pair_kernel<PBN, EPI>, &cfg);
     if (ce != cudaSuccess) return (int)ce;
     if (n < 1) return KVB_ERR_BAD_SIZE;
     max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;
   }
   const int total = p.m_tiles * p.n_tiles;
   const int pairs = total < max_pairs ? total : max_pairs;
-  p.stages = kPairStages;
+  p.stages = pair_stages(PBN);
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.numAttrs = kvb_pdl_enabled() ? 2 : 1;
-  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_wide_pair_kernel<EPI>, mx, mw, p);
+  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_wide_pair_kernel<PBN, EPI>, mx, mw, p);
   if (le != cudaSuccess) return (int)le;
   return kvb_launch_result();
 }
@@ -697,10 +705,13 @@ KVB_EXPORT int kvb_gemm_wide(const void* x, int ldx, const void* w, int ldw, voi
       (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return KVB_ERR_ALIGN;
   if (bm == 0 && bn == 0) kvb_gemm_wide_tile(M, N, epilogue, &bm, &bn, &pair);
-  if (bn != 64 && bn != 128 && bn != 256) return KVB_ERR_BAD_SIZE;
-  if (bm != 128 && !(bm == 256 && bn == 256)) return KVB_ERR_BAD_SIZE;
-  if (bn == 64 && epilogue == EPI_SWIGLU) return KVB_ERR_BAD_SIZE;
-  if (pair && !(bm == 256 && bn == 256)) return KVB_ERR_BAD_SIZE;
+  if (pair) {
+    if (bm != 256 || bn != 256) return KVB_ERR_BAD_SIZE;
+  } else {
+    if (bn != 64 && bn != 128 && bn != 256) return KVB_ERR_BAD_SIZE;
+    if (bm != 128 && !(bm == 256 && bn == 256)) return KVB_ERR_BAD_SIZE;
+    if (bn == 64 && epilogue == EPI_SWIGLU) return KVB_ERR_BAD_SIZE;
+  }
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.m_tiles = (M + bm - 1) / bm;
@@ -715,9 +726,9 @@ KVB_EXPORT int kvb_gemm_wide(const void* x, int ldx, const void* w, int ldw, voi
   CUtensorMap mx, mw;
   int e = make_map(&mx, x, M, K, ldx, pair ? BM : bm);
   if (e) return e;
-  e = cached_map(&mw, w, N, K, ldw, pair ? kPairBN / 2 : bn);
+  e = cached_map(&mw, w, N, K, ldw, pair ? bn / 2 : bn);
   if (e) return e;
-  if (pair) return epilogue == EPI_STORE ? launch_pair<EPI_STORE>(mx, mw, p, stream) : launch_pair<EPI_SWIGLU>(mx, mw, p, stream);
+  if (pair) return epilogue == EPI_STORE ? launch_pair<256, EPI_STORE>(mx, mw, p, stream) : launch_pair<256, EPI_SWIGLU>(mx, mw, p, stream);
   if (epilogue == EPI_STORE) {
     if (bm == 256) return launch_wide<2, 256, EPI_STORE>(mx, mw, p, stream);
     if (bn == 64) return launch_wide<1, 64, EPI_STORE>(mx, mw, p, stream);
