@@ -41,7 +41,20 @@ constexpr int BK = 64;       // one 128-byte swizzle row of bfloat16
 constexpr unsigned kSpinLimit = 20u * 1000u * 1000u;
 constexpr int kMaxStages = 8;
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+// What happens to the finished sums (the same three as for steps of few rows, gemm_bf16.cu):
+//   EPI_STORE     C[m, n] = sum
+//   EPI_SWIGLU    the rows of W come in blocks of 128: 64 gate features, then the 64 up features of
+//                 the same indices; out[m, 64 t + j] = silu(gate) * up
+//   EPI_RESIDUAL  resid[m, n] += sum, in float32 and in place (every element has one owner);
+//                 xb[m, n] = bfloat16(new resid[m, n]), the rows that the next product reads;
+//                 sumsq[m, tile] = the sum of the squares of the new resid[m, n] over the tile's
+//                 256 features, added up in the order of the features.
+// Row scale (x_sumsq != nullptr, not with EPI_RESIDUAL): the finished sum of row m is multiplied
+// by rsqrt(sum_p x_sumsq[m, p] / K + eps) first.  With the RMSNorm's weight multiplied into the
+// columns of W beforehand, the product over the bare residual rows, scaled so, is the product
+// over the normalised rows, and the add and the norm between two products (upstream: two
+// kernels, base/src/kernels.cu:10-43) need no kernel of their own.
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESIDUAL = 2 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
@@ -133,6 +146,13 @@ struct Params {
   __nv_bfloat16* out;
   int ldo;          // elements between rows of out
   int store32;      // rows of out start on 32-byte boundaries and N is a multiple of 16: whole sectors per store
+  const float* x_sumsq;   // row scale: [M, x_parts] partial sums of squares of the rows' source, or nullptr
+  int x_parts;
+  float eps;
+  float* resid;           // EPI_RESIDUAL: [M, ld_resid] float32, updated in place
+  int ld_resid;
+  __nv_bfloat16* xb_out;  // EPI_RESIDUAL: [M, N] bfloat16 copy of the new residual rows
+  float* sumsq_out;       // EPI_RESIDUAL: [M, n_tiles]
   int* status;
   unsigned long long* trace;   // nullptr, or [64][8] uint64: phase stamps of the first pair's first 64 stages (profiling)
 };
@@ -158,12 +178,49 @@ __device__ __forceinline__ float silu_fast(float g) { return g * __fdividef(1.0f
 // reads, whatever its row.
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_rows(const Params& p, unsigned cols, int m, int n0) {
-  if (EPI == EPI_STORE) {
+  float rstd = 1.0f;
+  if (EPI != EPI_RESIDUAL && p.x_sumsq != nullptr && m < p.M) {
+    const float* src = p.x_sumsq + (size_t)m * p.x_parts;
+    float ss = 0.f;
+    for (int i = 0; i < p.x_parts; ++i) ss += src[i];      // one fixed order
+    rstd = rsqrtf(ss / (float)p.K + p.eps);
+  }
+  if (EPI == EPI_RESIDUAL) {
+    // this thread's row of the residual, BN features from n0: 128 bytes of float32 per 32 features
+    float* res = p.resid + (size_t)m * p.ld_resid + n0;
+    __nv_bfloat16* xb = p.xb_out + (size_t)m * p.N + n0;
+    float ss = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      float v[32];
+      tmem_ld32(cols + c, v);     // every lane of the warp takes part, whatever its row
+      if (m < p.M) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          if (n0 + c + j < p.N) {   // N is a multiple of 8
+            const float4 r0 = *reinterpret_cast<const float4*>(res + c + j);
+            const float4 r1 = *reinterpret_cast<const float4*>(res + c + j + 4);
+            const float4 a0 = make_float4(r0.x + v[j], r0.y + v[j + 1], r0.z + v[j + 2], r0.w + v[j + 3]);
+            const float4 a1 = make_float4(r1.x + v[j + 4], r1.y + v[j + 5], r1.z + v[j + 6], r1.w + v[j + 7]);
+            *reinterpret_cast<float4*>(res + c + j) = a0;
+            *reinterpret_cast<float4*>(res + c + j + 4) = a1;
+            *reinterpret_cast<uint4*>(xb + c + j) = make_uint4(pack_bf16(a0.x, a0.y), pack_bf16(a0.z, a0.w),
+                                                              pack_bf16(a1.x, a1.y), pack_bf16(a1.z, a1.w));
+            ss += a0.x * a0.x; ss += a0.y * a0.y; ss += a0.z * a0.z; ss += a0.w * a0.w;
+            ss += a1.x * a1.x; ss += a1.y * a1.y; ss += a1.z * a1.z; ss += a1.w * a1.w;
+          }
+        }
+      }
+    }
+    if (m < p.M) p.sumsq_out[(size_t)m * p.n_tiles + n0 / BN] = ss;
+  } else if (EPI == EPI_STORE) {
     __nv_bfloat16* dst = p.out + (size_t)m * p.ldo + n0;
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
       float v[32];
       tmem_ld32(cols + c, v);     // every lane of the warp takes part, whatever its row
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= rstd;
       if (m < p.M) {
         if (p.store32) {
 #pragma unroll
@@ -202,8 +259,8 @@ __device__ __forceinline__ void epilogue_rows(const Params& p, unsigned cols, in
             unsigned pk[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const float g0 = g[j + 2 * q], g1 = g[j + 2 * q + 1];
-              pk[q] = pack_bf16(silu_fast(g0) * u[j + 2 * q], silu_fast(g1) * u[j + 2 * q + 1]);
+              const float g0 = g[j + 2 * q] * rstd, g1 = g[j + 2 * q + 1] * rstd;
+              pk[q] = pack_bf16(silu_fast(g0) * (u[j + 2 * q] * rstd), silu_fast(g1) * (u[j + 2 * q + 1] * rstd));
             }
             if (p.store32) {
               st_global_32(dst + c / 2 + h + j, pk);
@@ -677,6 +734,7 @@ KVB_EXPORT int kvb_gemm_wide_tile(int M, int N, int epilogue, int* rows, int* co
   for (int form = 0; form < 5; ++form) {
     const int bm = form >= 3 ? 256 : 128, bn = form == 0 ? 64 : form == 1 ? 128 : 256, pr = form == 4;
     if (epilogue == EPI_SWIGLU && bn == 64) continue;
+    if (epilogue == EPI_RESIDUAL && form != 2 && form != 4) continue;
     const double per_tile = form == 0 ? 0.40 : form == 1 ? 0.41 : form == 2 ? 0.45
                           : form == 3 ? (epilogue == EPI_SWIGLU ? 0.95 : 0.83) : 0.36;
     const int tiles = ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
@@ -686,6 +744,76 @@ KVB_EXPORT int kvb_gemm_wide_tile(int M, int N, int epilogue, int* rows, int* co
   }
   return 0;
 }
+
+namespace {
+
+struct Extras {
+  // row scale
+  const float* x_sumsq = nullptr; int x_parts = 0; float eps = 0.f;
+  // EPI_RESIDUAL
+  float* resid = nullptr; int ld_resid = 0; __nv_bfloat16* xb_out = nullptr; float* sumsq_out = nullptr;
+};
+
+int gemm_wide_launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
+                     int epilogue, int bm, int bn, int pair, const Extras& ex, int* status, cudaStream_t stream) {
+  if (M < 1 || N < 1) return 0;
+  if (K < 8 || (K & 7) || epilogue < EPI_STORE || epilogue > EPI_RESIDUAL) return KVB_ERR_BAD_SIZE;
+  if (epilogue == EPI_SWIGLU ? (N & 127) : (N & 7)) return KVB_ERR_BAD_SIZE;
+  if ((ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return KVB_ERR_ALIGN;
+  if (epilogue == EPI_RESIDUAL) {
+    if (!ex.resid || !ex.xb_out || !ex.sumsq_out || ex.x_sumsq || ex.ld_resid < N) return KVB_ERR_BAD_SIZE;
+    if ((ex.ld_resid & 3) || (reinterpret_cast<uintptr_t>(ex.resid) & 15) || (reinterpret_cast<uintptr_t>(ex.xb_out) & 15))
+      return KVB_ERR_ALIGN;
+  } else {
+    if ((ldo & 7) || (reinterpret_cast<uintptr_t>(out) & 15)) return KVB_ERR_ALIGN;
+    if (ex.x_sumsq && ex.x_parts < 1) return KVB_ERR_BAD_SIZE;
+  }
+  if (bm == 0 && bn == 0) kvb_gemm_wide_tile(M, N, epilogue, &bm, &bn, &pair);
+  if (pair) {
+    if (bm != 256 || bn != 256) return KVB_ERR_BAD_SIZE;
+  } else {
+    if (bn != 64 && bn != 128 && bn != 256) return KVB_ERR_BAD_SIZE;
+    if (bm != 128 && !(bm == 256 && bn == 256)) return KVB_ERR_BAD_SIZE;
+    if (bn == 64 && epilogue == EPI_SWIGLU) return KVB_ERR_BAD_SIZE;
+    if (epilogue == EPI_RESIDUAL && !(bm == 128 && bn == 256)) return KVB_ERR_BAD_SIZE;
+  }
+  Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.m_tiles = (M + bm - 1) / bm;
+  p.n_tiles = (N + bn - 1) / bn;
+  p.k_tiles = (K + BK - 1) / BK;
+  p.stages = 0;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.store32 = (ldo % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 32 == 0) && (N % 16 == 0);
+  p.x_sumsq = ex.x_sumsq; p.x_parts = ex.x_parts; p.eps = ex.eps;
+  p.resid = ex.resid; p.ld_resid = ex.ld_resid; p.xb_out = ex.xb_out; p.sumsq_out = ex.sumsq_out;
+  p.status = status;
+  p.trace = g_trace;
+  CUtensorMap mx, mw;
+  int e = make_map(&mx, x, M, K, ldx, pair ? BM : bm);
+  if (e) return e;
+  e = cached_map(&mw, w, N, K, ldw, pair ? bn / 2 : bn);
+  if (e) return e;
+  if (pair) {
+    if (epilogue == EPI_STORE) return launch_pair<256, EPI_STORE>(mx, mw, p, stream);
+    if (epilogue == EPI_SWIGLU) return launch_pair<256, EPI_SWIGLU>(mx, mw, p, stream);
+    return launch_pair<256, EPI_RESIDUAL>(mx, mw, p, stream);
+  }
+  if (epilogue == EPI_RESIDUAL) return launch_wide<1, 256, EPI_RESIDUAL>(mx, mw, p, stream);
+  if (epilogue == EPI_STORE) {
+    if (bm == 256) return launch_wide<2, 256, EPI_STORE>(mx, mw, p, stream);
+    if (bn == 64) return launch_wide<1, 64, EPI_STORE>(mx, mw, p, stream);
+    if (bn == 128) return launch_wide<1, 128, EPI_STORE>(mx, mw, p, stream);
+    return launch_wide<1, 256, EPI_STORE>(mx, mw, p, stream);
+  }
+  if (bm == 256) return launch_wide<2, 256, EPI_SWIGLU>(mx, mw, p, stream);
+  if (bn == 128) return launch_wide<1, 128, EPI_SWIGLU>(mx, mw, p, stream);
+  return launch_wide<1, 256, EPI_SWIGLU>(mx, mw, p, stream);
+}
+
+}  // namespace
 
 // C = X[M,K] . W[N,K]^T, bfloat16, float32 accumulation.  ldx, ldw, ldo in elements; x, w and
 // out aligned to 16 bytes, ldx, ldw, ldo and K multiples of 8.
@@ -698,46 +826,26 @@ KVB_EXPORT int kvb_gemm_wide_tile(int M, int N, int epilogue, int* rows, int* co
 // two blocks of a cluster (cta_group::2).  Uses no memory beyond its operands.
 KVB_EXPORT int kvb_gemm_wide(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N, int K,
                              int epilogue, int bm, int bn, int pair, int* status, cudaStream_t stream) {
-  if (M < 1 || N < 1) return 0;
-  if (K < 8 || (K & 7) || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU)) return KVB_ERR_BAD_SIZE;
-  if (epilogue == EPI_STORE ? (N & 7) : (N & 127)) return KVB_ERR_BAD_SIZE;
-  if ((ldx & 7) || (ldw & 7) || (ldo & 7) || (reinterpret_cast<uintptr_t>(x) & 15) ||
-      (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
-    return KVB_ERR_ALIGN;
-  if (bm == 0 && bn == 0) kvb_gemm_wide_tile(M, N, epilogue, &bm, &bn, &pair);
-  if (pair) {
-    if (bm != 256 || bn != 256) return KVB_ERR_BAD_SIZE;
-  } else {
-    if (bn != 64 && bn != 128 && bn != 256) return KVB_ERR_BAD_SIZE;
-    if (bm != 128 && !(bm == 256 && bn == 256)) return KVB_ERR_BAD_SIZE;
-    if (bn == 64 && epilogue == EPI_SWIGLU) return KVB_ERR_BAD_SIZE;
-  }
-  Params p;
-  p.M = M; p.N = N; p.K = K;
-  p.m_tiles = (M + bm - 1) / bm;
-  p.n_tiles = (N + bn - 1) / bn;
-  p.k_tiles = (K + BK - 1) / BK;
-  p.stages = 0;
-  p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  p.ldo = ldo;
-  p.store32 = (ldo % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 32 == 0) && (N % 16 == 0);
-  p.status = status;
-  p.trace = g_trace;
-  CUtensorMap mx, mw;
-  int e = make_map(&mx, x, M, K, ldx, pair ? BM : bm);
-  if (e) return e;
-  e = cached_map(&mw, w, N, K, ldw, pair ? bn / 2 : bn);
-  if (e) return e;
-  if (pair) return epilogue == EPI_STORE ? launch_pair<256, EPI_STORE>(mx, mw, p, stream) : launch_pair<256, EPI_SWIGLU>(mx, mw, p, stream);
-  if (epilogue == EPI_STORE) {
-    if (bm == 256) return launch_wide<2, 256, EPI_STORE>(mx, mw, p, stream);
-    if (bn == 64) return launch_wide<1, 64, EPI_STORE>(mx, mw, p, stream);
-    if (bn == 128) return launch_wide<1, 128, EPI_STORE>(mx, mw, p, stream);
-    return launch_wide<1, 256, EPI_STORE>(mx, mw, p, stream);
-  }
-  if (bm == 256) return launch_wide<2, 256, EPI_SWIGLU>(mx, mw, p, stream);
-  if (bn == 128) return launch_wide<1, 128, EPI_SWIGLU>(mx, mw, p, stream);
-  return launch_wide<1, 256, EPI_SWIGLU>(mx, mw, p, stream);
+  if (epilogue == EPI_RESIDUAL) return KVB_ERR_BAD_SIZE;
+  return gemm_wide_launch(x, ldx, w, ldw, out, ldo, M, N, K, epilogue, bm, bn, pair, Extras(), status, stream);
+}
+
+// The same product with the residual stream's add and RMSNorm folded around it.
+//  - x_sumsq != nullptr (row scale): row m of the result is multiplied by
+//    rsqrt(sum_p x_sumsq[m, p] / K + eps) before the epilogue (0 or 1) sees it; x holds the
+//    bare residual rows in bfloat16 and W has the norm's weight multiplied into its columns.
+//  - epilogue 2 (EPI_RESIDUAL): resid[M, ld_resid] += X . W^T in place (float32, 16-byte aligned
+//    rows), xb_out[M, N] gets the new rows in bfloat16 and sumsq_out[M, ceil(N/256)] their partial
+//    sums of squares; out unused; tiles of 128 x 256, or 256 x 256 on pairs.
+KVB_EXPORT int kvb_gemm_wide_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int N,
+                                   int K, int epilogue, int bm, int bn, int pair, const float* x_sumsq, int x_parts,
+                                   float eps, float* resid, int ld_resid, void* xb_out, float* sumsq_out, int* status,
+                                   cudaStream_t stream) {
+  Extras ex;
+  ex.x_sumsq = x_sumsq; ex.x_parts = x_parts; ex.eps = eps;
+  ex.resid = resid; ex.ld_resid = ld_resid; ex.xb_out = reinterpret_cast<__nv_bfloat16*>(xb_out);
+  ex.sumsq_out = sumsq_out;
+  return gemm_wide_launch(x, ldx, w, ldw, out, ldo, M, N, K, epilogue, bm, bn, pair, ex, status, stream);
 }
 
 // Profiling: the kernels of pairs write the phase stamps (globaltimer, ns) of the first pair's

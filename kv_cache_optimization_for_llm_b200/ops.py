@@ -247,6 +247,9 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
         if into is None and fused_norm_rows(x.xb.shape[0], x.dtype) and w.dtype == torch.bfloat16:
             return gemm_skinny_fused(x.xb, w, kernel_status(w.device), row_scale=x,
                                      x_is_static=torch.cuda.is_current_stream_capturing())
+        if (into is None and wide_fused_rows(x.xb.shape[0], x.dtype) and _wide_ok(x.xb, w, 8)
+                and (out_dtype is None or out_dtype == x.dtype)):
+            return gemm_wide(x.xb, w, kernel_status(w.device), row_scale=x)
         x = x.materialize()
     _need_cuda(x, w)
     M, K = x.shape
@@ -256,6 +259,9 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
             and into.dtype == torch.float32 and into.shape == (M, N) and into.is_contiguous()):
         return gemm_skinny_fused(x, w, kernel_status(w.device), into=into,
                                  x_is_static=torch.cuda.is_current_stream_capturing())
+    if (into is not None and wide_fused_rows(M, x.dtype) and _wide_ok(x, w, 8) and into.dtype == torch.float32
+            and into.shape == (M, N) and into.is_contiguous() and N % 4 == 0):
+        return gemm_wide(x, w, kernel_status(w.device), into=into)
     if x.dtype == torch.float32:
         assert x.stride(1) == 1 and w.stride(1) == 1
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
@@ -281,6 +287,16 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
 #   "off"   none (the library product, then the activation kernel)
 WIDE = __import__('os').environ.get('KVB200_WIDE', 'auto')
 WIDE_MIN_ROWS = 128
+# From this many rows on the products of a step also take the residual add and the RMSNorm into
+# themselves (as the products of few rows do), which makes every product of the step this
+# package's: below it the library's split of K is the faster way through the narrow products.  0: never.
+WIDE_FUSED_MIN_ROWS = int(__import__('os').environ.get('KVB200_WIDE_FUSED_MIN_ROWS', '0'))
+
+
+def wide_fused_rows(rows: int, dtype: torch.dtype) -> bool:
+    """Whether products over ``rows`` rows (many) fold the residual add and the norm into themselves."""
+    return (FUSED_NORM and WIDE != "off" and WIDE_FUSED_MIN_ROWS > 0 and dtype == torch.bfloat16
+            and rows >= WIDE_FUSED_MIN_ROWS)
 
 
 def _wide_ok(x: torch.Tensor, w: torch.Tensor, n_multiple: int) -> bool:
@@ -308,6 +324,8 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, block: int) -> torch.T
                 return gemm_skinny_fused(x.xb, gate_up, st, row_scale=x, epilogue="swiglu", x_is_static=static)
             return silu_mul(gemm_skinny_fused(x.xb, gate_up, st, row_scale=x, x_is_static=static),
                             block=block if block != I else None)
+        if wide_fused_rows(x.xb.shape[0], x.dtype) and block == 64 and _wide_ok(x.xb, gate_up, 128):
+            return gemm_wide(x.xb, gate_up, kernel_status(gate_up.device), epilogue="swiglu", row_scale=x)
         x = x.materialize()
     if block == 64 and _skinny_ok(x, min(SKINNY_MAX_ROWS, FUSED_EPILOGUE_MAX_ROWS)) \
             and gate_up.shape[0] % 128 == 0:
@@ -633,30 +651,48 @@ def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, ro
 
 
 def gemm_wide(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, epilogue: str = "store",
-              tile=(0, 0)) -> torch.Tensor:
+              tile=(0, 0), row_scale: Optional[PendingNorm] = None, into: Optional[torch.Tensor] = None):
     """``x . w^T`` for steps of many rows on tcgen05 tensor cores: a persistent kernel with a TMA
     loader warp, an issuing warp and four epilogue warps, two accumulators in tensor memory.
 
     ``epilogue``: "store", or "swiglu": ``w`` holds gate and up rows in alternating blocks
     of 64 and ``silu(gate) * up`` [M, N/2] is returned.  ``tile``: (rows of x, features) per
     tile, one of (128, 64), (128, 128), (128, 256), (256, 256); (256, 256, 1): such a tile shared
-    by the two blocks of a cluster; (0, 0) for the kernel's own choice."""
+    by the two blocks of a cluster; (0, 0) for the kernel's own choice.
+
+    ``row_scale``: every row of ``x . w^T`` is multiplied by the 1/rms that follows from the
+    pending norm's partial sums (``x`` is then its bare bfloat16 rows, and ``w`` has the
+    norm's weight multiplied into its columns).  ``into``: the product is added into this
+    float32 residual in place and a :class:`Folded` is returned."""
     _need_cuda(x, w)
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
     assert w.shape[1] == K
-    code = {"store": 0, "swiglu": 1}[epilogue]
-    out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.bfloat16, device=x.device)
-    rc = lib("gemm_bf16_wide").kvb_gemm_wide(
-        _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(out.stride(0)), c_int(M), c_int(N),
-        c_int(K), c_int(code), c_int(tile[0]), c_int(tile[1]), c_int(tile[2] if len(tile) > 2 else 0), _p(status),
-        _stream())
+    ss, parts, eps = None, 0, 0.0
+    if row_scale is not None:
+        ss, eps = row_scale.sumsq, row_scale.eps
+        assert into is None and ss.dtype == torch.float32 and ss.is_contiguous() and ss.shape[0] == M
+        parts = ss.shape[1]
+    out = xb = sumsq = None
+    if into is not None:
+        assert epilogue == "store" and into.dtype == torch.float32 and into.shape == (M, N) and into.stride(1) == 1
+        code = 2
+        sumsq = torch.empty((M, -(-N // 256)), dtype=torch.float32, device=x.device)
+        xb = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        code = {"store": 0, "swiglu": 1}[epilogue]
+        out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.bfloat16, device=x.device)
+    rc = lib("gemm_bf16_wide").kvb_gemm_wide_fused(
+        _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(out.stride(0) if out is not None else 0),
+        c_int(M), c_int(N), c_int(K), c_int(code), c_int(tile[0]), c_int(tile[1]),
+        c_int(tile[2] if len(tile) > 2 else 0), _p(ss), c_int(parts), c_float(eps), _p(into),
+        c_int(into.stride(0) if into is not None else 0), _p(xb), _p(sumsq), _p(status), _stream())
     if rc in (-2, -3):
         raise KernelError(f"gemm_wide refuses M={M}, N={N}, K={K}, epilogue {epilogue}, tile {tile} (K and N "
                           "multiples of 8, N a multiple of 128 for swiglu, 16-byte aligned rows are required)")
     _check(rc, "gemm_wide")
-    return out
+    return Folded(xb, sumsq) if into is not None else out
 
 
 def wait_selftest(polls: int, status: torch.Tensor) -> None:

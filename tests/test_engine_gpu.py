@@ -271,15 +271,17 @@ def test_random_workload_ahead_and_waiting_agree():
                                       penalty=sp.repetition_penalty), i
 
 
-@pytest.mark.parametrize("mode", ["off", "auto", "all"])
+@pytest.mark.parametrize("mode", ["off", "auto", "all", "folded"])
 def test_long_portion_through_the_products_for_many_rows(mode, monkeypatch):
     """bfloat16, a portion of 200 tokens in one step (tiny_b): with the library products, with
-    this package's tcgen05 kernel for the gate|up product only, and with it for every product,
-    the logits at the first, the 128th, the 129th and the last place against the plain implementation."""
+    this package's tcgen05 kernel for the gate|up product only, with it for every product, and with the
+    residual add and the norm folded into its products; the logits at the first, the 128th, the 129th and the last place against the plain implementation."""
     from kv_cache_optimization_for_llm_b200 import EngineConfig, ops
     from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
     from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
-    monkeypatch.setattr(ops, "WIDE", mode)
+    # "folded": also the residual add and the norm inside the products, as for steps of few rows
+    monkeypatch.setattr(ops, "WIDE", "auto" if mode == "folded" else mode)
+    monkeypatch.setattr(ops, "WIDE_FUSED_MIN_ROWS", 128 if mode == "folded" else 0)
     mdir = model_dir("tiny_b", "bfloat16")
     cfg, w = P.read_model_dir(mdir)
     seq = _prompts(cfg, [203], 23)[0]

@@ -308,3 +308,56 @@ def test_gemm_wide_refuses_what_it_cannot_do():
         ops.gemm_wide(x, torch.zeros(60, 64, dtype=torch.bfloat16, device="cuda"), st)      # N no multiple of 8
     with pytest.raises(ops.KernelError):
         ops.gemm_wide(x, torch.zeros(192, 64, dtype=torch.bfloat16, device="cuda"), st, epilogue="swiglu")
+
+
+@pytest.mark.parametrize("tile", [(0, 0), (128, 256), (256, 256), (256, 256, 1)])
+@pytest.mark.parametrize("M,N,K,parts", [(200, 256, 192, 1), (517, 1024, 520, 5), (2048, 3072, 2048, 8)])
+def test_gemm_wide_row_scale(M, N, K, parts, tile):
+    """The product over bare rows, every row scaled by the 1/rms that follows from partial sums of
+    squares (the norm in front of it, not carried out), plain and with the SiLU * up epilogue."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    sumsq = (torch.rand(M, parts, generator=g, device="cuda") * K / parts * 4).contiguous()
+    eps = 1e-5
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pending = ops.PendingNorm(None, x, sumsq, eps, torch.bfloat16)
+    rstd = 1.0 / torch.sqrt(sumsq.double().sum(1) / K + eps)
+    ref = (x.double() @ w.double().t()) * rstd[:, None]
+    out = ops.gemm_wide(x, w, st, tile=tile, row_scale=pending)
+    assert (out.double() - ref).abs().max().item() < 5e-3 * ref.abs().max().item()
+    I = N // 2
+    gd = torch.cat([ref[:, i:i + 64] for i in range(0, N, 128)], dim=1)
+    ud = torch.cat([ref[:, i + 64:i + 128] for i in range(0, N, 128)], dim=1)
+    ref2 = gd / (1 + torch.exp(-gd)) * ud
+    out2 = ops.gemm_wide(x, w, st, epilogue="swiglu", tile=tile, row_scale=pending)
+    assert out2.shape == (M, I)
+    assert (out2.double() - ref2).abs().max().item() < 5e-3 * ref2.abs().max().item() + 1e-6
+    assert int(st.item()) == 0
+
+
+@pytest.mark.parametrize("tile", [(0, 0), (128, 256), (256, 256, 1)])
+@pytest.mark.parametrize("M,N,K", [(200, 192, 512), (391, 1000, 264), (2048, 2048, 8192)])
+def test_gemm_wide_adds_into_the_residual(M, N, K, tile):
+    """resid += x . w^T in float32 and in place; the new rows in bfloat16; partial sums of their
+    squares per 256 features that add up to the rows' sums of squares."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(M * 3 + N + K)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    resid = torch.randn(M, N, generator=g, device="cuda")
+    ref = resid.double() + x.double() @ w.double().t()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    folded = ops.gemm_wide(x, w, st, tile=tile, into=resid)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    scale = ref.abs().max().item()
+    assert (resid.double() - ref).abs().max().item() < 2e-5 * scale
+    assert torch.equal(folded.xb, resid.to(torch.bfloat16))
+    assert folded.sumsq.shape == (M, -(-N // 256))
+    ss = (resid.double() ** 2).sum(1)
+    assert ((folded.sumsq.double().sum(1) - ss).abs() / ss).max().item() < 1e-5
+    for t in range(folded.sumsq.shape[1]):
+        part = (resid[:, 256 * t:256 * (t + 1)].double() ** 2).sum(1)
+        assert ((folded.sumsq[:, t].double() - part).abs() / (part + 1e-9)).max().item() < 1e-5
