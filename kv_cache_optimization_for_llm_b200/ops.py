@@ -3,14 +3,17 @@ first use (building it if needed) and wraps the launchers.
 
 There is no fallback: on a machine with a GPU a missing or unbuildable library
 raises, and no operator here has a PyTorch or CPU stand-in.  Matrix products of
-the bfloat16 path go to the library (cuBLAS through ``torch.nn.functional.linear``)
-as upstream's do (cublasGemmEx, base/src/engine.cu:653-671); everything else,
-and every matrix product of the float32 path, is a kernel of this package.
+the bfloat16 path are this package's tcgen05 kernels for steps of up to 32 rows and,
+from 128 rows, for the gate|up product (``KVB200_WIDE=all``: for every product); the
+others go to the library (cuBLAS through ``torch.nn.functional.linear``) as all of
+upstream's do (cublasGemmEx, base/src/engine.cu:653-671).  Everything else, and
+every matrix product of the float32 path, is a kernel of this package.
 """
 
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
 from typing import Dict, Optional
 
@@ -181,7 +184,7 @@ def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token
 
 # ------------------------------------------------------------------ matrix products
 
-SKINNY_MAX_ROWS = int(__import__('os').environ.get('KVB200_SKINNY_MAX_ROWS', '32'))   # measured: the library product wins beyond
+SKINNY_MAX_ROWS = int(os.environ.get('KVB200_SKINNY_MAX_ROWS', '32'))   # measured: the library product wins beyond
 _status_word: Dict[int, torch.Tensor] = {}
 
 
@@ -225,7 +228,7 @@ class PendingNorm:
         return add_rmsnorm(self.resid, None, None, self.eps, self.dtype)
 
 
-FUSED_NORM = __import__('os').environ.get('KVB200_FUSED_NORM', '1') != '0'
+FUSED_NORM = os.environ.get('KVB200_FUSED_NORM', '1') != '0'
 
 
 def fused_norm_rows(rows: int, dtype: torch.dtype) -> bool:
@@ -285,12 +288,12 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
 #           others, at 512 rows the library's split of K wins for the down product)
 #   "all"   every one (no library product in a bfloat16 step)
 #   "off"   none (the library product, then the activation kernel)
-WIDE = __import__('os').environ.get('KVB200_WIDE', 'auto')
+WIDE = os.environ.get('KVB200_WIDE', 'auto')
 WIDE_MIN_ROWS = 128
 # From this many rows on the products of a step also take the residual add and the RMSNorm into
 # themselves (as the products of few rows do), which makes every product of the step this
 # package's: below it the library's split of K is the faster way through the narrow products.  0: never.
-WIDE_FUSED_MIN_ROWS = int(__import__('os').environ.get('KVB200_WIDE_FUSED_MIN_ROWS', '0'))
+WIDE_FUSED_MIN_ROWS = int(os.environ.get('KVB200_WIDE_FUSED_MIN_ROWS', '0'))
 
 
 def wide_fused_rows(rows: int, dtype: torch.dtype) -> bool:
@@ -383,9 +386,9 @@ def decode_attention(qkv, k_pages, v_pages, block_table, q_start, ctx_len, nq, n
     return out
 
 
-FLASH_WIDE = __import__('os').environ.get('KVB200_FLASH_WIDE', '1') != '0'
-FLASH_TC = __import__('os').environ.get('KVB200_FLASH_TC', '1') != '0'
-FLASH_TC_ROLES = __import__('os').environ.get('KVB200_FLASH_TC_ROLES', '1') != '0'
+FLASH_WIDE = os.environ.get('KVB200_FLASH_WIDE', '1') != '0'
+FLASH_TC = os.environ.get('KVB200_FLASH_TC', '1') != '0'
+FLASH_TC_ROLES = os.environ.get('KVB200_FLASH_TC_ROLES', '1') != '0'
 
 
 def flash_attention_supported(d: int, group: int, page_size: int) -> bool:
@@ -585,7 +588,7 @@ def gemm_skinny_plan(M: int, N: int, K: int):
     return splits.value, tiles.value
 
 
-FUSED_EPILOGUE_MAX_ROWS = int(__import__('os').environ.get('KVB200_FUSED_MAX_ROWS', '32'))   # the kernel takes up to 64
+FUSED_EPILOGUE_MAX_ROWS = int(os.environ.get('KVB200_FUSED_MAX_ROWS', '32'))   # the kernel takes up to 64
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor,
