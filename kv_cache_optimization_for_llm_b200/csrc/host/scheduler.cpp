@@ -68,6 +68,21 @@ int Scheduler::portion(const Req& r, int budget) const {
   return n;
 }
 
+int Scheduler::shrink_to_fit(const Req& r, int want) {
+  // A portion needs pages for all its tokens at once, in a windowed group too, where the pages
+  // that the window passes come back only after the step.  A request that nobody can make room
+  // for tries smaller portions, halving down to one token, before it is given up: in a windowed
+  // group the smaller portion is what lets a long prompt through a small pool.
+  bool windowed = false;
+  for (int g = 0; g < cache_->num_groups(); ++g) windowed = windowed || cache_->group(g).window > 0;
+  if (!windowed) return 0;
+  while (want > 1) {
+    want = (want + 1) / 2;
+    if (cache_->extend(r.id, r.computed + want)) return want;
+  }
+  return 0;
+}
+
 void Scheduler::finish(Req* r, FinishReason why) {
   const int64_t id = r->id;
   if (cache_->has(id)) cache_->release(id);
@@ -112,7 +127,7 @@ Plan Scheduler::schedule() {
   size_t i = 0;
   while (i < running_.size()) {
     Req& r = reqs_.at(running_[i]);
-    const int want = r.closing ? 0 : portion(r, budget);
+    int want = r.closing ? 0 : portion(r, budget);
     if (want <= 0) { ++i; continue; }  // budget spent (or only waiting for its last token): not in this step
     bool scheduled = true;
     while (!cache_->extend(r.id, r.computed + want)) {
@@ -120,6 +135,8 @@ Plan Scheduler::schedule() {
       // request itself if it is the latest.
       const size_t victim = running_.size() - 1;
       if (victim == i && running_.size() == 1) {
+        const int smaller = shrink_to_fit(r, want);
+        if (smaller > 0) { want = smaller; break; }   // its pages are in place
         // Alone and still too large for the pool: it can never finish.
         plan.finished.push_back(r.id);
         finish(&r, FinishReason::CacheExhausted);
@@ -150,15 +167,20 @@ Plan Scheduler::schedule() {
     Req& r = reqs_.at(waiting_.front());
     if (r.pending) break;                // its newest token is not known yet: next step
     if (cache_->admit(r.id) < 0) break;  // no state slot free
-    const int want = portion(r, budget);
+    int want = portion(r, budget);
     if (!cache_->extend(r.id, want)) {
-      cache_->release(r.id);
-      if (running_.empty()) {
-        plan.finished.push_back(r.id);
-        finish(&r, FinishReason::CacheExhausted);
-        continue;
+      const int smaller = running_.empty() ? shrink_to_fit(r, want) : 0;
+      if (smaller > 0) {
+        want = smaller;
+      } else {
+        cache_->release(r.id);
+        if (running_.empty()) {
+          plan.finished.push_back(r.id);
+          finish(&r, FinishReason::CacheExhausted);
+          continue;
+        }
+        break;
       }
-      break;
     }
     waiting_.pop_front();
     running_.push_back(r.id);

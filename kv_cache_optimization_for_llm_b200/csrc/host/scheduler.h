@@ -115,6 +115,9 @@ class Scheduler {
   void finish(Req* r, FinishReason why);
   void preempt(size_t running_index, Plan* plan);
   int portion(const Req& r, int budget) const;
+  // For a request that no preemption can make room for, in a model with a windowed group:
+  // the largest halving of `want` whose pages could be taken (they are then in place); 0: none.
+  int shrink_to_fit(const Req& r, int want);
 
   CacheManager* cache_;
   SchedulerConfig cfg_;

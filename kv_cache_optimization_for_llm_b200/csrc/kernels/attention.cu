@@ -441,10 +441,16 @@ decode_attention_fused_kernel(const T* __restrict__ qkv, int q_row_stride, T* __
   const int k_end_first = min(b_first * KB + KB, pos + 1);
   long long off = -1;
   const bool first_has_keys = b_first * KB + KB > lo;
-  if (first_has_keys) off = request_tile(b_first * KB, k_end_first, write_kv != 0);
+  // A layer that reads another layer's cache finds the key and value of the token's own position
+  // there: the owning layer wrote them earlier in this same step, several launches back.  Only the
+  // wait below orders this kernel behind all of those, so a first tile that holds that position
+  // is asked for after it.
+  const bool own_key_from_this_step = !write_kv && pos >= b_first * KB && pos < b_first * KB + kDecThreads;
+  if (first_has_keys && !own_key_from_this_step) off = request_tile(b_first * KB, k_end_first, write_kv != 0);
 
   pdl_wait();
   stamp(1);   // the kernel before this one has finished: its q, k, v rows may be read
+  if (first_has_keys && own_key_from_this_step) off = request_tile(b_first * KB, k_end_first, false);
   const T* row = qkv + (size_t)q_start[r] * q_row_stride;
   // the group's queries, rotated (pairs (j, j + rot/2) of the first rot dims), scaled
   for (int i = tid; i < G * D; i += kDecThreads) {
@@ -720,7 +726,7 @@ static int launch_decode(const void* q, int q_row_stride, const void* k_pages, c
                          const int* ctx_len, void* out, float* part_o, float* part_ml, int R, int nq, int nkv,
                          float scale, int window, int KB, int NB, int* status, cudaStream_t stream) {
   // about four blocks per SM in total, never more slots than key blocks
-  int slots = (4 * 148 + nkv * R - 1) / (nkv * R);
+  int slots = (4 * kvb_sm_count() + nkv * R - 1) / (nkv * R);
   slots = slots < 1 ? 1 : (slots > NB ? NB : slots);
   dim3 grid(nkv, R, slots);
   const size_t smem = (size_t)4 * 32 * D * sizeof(T);
@@ -836,7 +842,10 @@ KVB_EXPORT int kvb_decode_attention_noalloc(const void* q, int q_row_stride, con
   float* scratch = nullptr;
   const int rc = noalloc_scratch_for_current_device(&scratch);
   if (rc != 0) return rc;
-  // partial outputs first, then the (max, sum) pairs; both offsets keep 16-byte alignment
+  // Partial outputs first, then the (max, sum) pairs.  The array itself is aligned to 256 bytes;
+  // the second offset, R * nq * NB * d floats, is a multiple of 16 bytes because the split kernel
+  // takes head sizes 32, 64 and 128 only (any other d is refused by kvb_decode_attention below
+  // before anything is launched), so d floats are always a multiple of 128 bytes.
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)R * nq * NB * d;
   return kvb_decode_attention(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_size, num_pages,
@@ -852,7 +861,7 @@ static int launch_decode_fused(const void* qkv, int q_row_stride, void* k_pages,
                                int table_len, int rot, void* out, float* part_o, float* part_ml, int* counters,
                                int R, int nq, int nkv, float scale, int window, int KB, int NB, int* status,
                                unsigned long long* trace, cudaStream_t stream) {
-  int slots = (4 * 148 + nkv * R - 1) / (nkv * R);
+  int slots = (4 * kvb_sm_count() + nkv * R - 1) / (nkv * R);
   slots = slots < 1 ? 1 : (slots > NB ? NB : slots);
   dim3 grid(nkv, R, slots);
   const size_t smem = (size_t)2 * 4 * 32 * D * sizeof(T);   // a key tile and a value tile of 128 positions

@@ -85,6 +85,19 @@ static inline cudaError_t kvb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 b
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 
+// SMs of the current device, asked once per device: what launchers size their grids by.
+static inline int kvb_sm_count() {
+  static int count[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    count[dev] = n;
+  }
+  return count[dev];
+}
+
 static inline int kvb_launch_result() {
   cudaError_t e = cudaPeekAtLastError();
   return (int)e;

@@ -179,12 +179,21 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   while (my_first < t_first) my_first += C;
   int n_mine = (z < C && my_first < n_tiles) ? (n_tiles - 1 - my_first) / C + 1 : 0;   // a block beyond the classes has no tile
   unsigned have0 = 0, have1 = 0;
-  if (n_mine > 0) have0 = request_tile(my_first, 0, write_kv != 0);
-  cp_async_commit();
-  if (kStages > 1) {
-    if (n_mine > 1) have1 = request_tile(my_first + C, 1, write_kv != 0);
+  auto request_first_tiles = [&]() {
+    if (n_mine > 0) have0 = request_tile(my_first, 0, write_kv != 0);
     cp_async_commit();
-  }
+    if (kStages > 1) {
+      if (n_mine > 1) have1 = request_tile(my_first + C, 1, write_kv != 0);
+      cp_async_commit();
+    }
+  };
+  // A layer that reads another layer's cache finds the key and value of the token's own
+  // position there: the owning layer's attention wrote them earlier in this same step, several
+  // launches back.  The wait below orders this kernel behind all of those, a read in front of
+  // it does not; so a block whose first tiles hold that position asks for them after the wait.
+  const bool own_key_from_this_step = !bad && !write_kv && t_star >= my_first && (t_star - my_first) % C == 0 &&
+                                      (t_star - my_first) / C < kStages;
+  if (!own_key_from_this_step) request_first_tiles();
 
   // The new key and value are stored by the block that owns their tile; where they go does
   // not depend on the projection in front, so the page is looked up before the wait.
@@ -203,6 +212,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
 
   pdl_wait();
   stamp(1);   // the projection in front has finished
+  if (own_key_from_this_step) request_first_tiles();
   const __nv_bfloat16* row = qkv + (size_t)q_start[r] * q_row_stride;
   // the owner's loads go out first, so that they are under way while the queries are rotated
   float nk1 = 0.f, nk2 = 0.f, nc = 1.f, ns = 0.f;
@@ -537,9 +547,9 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
   // blocks per cluster: as many as there are classes while the grid stays small, fewer for
   // larger batches (every block then walks several classes and pays its fixed cost once)
   int S = cluster;
-  while (S > 1 && (long long)R * nkv * S > 4 * 148) S >>= 1;
+  while (S > 1 && (long long)R * nkv * S > 4 * kvb_sm_count()) S >>= 1;
   // two stages while every block of the grid fits on the GPU at once
-  const bool deep = (long long)R * nkv * S <= 2 * 148;
+  const bool deep = (long long)R * nkv * S <= 2 * kvb_sm_count();
 #define KVB_DM_ARGS qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, q_start, \
                     ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, S, status, trace, stream
 #define KVB_DM16(GP)                                                        \

@@ -235,7 +235,7 @@ KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int BL, in
       (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
     const size_t work8 = (size_t)T_ * (I / 8);
     const size_t want8 = (work8 + threads - 1) / threads;
-    const int blocks8 = (int)(want8 < (size_t)148 * 32 ? want8 : (size_t)148 * 32);
+    const int blocks8 = (int)(want8 < (size_t)kvb_sm_count() * 32 ? want8 : (size_t)kvb_sm_count() * 32);
     kvb_launch(silu_mul_bf16x8_kernel, dim3(blocks8), dim3(threads), 0, stream, (const __nv_bfloat16*)gu,
                (__nv_bfloat16*)out, I, BL, work8);
     return kvb_launch_result();
@@ -243,7 +243,7 @@ KVB_EXPORT int kvb_silu_mul(const void* gu, void* out, int T_, int I, int BL, in
   const bool vec = (BL % 4 == 0);
   const size_t work = vec ? (size_t)T_ * (I / 4) : (size_t)T_ * I;
   size_t want = (work + threads - 1) / threads;
-  const int blocks = (int)(want < (size_t)148 * 32 ? want : (size_t)148 * 32);
+  const int blocks = (int)(want < (size_t)kvb_sm_count() * 32 ? want : (size_t)kvb_sm_count() * 32);
   if (vec) {
     KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(silu_mul_vec_kernel<T>, dim3(blocks), dim3(threads), 0, stream,
                                               (const T*)gu, (T*)out, I, BL, work)));

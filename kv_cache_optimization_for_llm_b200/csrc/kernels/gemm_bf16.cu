@@ -549,7 +549,7 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
   if (M < 1 || M > 256 || N < 1 || K < 8 || (K & 7)) return KVB_ERR_BAD_SIZE;
   const int tiles = (N + TILE_N - 1) / TILE_N;
   const int k_tiles = (K + TILE_K - 1) / TILE_K;
-  int s = (2 * 148) / tiles;                 // two blocks per SM in flight
+  int s = (2 * kvb_sm_count()) / tiles;                 // two blocks per SM in flight
   if (s > k_tiles / 2) s = k_tiles / 2;      // at least two k tiles per block
   if (s > 8) s = 8;                          // the largest portable cluster
   if (s < 1) s = 1;

@@ -654,7 +654,7 @@ int sm_count() {
   if (!n) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1)
-      n = 148;
+      n = kvb_sm_count();
   }
   return n;
 }

@@ -48,6 +48,23 @@ class StepBatch:
     sampled: Optional[torch.Tensor] = None    # [n] int32 on the device: what ids below zero refer to
 
 
+# Decode launches and captured graphs come in classes by the step's longest context (up to
+# 2048 tokens, up to 8192, beyond); the block tables of a step are as wide as its class needs.
+CONTEXT_CLASS_BOUNDS = (2048, 8192)
+
+
+def table_columns(max_ctx_len: int, page_size: Optional[int], max_pages: int) -> int:
+    """Columns of a step's block tables: the pages that the upper end of the class of the
+    step's longest context spans, at most ``max_pages`` (all of them without a page size).
+    Every step of a class has the same width, so the graph captured for the class fits all."""
+    if page_size is None:
+        return max_pages
+    for bound in CONTEXT_CLASS_BOUNDS:
+        if max_ctx_len <= bound:
+            return max(1, min(max_pages, -(-bound // page_size)))
+    return max_pages
+
+
 class BatchBuilder:
     """Turns entries plus the cache manager's tables into device arrays.
 
@@ -56,21 +73,29 @@ class BatchBuilder:
     host buffer."""
 
     def __init__(self, max_tokens: int, max_reqs: int, max_pages_per_group: Sequence[int], device,
-                 status: torch.Tensor):
+                 status: torch.Tensor, page_size: Optional[int] = None):
+        """``page_size``: tokens per cache page.  When it is given, a step's block tables are
+        only as wide as the step's longest context needs (see :func:`table_columns`) and lie
+        packed behind one another; without it they always have ``max_pages_per_group`` columns."""
         self.max_tokens, self.max_reqs = int(max_tokens), int(max_reqs)
         self.max_pages = [int(m) for m in max_pages_per_group]
+        self.page_size = None if page_size is None else int(page_size)
         self.device = torch.device(device)
         self.status = status
         T, R = self.max_tokens, self.max_reqs
         sizes = [("token_ids", T), ("positions", T), ("token_req", T), ("q_start", R + 1),
                  ("req_start", R), ("ctx_len", R), ("slots", R), ("logit_rows", T)]
-        for g, mp in enumerate(self.max_pages):
-            sizes.append((f"bt{g}", R * mp))
         self.offsets = {}
         off = 0
         for name, n in sizes:
             self.offsets[name] = (off, n)
             off += (n + 3) // 4 * 4  # keep every array 16-byte aligned
+        # The block tables follow, one [requests, columns] array per cache group.  Their widths
+        # change with the step, so their places are worked out per step (a function of the number
+        # of requests and the widths only: a captured graph, keyed by both, finds them again).
+        self.tables_at = off
+        for mp in self.max_pages:
+            off += (R * mp + 3) // 4 * 4
         self.total = off
         use_cuda = self.device.type == "cuda"
         # Two pinned staging buffers, used in turn: the copy of one step may still be under
@@ -149,22 +174,23 @@ class BatchBuilder:
             raise ValueError(f"a token id is outside the vocabulary of {vocab_size}")
         lr = self._view(h, "logit_rows", len(rows))
         lr[:] = rows
-        for g, mp in enumerate(self.max_pages):
-            bt = self._view(h, f"bt{g}", R * mp).reshape(R, mp)
+        max_ctx = int(ctx.max())
+        widths = [table_columns(max_ctx, self.page_size, mp) for mp in self.max_pages]
+        places, off = [], self.tables_at
+        for g, cols in enumerate(widths):
+            places.append(off)
+            bt = h[off:off + R * cols].reshape(R, cols)
             bt.fill(-1)
             bt[n_real:, 0] = scratch_page
             for r, e in enumerate(entries[:n_real]):
                 table = cache.block_table(e.request_id, g)
-                if len(table) > mp:
+                if len(table) > self.max_pages[g]:
                     raise ValueError(f"request {e.request_id} holds {len(table)} pages in group {g}, "
-                                     f"tables were sized for {mp}")
-                bt[r, :len(table)] = table
-        # Block tables lie last, so one copy of the used prefix carries everything.
-        if self.max_pages:
-            g = len(self.max_pages) - 1
-            used = self.offsets[f"bt{g}"][0] + R * self.max_pages[g]
-        else:
-            used = self.total
+                                     f"tables were sized for {self.max_pages[g]}")
+                n = min(len(table), cols)      # pages beyond the step's longest context are not read
+                bt[r, :n] = table[:n]
+            off += (R * cols + 3) // 4 * 4
+        used = off      # the tables lie last, so one copy of the used prefix carries everything
         self.dev_buf[:used].copy_(stage["buf"][:used], non_blocking=True)
         if stage["event"] is not None:
             stage["event"].record()
@@ -177,10 +203,10 @@ class BatchBuilder:
             token_req=self._view(d, "token_req", T), q_start=self._view(d, "q_start", R + 1),
             req_start=self._view(d, "req_start", R), ctx_len=self._view(d, "ctx_len", R),
             slots=self._view(d, "slots", R),
-            block_tables=[self._view(d, f"bt{g}", R * mp).view(R, mp) for g, mp in enumerate(self.max_pages)],
+            block_tables=[d[at:at + R * cols].view(R, cols) for at, cols in zip(places, widths)],
             logit_rows=self._view(d, "logit_rows", len(rows)), num_logits=len(rows),
             max_q_len=max(len(e.tokens) for e in entries),
-            max_ctx_len=int(ctx.max()),
+            max_ctx_len=max_ctx,
             decode_only=all(len(e.tokens) == 1 for e in entries),
             status=self.status,
             host={"q_start": qs.copy(), "ctx_len": ctx.copy(), "req_start": rstart.copy()},

@@ -6,7 +6,7 @@ from typing import Dict, List, Mapping
 
 import torch
 
-from ..models.spec import ModelSpec, PartSpec, expected_weights
+from ..models.spec import ModelSpec, PartSpec, block_part_families, expected_weights
 from ..parts import BuildContext, lookup
 from ..weights.loader import to_compute
 
@@ -31,19 +31,20 @@ class DecoderModel:
             cls = lookup(family, ps.kind)
             return cls(ps.params, {role: dev[name] for role, name in ps.weights.items()}, ctx)
 
+        ctx.make = make     # parts that hold further parts build them through this
         self.embedding = make("embedding", spec.embedding)
         self.layers = []
         for ls in spec.layers:
             block_cls = lookup("block", ls.block)
-            self.layers.append(block_cls(make("mixer", ls.mixer), make("norm", ls.mixer_norm),
-                                         make("feed_forward", ls.feed_forward), make("norm", ls.ff_norm)))
+            self.layers.append(block_cls({name: make(family, ls.parts[name])
+                                          for name, family in block_part_families(ls.block).items()}))
         self.final_norm = make("norm", spec.final_norm)
         self.head = make("head", spec.lm_head)
         self.schedule = list(spec.schedule)
 
     def cache_specs(self):
         """Per schedule entry: what its mixer asks of the cache, and whose cache it reads."""
-        specs = [self.layers[e.layer].mixer.cache_spec() for e in self.schedule]
+        specs = [self.layers[e.layer].cache_spec() for e in self.schedule]
         return specs, [e.cache_of for e in self.schedule]
 
     def kernel_modules(self) -> List[str]:
@@ -67,7 +68,8 @@ def kernel_modules_of(spec: ModelSpec, dtype: torch.dtype) -> List[str]:
     for family, ps in iter_parts(spec):
         if family == "block":
             continue
-        for m in lookup(family, ps.kind).kernel_modules(ps.params, dtype):
+        cls = lookup(family, ps.kind)
+        for m in (cls.kernel_modules(ps.params, dtype) if hasattr(cls, "kernel_modules") else ()):
             if m not in mods:
                 mods.append(m)
     return mods

@@ -51,6 +51,9 @@ class ModelRunner:
         # float32 means float32: no reduced-precision matrix mode anywhere.
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
+        # bfloat16 library products add up in float32 whatever the split of K (upstream:
+        # CUBLAS_COMPUTE_32F, base/src/engine.cu:653-671)
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         self.model_dir = Path(model_dir) if model_dir is not None else None
         if self.model_dir is None and not random_init:
             raise ValueError("a model folder or random_init is required")
@@ -95,7 +98,8 @@ class ModelRunner:
                                 self.max_model_len, self.dtype, self.device)
         self.manager = self.cache.manager
         self.builder = BatchBuilder(self.config.max_num_batched_tokens, self.config.max_num_seqs,
-                                    self.cache.max_pages, self.device, self.status)
+                                    self.cache.max_pages, self.device, self.status,
+                                    page_size=self.config.page_size)
         self.vocab_size = self.spec.vocab_size
         # Where the sampling kernel leaves a step's tokens (one per sampled request, in the
         # step's order; the last entry carries the kernels' error word).  A step whose entries

@@ -24,8 +24,7 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
-        layers.append(LayerSpec(
-            block="prenorm",
+        layers.append(LayerSpec(block="prenorm", parts=dict(
             mixer=PartSpec("attention", {
                 "hidden_size": cfg.hidden_size,
                 "num_heads": cfg.num_attention_heads,
@@ -47,7 +46,7 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
             }),
             ff_norm=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps},
                              {"weight": p + "post_attention_layernorm.weight"}),
-        ))
+        )))
     embed_name = "model.embed_tokens.weight"
     spec = ModelSpec(
         architecture=cfg.architecture,

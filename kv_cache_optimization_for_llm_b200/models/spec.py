@@ -19,20 +19,24 @@ from ..weights.loader import WeightSpec
 class PartSpec:
     """One part: ``kind`` picks the class from its family's registry, ``params`` holds
     its sizes and constants, ``weights`` maps the part's tensor roles to checkpoint
-    tensor names."""
+    tensor names.  A part may hold further parts among its ``params`` (a mixer its
+    position encoding, a mixer a norm of its own, a feed-forward its experts): such a
+    nested part belongs to the family that its ``family`` names, or, if that is empty,
+    to the family called like the key it sits under."""
     kind: str
     params: dict = field(default_factory=dict)
     weights: Dict[str, str] = field(default_factory=dict)
+    family: str = ""
 
 
 @dataclass
 class LayerSpec:
-    """A layer: a block arrangement around a mixer and a feed-forward with their norms."""
+    """A layer: a block arrangement and the parts it arranges, by the names the block
+    gives them.  Which names a block takes, and of which family each is, is the block
+    class's ``part_families`` (the pre-norm block: mixer, mixer_norm, feed_forward,
+    ff_norm); a block with further norms or a third branch simply names more."""
     block: str
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    ff_norm: PartSpec
+    parts: Dict[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass
@@ -68,21 +72,51 @@ class ModelSpec:
                                  "which keeps none of its own")
 
 
+def _with_nested(family: str, ps: PartSpec):
+    """The part, then every part nested in its params (directly, or in lists, tuples and
+    dicts there), depth first."""
+    yield family, ps
+
+    def walk(key, value):
+        if isinstance(value, PartSpec):
+            yield from _with_nested(value.family or key, value)
+        elif isinstance(value, (list, tuple)):
+            for v in value:
+                yield from walk(key, v)
+        elif isinstance(value, dict):
+            for k, v in value.items():
+                yield from walk(k, v)
+
+    for key, value in ps.params.items():
+        yield from walk(key, value)
+
+
+def block_part_families(block_kind: str) -> Dict[str, str]:
+    """name -> family of the parts that a block arrangement takes."""
+    from ..parts import registry as parts
+    cls = parts.lookup("block", block_kind)
+    fam = getattr(cls, "part_families", None)
+    if not fam:
+        raise ValueError(f"block {block_kind!r} does not say which parts it takes (part_families)")
+    return dict(fam)
+
+
 def iter_parts(spec: ModelSpec):
-    """(family, PartSpec) of every part of the model, nested ones (a mixer's position
-    encoding) included."""
-    yield "embedding", spec.embedding
-    for layer in spec.layers:
+    """(family, PartSpec) of every part of the model, nested ones included, whatever
+    their family and however deep."""
+    yield from _with_nested("embedding", spec.embedding)
+    for i, layer in enumerate(spec.layers):
         yield "block", PartSpec(layer.block)
-        yield "mixer", layer.mixer
-        pos = layer.mixer.params.get("position")
-        if isinstance(pos, PartSpec):
-            yield "position", pos
-        yield "norm", layer.mixer_norm
-        yield "feed_forward", layer.feed_forward
-        yield "norm", layer.ff_norm
-    yield "norm", spec.final_norm
-    yield "head", spec.lm_head
+        families = block_part_families(layer.block)
+        missing = sorted(set(families) - set(layer.parts))
+        extra = sorted(set(layer.parts) - set(families))
+        if missing or extra:
+            raise ValueError(f"layer {i}: block {layer.block!r} takes the parts {sorted(families)}; "
+                             f"missing {missing}, not taken {extra}")
+        for name, family in families.items():
+            yield from _with_nested(family, layer.parts[name])
+    yield from _with_nested("norm", spec.final_norm)
+    yield from _with_nested("head", spec.lm_head)
 
 
 def expected_weights(spec: ModelSpec) -> Dict[str, WeightSpec]:
@@ -91,10 +125,11 @@ def expected_weights(spec: ModelSpec) -> Dict[str, WeightSpec]:
     from ..parts import registry as parts
     out: Dict[str, WeightSpec] = {}
     for family, ps in iter_parts(spec):
-        if family in ("block", "position"):
+        if family == "block":
             continue
         cls = parts.lookup(family, ps.kind)
-        for role, ws in cls.weight_specs(ps.params).items():
+        wanted = cls.weight_specs(ps.params) if hasattr(cls, "weight_specs") else {}
+        for role, ws in wanted.items():
             if role not in ps.weights:
                 raise ValueError(f"part {family}/{ps.kind} needs a tensor for role {role!r}, "
                                  f"the spec names only {sorted(ps.weights)}")

@@ -12,6 +12,7 @@ every matrix product of the float32 path, is a kernel of this package.
 
 from __future__ import annotations
 
+import collections
 import ctypes
 import os
 from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
@@ -23,6 +24,9 @@ from . import build
 
 _libs: Dict[str, ctypes.CDLL] = {}
 launch_count = 0  # kernels of this package launched so far (library calls are not counted)
+# Which kernel the dispatch below picked, how often (a launch that is captured into a graph counts
+# once, at capture): what a test reads to see that the path it means to check is the one that ran.
+choices: "collections.Counter[str]" = collections.Counter()
 
 _ERR = {-1: "unsupported dtype", -2: "a size this kernel refuses", -3: "misaligned pointer or stride"}
 
@@ -77,6 +81,17 @@ def _stream() -> c_void_p:
 
 def _p(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
+
+
+_sm_count: Dict[int, int] = {}
+
+
+def sm_count(device) -> int:
+    """SMs of the device (asked once): what the dispatch compares a step's tiles with."""
+    idx = torch.device(device).index or 0
+    if idx not in _sm_count:
+        _sm_count[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return _sm_count[idx]
 
 
 def dtype_code(dt: torch.dtype) -> int:
@@ -179,6 +194,7 @@ def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token
         _p(token_req), _p(out), c_int(T), c_int(nq), c_int(nkv), c_int(d), c_float(scale),
         c_int(int(window or 0)), c_int(dtype_code(qkv.dtype)), _p(status), _stream())
     _check(rc, "paged_attention_generic")
+    choices["paged_attention_generic"] += 1
     return out
 
 
@@ -271,12 +287,14 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
         rc = lib("gemm_f32").kvb_sgemm_nt(_p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out),
                                           c_int(N), c_int(M), c_int(N), c_int(K), _stream())
         _check(rc, "sgemm_nt")
+        choices["sgemm_nt"] += 1
         return out
     if M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
         return gemm_skinny(x, w, out_dtype or x.dtype, kernel_status(x.device),
                            x_is_static=torch.cuda.is_current_stream_capturing())
     if WIDE == "all" and _wide_ok(x, w, 8) and (out_dtype is None or out_dtype == x.dtype):
         return gemm_wide(x, w, kernel_status(x.device))
+    choices["library_product"] += 1
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, w.t(), out_dtype=out_dtype)
     return torch.nn.functional.linear(x, w)
@@ -435,7 +453,7 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
     # 128-row tiles when there are enough of them to keep every SM busy, else 64-row tiles
     nt128 = int(lib("flash_attention").kvb_flash_attention_tokens_per_tile(c_int(nq // nkv), c_int(1)))
     if wide is None:
-        wide = FLASH_WIDE and (T // nt128) * nkv >= 2 * 148
+        wide = FLASH_WIDE and (T // nt128) * nkv >= 2 * sm_count(qkv.device)
         if wide and FLASH_TC and d == 64:
             roles = (FLASH_TC_ROLES and k_pages.shape[2] >= 8 and k_pages.data_ptr() % 16 == 0
                      and v_pages.data_ptr() % 16 == 0)
@@ -448,6 +466,7 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
         c_int(int(wide)), _p(out), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), _p(batch.status),
         _stream())
     _check(rc, "paged_flash_attention")
+    choices[f"flash_attention_{int(wide)}"] += 1
     return out
 
 
@@ -474,6 +493,7 @@ def decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, q_start
         _p(counters), c_int(R), c_int(nq), c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)),
         c_int(kb), c_int(nb), c_int(dtype_code(qkv.dtype)), _p(status), _p(trace), _stream())
     _check(rc, "decode_attention_fused")
+    choices["decode_attention_fused"] += 1
     return out
 
 
@@ -487,15 +507,17 @@ def decode_context_class(max_ctx: int) -> int:
     """The classes of 128-key tiles (4, 8 or 16) that the longest context of a decode step
     needs in the tensor-core decode attention.  The launch (kernel variant, blocks per request)
     depends on it, the results do not; steps are replayed from graphs captured per class."""
-    return 4 if max_ctx <= 2048 else (8 if max_ctx <= 8192 else 16)
+    from .engine.batch import CONTEXT_CLASS_BOUNDS as bounds   # the block tables' widths follow the same classes
+    return 4 if max_ctx <= bounds[0] else (8 if max_ctx <= bounds[1] else 16)
 
 
 def decode_launch_context(batch) -> int:
     """The context length a decode step's launches are sized for: the upper end of the class
     of the step's longest context, so that every step of a class launches alike (a captured
     graph is replayed for all of them)."""
+    from .engine.batch import CONTEXT_CLASS_BOUNDS as bounds
     c = decode_context_class(int(batch.max_ctx_len))
-    return 2048 if c == 4 else (8192 if c == 8 else 1 << 30)
+    return bounds[0] if c == 4 else (bounds[1] if c == 8 else 1 << 30)
 
 
 def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
@@ -519,6 +541,7 @@ def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, 
         c_int(nkv), c_int(d), c_float(scale), c_int(int(window or 0)), c_int(int(max_ctx)),
         _p(status), _p(trace), _stream())
     _check(rc, "decode_attention_mma")
+    choices["decode_attention_mma"] += 1
     return out
 
 
@@ -610,6 +633,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
     if rc == -2:
         raise KernelError(f"gemm_skinny refuses M={M}, N={N}, K={K} (M <= 256 and K a multiple of 8 are required)")
     _check(rc, "gemm_skinny")
+    choices["gemm_skinny"] += 1
     return out
 
 
@@ -650,6 +674,7 @@ def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, ro
     if rc == -2:
         raise KernelError(f"gemm_skinny_fused refuses M={M}, N={N}, K={K}, epilogue {epilogue}")
     _check(rc, "gemm_skinny_fused")
+    choices["gemm_skinny_fused"] += 1
     return Folded(xb, sumsq) if into is not None else out
 
 
@@ -695,6 +720,7 @@ def gemm_wide(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, epilogue: 
         raise KernelError(f"gemm_wide refuses M={M}, N={N}, K={K}, epilogue {epilogue}, tile {tile} (K and N "
                           "multiples of 8, N a multiple of 128 for swiglu, 16-byte aligned rows are required)")
     _check(rc, "gemm_wide")
+    choices["gemm_wide"] += 1
     return Folded(xb, sumsq) if into is not None else out
 
 

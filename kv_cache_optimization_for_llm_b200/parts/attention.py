@@ -54,7 +54,8 @@ class GroupedQueryAttention(Part):
         pos = params.get("position")
         self.position = None
         if pos is not None:
-            self.position = lookup("position", pos.kind)(pos.params, {}, ctx)
+            self.position = (ctx.make("position", pos) if ctx.make is not None
+                             else lookup("position", pos.kind)(pos.params, {}, ctx))
 
     fuses_residual = True
 

@@ -10,7 +10,11 @@ nothing of the model it sits in.  Interfaces by family:
                  ``forward(x, batch, cache) -> delta``
 * feed_forward:  ``forward(x, batch) -> delta``
 * position:      whatever its mixer uses (rope: ``tables() -> (cos, sin)``)
-* block:         ``forward(residual, delta, batch, cache) -> (residual, delta)``
+* block:         ``part_families`` (name -> family of the parts it arranges), built from a
+                 mapping name -> part; ``cache_spec()`` (what the layer asks of the cache) and
+                 ``forward(residual, delta, batch, cache) -> (residual, delta)``
+* a part that holds further parts (a ``PartSpec`` among its params) builds them with
+  ``ctx.make(family, spec)``, which also hands them their tensors
 * a mixer or feed-forward may set ``fuses_residual = True``; it then has
   ``fold_input_scale(vector)``, and its ``forward`` also takes ``into=residual`` and may get
   ``x`` as an ``ops.PendingNorm`` (see the prenorm block)
@@ -21,7 +25,7 @@ nothing of the model it sits in.  Interfaces by family:
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Mapping
+from typing import Callable, Dict, Mapping, Optional
 
 import torch
 
@@ -35,6 +39,7 @@ class BuildContext:
     max_positions: int          # positions the engine may ever see
     status: torch.Tensor        # [1] int32 device word for kernel-side error reports
     shared: dict = field(default_factory=dict)  # tables shared between equal parts
+    make: Optional[Callable] = None  # (family, PartSpec) -> the built part with its tensors; set by the model
 
 
 class Part:

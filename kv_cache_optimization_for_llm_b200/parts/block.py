@@ -23,13 +23,20 @@ class PreNormBlock(Part):
     an ``ops.PendingNorm``, carried out by the part's first product, and gets the residual as
     ``into=``, which its last product may add to itself, returning an ``ops.Folded``."""
 
-    def __init__(self, mixer, mixer_norm, feed_forward, ff_norm):
-        self.mixer, self.mixer_norm = mixer, mixer_norm
-        self.feed_forward, self.ff_norm = feed_forward, ff_norm
-        for part, norm in ((mixer, mixer_norm), (feed_forward, ff_norm)):
+    # the parts this arrangement takes, by name, and the family each is looked up in
+    part_families = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "ff_norm": "norm"}
+
+    def __init__(self, parts):
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.feed_forward, self.ff_norm = parts["feed_forward"], parts["ff_norm"]
+        for part, norm in ((self.mixer, self.mixer_norm), (self.feed_forward, self.ff_norm)):
             if (getattr(part, "fuses_residual", False) and part.ctx.dtype == torch.bfloat16
                     and hasattr(norm, "give_up_weight") and norm.weight is not None):
                 part.fold_input_scale(norm.give_up_weight())
+
+    def cache_spec(self):
+        """What this layer asks of the cache: its mixer's wish."""
+        return self.mixer.cache_spec()
 
     def forward(self, residual, delta, batch, cache):
         if getattr(self.mixer, "fuses_residual", False):

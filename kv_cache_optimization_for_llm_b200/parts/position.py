@@ -18,6 +18,10 @@ def rope_inv_freq(head_dim: int, theta: float, scaling) -> torch.Tensor:
     inv = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float64), 2.0 * i / head_dim)
     if not scaling:
         return inv
+    kind = scaling.get("rope_type", scaling.get("type", "llama3"))
+    if kind != "llama3":
+        raise ValueError(f"rope scaling of type {kind!r} is not known to this position encoding "
+                         "(known: none, 'llama3')")
     factor = float(scaling["factor"])
     low_ff, high_ff = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
     orig = float(scaling["original_max_position_embeddings"])
@@ -45,7 +49,7 @@ class RotaryEncoding(Part):
         if self.rotary_dim % 2 or self.rotary_dim > params["head_dim"]:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim")
         key = ("rope", self.rotary_dim, float(params["theta"]),
-               tuple(sorted((params["scaling"] or {}).items())), ctx.max_positions)
+               tuple(sorted((k, str(v)) for k, v in (params["scaling"] or {}).items())), ctx.max_positions)
         if key not in ctx.shared:
             inv = rope_inv_freq(self.rotary_dim, params["theta"], params["scaling"])
             ang = torch.arange(ctx.max_positions, dtype=torch.float64)[:, None] * inv[None, :]

@@ -185,10 +185,12 @@ def decoder_layer(h, w, layer, cfg, positions, inv_freq):
     return h
 
 
-def forward(cfg, w, tokens):
+def forward(cfg, w, tokens, rows=None):
     """Logits [T, vocab] of one whole sequence: embedding gather (no scale),
     the layers, final norm, LM head = embedding when tied
-    (base/src/engine.cu:637,639-890)."""
+    (base/src/engine.cu:637,639-890).  ``rows``: the positions whose logits are
+    wanted (the head then runs on those rows only, as upstream's does on the last
+    row of each prompt, base/src/engine.cu:862-890); None: all."""
     tokens = np.asarray(tokens, dtype=np.int64)
     nq = cfg["num_attention_heads"]
     d = cfg.get("head_dim") or cfg["hidden_size"] // nq
@@ -197,6 +199,8 @@ def forward(cfg, w, tokens):
     h = w["model.embed_tokens.weight"][tokens]
     for layer in range(cfg["num_hidden_layers"]):
         h = decoder_layer(h, w, layer, cfg, positions, inv_freq)
+    if rows is not None:
+        h = h[np.asarray(list(rows), dtype=np.int64)]
     x = rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return linear(x, head)

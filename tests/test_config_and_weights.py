@@ -164,3 +164,63 @@ def test_no_gpu_means_a_clear_error_not_a_fallback():
     from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
     with pytest.raises(RuntimeError, match="no CPU path"):
         ModelRunner(model_dir("tiny_a"), EngineConfig(dtype="float32", num_pages=4))
+
+
+def test_checkpoint_in_two_shards_with_an_index():
+    """model.safetensors.index.json names the file of every tensor; the loader reads all the
+    files it names and reports a tensor that none of them holds like any other missing one."""
+    arch = resolve_architecture(TINY_B)
+    want = expected_weights(arch.build_spec(arch.parse_config(TINY_B)))
+    good = read_tensors(os.path.join(model_dir("tiny_b"), "model.safetensors"))
+    names = sorted(good)
+    half = len(names) // 2
+    shards = {"model-00001-of-00002.safetensors": names[:half], "model-00002-of-00002.safetensors": names[half:]}
+    d = tempfile.mkdtemp()
+    try:
+        json.dump(TINY_B, open(os.path.join(d, "config.json"), "w"))
+        for fname, ns in shards.items():
+            write_tensors(os.path.join(d, fname), {n: good[n] for n in ns})
+        index = {"metadata": {}, "weight_map": {n: f for f, ns in shards.items() for n in ns}}
+        json.dump(index, open(os.path.join(d, "model.safetensors.index.json"), "w"))
+        got = check_and_load(d, want)
+        assert set(got) == set(want) and all(torch.equal(got[n], good[n]) for n in want)
+        # the second shard loses a tensor
+        lost = names[-1]
+        write_tensors(os.path.join(d, "model-00002-of-00002.safetensors"), {n: good[n] for n in names[half:-1]})
+        with pytest.raises(WeightError) as ei:
+            check_and_load(d, want)
+        assert ei.value.missing == [lost]
+    finally:
+        shutil.rmtree(d)
+
+
+def test_layer_parts_are_a_mapping_and_nested_parts_are_found():
+    """A layer names its parts as the block arrangement calls them; a part nested in another
+    part's params, whatever its family and however deep, counts for the expected tensors and
+    the kernel modules; a layer that names a part the block does not take is refused."""
+    from kv_cache_optimization_for_llm_b200.engine.model import kernel_modules_of
+    from kv_cache_optimization_for_llm_b200.models.spec import PartSpec, iter_parts
+    arch = resolve_architecture(TINY_A)
+    spec = arch.build_spec(arch.parse_config(TINY_A))
+    fams = [f for f, _ in iter_parts(spec)]
+    assert fams.count("position") == 2 and fams.count("mixer") == 2 and fams.count("norm") == 5
+    assert set(spec.layers[0].parts) == {"mixer", "mixer_norm", "feed_forward", "ff_norm"}
+    # a norm of its own inside the mixer's params, inside a list, under a key that is no family name
+    inner = PartSpec("rmsnorm", {"size": 16, "eps": 1e-6}, {"weight": "model.layers.0.self_attn.q_norm.weight"},
+                     family="norm")
+    spec.layers[0].parts["mixer"].params["extras"] = [{"q_norm": inner}]
+    assert ("norm", inner) in list(iter_parts(spec))
+    assert expected_weights(spec)["model.layers.0.self_attn.q_norm.weight"].shape == (16,)
+    assert "elementwise" in kernel_modules_of(spec, torch.float32)
+    spec.layers[1].parts["post_norm"] = inner
+    with pytest.raises(ValueError, match="not taken \\['post_norm'\\]"):
+        list(iter_parts(spec))
+
+
+def test_rotary_part_refuses_a_scaling_it_does_not_know():
+    from kv_cache_optimization_for_llm_b200.parts.position import rope_inv_freq
+    ok = rope_inv_freq(64, 500000.0, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                      "high_freq_factor": 4.0, "original_max_position_embeddings": 64})
+    assert ok.shape == (32,)
+    with pytest.raises(ValueError, match="yarn"):
+        rope_inv_freq(64, 500000.0, {"rope_type": "yarn", "factor": 8.0})

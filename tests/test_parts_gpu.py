@@ -182,7 +182,8 @@ def _register_toy():
         for i, kind in enumerate(cfg["mixers"]):
             p = f"l{i}."
             mixer = attn(p, windows[i]) if kind == "attention" else PartSpec("toy_decay", {"hidden_size": H, "decay": cfg["decay"]}, {"w": p + "decay.w"})
-            layers.append(LayerSpec("prenorm", mixer, norm(p + "n1"), ff(p), norm(p + "n2")))
+            layers.append(LayerSpec("prenorm", dict(mixer=mixer, mixer_norm=norm(p + "n1"), feed_forward=ff(p),
+                                                    ff_norm=norm(p + "n2"))))
         return ModelSpec(architecture="ToyForCausalLM", hidden_size=H, vocab_size=V, max_position=cfg["max_pos"],
                          embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, {"table": "emb"}),
                          layers=layers,
@@ -324,3 +325,40 @@ def test_windowed_and_full_layers_have_page_groups_of_their_own():
         r.check_status()
         r.release(0)
         assert m.free_pages(gw) == 24 and m.free_pages(gf) == 24
+
+
+TOY_SHARED_64 = {"architectures": ["ToyForCausalLM"], "hidden_size": 96, "vocab_size": 211, "inter": 128, "eps": 1e-5,
+                 "heads": 4, "kv_heads": 2, "head_dim": 64, "max_pos": 320, "decay": 0.8,
+                 # layers 1 and 2 read the keys and values that layer 0 wrote in the same step
+                 "mixers": ["attention", "attention", "attention"],
+                 "schedule": [[0, None], [1, 0], [2, 0], [1, None]]}
+
+
+def test_layers_that_read_another_layers_cache_decode_in_bfloat16_through_the_engine():
+    """Head size 64, bfloat16, the engine one step ahead, decode steps from captured graphs with
+    every kernel launched as a programmatic dependent of the one in front: a layer that keeps
+    no cache of its own must still see the key and value that the owning layer wrote for the
+    step's own token a few launches earlier.  Logits of every sampled row against the plain
+    restatement, for two requests of different lengths beside each other."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, SamplingParams
+    from kv_cache_optimization_for_llm_b200.engine.llm_engine import LLMEngine
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+    from logit_hook import LogitRecorder
+    _register_toy()
+    d = tempfile.mkdtemp(prefix="kvb200_toy64_")
+    write_random_model(d, TOY_SHARED_64, seed=9, std=0.1, storage_dtype="bfloat16")
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    eng = LLMEngine(d, EngineConfig(dtype="bfloat16", page_size=16, num_pages=48, max_num_seqs=4,
+                                    max_num_batched_tokens=64, max_model_len=320, use_cuda_graphs=True, run_ahead=True))
+    rec = LogitRecorder(eng.runner)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 211, n).tolist() for n in (5, 130, 61)]
+    ids = [eng.add_request(p, SamplingParams(max_tokens=40, temperature=0.8, seed=i, ignore_eos=True))
+           for i, p in enumerate(prompts)]
+    while eng.has_unfinished():
+        eng.step()
+    seqs = {rid: prompts[i] + eng.output(rid) for i, rid in enumerate(ids)}
+    n, worst = rec.compare(seqs, lambda rid: _toy_plain(TOY_SHARED_64, w, seqs[rid]), 4e-2, "toy with shared caches")
+    assert n >= 3 * 40 and eng.runner._graphs
+    assert eng.runner.manager.check() == ""
+    print(f"shared caches, head size 64: {n} rows, worst relative error {worst:.3e}")

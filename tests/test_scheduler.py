@@ -285,3 +285,34 @@ def test_pending_token_protocol():
     s.abort(1)
     assert s.resolve(1, 9) == H.FinishReason.ABORTED and s.output(1) == []
     assert cache.check() == "" and cache.free_pages(0) == 8
+
+
+def test_a_long_prompt_goes_through_a_small_windowed_pool_in_smaller_portions():
+    """Only windowed layers (window 8, pages of 4), a pool of 6 pages = 24 tokens, a budget of
+    64 tokens per step and a prompt of 100: one portion of 64 tokens would need 16 pages at once.
+    The scheduler halves the portion until its pages fit, the window gives pages back after every
+    step, and the request finishes with all its tokens instead of ending with an error."""
+    cache = H.CacheManager([H.GroupSpec(4, 8)], [6], 2)
+    s = H.Scheduler(cache, H.SchedulerConfig(2, 64, 256, 0))
+    s.add(0, list(range(100)), 5)
+    sizes = []
+    steps = 0
+    while s.has_unfinished():
+        plan, _ = run_step(s)
+        assert not plan.finished, "ended with an error although smaller portions fit"
+        sizes.append([len(e.tokens) for e in plan.entries])
+        assert cache.check() == ""
+        steps += 1
+        assert steps < 200
+    assert s.finish_reason(0) == H.FinishReason.LENGTH and len(s.output(0)) == 5
+    assert sum(n for step in sizes for n in step) == 100 + 4
+    assert max(n for step in sizes for n in step) <= 16 and cache.free_pages(0) == 6
+    # a pool that keeps every key gets no smaller portions: the request that is alone and
+    # too large still ends at once (the prompt fits, its output does not)
+    cache2, s2 = make(pages=3, page_size=4, budget=64)
+    s2.add(0, list(range(11)), 8)
+    reasons = []
+    for _ in range(6):
+        plan, _ = run_step(s2)
+        reasons += [s2.finish_reason(i) for i in plan.finished]
+    assert reasons == [H.FinishReason.CACHE_EXHAUSTED]

@@ -74,8 +74,14 @@ def _register():
     class ParallelBlock:
         """``h += mixer(norm1(h)) + ff(norm2(h))``: both branches read the same residual."""
 
-        def __init__(self, mixer, mixer_norm, feed_forward, ff_norm):
-            self.mixer, self.mixer_norm, self.feed_forward, self.ff_norm = mixer, mixer_norm, feed_forward, ff_norm
+        part_families = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "ff_norm": "norm"}
+
+        def __init__(self, parts):
+            self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+            self.feed_forward, self.ff_norm = parts["feed_forward"], parts["ff_norm"]
+
+        def cache_spec(self):
+            return self.mixer.cache_spec()
 
         def forward(self, residual, delta, batch, cache):
             x1 = self.mixer_norm.forward(residual, delta)      # adds what the layer before left pending
@@ -103,7 +109,8 @@ def _register():
             else:
                 ff = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": lc["inter"]},
                               {"gate": p + "ff.gate", "up": p + "ff.up", "down": p + "ff.down"})
-            layers.append(LayerSpec(lc["block"], mixer, norm(p + "n1"), ff, norm(p + "n2")))
+            layers.append(LayerSpec(lc["block"], dict(mixer=mixer, mixer_norm=norm(p + "n1"), feed_forward=ff,
+                                                     ff_norm=norm(p + "n2"))))
         return ModelSpec(architecture="ToyRoutedForCausalLM", hidden_size=H, vocab_size=V, max_position=cfg["max_pos"],
                          embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, {"table": "emb"}),
                          layers=layers, schedule=[ScheduleEntry(i) for i in range(len(layers))],

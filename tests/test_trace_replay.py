@@ -43,6 +43,18 @@ def cut(n, sizes):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d", "tiny_e"])
 def test_replay_all_cuttings(name, dtype):
+    _replay(name, dtype)
+
+
+@pytest.mark.parametrize("name,dtype", [("tiny_b", "float32"), ("tiny_d", "bfloat16"), ("tiny_e", "bfloat16")])
+def test_replay_all_cuttings_with_cuda_graphs(name, dtype):
+    """The same matrix with steps of single tokens replayed from captured graphs, as generation
+    runs them: one, two and up to four live requests (graphs of 1, 2 and 4 rows, the last with a
+    padding row when three are live)."""
+    _replay(name, dtype, ("--cuda-graphs",))
+
+
+def _replay(name, dtype, flags=()):
     cfg_dict, seed, _ = CONFIGS[name]
     storage = "float32" if dtype == "float32" else "bfloat16"
     mdir = model_dir(name, storage)
@@ -55,7 +67,7 @@ def test_replay_all_cuttings(name, dtype):
     # that the single-request phases before it already reuse pages again and again.
     max_tokens = sum(ceil64(len(s)) for s in seqs)
     extra = {"tiny_a": ("--page-size", "4"), "tiny_e": ("--page-size", "8")}.get(name, ())
-    tr = TraceRun(mdir, dtype, max_tokens, extra)
+    tr = TraceRun(mdir, dtype, max_tokens, tuple(extra) + tuple(flags))
     worst = 0.0
     try:
         # 1. each request alone and whole
