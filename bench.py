@@ -95,9 +95,11 @@ class ClockSampler:
         """Clocks of the samples that fall inside the timed windows [(t0, t1), ...]."""
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for t, line in self.lines:
-            if not any(a <= t <= b for a, b in windows):
-                continue
+        inside = [(t, line) for t, line in self.lines if any(a <= t <= b for a, b in windows)]
+        if len(inside) < 3:
+            # timed regions shorter than the sampling period: take the samples next to them as well
+            inside = [(t, line) for t, line in self.lines if any(a - 0.25 <= t <= b + 0.25 for a, b in windows)]
+        for t, line in inside:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -216,10 +218,10 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "upstream is a CMake/CUDA program with no setup.py or pyproject.toml (pip: 'not installable'), "
-                          "its sizes are compile-time constants for sm_75 and it needs the real checkpoint"}))
-        return 0
+        # upstream's own engine, unmodified, driven through its standard input and output
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import reference_arm
+        return reference_arm.run(args, dict(LLAMA_1B), PROMPT_LEN, NEW_TOKENS, ClockSampler)
     if args.gpus != 1:
         print(f"bench.py measures one GPU only (this engine runs on one GPU); got --gpus {args.gpus}")
         return 2
@@ -257,14 +259,18 @@ def main():
 
     step_bytes = nums["weight_bytes"] + args.batch * mean_ctx * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms_per_step / 1000.0) / 1e9
-    points, prefill = {}, None
+    points, point_rooflines, prefill = {}, {}, None
     if not args.skip_points:
         for b in (1, 64):
             log(f"decode, batch {b}")
-            s, _, _, win = run_decode(llm, b, args.steps, args.warmup, False, seed=2 + b)
+            s, ctx_b, _, win = run_decode(llm, b, args.steps, args.warmup, False, seed=2 + b)
             windows.append(win)
             points[f"decode_b{b}"] = round(b * args.steps / s, 1)
-            log(f"  {points[f'decode_b{b}']:.0f} tok/s")
+            bytes_b = nums["weight_bytes"] + b * ctx_b * nums["kv_bytes_per_token"]
+            gbs = bytes_b / (s / args.steps) / 1e9
+            point_rooflines[f"decode_b{b}"] = {"ms_per_step": round(1000.0 * s / args.steps, 4), "bytes": int(bytes_b),
+                                               "achieved": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 4)}
+            log(f"  {points[f'decode_b{b}']:.0f} tok/s, {gbs:.0f} GB/s = {gbs / pk['hbm_gbs']:.3f} of {pk['source']} HBM peak")
         log(f"prefill of {PREFILL_TOKENS} tokens")
         w0 = time.perf_counter()
         ms = run_prefill(llm, reps=5, warmup=3, seed=9)
@@ -298,7 +304,8 @@ def main():
                 "d2h_bytes_per_step": int(b_out)},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]},
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"], "bytes": int(step_bytes),
+                     "points": point_rooflines},
         "clocks": clocks,
     }
     if prefill is not None:
