@@ -33,6 +33,23 @@ LLAMA_1B = {
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
     "max_position_embeddings": 131072, "tie_word_embeddings": True, "hidden_act": "silu",
 }
+_LLAMA3_ROPE = {"rope_type": "llama3", "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                "original_max_position_embeddings": 8192}
+LLAMA_3B = dict(LLAMA_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, num_key_value_heads=8,
+                head_dim=128, intermediate_size=8192, rope_scaling=dict(_LLAMA3_ROPE, factor=32.0))
+LLAMA_8B = dict(LLAMA_1B, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=14336, tie_word_embeddings=False,
+                rope_scaling=dict(_LLAMA3_ROPE, factor=8.0))
+# The two serving workloads beside the headline: continuous batching under Poisson arrivals at the
+# 3B shape, and 64 long requests at the 8B shape in a pool that cannot hold them all.
+WORKLOADS = {
+    "serve3b": {"model": LLAMA_3B, "name": "Llama-3.2-3B shape", "requests": 256, "prompt_len": (128, 2048),
+                "output_len": (64, 512), "arrival_rate": 64.0, "context_len": 8192, "max_num_seqs": 256,
+                "pool_fraction_of_need": 0.6},
+    "stress8b": {"model": LLAMA_8B, "name": "Llama-3.1-8B shape", "requests": 64, "prompt_len": (4096, 4096),
+                 "output_len": (512, 512), "arrival_rate": 0.0, "context_len": 16384, "max_num_seqs": 64,
+                 "pool_fraction_of_need": 0.75},
+}
 FULL_LAYERS = LLAMA_1B["num_hidden_layers"]
 CONTEXT_LEN = 4096
 PROMPT_LEN = 512
@@ -177,6 +194,7 @@ def run_decode(llm, batch, steps, warmup, end_to_end, seed):
     assert n_tok == batch * steps, f"{n_tok} tokens from {batch} requests in {steps} steps"
     launches = ops.launch_count + eng.runner.graph_launches - launches0
     seconds = (w1 - w0) if end_to_end else start.elapsed_time(stop) / 1000.0
+    run_decode.h2d_bytes = eng.runner.builder.last_h2d_bytes      # of one decode step of this batch
     for i in ids:
         eng.abort(i)
     assert eng.runner.manager.check() == "" and eng.runner.manager.live_requests() == 0
@@ -206,6 +224,97 @@ def run_prefill(llm, reps, warmup, seed):
     return statistics.median(times)
 
 
+def _pct(xs, p):
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(round(p / 100.0 * (len(xs) - 1))))] if xs else None
+
+
+def run_workload(name, seed=0):
+    """One of WORKLOADS through the engine's own entry points (add_request, step), requests arriving
+    in real time.  Every request must emit exactly its budget and no page may be lost; returns
+    output tokens a second, time to the first token and time per further token, and what the
+    scheduler had to drop and recompute."""
+    import gc
+    import numpy as np
+    import torch
+    from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
+    wl = WORKLOADS[name]
+    cfg = dict(wl["model"])
+    rng = np.random.default_rng(seed)
+    n = wl["requests"]
+    p_len = rng.integers(wl["prompt_len"][0], wl["prompt_len"][1] + 1, n)
+    o_len = rng.integers(wl["output_len"][0], wl["output_len"][1] + 1, n)
+    gaps = rng.exponential(1.0 / wl["arrival_rate"], n) if wl["arrival_rate"] > 0 else np.zeros(n)
+    arrive = np.cumsum(gaps) - gaps[0]
+    need_tokens = int((p_len + o_len).sum())
+    pool_tokens = int(need_tokens * wl["pool_fraction_of_need"])
+    num_pages = max(pool_tokens // PAGE_SIZE, (int((p_len + o_len).max()) + PAGE_SIZE) // PAGE_SIZE + 1)
+    log(f"{name}: building {wl['name']}, {cfg['num_hidden_layers']} layers, pool of {num_pages} pages "
+        f"({num_pages * PAGE_SIZE} tokens; all requests together need {need_tokens})")
+    llm = LLM.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", page_size=PAGE_SIZE, num_pages=num_pages,
+                          max_num_seqs=wl["max_num_seqs"], max_num_batched_tokens=PREFILL_TOKENS,
+                          max_model_len=wl["context_len"], capture_graphs_at_start=True)
+    eng = llm.engine
+    kv_bytes = eng.runner.cache.bytes_per_page() * num_pages
+    prompts = [rng.integers(0, cfg["vocab_size"], int(k)).tolist() for k in p_len]
+    # warm-up: a prompt of two portions and a few decode steps (kernels loaded, allocator warm)
+    eng.generate([prompts[0][:128] * 20], SamplingParams(max_tokens=4, ignore_eos=True))
+    torch.cuda.synchronize()
+    first, last, count = {}, {}, {i: 0 for i in range(n)}
+    errors = []
+    nxt = 0
+    t0 = time.perf_counter()
+    while nxt < n or eng.has_unfinished():
+        now = time.perf_counter() - t0
+        while nxt < n and arrive[nxt] <= now:
+            eng.add_request(prompts[nxt], SamplingParams(max_tokens=int(o_len[nxt]), ignore_eos=True), request_id=1000 + nxt)
+            nxt += 1
+        if not eng.has_unfinished():
+            time.sleep(max(0.0, min(0.001, arrive[nxt] - now)))
+            continue
+        for ev in eng.step():
+            t = time.perf_counter() - t0
+            i = ev.request_id - 1000
+            if ev.token is not None:
+                count[i] += 1
+                first.setdefault(i, t)
+                last[i] = t
+            if ev.finished and ev.reason != "length":
+                errors.append((i, ev.reason))
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    st = eng.stats()
+    wrong = [i for i in range(n) if count[i] != int(o_len[i])]
+    assert not errors and not wrong, f"{name}: requests ended early {errors[:3]} or with other counts than their budget {wrong[:3]}"
+    assert eng.runner.manager.check() == "" and st["free_pages"] == [num_pages], "a page was lost"
+    ttft = [1000.0 * (first[i] - arrive[i]) for i in range(n)]
+    tpot = [1000.0 * (last[i] - first[i]) / (count[i] - 1) for i in range(n) if count[i] > 1]
+    out_tokens = int(o_len.sum())
+    res = {
+        "value": round(out_tokens / seconds, 1), "unit": "output tokens/s", "seconds": round(seconds, 3),
+        "requests": n, "prompt_tokens": int(p_len.sum()), "output_tokens": out_tokens,
+        "total_tokens_per_s": round((out_tokens + int(p_len.sum())) / seconds, 1),
+        "ttft_ms": {"p50": round(_pct(ttft, 50), 2), "p99": round(_pct(ttft, 99), 2)},
+        "per_token_ms": {"p50": round(_pct(tpot, 50), 3), "p99": round(_pct(tpot, 99), 3)},
+        "steps": int(st["steps"]), "preemptions": int(st["preemptions"]), "recomputed_tokens": int(st["recomputed_tokens"]),
+        "config": {"model": wl["name"], "layers": cfg["num_hidden_layers"], "hidden_size": cfg["hidden_size"],
+                   "heads": f"{cfg['num_attention_heads']}/{cfg['num_key_value_heads']}", "head_dim": cfg["head_dim"],
+                   "intermediate_size": cfg["intermediate_size"], "tied_lm_head": bool(cfg["tie_word_embeddings"]),
+                   "prompt_len": list(wl["prompt_len"]), "output_len": list(wl["output_len"]),
+                   "arrivals": f"Poisson, {wl['arrival_rate']}/s" if wl["arrival_rate"] > 0 else "all at once",
+                   "context_len": wl["context_len"], "page_size": PAGE_SIZE, "max_num_seqs": wl["max_num_seqs"],
+                   "tokens_per_step": PREFILL_TOKENS, "pool_pages": num_pages, "pool_gb": round(kv_bytes / 1e9, 2),
+                   "all_resident_gb": round(kv_bytes / num_pages / PAGE_SIZE * need_tokens / 1e9, 2), "seed": seed},
+    }
+    log(f"  {res['value']:.0f} output tok/s in {seconds:.2f} s, {st['steps']} steps, TTFT p50 {res['ttft_ms']['p50']:.0f} ms, "
+        f"per token p50 {res['per_token_ms']['p50']:.2f} ms, {st['preemptions']} preemptions "
+        f"({st['recomputed_tokens']} tokens recomputed)")
+    del eng, llm
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,6 +324,9 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
+    ap.add_argument("--workload", default="all", choices=["all", "none", *WORKLOADS],
+                    help="the serving workloads measured beside the headline (3B continuous batching, 8B under a "
+                         "pool that is too small); one name runs that workload alone and prints its own JSON line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -232,6 +344,9 @@ def main():
     import torch
     from kv_cache_optimization_for_llm_b200 import LLM
 
+    if args.workload in WORKLOADS:
+        print(json.dumps({"workload": args.workload, **run_workload(args.workload)}), flush=True)
+        return 0
     cfg = dict(LLAMA_1B)
     cfg["num_hidden_layers"] = args.layers
     pk = peaks()
@@ -255,6 +370,7 @@ def main():
     sec_e, _, _, win = run_decode(llm, args.batch, args.steps, args.warmup, True, seed=1)
     windows.append(win)
     e2e = args.batch * args.steps / sec_e
+    b_in = run_decode.h2d_bytes + 4 * 4 * args.batch   # batch arrays + sampler parameters
     log(f"  {e2e:.0f} tok/s")
 
     step_bytes = nums["weight_bytes"] + args.batch * mean_ctx * nums["kv_bytes_per_token"]
@@ -281,9 +397,21 @@ def main():
         log(f"  {prefill['value']:.0f} tok/s, {ms:.2f} ms, {prefill['frac']:.3f} of {pk['source']} bf16 peak")
     sampler.stop()
     clocks = sampler.summary(windows)
-
-    b_in = llm.engine.runner.builder.last_h2d_bytes + 4 * 4 * args.batch   # batch arrays + sampler parameters
     b_out = 4 * args.batch + 4                                              # sampled ids + the status word
+    graphs_on = bool(llm.engine.config.use_cuda_graphs)
+    workloads = {}
+    if args.workload == "all" and not args.skip_points:
+        del llm
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        for name in WORKLOADS:
+            try:
+                workloads[name] = run_workload(name)
+            except Exception as e:       # the headline must not be lost to a side measurement
+                workloads[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                log(f"{name} failed: {workloads[name]['error']}")
+
     line = {
         "metric": "decode tok/s (Llama-3.2-1B shape, bf16, batch 8, 512-token prompts)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -298,7 +426,7 @@ def main():
             "global_batch": args.batch, "prompt_len": PROMPT_LEN, "new_tokens": NEW_TOKENS,
             "context_len": CONTEXT_LEN, "page_size": PAGE_SIZE, "kv_dtype": "bf16", "parallelism": "none (1 GPU)",
             "l2": "inputs larger than L2: 2.47 GB of weights are streamed every step",
-            "cuda_graphs": bool(llm.engine.config.use_cuda_graphs),
+            "cuda_graphs": graphs_on,
         },
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(b_in),
                 "d2h_bytes_per_step": int(b_out)},
@@ -312,6 +440,8 @@ def main():
         line["prefill"] = prefill
     if points:
         line["points"] = points
+    if workloads:
+        line["workloads"] = workloads
     print(json.dumps(line), flush=True)
     return 0
 

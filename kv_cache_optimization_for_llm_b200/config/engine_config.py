@@ -34,6 +34,7 @@ class EngineConfig:
     max_prefill_chunk: int = 0          # 0: only the token budget cuts a prompt
     seed: int = 0                       # engine-wide sampling seed (upstream's SAMPLING_SEED)
     use_cuda_graphs: bool = True        # replay decode-only steps from captured graphs
+    capture_graphs_at_start: bool = False  # capture every decode graph when the engine is built, not at first use
     run_ahead: bool = True              # launch the next step before the last step's tokens reach the host
     device: str = "cuda:0"
 

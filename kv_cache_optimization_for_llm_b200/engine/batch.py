@@ -115,20 +115,22 @@ class BatchBuilder:
 
     def build(self, entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None,
               pad_reqs_to: int = 0, scratch_page: int = -1, scratch_slot: int = 0,
-              sampled: Optional[torch.Tensor] = None) -> StepBatch:
+              sampled: Optional[torch.Tensor] = None, pad_ctx: int = 1) -> StepBatch:
         """``cache`` is the CacheManager; every entry's pages must already cover
         ``start + len(tokens)``.
 
         ``pad_reqs_to`` > len(entries) appends single-token dummy requests (token 0 at
         position 0, writing to ``scratch_page`` and ``scratch_slot``, which no real
         request owns) so that a decode batch fills a captured graph's fixed shape;
-        their rows follow the real ones and their logits are never read.
+        their rows follow the real ones and their logits are never read.  ``pad_ctx`` > 1
+        gives the dummy requests a context of that many tokens, all of it the scratch page
+        (what a graph captured ahead of any request is shaped with).
 
         ``sampled``: the device buffer that token ids below zero refer to (see StepEntry);
         without it such ids are refused."""
         n_real = len(entries)
         if pad_reqs_to > n_real:
-            entries = list(entries) + [StepEntry(-1, (0,), 0, ()) for _ in range(pad_reqs_to - n_real)]
+            entries = list(entries) + [StepEntry(-1, (0,), max(0, pad_ctx - 1), ()) for _ in range(pad_reqs_to - n_real)]
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         if R == 0 or T == 0:
@@ -181,7 +183,7 @@ class BatchBuilder:
             places.append(off)
             bt = h[off:off + R * cols].reshape(R, cols)
             bt.fill(-1)
-            bt[n_real:, 0] = scratch_page
+            bt[n_real:, :max(1, min(cols, -(-pad_ctx // (self.page_size or pad_ctx))))] = scratch_page
             for r, e in enumerate(entries[:n_real]):
                 table = cache.block_table(e.request_id, g)
                 if len(table) > self.max_pages[g]:

@@ -116,6 +116,8 @@ class ModelRunner:
                 self.graph_buckets.append(b)
                 b *= 2
             self.graph_buckets.append(self.config.max_num_seqs)
+            if self.config.capture_graphs_at_start:
+                self.capture_decode_graphs()
 
     # ---------------------------------------------------------------- the step function
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -126,17 +128,34 @@ class ModelRunner:
         batch = self.builder.build(entries, self.manager, self.vocab_size, sampled=self.sampled[:-1])
         return self.model.forward(batch, self.cache)
 
-    def _run_decode_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def capture_decode_graphs(self) -> int:
+        """Captures, before any request, the graph of every batch-size bucket for every class of
+        context length that ``max_model_len`` allows, on dummy rows that read and write the
+        scratch page only.  Returns how many graphs were captured.  Without it each graph is
+        captured by the first step that needs it."""
+        from .batch import CONTEXT_CLASS_BOUNDS
+        before = len(self._graphs)
+        contexts = [1] + [b + 1 for b in CONTEXT_CLASS_BOUNDS if b + 1 <= self.max_model_len]
+        for ctx in contexts:
+            for bucket in self.graph_buckets:
+                self._run_decode_graph([], bucket=bucket, pad_ctx=ctx)
+        torch.cuda.synchronize(self.device)
+        self.status.zero_()
+        return len(self._graphs) - before
+
+    def _run_decode_graph(self, entries: Sequence[StepEntry], bucket: Optional[int] = None,
+                          pad_ctx: int = 1) -> torch.Tensor:
         """A step of single tokens only: padded to the next captured batch size and
         replayed as one CUDA graph (captured at first use).  The graph reads the
         batch arrays at their fixed device addresses; only their contents change."""
         n = len(entries)
-        bucket = next(b for b in self.graph_buckets if b >= n)
+        if bucket is None:
+            bucket = next(b for b in self.graph_buckets if b >= n)
         wants = [bool(e.want) for e in entries]
         padded = [StepEntry(e.request_id, e.tokens, e.start, (0,)) for e in entries]
         batch = self.builder.build(padded, self.manager, self.vocab_size, pad_reqs_to=bucket,
                                    scratch_page=self.cache.scratch_page, scratch_slot=self.cache.scratch_slot,
-                                   sampled=self.sampled[:-1])
+                                   sampled=self.sampled[:-1], pad_ctx=pad_ctx)
         # one graph per padded batch size and class of context length (launches are sized by both)
         key = (bucket, ops.decode_context_class(batch.max_ctx_len))
         got = self._graphs.get(key)
