@@ -1,0 +1,97 @@
+"""The memory that a step's activations live in: allocated once, handed out again every step.
+
+Upstream allocates every buffer of a pass once at start-up, sized by MAX_BATCH_TOKENS
+(allocateDeviceBuffers, base/src/engine.cu:62-122, base/src/engine.cuh:29-74), and its two
+passes write into them by name.  Here the parts of a layer are not known in advance, so the
+arena is handed out by bumping an offset instead: one region that lives for the whole step
+(the float32 residual, the rows picked for the head, the logits) and two regions that layers
+use in turn.  A layer's results stay valid while the layer behind it runs and are overwritten
+by the layer after that; nothing is ever given back to an allocator, and a step of the same
+shape finds every tensor at the same address as the step before (which is also what lets a
+captured graph and the steps launched around it share the memory).
+
+A region that turns out too small (a part nobody declared widths for) gets one more block, which
+it keeps; a single tensor larger than a whole region (logits for thousands of rows at once)
+bypasses the arena and comes from the allocator.
+"""
+
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+_ALIGN = 256
+_ESIZE = {torch.float32: 4, torch.bfloat16: 2, torch.int32: 4, torch.float16: 2, torch.uint8: 1, torch.int64: 8}
+
+
+class _Region:
+    def __init__(self, nbytes: int, device):
+        self.device = device
+        self.capacity = max(_ALIGN, -(-int(nbytes) // _ALIGN) * _ALIGN)
+        self.blocks: List[torch.Tensor] = [torch.empty(self.capacity, dtype=torch.uint8, device=device)]
+        self.block, self.offset = 0, 0
+        self.grown = 0
+
+    def reset(self) -> None:
+        self.block, self.offset = 0, 0
+
+    def take(self, nbytes: int):
+        """A run of ``nbytes`` bytes, or None if the request is larger than the region was built for."""
+        need = -(-nbytes // _ALIGN) * _ALIGN
+        if need > self.capacity:
+            return None
+        while True:
+            buf = self.blocks[self.block]
+            if self.offset + need <= buf.numel():
+                out = buf[self.offset:self.offset + nbytes]
+                self.offset += need
+                return out
+            self.block += 1
+            self.offset = 0
+            if self.block == len(self.blocks):
+                self.blocks.append(torch.empty(self.capacity, dtype=torch.uint8, device=self.device))
+                self.grown += 1
+
+
+class StepArena:
+    def __init__(self, device, step_bytes: int, layer_bytes: int):
+        self.device = torch.device(device)
+        self.step = _Region(step_bytes, self.device)
+        self.halves = (_Region(layer_bytes, self.device), _Region(layer_bytes, self.device))
+        self.turn = 0
+        self.current = self.step
+        self.bypassed = 0        # tensors that were too large for a region and came from the allocator
+
+    def begin_step(self) -> None:
+        self.step.reset()
+        self.turn = 0
+        self.current = self.step
+
+    def begin_layer(self) -> None:
+        """The region that the layer before last used is the next layer's."""
+        self.turn ^= 1
+        self.current = self.halves[self.turn]
+        self.current.reset()
+
+    def end_layers(self) -> None:
+        self.current = self.step
+
+    def new(self, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * _ESIZE[dtype]
+        if nbytes == 0:
+            return torch.empty(tuple(shape), dtype=dtype, device=self.device)
+        raw = self.current.take(nbytes)
+        if raw is None:
+            self.bypassed += 1
+            return torch.empty(tuple(shape), dtype=dtype, device=self.device)
+        return raw.view(dtype).view(tuple(shape))
+
+    def bytes_held(self) -> int:
+        return sum(b.numel() for r in (self.step, *self.halves) for b in r.blocks)
+
+    def blocks_grown(self) -> int:
+        return sum(r.grown for r in (self.step, *self.halves))

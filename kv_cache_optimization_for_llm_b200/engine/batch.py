@@ -46,6 +46,8 @@ class StepBatch:
     status: torch.Tensor         # [1] int32 device word that kernels report into
     host: dict = field(default_factory=dict)  # numpy mirrors of the arrays above
     sampled: Optional[torch.Tensor] = None    # [n] int32 on the device: what ids below zero refer to
+    tiles: dict = field(default_factory=dict)  # tokens per tile -> [n, 4] int32 query tiles (request row, first
+                                               # token row, tokens, 0) for the heights the mixers asked for
 
 
 # Decode launches and captured graphs come in classes by the step's longest context (up to
@@ -73,13 +75,16 @@ class BatchBuilder:
     host buffer."""
 
     def __init__(self, max_tokens: int, max_reqs: int, max_pages_per_group: Sequence[int], device,
-                 status: torch.Tensor, page_size: Optional[int] = None):
+                 status: torch.Tensor, page_size: Optional[int] = None, tile_heights: Sequence[int] = ()):
         """``page_size``: tokens per cache page.  When it is given, a step's block tables are
         only as wide as the step's longest context needs (see :func:`table_columns`) and lie
         packed behind one another; without it they always have ``max_pages_per_group`` columns."""
         self.max_tokens, self.max_reqs = int(max_tokens), int(max_reqs)
         self.max_pages = [int(m) for m in max_pages_per_group]
         self.page_size = None if page_size is None else int(page_size)
+        # Tokens per query tile that mixers cut a step's runs of tokens into (attention kernels for
+        # prompt portions): the tiles of every height are laid out behind the block tables.
+        self.tile_heights = sorted({int(h) for h in tile_heights if int(h) > 0})
         self.device = torch.device(device)
         self.status = status
         T, R = self.max_tokens, self.max_reqs
@@ -96,6 +101,8 @@ class BatchBuilder:
         self.tables_at = off
         for mp in self.max_pages:
             off += (R * mp + 3) // 4 * 4
+        for h in self.tile_heights:
+            off += 4 * (T // h + R + 1)
         self.total = off
         use_cuda = self.device.type == "cuda"
         # Two pinned staging buffers, used in turn: the copy of one step may still be under
@@ -192,7 +199,24 @@ class BatchBuilder:
                 n = min(len(table), cols)      # pages beyond the step's longest context are not read
                 bt[r, :n] = table[:n]
             off += (R * cols + 3) // 4 * 4
-        used = off      # the tables lie last, so one copy of the used prefix carries everything
+        decode_only = all(len(e.tokens) == 1 for e in entries)
+        tile_places = {}
+        if not decode_only:
+            for nt in self.tile_heights:
+                n_tiles = 0
+                for r, e in enumerate(entries):
+                    a, b = int(qs[r]), int(qs[r]) + len(e.tokens)
+                    k = -(-(b - a) // nt)
+                    tile = h[off + 4 * n_tiles:off + 4 * (n_tiles + k)].reshape(k, 4)
+                    starts = np.arange(a, b, nt, dtype=np.int32)
+                    tile[:, 0] = r
+                    tile[:, 1] = starts
+                    tile[:, 2] = np.minimum(nt, b - starts)
+                    tile[:, 3] = 0
+                    n_tiles += k
+                tile_places[nt] = (off, n_tiles)
+                off += 4 * n_tiles
+        used = off      # tables and tiles lie last, so one copy of the used prefix carries everything
         self.dev_buf[:used].copy_(stage["buf"][:used], non_blocking=True)
         if stage["event"] is not None:
             stage["event"].record()
@@ -209,7 +233,8 @@ class BatchBuilder:
             logit_rows=self._view(d, "logit_rows", len(rows)), num_logits=len(rows),
             max_q_len=max(len(e.tokens) for e in entries),
             max_ctx_len=max_ctx,
-            decode_only=all(len(e.tokens) == 1 for e in entries),
+            decode_only=decode_only,
+            tiles={nt: d[at:at + 4 * n].view(n, 4) for nt, (at, n) in tile_places.items()},
             status=self.status,
             host={"q_start": qs.copy(), "ctx_len": ctx.copy(), "req_start": rstart.copy()},
             sampled=sampled,

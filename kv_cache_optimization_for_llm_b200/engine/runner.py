@@ -99,7 +99,11 @@ class ModelRunner:
         self.manager = self.cache.manager
         self.builder = BatchBuilder(self.config.max_num_batched_tokens, self.config.max_num_seqs,
                                     self.cache.max_pages, self.device, self.status,
-                                    page_size=self.config.page_size)
+                                    page_size=self.config.page_size, tile_heights=self.model.query_tile_heights())
+        # Everything a step computes lives here; steps allocate nothing.
+        from .arena import StepArena
+        self.arena = StepArena(self.device, *self.model.arena_bytes(self.config.max_num_batched_tokens,
+                                                                     self.config.max_num_seqs))
         self.vocab_size = self.spec.vocab_size
         # Where the sampling kernel leaves a step's tokens (one per sampled request, in the
         # step's order; the last entry carries the kernels' error word).  A step whose entries
@@ -126,7 +130,7 @@ class ModelRunner:
         if self.graph_buckets and all(len(e.tokens) == 1 for e in entries):
             return self._run_decode_graph(entries)
         batch = self.builder.build(entries, self.manager, self.vocab_size, sampled=self.sampled[:-1])
-        return self.model.forward(batch, self.cache)
+        return self.model.forward(batch, self.cache, self.arena)
 
     def capture_decode_graphs(self) -> int:
         """Captures, before any request, the graph of every batch-size bucket for every class of
@@ -166,12 +170,12 @@ class ModelRunner:
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
-                self.model.forward(batch, self.cache)      # warm-up outside the capture
+                self.model.forward(batch, self.cache, self.arena)      # warm-up outside the capture
             torch.cuda.current_stream().wait_stream(side)
             before = ops.launch_count
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                out = self.model.forward(batch, self.cache)
+                out = self.model.forward(batch, self.cache, self.arena)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
             got = (graph, out, ops.launch_count - before, rows)

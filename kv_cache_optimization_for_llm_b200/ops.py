@@ -102,6 +102,36 @@ def dtype_code(dt: torch.dtype) -> int:
     raise KernelError(f"dtype {dt} has no kernels (float32 and bfloat16 do)")
 
 
+_arena = None      # the running step's arena (engine/arena.py), None outside a step
+
+
+class use_arena:
+    """While active, the tensors that the operators below produce come out of ``arena``
+    instead of the allocator."""
+
+    def __init__(self, arena):
+        self.arena = arena
+
+    def __enter__(self):
+        global _arena
+        self.before, _arena = _arena, self.arena
+        return self.arena
+
+    def __exit__(self, *exc):
+        global _arena
+        _arena = self.before
+        return False
+
+
+def new(shape, dtype: torch.dtype, device) -> torch.Tensor:
+    """An uninitialised result tensor: out of the running step's arena when there is one (on
+    its device), otherwise from the allocator (operators called on their own)."""
+    a = _arena
+    if a is not None and a.device == device:
+        return a.new(shape, dtype)
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
 def _need_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -118,7 +148,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
     assert sampled is None or (sampled.dtype == torch.int32 and sampled.is_contiguous())
     V, H = table.shape
     T = ids.numel()
-    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    out = new((T, H), torch.float32, table.device)
     rc = lib("elementwise").kvb_embed_gather(_p(table), dtype_code(table.dtype), _p(ids), _p(sampled),
                                              c_int(0 if sampled is None else sampled.numel()), _p(out),
                                              c_int(T), c_int(H), c_int(V), _p(status), _stream())
@@ -136,7 +166,7 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     assert weight is None or (weight.dtype == torch.float32 and weight.numel() == resid.shape[1])
     T, H = resid.shape
     n = T if rows is None else rows.numel()
-    out = torch.empty((n, H), dtype=out_dtype, device=resid.device)
+    out = new((n, H), out_dtype, resid.device)
     if delta is not None:
         assert delta.shape == resid.shape and delta.dtype == out_dtype and delta.is_contiguous()
     rc = lib("elementwise").kvb_add_rmsnorm(_p(resid), _p(delta), _p(weight), _p(out), _p(rows), c_int(n),
@@ -152,7 +182,7 @@ def silu_mul(gate_up: torch.Tensor, block: Optional[int] = None) -> torch.Tensor
     assert gate_up.is_contiguous()
     T, two_i = gate_up.shape
     I = two_i // 2
-    out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
+    out = new((T, I), gate_up.dtype, gate_up.device)
     rc = lib("elementwise").kvb_silu_mul(_p(gate_up), _p(out), c_int(T), c_int(I), c_int(block or I),
                                          c_int(dtype_code(gate_up.dtype)), _stream())
     _check(rc, "silu_mul")
@@ -186,7 +216,7 @@ def paged_attention_generic(qkv, k_pages, v_pages, block_table, positions, token
     """Attention of every token in ``qkv`` (q part) over its request's cached keys."""
     _need_cuda(qkv, k_pages)
     T = qkv.shape[0]
-    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+    out = new((T, nq * d), qkv.dtype, qkv.device)
     page_size = k_pages.shape[2]
     rc = lib("attention").kvb_paged_attention_generic(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table),
@@ -283,7 +313,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
         return gemm_wide(x, w, kernel_status(w.device), into=into)
     if x.dtype == torch.float32:
         assert x.stride(1) == 1 and w.stride(1) == 1
-        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        out = new((M, N), torch.float32, x.device)
         rc = lib("gemm_f32").kvb_sgemm_nt(_p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out),
                                           c_int(N), c_int(M), c_int(N), c_int(K), _stream())
         _check(rc, "sgemm_nt")
@@ -295,9 +325,25 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
     if WIDE == "all" and _wide_ok(x, w, 8) and (out_dtype is None or out_dtype == x.dtype):
         return gemm_wide(x, w, kernel_status(x.device))
     choices["library_product"] += 1
-    if out_dtype is not None and out_dtype != x.dtype:
-        return torch.mm(x, w.t(), out_dtype=out_dtype)
-    return torch.nn.functional.linear(x, w)
+    return _library_product(x, w, out_dtype or x.dtype)
+
+
+_mm_takes_out_with_dtype = True    # whether torch.mm accepts out= together with out_dtype= (found out at first use)
+
+
+def _library_product(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``x . w^T`` by the library (cuBLAS, float32 accumulation), written into a tensor of the
+    step's arena."""
+    global _mm_takes_out_with_dtype
+    out = new((x.shape[0], w.shape[0]), out_dtype, x.device)
+    if out_dtype == x.dtype:
+        return torch.matmul(x, w.t(), out=out)
+    if _mm_takes_out_with_dtype:
+        try:
+            return torch.mm(x, w.t(), out_dtype=out_dtype, out=out)
+        except (TypeError, RuntimeError, NotImplementedError):
+            _mm_takes_out_with_dtype = False
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
 
 
 # Which products of steps with many rows run on this package's tcgen05 kernel (gemm_bf16_wide.cu):
@@ -392,7 +438,7 @@ def decode_attention(qkv, k_pages, v_pages, block_table, q_start, ctx_len, nq, n
     cap = max(R, reqs_capacity or 0)
     part_o = scratch(("dec_o", qkv.device.index, cap, nq, nb, d), (cap, nq, nb, d), torch.float32, qkv.device)
     part_ml = scratch(("dec_ml", qkv.device.index, cap, nq, nb), (cap, nq, nb, 2), torch.float32, qkv.device)
-    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+    out = new((T, nq * d), qkv.dtype, qkv.device)
     rc = lib("attention").kvb_decode_attention(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
         c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len), _p(out), _p(part_o),
@@ -415,11 +461,27 @@ def flash_attention_supported(d: int, group: int, page_size: int) -> bool:
     return bool(lib("flash_attention").kvb_flash_attention_supported(c_int(d), c_int(group), c_int(page_size)))
 
 
+_tokens_per_tile: Dict[tuple, int] = {}
+
+
+def flash_tokens_per_tile(group: int, wide: bool) -> int:
+    """Query tokens in one tile of the tensor-core attention for prompt portions: 64 rows
+    (``wide`` False) or 128 rows of (token, head of the group) pairs."""
+    key = (int(group), bool(wide))
+    if key not in _tokens_per_tile:
+        _tokens_per_tile[key] = int(lib("flash_attention").kvb_flash_attention_tokens_per_tile(
+            c_int(key[0]), c_int(1 if wide else 0)))
+    return _tokens_per_tile[key]
+
+
 def flash_tiles(batch, group: int, wide: bool) -> torch.Tensor:
     """The query tiles of a step for a group size: [n, 4] int32 rows (request row, first
     token row, tokens, 0), each tile holding consecutive tokens of one request.  Built
     once per step, group size and tile height, kept on the batch."""
-    nt = int(lib("flash_attention").kvb_flash_attention_tokens_per_tile(c_int(group), c_int(1 if wide else 0)))
+    nt = flash_tokens_per_tile(group, bool(wide))
+    ready = batch.tiles.get(nt) if batch.tiles else None
+    if ready is not None:
+        return ready            # laid out with the batch's other arrays and copied with them
     cache = batch.host.setdefault("flash_tiles", {})
     got = cache.get(nt)
     if got is None:
@@ -451,7 +513,7 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
     _need_cuda(qkv, k_pages)
     T = qkv.shape[0]
     # 128-row tiles when there are enough of them to keep every SM busy, else 64-row tiles
-    nt128 = int(lib("flash_attention").kvb_flash_attention_tokens_per_tile(c_int(nq // nkv), c_int(1)))
+    nt128 = flash_tokens_per_tile(nq // nkv, True)
     if wide is None:
         wide = FLASH_WIDE and (T // nt128) * nkv >= 2 * sm_count(qkv.device)
         if wide and FLASH_TC and d == 64:
@@ -459,7 +521,7 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
                      and v_pages.data_ptr() % 16 == 0)
             wide = 3 if roles else 2
     tiles = flash_tiles(batch, nq // nkv, wide)
-    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+    out = new((T, nq * d), qkv.dtype, qkv.device)
     rc = lib("flash_attention").kvb_paged_flash_attention(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
         c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]),
@@ -485,7 +547,7 @@ def decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, q_start
     if counters is None or counters.numel() < R * nkv:
         counters = torch.zeros(max(R * nkv, 4096), dtype=torch.int32, device=dev)
         _scratch[("dec_counters", dev.index)] = counters
-    out = torch.empty((T, nq * d), dtype=qkv.dtype, device=dev)
+    out = new((T, nq * d), qkv.dtype, dev)
     rc = lib("attention").kvb_decode_attention_fused(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), c_int(1 if write_kv else 0), _p(block_table),
         c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
@@ -533,7 +595,7 @@ def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, 
     _need_cuda(qkv, k_pages)
     assert qkv.dtype == torch.bfloat16
     R = ctx_len.numel()
-    out = torch.empty((qkv.shape[0], nq * d), dtype=qkv.dtype, device=qkv.device)
+    out = new((qkv.shape[0], nq * d), qkv.dtype, qkv.device)
     rc = lib("decode_attention").kvb_decode_attention_mma(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), c_int(1 if write_kv else 0), _p(block_table),
         c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
@@ -583,7 +645,7 @@ def sample(logits, temperature, seed, key, pos, penalty, mask, slots, out=None, 
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     R, V = logits.shape
     if out is None:
-        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        out = new((R,), torch.int32, logits.device)
     rc = lib("sampling").kvb_sample(_p(logits), c_int(R), c_int(V), _p(temperature), _p(seed), _p(key),
                                     _p(pos), _p(penalty), _p(mask), _p(slots), _p(out), _p(status),
                                     c_int(status_at), _stream())
@@ -625,7 +687,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, status
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
     code = {"store": 0, "swiglu": 1}[epilogue]
-    out = torch.empty((M, N // 2 if code == 1 else N), dtype=out_dtype, device=x.device)
+    out = new((M, N // 2 if code == 1 else N), out_dtype, x.device)
     rc = lib("gemm_bf16").kvb_gemm_skinny(
         _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(1 if out_dtype == torch.float32 else 0),
         c_int(M), c_int(N), c_int(K), c_int(1 if x_is_static else 0), c_int(code), _p(status), _p(trace),
@@ -661,11 +723,11 @@ def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, ro
     if into is not None:
         assert epilogue == "store" and into.dtype == torch.float32 and into.shape == (M, N) and into.stride(1) == 1
         code = 2
-        sumsq = torch.empty((M, -(-N // 128)), dtype=torch.float32, device=x.device)
-        xb = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        sumsq = new((M, -(-N // 128)), torch.float32, x.device)
+        xb = new((M, N), torch.bfloat16, x.device)
     else:
         code = {"store": 0, "swiglu": 1}[epilogue]
-        out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.bfloat16, device=x.device)
+        out = new((M, N // 2 if code == 1 else N), torch.bfloat16, x.device)
     rc = lib("gemm_bf16").kvb_gemm_skinny_fused(
         _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(M), c_int(N), c_int(K),
         c_int(1 if x_is_static else 0), c_int(code), _p(ss), c_int(parts), c_float(eps),
@@ -706,11 +768,11 @@ def gemm_wide(x: torch.Tensor, w: torch.Tensor, status: torch.Tensor, epilogue: 
     if into is not None:
         assert epilogue == "store" and into.dtype == torch.float32 and into.shape == (M, N) and into.stride(1) == 1
         code = 2
-        sumsq = torch.empty((M, -(-N // 256)), dtype=torch.float32, device=x.device)
-        xb = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        sumsq = new((M, -(-N // 256)), torch.float32, x.device)
+        xb = new((M, N), torch.bfloat16, x.device)
     else:
         code = {"store": 0, "swiglu": 1}[epilogue]
-        out = torch.empty((M, N // 2 if code == 1 else N), dtype=torch.bfloat16, device=x.device)
+        out = new((M, N // 2 if code == 1 else N), torch.bfloat16, x.device)
     rc = lib("gemm_bf16_wide").kvb_gemm_wide_fused(
         _p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(out), c_int(out.stride(0) if out is not None else 0),
         c_int(M), c_int(N), c_int(K), c_int(code), c_int(tile[0]), c_int(tile[1]),

@@ -67,6 +67,20 @@ class GroupedQueryAttention(Part):
     def cache_spec(self):
         return PagedKVSpec(self.nkv, self.d, self.window)
 
+    def activation_widths(self):
+        """Elements per token of the tensors one call produces: q|k|v, the attention output, and
+        the projected output (or its bfloat16 copy with the partial sums of squares)."""
+        hidden = self.o.shape[0]
+        return [(self.nq + 2 * self.nkv) * self.d, self.nq * self.d, 2 * hidden]
+
+    def query_tile_heights(self):
+        """Tokens per tile of the tensor-core attention for prompt portions (bfloat16, head sizes
+        it takes): the step's batch lays the tiles out for them."""
+        if self.ctx.dtype != torch.bfloat16 or self.d not in (64, 128):
+            return []
+        g = self.nq // self.nkv
+        return [ops.flash_tokens_per_tile(g, False), ops.flash_tokens_per_tile(g, True)]
+
     def forward(self, x, batch, cache, into=None):
         qkv = ops.linear(x, self.qkv)
         cos, sin = self.position.tables() if self.position is not None else (None, None)

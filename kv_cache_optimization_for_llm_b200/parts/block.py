@@ -27,6 +27,7 @@ class PreNormBlock(Part):
     part_families = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "ff_norm": "norm"}
 
     def __init__(self, parts):
+        self.parts = dict(parts)
         self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
         self.feed_forward, self.ff_norm = parts["feed_forward"], parts["ff_norm"]
         for part, norm in ((self.mixer, self.mixer_norm), (self.feed_forward, self.ff_norm)):

@@ -48,6 +48,12 @@ class SwiGLU(Part):
         columns of the gate and up matrix, so that the norm itself can go without."""
         self.gate_up = (self.gate_up.float() * scale.float()[None, :]).to(self.gate_up.dtype).contiguous()
 
+    def activation_widths(self):
+        """Elements per token of the tensors one call produces: gate|up (when the activation is a
+        kernel of its own), the activation, and the output (or its bfloat16 copy with sums)."""
+        inter, hidden = self.gate_up.shape[0] // 2, self.down.shape[0]
+        return [2 * inter, inter, 2 * hidden]
+
     def forward(self, x, batch, into=None):
         a = ops.linear_swiglu(x, self.gate_up, self.block)
         return ops.linear(a, self.down, into=into)

@@ -26,7 +26,11 @@ class RMSNorm(Part):
     def __init__(self, params, weights, ctx):
         super().__init__(params, weights, ctx)
         self.eps = float(params["eps"])
+        self.size = int(params["size"])
         self.weight = weights["weight"]
+
+    def activation_widths(self):
+        return [self.size]
 
     def give_up_weight(self):
         """Hands the weight to a part that multiplies it into its own matrices

@@ -584,3 +584,41 @@ def test_tensor_core_decode_attention_long_contexts():
                                    dev([0, 1], torch.int32), dev(ctxs[1:2], torch.int32), None, None, 0, nq, nkv, d,
                                    1 / math.sqrt(d), None, st, max_ctx=ctxs[1])
     assert torch.equal(one[0], out[1])
+
+
+@pytest.mark.parametrize("d,nq,nkv", [(64, 8, 2), (128, 6, 2)])
+@pytest.mark.parametrize("window", [100, 129])
+@pytest.mark.parametrize("inside", [False, True])
+def test_window_edge_with_a_key_that_stands_out(d, nq, nkv, window, inside):
+    """The window's edge in the bfloat16 tensor-core kernels, shown by one key whose score
+    stands out for the newest query: at position ``pos - window`` it must be ignored, at
+    ``pos - window + 1`` it must be found.  One key too many or too few changes the newest
+    row's output from "the mean of a hundred values" to "that key's value" or back.  A
+    37-token portion whose rows straddle a key tile and a page edge (every prompt kernel),
+    and the single newest token (the decode kernel)."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    ctx, page_size = 900, 16
+    pos = ctx - 1
+    spike = pos - window + (1 if inside else 0)
+    scale = 1 / math.sqrt(d)
+    c = _attention_case("bfloat16", nq, nkv, d, ctxs=[ctx], q_lens=[37], page_size=page_size, window=window,
+                        seed=d + window + inside, spike=spike)
+    page, slot = int(c["table"][0, spike // page_size]), spike % page_size
+    spike_value = np.repeat(as64(c["vp"][page, :, slot]), nq // nkv, axis=0).reshape(-1)
+    # the plain result itself shows the difference: the newest row is that key's value, or far from it
+    assert (np.abs(c["ref"][-1] - spike_value).max() < 0.05) == inside
+    forms = [False, True] + ([2, 3] if d == 64 else [])
+    for wide in forms:
+        fb = _FakeBatch(c)
+        out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, scale, window, wide=wide)
+        assert int(fb.status.item()) == 0
+        assert rel_err(out, c["ref"]) < TOL["bfloat16"], wide
+        assert (np.abs(as64(out)[-1] - spike_value).max() < 0.08) == inside, wide
+    one = _attention_case("bfloat16", nq, nkv, d, ctxs=[ctx], q_lens=[1], page_size=page_size, window=window,
+                          seed=d + window + inside, spike=spike)
+    st = status()
+    out = ops.decode_attention_mma(one["qkv"], one["kp"], one["vp"], False, one["table"], one["q_start"],
+                                   one["ctx_len"], None, None, 0, nq, nkv, d, scale, window, st, max_ctx=ctx)
+    assert int(st.item()) == 0
+    assert rel_err(out, one["ref"]) < TOL["bfloat16"] * 1.5
+    assert (np.abs(as64(out)[-1] - spike_value).max() < 0.08) == inside

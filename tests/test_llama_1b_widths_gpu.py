@@ -107,6 +107,16 @@ def test_one_2048_token_portion(model, dtype):
         assert ops.choices["sgemm_nt"] > 0 and ops.choices["library_product"] == 0, dict(ops.choices)
     print(f"2048-token step, {dtype}: relative error {err:.3e}")
     assert r.manager.check() == ""
+    # the same step once more, now warm: it asks the allocator for nothing
+    import torch
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    again = r.step([StepEntry(3, seq, 0, rows)])
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
+    assert r.arena.blocks_grown() == 0 and r.arena.bypassed == 0
+    _check(again.cpu().numpy(), ref[pick], dtype, "2048 tokens in one step, again")
+    r.release(3)
 
 
 def _portion_spans():
