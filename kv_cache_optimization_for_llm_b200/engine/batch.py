@@ -88,17 +88,11 @@ class BatchBuilder:
         self.device = torch.device(device)
         self.status = status
         T, R = self.max_tokens, self.max_reqs
-        sizes = [("token_ids", T), ("positions", T), ("token_req", T), ("q_start", R + 1),
-                 ("req_start", R), ("ctx_len", R), ("slots", R), ("logit_rows", T)]
-        self.offsets = {}
-        off = 0
-        for name, n in sizes:
-            self.offsets[name] = (off, n)
-            off += (n + 3) // 4 * 4  # keep every array 16-byte aligned
-        # The block tables follow, one [requests, columns] array per cache group.  Their widths
-        # change with the step, so their places are worked out per step (a function of the number
-        # of requests and the widths only: a captured graph, keyed by both, finds them again).
-        self.tables_at = off
+        # The arrays of a step lie packed behind one another, each only as long as the step needs,
+        # so that one short copy carries a short step.  Where each lies is a function of the step's
+        # numbers of tokens and requests and of the widths of its block tables only: a captured
+        # graph, keyed by all of these, finds them again.
+        off = self._place(T, R)[1]
         for mp in self.max_pages:
             off += (R * mp + 3) // 4 * 4
         for h in self.tile_heights:
@@ -116,9 +110,17 @@ class BatchBuilder:
         self.dev_buf = torch.zeros(self.total, dtype=torch.int32, device=self.device)
         self.last_h2d_bytes = 0
 
-    def _view(self, buf, name, n=None):
-        off, cap = self.offsets[name]
-        return buf[off:off + (cap if n is None else n)]
+    @staticmethod
+    def _place(T: int, R: int):
+        """Offsets of the per-token and per-request arrays of a step with T tokens and R requests
+        (every array 16-byte aligned; the wanted rows get room for all T), and where the block
+        tables start."""
+        at, off = {}, 0
+        for name, n in (("token_ids", T), ("positions", T), ("token_req", T), ("logit_rows", T),
+                        ("q_start", R + 1), ("req_start", R), ("ctx_len", R), ("slots", R)):
+            at[name] = off
+            off += (n + 3) // 4 * 4
+        return at, off
 
     def build(self, entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None,
               pad_reqs_to: int = 0, scratch_page: int = -1, scratch_slot: int = 0,
@@ -152,13 +154,14 @@ class BatchBuilder:
             stage["event"].synchronize()
             stage["busy"] = False
         h = stage["np"]
-        tok = self._view(h, "token_ids", T)
-        pos = self._view(h, "positions", T)
-        treq = self._view(h, "token_req", T)
-        qs = self._view(h, "q_start", R + 1)
-        rstart = self._view(h, "req_start", R)
-        ctx = self._view(h, "ctx_len", R)
-        slots = self._view(h, "slots", R)
+        at, tables_at = self._place(T, R)
+        tok = h[at["token_ids"]:at["token_ids"] + T]
+        pos = h[at["positions"]:at["positions"] + T]
+        treq = h[at["token_req"]:at["token_req"] + T]
+        qs = h[at["q_start"]:at["q_start"] + R + 1]
+        rstart = h[at["req_start"]:at["req_start"] + R]
+        ctx = h[at["ctx_len"]:at["ctx_len"] + R]
+        slots = h[at["slots"]:at["slots"] + R]
         rows: List[int] = []
         t = 0
         for r, e in enumerate(entries):
@@ -181,11 +184,10 @@ class BatchBuilder:
         lowest = 0 if sampled is None else -int(sampled.numel())
         if vocab_size is not None and (tok.min() < lowest or tok.max() >= vocab_size):
             raise ValueError(f"a token id is outside the vocabulary of {vocab_size}")
-        lr = self._view(h, "logit_rows", len(rows))
-        lr[:] = rows
+        h[at["logit_rows"]:at["logit_rows"] + len(rows)] = rows
         max_ctx = int(ctx.max())
         widths = [table_columns(max_ctx, self.page_size, mp) for mp in self.max_pages]
-        places, off = [], self.tables_at
+        places, off = [], tables_at
         for g, cols in enumerate(widths):
             places.append(off)
             bt = h[off:off + R * cols].reshape(R, cols)
@@ -225,16 +227,16 @@ class BatchBuilder:
         d = self.dev_buf
         batch = StepBatch(
             num_tokens=T, num_reqs=R,
-            token_ids=self._view(d, "token_ids", T), positions=self._view(d, "positions", T),
-            token_req=self._view(d, "token_req", T), q_start=self._view(d, "q_start", R + 1),
-            req_start=self._view(d, "req_start", R), ctx_len=self._view(d, "ctx_len", R),
-            slots=self._view(d, "slots", R),
-            block_tables=[d[at:at + R * cols].view(R, cols) for at, cols in zip(places, widths)],
-            logit_rows=self._view(d, "logit_rows", len(rows)), num_logits=len(rows),
+            token_ids=d[at["token_ids"]:at["token_ids"] + T], positions=d[at["positions"]:at["positions"] + T],
+            token_req=d[at["token_req"]:at["token_req"] + T], q_start=d[at["q_start"]:at["q_start"] + R + 1],
+            req_start=d[at["req_start"]:at["req_start"] + R], ctx_len=d[at["ctx_len"]:at["ctx_len"] + R],
+            slots=d[at["slots"]:at["slots"] + R],
+            block_tables=[d[o:o + R * cols].view(R, cols) for o, cols in zip(places, widths)],
+            logit_rows=d[at["logit_rows"]:at["logit_rows"] + len(rows)], num_logits=len(rows),
             max_q_len=max(len(e.tokens) for e in entries),
             max_ctx_len=max_ctx,
             decode_only=decode_only,
-            tiles={nt: d[at:at + 4 * n].view(n, 4) for nt, (at, n) in tile_places.items()},
+            tiles={nt: d[o:o + 4 * n].view(n, 4) for nt, (o, n) in tile_places.items()},
             status=self.status,
             host={"q_start": qs.copy(), "ctx_len": ctx.copy(), "req_start": rstart.copy()},
             sampled=sampled,

@@ -479,7 +479,7 @@ def flash_tiles(batch, group: int, wide: bool) -> torch.Tensor:
     token row, tokens, 0), each tile holding consecutive tokens of one request.  Built
     once per step, group size and tile height, kept on the batch."""
     nt = flash_tokens_per_tile(group, bool(wide))
-    ready = batch.tiles.get(nt) if batch.tiles else None
+    ready = (getattr(batch, "tiles", None) or {}).get(nt)
     if ready is not None:
         return ready            # laid out with the batch's other arrays and copied with them
     cache = batch.host.setdefault("flash_tiles", {})

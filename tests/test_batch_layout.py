@@ -1,0 +1,77 @@
+"""The arrays of a step as the kernels read them, built on the CPU: runs of tokens, positions,
+wanted rows, block tables only as wide as the step's context class, query tiles of the heights
+the mixers ask for, padding rows of a graph's fixed shape; and that short steps make short copies."""
+
+import numpy as np
+import torch
+
+from kv_cache_optimization_for_llm_b200.engine.batch import BatchBuilder, StepEntry, table_columns
+
+
+class _Manager:
+    def __init__(self, tables, slots):
+        self.tables, self.slots = tables, slots
+
+    def slot_of(self, rid):
+        return self.slots[rid]
+
+    def block_table(self, rid, g):
+        return self.tables[rid]
+
+
+def _builder(**kw):
+    return BatchBuilder(256, 8, [4096 // 16], torch.device("cpu"), torch.zeros(1, dtype=torch.int32), page_size=16, **kw)
+
+
+def test_table_width_follows_the_context_class():
+    assert table_columns(1, 16, 8192) == 128 and table_columns(2048, 16, 8192) == 128
+    assert table_columns(2049, 16, 8192) == 512 and table_columns(8193, 16, 8192) == 8192
+    assert table_columns(100, 16, 40) == 40 and table_columns(100, None, 40) == 40
+
+
+def test_mixed_step_arrays_tables_and_tiles():
+    b = _builder(tile_heights=[16, 32])
+    m = _Manager({7: [5, 9, 2], 3: [11], 4: [8, 1, 6, 0, 13]}, {7: 2, 3: 0, 4: 1})
+    batch = b.build([StepEntry(7, [10, 11, 12], 40, [2]), StepEntry(3, [99], 0, [0]),
+                     StepEntry(4, list(range(50)), 20, [0, 49])], m, vocab_size=100)
+    assert batch.num_tokens == 54 and batch.num_reqs == 3 and not batch.decode_only
+    assert batch.token_ids.tolist() == [10, 11, 12, 99] + list(range(50))
+    assert batch.positions.tolist() == [40, 41, 42, 0] + list(range(20, 70))
+    assert batch.token_req.tolist() == [0] * 3 + [1] + [2] * 50
+    assert batch.q_start.tolist() == [0, 3, 4, 54] and batch.ctx_len.tolist() == [43, 1, 70]
+    assert batch.req_start.tolist() == [40, 0, 20] and batch.slots.tolist() == [2, 0, 1]
+    assert batch.logit_rows.tolist() == [2, 3, 4, 53] and batch.num_logits == 4
+    assert batch.max_ctx_len == 70 and batch.max_q_len == 50
+    bt = batch.block_tables[0]
+    assert tuple(bt.shape) == (3, 128)          # the class of contexts up to 2048 tokens, not all 256 columns
+    assert bt[0, :4].tolist() == [5, 9, 2, -1] and bt[1, :2].tolist() == [11, -1] and bt[2, :6].tolist() == [8, 1, 6, 0, 13, -1]
+    # query tiles: consecutive tokens of one request, at most `height` each
+    assert batch.tiles[16].tolist() == [[0, 0, 3, 0], [1, 3, 1, 0], [2, 4, 16, 0], [2, 20, 16, 0], [2, 36, 16, 0], [2, 52, 2, 0]]
+    assert batch.tiles[32].tolist() == [[0, 0, 3, 0], [1, 3, 1, 0], [2, 4, 32, 0], [2, 36, 18, 0]]
+    # everything lies packed in one buffer: the copy is a few hundred integers, not the engine's capacity
+    assert b.last_h2d_bytes < 4 * (4 * 56 + 3 * 4 + 4 + 3 * 128 + 4 * 10 + 64)
+    assert b.last_h2d_bytes < 4 * b.total // 3
+
+
+def test_decode_step_padding_rows_and_fixed_places():
+    b = _builder(tile_heights=[16])
+    m = _Manager({1: [3, 4], 2: [7]}, {1: 0, 2: 1})
+    entries = [StepEntry(1, [5], 17, [0]), StepEntry(2, [-1], 3, [0])]
+    sampled = torch.zeros(8, dtype=torch.int32)
+    one = b.build(entries, m, 100, pad_reqs_to=4, scratch_page=77, scratch_slot=8, sampled=sampled)
+    assert one.decode_only and one.num_reqs == 4 and not one.tiles
+    assert one.token_ids.tolist() == [5, -1, 0, 0] and one.ctx_len.tolist() == [18, 4, 1, 1]
+    assert one.slots.tolist() == [0, 1, 8, 8]
+    bt = one.block_tables[0]
+    assert bt[2, :2].tolist() == [77, -1] and bt[3, 0].item() == 77 and bt[0, :3].tolist() == [3, 4, -1]
+    assert b.last_h2d_bytes <= 4 * (4 * 4 + 8 + 3 * 4 + 4 * 128)
+    # another step of the same shape finds every array at the same place (what a captured graph relies on)
+    two = b.build([StepEntry(2, [9], 4, [0])], m, 100, pad_reqs_to=4, scratch_page=77, scratch_slot=8, sampled=sampled)
+    for name in ("token_ids", "positions", "q_start", "ctx_len", "slots", "logit_rows"):
+        assert getattr(one, name).data_ptr() == getattr(two, name).data_ptr(), name
+    assert one.block_tables[0].data_ptr() == two.block_tables[0].data_ptr()
+    # dummy requests with a context of their own (graphs captured ahead of any request)
+    far = b.build([], m, 100, pad_reqs_to=2, scratch_page=77, scratch_slot=8, sampled=sampled, pad_ctx=2049)
+    assert far.ctx_len.tolist() == [2049, 2049] and far.positions.tolist() == [2048, 2048]
+    assert tuple(far.block_tables[0].shape) == (2, 256)       # the class up to 8192 tokens, capped by the 256 pages of this engine
+    assert far.block_tables[0][0, :130].tolist() == [77] * 129 + [-1]
