@@ -49,6 +49,9 @@ __device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
   unsigned ok;
   asm volatile(
@@ -152,6 +155,7 @@ struct Params {
   int M, N, K, MP;            // MP: rows padded to the UMMA N extent
   int k_tiles, splits;        // k tiles in all, blocks along K
   int stages;
+  int accs;                   // issuing warps, each with an accumulator of its own in tensor memory (1 or 2)
   int red_bytes;              // shared memory set aside for the partials that peers send (splits > 1)
   int out_f32;                // 1: C is float32, 0: bfloat16
   void* out;                  // [M, N]; EPI_SWIGLU: [M, N/2]
@@ -205,7 +209,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int kt0 = blockIdx.y * per;
   const int kt1 = min(p.k_tiles, kt0 + per);
   const int my_tiles = max(0, kt1 - kt0);
-  const unsigned tmem_cols = p.MP < 32 ? 32u : (unsigned)p.MP;
+  // One thread issues a 128 x rows x 16 product about every 110 cycles however few the rows (measured:
+  // 439 cycles per tile of four; two threads of different warps issuing side by side reach one per
+  // 42 cycles between them), while 16 KB of weights per tile arrive faster than that when the block
+  // has an SM to itself.  So two warps issue, tile about, each into an accumulator of its own; the
+  // epilogue adds the two up.
+  const unsigned acc_stride = p.MP < 32 ? 32u : (unsigned)p.MP;
+  const unsigned tmem_cols = acc_stride * (unsigned)p.accs;
 
   // Which rows' final sums this block holds.  K not split: all.  K split: groups of four
   // consecutive rows go round the blocks, group g to block g mod splits, so that a sender hands
@@ -221,7 +231,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int first = min(p.stages, my_tiles);
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(accum, 1);
+    mbar_init(accum, (unsigned)p.accs);
     mbar_init(red_bar, 1);
     flags[0] = 0; flags[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -263,36 +273,37 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       tma_load_2d(a_s + (size_t)s * a_bytes, &map_w, (kt0 + i) * TILE_K, n0, &full[s]);
       tma_load_2d(b_s + (size_t)s * b_bytes, &map_x, (kt0 + i) * TILE_K, 0, &full[s]);
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---- MMA issuer
+  } else if ((warp == 1 || (warp == 2 && p.accs == 2)) && lane == 0) {
+    // ---- MMA issuers: warp 1 takes the even tiles, warp 2 (when there are two) the odd ones
+    const int w = warp - 1;
     const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.MP >> 3) << 17) | ((unsigned)(TILE_N >> 4) << 24);
+    const unsigned acc = tmem_d + (unsigned)w * acc_stride;
     bool ok = true;
-    for (int i = 0; i < my_tiles && ok; ++i) {
+    for (int i = w; i < my_tiles && ok; i += p.accs) {
       const int s = i % p.stages;
       const unsigned phase = (i / p.stages) & 1;
       if (!mbar_wait(&full[s], phase)) { atomicExch(&flags[0], 1); ok = false; break; }
       if (i == 0) stamp(p, 3);   // first tile arrived
-      tc_fence_after();
       const unsigned long long ad = smem_desc_sw128(smem_u32(a_s + (size_t)s * a_bytes));
       const unsigned long long bd = smem_desc_sw128(smem_u32(b_s + (size_t)s * b_bytes));
 #pragma unroll
       for (int k = 0; k < TILE_K / 16; ++k)  // 32 bytes further along K per step: +2 in the address field
-        umma_bf16(tmem_d, ad + 2 * k, bd + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_bf16(acc, ad + 2 * k, bd + 2 * k, idesc, (i > w || k > 0) ? 1u : 0u);
       umma_commit(&empty[s]);   // the stage is free once these products have read it
     }
-    stamp(p, 4);                // last product issued
-    umma_commit(accum);         // everything issued so far has landed in tensor memory
+    if (w == 0) stamp(p, 4);    // last product issued
+    // everything this warp issued has landed in tensor memory (a warp without a tile just arrives)
+    if (my_tiles > w) umma_commit(accum); else mbar_arrive(accum);
   }
   __syncwarp();
 
   // ---- epilogue: all four warps (the accumulator depends on rows loaded after pdl_wait;
   // the explicit wait also covers blocks that had no k tile)
   pdl_wait();
-  if (p.x_sumsq && warp >= 2) {
-    // Row scale: warps 2 and 3 have nothing else to do while the products run.  A thread takes
-    // a row and adds up its parts in their order.
-    const int r = tid - 64;
-    if (r < p.M) {
+  if (p.x_sumsq && warp == 3) {
+    // Row scale: warp 3 has nothing else to do while the products run.  A thread takes a row (two
+    // beyond 32 rows) and adds up its parts in their order.
+    for (int r = lane; r < p.M; r += 32) {
       float ss = 0.f;
       const float* src = p.x_sumsq + (size_t)r * p.x_parts;
       int q = 0;
@@ -320,6 +331,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (aborted && tid == 0) atomicCAS(p.status, 0, KVB_STATUS_WAIT_TIMEOUT);
   if (tid == 0) stamp(p, 5);   // accumulator complete
 
+  // 16 rows (columns c .. c+15 of this thread's feature) of the finished sums: the issuing warps' accumulators added up
+  auto load_sums = [&](int c, float* v) {
+    tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
+    if (p.accs == 2 && my_tiles > 1) {
+      float w1[16];
+      tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + acc_stride + c, w1);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] += w1[i];
+    }
+  };
   const int n = n0 + warp * 32 + lane;           // the feature this thread holds
   // What this block does with the final sum of (row m, its j-th own row, this thread's feature).
   const bool scaled = p.x_sumsq != nullptr;
@@ -351,7 +372,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (S == 1) {
       for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
-        if (my_tiles > 0) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
+        if (my_tiles > 0) load_sums(c, v);
         else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
@@ -365,7 +386,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       // up sends zeros, so that the byte counts of its peers still come out.
       for (int c = 0; c < p.MP && c < p.M; c += 16) {
         float v[16];
-        if (my_tiles > 0 && !aborted) tmem_ld16(tmem_d + ((unsigned)(warp * 32) << 16) + c, v);
+        if (my_tiles > 0 && !aborted) load_sums(c, v);
         else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
@@ -551,7 +572,8 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
   const int k_tiles = (K + TILE_K - 1) / TILE_K;
   int s = (2 * kvb_sm_count()) / tiles;                 // two blocks per SM in flight
   if (s > k_tiles / 2) s = k_tiles / 2;      // at least two k tiles per block
-  if (s > 8) s = 8;                          // the largest portable cluster
+  if (s > 8) s = 8;                          // the largest portable cluster (clusters of 16 were measured: they
+                                             // do not all fit at once, and the second wave costs more than they gain)
   if (s < 1) s = 1;
   while (s > 1 && (k_tiles + s - 1) / s * (s - 1) >= k_tiles) --s;  // no block without work
   *splits = s;
@@ -582,6 +604,7 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
   p.M = M; p.N = N; p.K = K; p.MP = MP;
   p.k_tiles = (K + TILE_K - 1) / TILE_K;
   p.splits = splits;
+  p.accs = 2;                       // two issuing warps: 2 x max(32, MP) columns, at most all 512 (256 rows, one block per SM)
   p.out_f32 = out_f32; p.out = out; p.status = status; p.trace = trace;
   if (epilogue < EPI_STORE || epilogue > EPI_RESIDUAL) return KVB_ERR_BAD_SIZE;
   if (epilogue != EPI_STORE && (M > 64 || out_f32)) return KVB_ERR_BAD_SIZE;
@@ -616,6 +639,11 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
   const int per = (p.k_tiles + splits - 1) / splits;
   if (stages > per) stages = per;
   if (stages < 2) stages = 2;
+  // Two issuing warps take the tiles in turn.  A stage must always be read by the same warp, tile
+  // after tile in order: a wait on a stage's barrier tells a phase only from the one before it, and a
+  // warp that ran two uses of a stage ahead of the other would take the old phase for the new one.
+  // With an even number of stages tile i and stage i mod stages have the same parity.
+  if (p.accs == 2) stages &= ~1;
   p.stages = stages;
   const size_t smem = 1024 + (size_t)stages * stage_bytes + red_bytes + p.fin_bytes + (2 * stages + 2) * 8 + 16 + 256;
   CUtensorMap mw, mx;
