@@ -68,6 +68,22 @@ int Scheduler::portion(const Req& r, int budget) const {
   return n;
 }
 
+bool Scheduler::room_for_all_of(const Req& r) const {
+  // Beside running requests a request is admitted only when the groups that keep every key have
+  // free pages for all the tokens it has by now (its prompt, and what it produced before it was
+  // dropped) and one more, plus a page of growth for each running request.  Admitting on the first
+  // portion alone lets a long request in, reads part of it, and drops it again as soon as the
+  // others grow: the same tokens are then computed over and over (upstream admits a prompt only
+  // when all its pages are free, paged_attention/src/engine.cu:294-370).
+  for (int g = 0; g < cache_->num_groups(); ++g) {
+    const GroupSpec& gs = cache_->group(g);
+    if (gs.window > 0) continue;
+    const int need = ((int)r.tokens.size() + 1 + gs.page_size - 1) / gs.page_size;
+    if (need + (int)running_.size() > cache_->free_pages(g)) return false;
+  }
+  return true;
+}
+
 int Scheduler::shrink_to_fit(const Req& r, int want) {
   // A portion needs pages for all its tokens at once, in a windowed group too, where the pages
   // that the window passes come back only after the step.  A request that nobody can make room
@@ -166,6 +182,7 @@ Plan Scheduler::schedule() {
          budget > 0) {
     Req& r = reqs_.at(waiting_.front());
     if (r.pending) break;                // its newest token is not known yet: next step
+    if (!running_.empty() && !room_for_all_of(r)) break;   // it would only be dropped again
     if (cache_->admit(r.id) < 0) break;  // no state slot free
     int want = portion(r, budget);
     if (!cache_->extend(r.id, want)) {

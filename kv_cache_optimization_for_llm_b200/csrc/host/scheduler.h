@@ -118,6 +118,9 @@ class Scheduler {
   // For a request that no preemption can make room for, in a model with a windowed group:
   // the largest halving of `want` whose pages could be taken (they are then in place); 0: none.
   int shrink_to_fit(const Req& r, int want);
+  // Whether the pools that keep every key have room for everything `r` holds by now, beside the
+  // growth of the running requests (the test for admission while others run).
+  bool room_for_all_of(const Req& r) const;
 
   CacheManager* cache_;
   SchedulerConfig cfg_;

@@ -18,15 +18,14 @@ LENGTHS = [33, 70, 120, 9, 50, 64, 17]
 
 
 @pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
-@pytest.mark.parametrize("n_reqs,num_pages", [(3, 40), (5, 40), (7, 22)])
-def test_bf16_engine_logits_with_graphs_padding_rows_and_preemption(name, n_reqs, num_pages):
+@pytest.mark.parametrize("n_reqs,num_pages,n_new", [(3, 40, 24), (5, 40, 24), (7, 18, 48)])
+def test_bf16_engine_logits_with_graphs_padding_rows_and_preemption(name, n_reqs, num_pages, n_new):
     from kv_cache_optimization_for_llm_b200 import EngineConfig, SamplingParams
     from kv_cache_optimization_for_llm_b200.engine.llm_engine import LLMEngine
     mdir = model_dir(name, "bfloat16")
     cfg, w = P.read_model_dir(mdir)
     rng = np.random.default_rng(40 + n_reqs)
     prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in LENGTHS[:n_reqs]]
-    n_new = 24
     eng = LLMEngine(mdir, EngineConfig(dtype="bfloat16", page_size=16, num_pages=num_pages, max_num_seqs=8,
                                        max_num_batched_tokens=48, max_model_len=320, seed=5,
                                        use_cuda_graphs=True, run_ahead=True))

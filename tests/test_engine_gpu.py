@@ -68,17 +68,18 @@ def test_stop_token_ends_request_and_is_not_returned():
 
 def test_temperature_sampling_with_preemption_tiny_b():
     """float32, temperature 0.7 with per-request seeds, five prompts arriving two steps
-    apart so that prompt portions share steps with decode tokens, in 14 pages of 16
-    tokens (all five together need 23), so requests are dropped and recomputed.  Every request's
-    tokens still equal the plain implementation's, which knows no cache at all."""
+    apart so that prompt portions share steps with decode tokens, 60 new tokens each, in 13
+    pages of 16 tokens (all five together grow to 36): the longest prompt waits until its pages
+    are free, and as the running requests grow the latest of them is dropped and recomputed.
+    Every request's tokens still equal the plain implementation's, which knows no cache at all."""
     from kv_cache_optimization_for_llm_b200 import EngineConfig, SamplingParams
     from kv_cache_optimization_for_llm_b200.engine.llm_engine import LLMEngine
     mdir = model_dir("tiny_b", "float32")
     cfg, w = P.read_model_dir(mdir)
     lengths = [1, 9, 33, 70, 120]
     prompts = _prompts(cfg, lengths, 5)
-    n_new = 16
-    eng = LLMEngine(mdir, EngineConfig(dtype="float32", page_size=16, num_pages=14, max_num_seqs=5,
+    n_new = 60
+    eng = LLMEngine(mdir, EngineConfig(dtype="float32", page_size=16, num_pages=13, max_num_seqs=5,
                                        max_num_batched_tokens=48, max_model_len=256, seed=99))
     params = [SamplingParams(max_tokens=n_new, temperature=0.7, seed=1000 + i, ignore_eos=True) for i in range(5)]
     ids, step = [], 0
@@ -91,7 +92,7 @@ def test_temperature_sampling_with_preemption_tiny_b():
         assert step < 2000
     st = eng.stats()
     assert st["preemptions"] > 0, "the pool was meant to be too small"
-    assert st["free_pages"] == [14]
+    assert st["free_pages"] == [13]
     for i, rid in enumerate(ids):
         ref = P.generate(cfg, w, prompts[i], n_new, temperature=0.7, seed=1000 + i, key=rid)
         assert eng.output(rid) == ref, f"request {i} (preempted {eng.preemptions_of(rid)} times)"
@@ -187,7 +188,7 @@ def test_running_ahead_changes_no_token():
     mdir = model_dir("tiny_a", "float32")
     cfg, w = P.read_model_dir(mdir)
     prompts = _prompts(cfg, [5, 30, 17, 9], 31)
-    free = [P.generate(cfg, w, p, 24) for p in prompts]
+    free = [P.generate(cfg, w, p, 32) for p in prompts]
     d = tempfile.mkdtemp(prefix="kvb200_ahead_")
     try:
         shutil.copy(os.path.join(mdir, "model.safetensors"), d)
@@ -195,20 +196,20 @@ def test_running_ahead_changes_no_token():
         c["eos_token_id"] = [int(free[0][6]), int(free[2][15])]       # both stop somewhere in the middle
         json.dump(c, open(os.path.join(d, "config.json"), "w"))
         _, w2 = P.read_model_dir(d)
-        ref = [P.generate(c, w2, p, 24, eos=c["eos_token_id"]) for p in prompts]
-        assert any(len(r) < 24 for r in ref)
+        ref = [P.generate(c, w2, p, 32, eos=c["eos_token_id"]) for p in prompts]
+        assert any(len(r) < 32 for r in ref)
         outs = {}
         for ahead in (False, True):
-            llm = LLM(d, dtype="float32", page_size=4, num_pages=16, max_num_seqs=4, max_num_batched_tokens=16,
+            llm = LLM(d, dtype="float32", page_size=4, num_pages=21, max_num_seqs=4, max_num_batched_tokens=16,
                       run_ahead=ahead)
-            outs[ahead] = llm.generate(prompts, SamplingParams(max_tokens=24))
+            outs[ahead] = llm.generate(prompts, SamplingParams(max_tokens=32))
             assert llm.engine.stats()["preemptions"] > 0
-            assert llm.engine.runner.manager.check() == "" and llm.engine.runner.manager.free_pages(0) == 16
+            assert llm.engine.runner.manager.check() == "" and llm.engine.runner.manager.free_pages(0) == 21
         assert outs[True] == outs[False] == ref
         # withdrawn in flight
         llm = LLM(d, dtype="float32", page_size=4, num_pages=40, max_num_seqs=4, run_ahead=True)
         eng = llm.engine
-        ids = [eng.add_request(p, SamplingParams(max_tokens=24)) for p in prompts[:2]]
+        ids = [eng.add_request(p, SamplingParams(max_tokens=32)) for p in prompts[:2]]
         got = {i: [] for i in ids}
         for _ in range(4):
             for ev in eng.step():
@@ -245,7 +246,7 @@ def test_random_workload_ahead_and_waiting_agree():
         reqs.append((prompt, sp, rng.randrange(0, 3)))        # tokens, sampling, steps until the next arrival
 
     def run(run_ahead):
-        eng = LLMEngine(mdir, EngineConfig(dtype="float32", page_size=4, num_pages=70, max_num_seqs=6,
+        eng = LLMEngine(mdir, EngineConfig(dtype="float32", page_size=4, num_pages=50, max_num_seqs=6,
                                            max_num_batched_tokens=24, max_model_len=128, run_ahead=run_ahead))
         out, waiting, gap, steps = {}, list(enumerate(reqs)), 0, 0
         while waiting or eng.has_unfinished():
@@ -260,7 +261,7 @@ def test_random_workload_ahead_and_waiting_agree():
             steps += 1
             assert steps < 20000
         assert eng.stats()["preemptions"] > 0
-        assert eng.runner.manager.check() == "" and eng.runner.manager.free_pages(0) == 70
+        assert eng.runner.manager.check() == "" and eng.runner.manager.free_pages(0) == 50
         return out
 
     ahead, waited = run(True), run(False)

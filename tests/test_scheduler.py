@@ -106,18 +106,18 @@ def test_bad_requests_are_refused_at_the_door():
 
 
 def test_out_of_pages_drops_the_latest_arrival_and_recomputes_it():
-    cache, s = make(pages=6, page_size=4, budget=64)
+    cache, s = make(pages=8, page_size=4, budget=64)
     s.add(0, [1] * 7, 10)     # 2 pages, grows to 5
     s.add(1, [2] * 7, 10)
     s.add(2, [3] * 7, 10)
-    plan, _ = run_step(s)     # all admitted: 6 pages taken
-    assert len(plan.entries) == 3 and cache.free_pages(0) == 0
+    plan, _ = run_step(s)     # all admitted (the third finds its 2 pages and one of growth for each of the others)
+    assert len(plan.entries) == 3 and cache.free_pages(0) == 2
     plan, _ = run_step(s)     # token 8 of each fits its second page
     assert plan.preempted == []
-    plan, _ = run_step(s)     # token 9 needs a third page each: 2 (the latest) is dropped, 0 and 1 go on
+    plan, _ = run_step(s)     # token 9 needs a third page each, two are left: 2 (the latest) is dropped, 0 and 1 go on
     assert plan.preempted == [2] and [e.id for e in plan.entries] == [0, 1]
     assert s.num_waiting() == 1 and s.preemptions_of(2) == 1 and s.preemptions_of(1) == 0
-    assert cache.check() == "" and cache.live_requests() == 2 and cache.free_pages(0) == 0
+    assert cache.check() == "" and cache.live_requests() == 2 and cache.free_pages(0) == 2
     before = list(s.tokens(2))
     assert len(before) == 9   # its prompt and the two tokens it had produced
     came_back = None
@@ -139,18 +139,44 @@ def test_out_of_pages_drops_the_latest_arrival_and_recomputes_it():
         # no token was produced twice or lost: outputs follow the position rule
         assert s.output(i) == [(i * 31 + p) % 97 for p in range(7, 17)]
     assert s.stats().preemptions >= 1 and s.stats().recomputed_tokens > 0
-    assert cache.free_pages(0) == 6 and cache.free_slots() == 4
+    assert cache.free_pages(0) == 8 and cache.free_slots() == 4
 
 
 def test_no_admission_in_a_step_that_preempted():
-    cache, s = make(pages=4, page_size=4, budget=64, seqs=4)
+    cache, s = make(pages=5, page_size=4, budget=64, seqs=4)
     s.add(0, [1] * 8, 20)
     s.add(1, [2] * 7, 20)
-    run_step(s)
+    run_step(s)               # both admitted: 2 pages each, one left
     s.add(2, [3] * 2, 5)
-    plan, _ = run_step(s)     # 0 needs a third page: 1 is dropped; 2 must not slip in ahead of it
+    plan, _ = run_step(s)     # 0 takes the last page; 2 finds no room beside two running requests
+    assert plan.preempted == [] and [e.id for e in plan.entries] == [0, 1] and s.num_waiting() == 1
+    plan, _ = run_step(s)     # 1 needs a third page: it is the latest and is dropped; 2 must not slip in ahead of it
     assert plan.preempted == [1] and [e.id for e in plan.entries] == [0]
-    assert s.num_waiting() == 2
+    assert s.num_waiting() == 2 and list(s.tokens(1))[:7] == [2] * 7
+
+
+def test_admission_waits_for_room_for_the_whole_request():
+    """Beside running requests a request is let in only when there are free pages for all its
+    tokens and one page of growth for each running request; a request that was dropped waits
+    the same way, so it is not read again just to be dropped again.  Alone, a request is let in
+    on its first portion."""
+    cache, s = make(pages=10, page_size=4, budget=8, seqs=4)
+    s.add(0, [1] * 30, 4)     # alone: admitted on its first portion of 8 tokens
+    plan, _ = run_step(s)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(0, 8)]
+    s.add(1, [2] * 9, 4)      # 10 tokens = 3 pages, plus one for request 0: 4 <= 8 free pages
+    s.add(2, [3] * 26, 4)     # 27 tokens = 7 pages, plus two: more than will be free while 0 and 1 run
+    plan, _ = run_step(s)     # 0 continues (8 tokens): the budget is spent, nobody is admitted
+    assert [e.id for e in plan.entries] == [0]
+    for _ in range(3):
+        plan, _ = run_step(s)
+    # by now 0 has read its prompt (8 pages); 1 would need 3 + 1 pages: 2 are free
+    assert s.num_running() == 1 and s.num_waiting() == 2 and s.stats().preemptions == 0
+    while s.has_unfinished():
+        run_step(s)
+        assert cache.check() == ""
+    assert s.stats().preemptions == 0 and all(len(s.output(i)) == 4 for i in range(3))
+    assert cache.free_pages(0) == 10
 
 
 def test_a_request_too_large_for_the_pool_ends_with_an_error():
