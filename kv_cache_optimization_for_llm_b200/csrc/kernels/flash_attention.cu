@@ -764,7 +764,12 @@ __device__ __forceinline__ bool wait_or_abort(void* bar, unsigned parity, volati
   return false;
 }
 
-__global__ void __launch_bounds__(kWsThreads, 2)
+// DH: the head size, 64 or 128.  Operands wider than 64 elements lie in shared memory as sub-tiles of
+// 64 columns side by side (a row of the 128-byte swizzle holds 64 bfloat16): Q, K and V have DH / 64
+// of them.  The scores take DH / 16 products of 16 along the head, the output DH / 64 times 4
+// products of 64 columns each; tensor memory holds the output in columns 128 .. 128 + DH.
+template <int DH>
+__global__ void __launch_bounds__(kWsThreads, DH == 64 ? 2 : 1)
 paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                 int box_rows, const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
                                 const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
@@ -773,10 +778,13 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
                                 float scale_log2, int window, int* status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* q_s = base;                           // [128 rows][64]
-  unsigned char* k_s = q_s + kQBytes;                  // [3][64 keys][64]
-  unsigned char* v_s = k_s + kStages * kKVBytes;       // [3][64 keys][64]
-  unsigned char* p_s = v_s + kStages * kKVBytes;       // [2][128 rows][64 keys]
+  constexpr int kSub = DH / 64;                        // sub-tiles of 64 columns in Q, K and V
+  constexpr int kQSub = BM * 128, kKVSub = BNK * 128;  // bytes of one sub-tile: rows x 128 bytes
+  constexpr int kQB = kSub * kQSub, kKVB = kSub * kKVSub;
+  unsigned char* q_s = base;                           // [DH/64][128 rows][64]
+  unsigned char* k_s = q_s + kQB;                      // [3][DH/64][64 keys][64]
+  unsigned char* v_s = k_s + kStages * kKVB;           // [3][DH/64][64 keys][64]
+  unsigned char* p_s = v_s + kStages * kKVB;           // [2][128 rows][64 keys]
   WsBars* bars = reinterpret_cast<WsBars*>(p_s + 2 * kPBytes);
   unsigned* tmem_holder = reinterpret_cast<unsigned*>(bars + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
@@ -842,7 +850,7 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       return lp < max_pages ? __ldg(table + lp) : -1;
     };
     auto request = [&](int i, int pg, unsigned char* dst, const CUtensorMap* map, void* bar) {
-      if (lane == 0) mbar_expect_tx(bar, kKVBytes);
+      if (lane == 0) mbar_expect_tx(bar, kKVB);
       __syncwarp();                                              // the bytes are expected before any copy can report
       const int page = __shfl_sync(0xffffffffu, pg, (i * n_box + lane) & 31);
       if (lane < n_box) {                                        // lane c requests box c of the tile
@@ -853,7 +861,9 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
         } else if (kj < k_hi && kj + box_rows > k_lo) {
           atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);        // keys that a row reads
         }
-        tma_load_2d(dst + lane * box_rows * (D * 2), map, 0, row, bar);
+#pragma unroll
+        for (int sub = 0; sub < kSub; ++sub)                     // columns 64 sub .. 64 sub + 63 of the box's rows
+          tma_load_2d(dst + sub * kKVSub + lane * box_rows * 128, map, 64 * sub, row, bar);
       }
     };
     int pg_k = -1, pg_v = -1, chunk_k = -1, chunk_v = -1;
@@ -867,7 +877,7 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
           failed = true;
         failed = __shfl_sync(0xffffffffu, (int)failed, 0) != 0;
         if (failed) break;
-        request(kt, pg_k, k_s + (kt % kStages) * kKVBytes, &map_k, &bars->k_full[kt % kStages]);
+        request(kt, pg_k, k_s + (kt % kStages) * kKVB, &map_k, &bars->k_full[kt % kStages]);
       }
       if (vt >= 0) {
         const int chunk = (vt * n_box) >> 5;
@@ -877,7 +887,7 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
           failed = true;
         failed = __shfl_sync(0xffffffffu, (int)failed, 0) != 0;
         if (failed) break;
-        request(vt, pg_v, v_s + (vt % kStages) * kKVBytes, &map_v, &bars->v_full[vt % kStages]);
+        request(vt, pg_v, v_s + (vt % kStages) * kKVB, &map_v, &bars->v_full[vt % kStages]);
       }
     }
   } else if (warp <= 2) {
@@ -886,18 +896,20 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
     // scores, lane 1 the P V products (in order: the output accumulates).
     const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BNK >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
     const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) /* B is MN-major */ |
-                             ((unsigned)(D >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+                             ((unsigned)(64 >> 3) << 17) | ((unsigned)(BM >> 4) << 24);   // 64 output columns at a time
     if (warp == 1 && lane == 0) {
-      const unsigned long long qd = smem_desc_sw128(smem_u32(q_s));
       if (!wait_or_abort(&bars->q_full, 0, abort_flag)) failed = true;
       for (int i = 0; i < n_tiles && !failed; ++i) {
         // S(i) = Q K(i)^T into score buffer i mod 2, which the softmax has read (tile i - 2)
         if (!wait_or_abort(&bars->k_full[i % kStages], (unsigned)(i / kStages) & 1u, abort_flag)) { failed = true; break; }
         if (i >= 2 && !wait_or_abort(&bars->s_free[i & 1], (unsigned)((i - 2) >> 1) & 1u, abort_flag)) { failed = true; break; }
         tc_fence_after();
-        const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i % kStages) * kKVBytes));
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem + 64 * (i & 1), qd + 2 * kk, kd + 2 * kk, idesc_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < DH / 16; ++kk) {   // 16 of the head per step: sub-tile kk / 4, 32 bytes further along its rows
+          const unsigned long long qd = smem_desc_sw128(smem_u32(q_s + (kk >> 2) * kQSub));
+          const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i % kStages) * kKVB + (kk >> 2) * kKVSub));
+          umma_bf16(tmem + 64 * (i & 1), qd + 2 * (kk & 3), kd + 2 * (kk & 3), idesc_s, kk > 0 ? 1u : 0u);
+        }
         umma_commit(&bars->k_empty[i % kStages]);
         umma_commit(&bars->s_full[i & 1]);
       }
@@ -908,10 +920,13 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
         if (!wait_or_abort(&bars->v_full[j % kStages], (unsigned)(j / kStages) & 1u, abort_flag)) { failed = true; break; }
         tc_fence_after();
         const unsigned long long pd = smem_desc_sw128(smem_u32(p_s + (j & 1) * kPBytes));
-        const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (j % kStages) * kKVBytes));
 #pragma unroll
-        for (int kk = 0; kk < BNK / 16; ++kk)   // 16 keys per step: 32 bytes along a row of P, 16 rows of V
-          umma_bf16(tmem + 128, pd + 2 * kk, vd + 128 * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int sub = 0; sub < kSub; ++sub) {    // output columns 64 sub .. 64 sub + 63 from V's sub-tile
+          const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (j % kStages) * kKVB + sub * kKVSub));
+#pragma unroll
+          for (int kk = 0; kk < BNK / 16; ++kk)   // 16 keys per step: 32 bytes along a row of P, 16 rows of V
+            umma_bf16(tmem + 128 + 64 * sub, pd + 2 * kk, vd + 128 * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
         umma_commit(&bars->v_empty[j % kStages]);
         umma_commit(&bars->o_done[j & 1]);
       }
@@ -926,9 +941,9 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     {
       const __nv_bfloat16* src = q_base + (size_t)(tile.t0 + (row_ok ? ti : 0)) * q_row_stride +
-                                 (size_t)(hk * G + (row_ok ? hi : 0)) * D;
+                                 (size_t)(hk * G + (row_ok ? hi : 0)) * DH;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) cp_async_16_zfill(q_s + swz<D>(r, i), src + i * 8, row_ok);
+      for (int i = 0; i < DH / 8; ++i) cp_async_16_zfill(q_s + (i >> 3) * kQSub + swz<64>(r, i & 7), src + i * 8, row_ok);
       cp_async_commit();
       cp_async_wait<0>();
       fence_async_smem();
@@ -986,7 +1001,7 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
           // the second half of the scores is kept across the rescaling: it goes through the
           // same 32 registers in two parts
 #pragma unroll
-          for (int part = 0; part < 4; ++part) {
+          for (int part = 0; part < DH / 16; ++part) {
             float ov[16];
             tmem_ld16(o_cols + 16 * part, ov);
 #pragma unroll
@@ -1014,7 +1029,7 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
             l4[j] += p0 + p1;
             pk[j] = pack_bf16(p0, p1);
           }
-          *reinterpret_cast<uint4*>(pb + swz<D>(r, 4 * hh + q4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(pb + swz<64>(r, 4 * hh + q4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
       };
       probabilities(1);
@@ -1035,9 +1050,9 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
     if (!failed) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      __nv_bfloat16* dst = out + ((size_t)(tile.t0 + ti) * nq + hk * G + hi) * D;
+      __nv_bfloat16* dst = out + ((size_t)(tile.t0 + ti) * nq + hk * G + hi) * DH;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int half = 0; half < DH / 32; ++half) {
         float o[32];
         tmem_ld32(o_cols + 32 * half, o);
         if (row_ok) {
@@ -1062,14 +1077,14 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
   if (warp == 0) tmem_dealloc(tmem, kWsTmemCols);
 }
 
-// The pages of one layer, [num_pages x nkv x page_size rows][64] bfloat16, as a 2-D tensor map
-// with boxes of box_rows x 64 and the 128-byte swizzle.  Encoded once per address and shape.
+// The pages of one layer, [num_pages x nkv x page_size rows][head size] bfloat16, as a 2-D tensor
+// map with boxes of box_rows x 64 and the 128-byte swizzle.  Encoded once per address and shape.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 struct MapKey {
-  const void* ptr; long long rows; int box;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && box == o.box; }
+  const void* ptr; long long rows; int box, dh;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && box == o.box && dh == o.dh; }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 2654435761u ^ (size_t)k.box; }
@@ -1077,7 +1092,7 @@ struct MapKeyHash {
 std::mutex g_map_mutex;
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
-int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows) {
+int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows, int dh) {
   static EncodeTiledFn fn = nullptr;
   std::lock_guard<std::mutex> lock(g_map_mutex);
   if (!fn) {
@@ -1088,13 +1103,13 @@ int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows) {
       return KVB_ERR_BAD_SIZE;
     fn = reinterpret_cast<EncodeTiledFn>(p);
   }
-  MapKey key{ptr, rows, box_rows};
+  MapKey key{ptr, rows, box_rows, dh};
   auto it = g_maps.find(key);
   if (it == g_maps.end()) {
     CUtensorMap m;
-    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)box_rows};
+    cuuint64_t dims[2] = {(cuuint64_t)dh, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)dh * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1107,6 +1122,7 @@ int pages_map(CUtensorMap* out, const void* ptr, long long rows, int box_rows) {
   return 0;
 }
 
+template <int DH>
 int launch_ws(const void* q, int q_row_stride, const void* k_pages, const void* v_pages, const int* block_table,
               int max_pages, int page_shift, int num_pages, const int* positions, const void* tiles, int num_tiles,
               void* out, int nq, int nkv, int G, int gp_shift, float scale, int window, int* status,
@@ -1116,24 +1132,24 @@ int launch_ws(const void* q, int q_row_stride, const void* k_pages, const void* 
   const long long rows = (long long)num_pages * nkv * page_size;
   if (rows >= (1ll << 31)) return KVB_ERR_BAD_SIZE;
   CUtensorMap mk, mv;
-  int e = pages_map(&mk, k_pages, rows, box_rows);
+  int e = pages_map(&mk, k_pages, rows, box_rows, DH);
   if (e) return e;
-  e = pages_map(&mv, v_pages, rows, box_rows);
+  e = pages_map(&mv, v_pages, rows, box_rows, DH);
   if (e) return e;
-  const size_t smem = 1024 + (size_t)kQBytes + 2 * kStages * (size_t)kKVBytes + 2 * kPBytes + sizeof(WsBars) + 64;
+  const size_t smem = 1024 + (size_t)BM * DH * 2 + 2 * kStages * (size_t)BNK * DH * 2 + 2 * kPBytes + sizeof(WsBars) + 64;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)smem);
     if (ce != cudaSuccess) return (int)ce;
     // two blocks per SM need the largest shared-memory configuration
-    ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+    ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel<DH>, cudaFuncAttributePreferredSharedMemoryCarveout,
                               (int)cudaSharedmemCarveoutMaxShared);
     if (ce != cudaSuccess) return (int)ce;
     attr_set = true;
   }
   dim3 grid(num_tiles, nkv);
-  kvb_launch(paged_flash_attention_ws_kernel, grid, dim3(kWsThreads), smem, stream, mk, mv, box_rows,
+  kvb_launch(paged_flash_attention_ws_kernel<DH>, grid, dim3(kWsThreads), smem, stream, mk, mv, box_rows,
              (const __nv_bfloat16*)q, q_row_stride, block_table, max_pages, page_shift,
              num_pages, positions, (const TileDesc*)tiles, (__nv_bfloat16*)out, nq, nkv, G, gp_shift,
              scale * 1.4426950408889634f, window, status);
@@ -1190,7 +1206,7 @@ KVB_EXPORT int kvb_flash_attention_tokens_per_tile(int group, int wide) {
 // int32.  The tokens of a tile are consecutive tokens of one request, positions ascending.
 // wide: 0: the tiles were cut for 64 query rows per block; 1: for 128; 2: for 128, and the
 // kernel is the tcgen05 form (head size 64 only); 3: for 128, the tcgen05 form with roles
-// (head size 64, pages of at least 8 rows, page pools aligned to 16 bytes).
+// (head size 64 or 128, pages of at least 8 rows, page pools aligned to 16 bytes).
 // bfloat16 only.  out is [T, nq*d].
 KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                          const int* block_table, int max_pages, int page_size, int num_pages,
@@ -1206,11 +1222,14 @@ KVB_EXPORT int kvb_paged_flash_attention(const void* q, int q_row_stride, const 
   const int page_shift = log2_exact(page_size);
   if (wide && (128 >> gp_shift) < 1) return KVB_ERR_BAD_SIZE;
   if (wide == 3) {   // tcgen05 form with roles
-    if (d != 64 || (reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7) || page_size < 8 ||
+    if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7) || page_size < 8 ||
         (reinterpret_cast<uintptr_t>(k_pages) & 15) || (reinterpret_cast<uintptr_t>(v_pages) & 15))
       return KVB_ERR_BAD_SIZE;
-    return tc5::launch_ws(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages, positions,
-                          tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream);
+    if (d == 64)
+      return tc5::launch_ws<64>(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages,
+                                positions, tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream);
+    return tc5::launch_ws<128>(q, q_row_stride, k_pages, v_pages, block_table, max_pages, page_shift, num_pages,
+                               positions, tiles, num_tiles, out, nq, nkv, G, gp_shift, scale, window, status, stream);
   }
   if (wide == 2) {   // tcgen05 form
     if (d != 64 || (reinterpret_cast<uintptr_t>(q) & 15) || (q_row_stride & 7)) return KVB_ERR_BAD_SIZE;

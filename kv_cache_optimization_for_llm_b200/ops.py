@@ -508,18 +508,23 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
     """Tensor-core attention for steps with runs of query tokens (bfloat16).  ``wide``:
     False: 64 query rows per block (mma.sync); True: 128 rows (mma.sync); 2: 128 rows on
     tcgen05 with the scores in tensor memory (head size 64); 3: the same with roles (a TMA
-    loader warp, two issuing warps, four softmax warps; pages of at least 8 rows); None:
+    loader warp, two issuing warps, four softmax warps; head size 64 or 128, pages of at least
+    8 rows); None:
     chosen from the step's size, the head size and the page size."""
     _need_cuda(qkv, k_pages)
     T = qkv.shape[0]
     # 128-row tiles when there are enough of them to keep every SM busy, else 64-row tiles
     nt128 = flash_tokens_per_tile(nq // nkv, True)
     if wide is None:
-        wide = FLASH_WIDE and (T // nt128) * nkv >= 2 * sm_count(qkv.device)
-        if wide and FLASH_TC and d == 64:
+        # 128-row tiles when they fill the GPU: two blocks per SM at head size 64, one at 128
+        wide = FLASH_WIDE and (T // nt128) * nkv >= (2 if d == 64 else 1) * sm_count(qkv.device)
+        if wide and FLASH_TC:
             roles = (FLASH_TC_ROLES and k_pages.shape[2] >= 8 and k_pages.data_ptr() % 16 == 0
-                     and v_pages.data_ptr() % 16 == 0)
-            wide = 3 if roles else 2
+                     and v_pages.data_ptr() % 16 == 0 and qkv.data_ptr() % 16 == 0 and qkv.stride(0) % 8 == 0)
+            if roles:
+                wide = 3
+            elif d == 64:
+                wide = 2
     tiles = flash_tiles(batch, nq // nkv, wide)
     out = new((T, nq * d), qkv.dtype, qkv.device)
     rc = lib("flash_attention").kvb_paged_flash_attention(

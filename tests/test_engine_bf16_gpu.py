@@ -55,3 +55,49 @@ def test_bf16_engine_logits_with_graphs_padding_rows_and_preemption(name, n_reqs
         bucket = next(b for b in eng.runner.graph_buckets if b >= rows)
         assert any(key[0] == bucket for key in eng.runner._graphs), (rows, list(eng.runner._graphs))
     print(f"{name}, {n_reqs} requests: {n} rows, worst relative error {worst:.3e}, preemptions {st['preemptions']}")
+
+
+# head size 128 in groups of four, long enough a portion that the 128-row query tiles fill the GPU
+WIDE_128 = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 600, "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2,
+    "num_attention_heads": 16, "num_key_value_heads": 4, "head_dim": 128,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
+    "max_position_embeddings": 1536, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+
+
+def test_long_portion_at_head_size_128_through_the_engine():
+    """bfloat16, head size 128: a portion of 1280 tokens in one step takes the warp-specialised
+    tcgen05 attention (the kernel the 3B and 8B shapes read their prompts with); then a second
+    portion over the cache the first left, and single tokens.  Logits against the plain
+    implementation at the first row, across tile and page edges, and at the end."""
+    import tempfile, shutil
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, ops
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+    d = tempfile.mkdtemp(prefix="kvb200_wide128_")
+    try:
+        write_random_model(d, WIDE_128, seed=7, std=0.05, storage_dtype="bfloat16")
+        cfg, w = P.read_model_dir(d)
+        seq = np.random.default_rng(3).integers(0, 600, 1500).tolist()
+        rows_a, rows_b = [0, 31, 32, 63, 64, 127, 128, 700, 1279], [0, 1, 100, 199]
+        ref = P.forward(cfg, w, seq, rows=rows_a + [1280 + r for r in rows_b] + list(range(1480, 1500)))
+        r = ModelRunner(d, EngineConfig(dtype="bfloat16", page_size=16, num_pages=100, max_num_seqs=2,
+                                        max_num_batched_tokens=1280, max_model_len=1536, use_cuda_graphs=False))
+        ops.choices.clear()
+        got = [r.step([StepEntry(0, seq[:1280], 0, rows_a)]).cpu().numpy()]
+        assert ops.choices["flash_attention_3"] == WIDE_128["num_hidden_layers"], dict(ops.choices)
+        got.append(r.step([StepEntry(0, seq[1280:1480], 1280, rows_b)]).cpu().numpy())   # over the cache, smaller tiles
+        for i in range(1480, 1500):
+            got.append(r.step([StepEntry(0, [seq[i]], i, [0])]).cpu().numpy())
+        r.check_status()
+        got = np.concatenate(got)
+        err = np.abs(got - ref).max() / np.abs(ref).max()
+        assert err < 4e-2, err
+        print(f"head size 128, 1280-token portion: worst relative error {err:.3e}")
+    finally:
+        shutil.rmtree(d)

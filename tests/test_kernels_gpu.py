@@ -354,7 +354,7 @@ def test_flash_attention_mixed_runs(nq, nkv, d, page_size, window):
     assert ops.flash_attention_supported(d, nq // nkv, page_size)
     c = _attention_case("bfloat16", nq, nkv, d, ctxs=[1, 70, 130, 64, 400, 257, 2], q_lens=[1, 70, 2, 1, 150, 40, 2],
                         page_size=page_size, window=window, seed=d + nq + page_size)
-    for wide in (False, True) + ((2,) if d == 64 else ()) + ((3,) if d == 64 and page_size >= 8 else ()):   # 64 and 128 query rows per block (mma.sync), 128 on tcgen05 (two forms)
+    for wide in (False, True) + ((2,) if d == 64 else ()) + ((3,) if page_size >= 8 else ()):   # 64 and 128 query rows per block (mma.sync), 128 on tcgen05 (two forms; the one with roles also at head size 128)
         fb = _FakeBatch(c)
         out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), window,
                                   wide=wide)
@@ -362,13 +362,14 @@ def test_flash_attention_mixed_runs(nq, nkv, d, page_size, window):
         assert rel_err(out, c["ref"]) < TOL["bfloat16"], wide
 
 
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("spike", [0, 63, 64, 511, 777])
-def test_flash_attention_finds_a_far_key(spike):
+def test_flash_attention_finds_a_far_key(spike, d):
     from kv_cache_optimization_for_llm_b200 import ops
-    nq, nkv, d = 8, 2, 64
+    nq, nkv = (8, 2) if d == 64 else (6, 2)
     c = _attention_case("bfloat16", nq, nkv, d, ctxs=[900], q_lens=[37], page_size=16, window=None, seed=spike,
                         spike=spike)
-    for wide in (None, 2, 3):
+    for wide in (None, 2, 3) if d == 64 else (None, True, 3):
         fb = _FakeBatch(c)
         out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, 1 / math.sqrt(d), None,
                                   wide=wide)
@@ -607,7 +608,7 @@ def test_window_edge_with_a_key_that_stands_out(d, nq, nkv, window, inside):
     spike_value = np.repeat(as64(c["vp"][page, :, slot]), nq // nkv, axis=0).reshape(-1)
     # the plain result itself shows the difference: the newest row is that key's value, or far from it
     assert (np.abs(c["ref"][-1] - spike_value).max() < 0.05) == inside
-    forms = [False, True] + ([2, 3] if d == 64 else [])
+    forms = [False, True, 3] + ([2] if d == 64 else [])
     for wide in forms:
         fb = _FakeBatch(c)
         out = ops.flash_attention(c["qkv"], c["kp"], c["vp"], c["table"], fb, nq, nkv, d, scale, window, wide=wide)
