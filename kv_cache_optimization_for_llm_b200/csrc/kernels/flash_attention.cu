@@ -374,6 +374,27 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 64 consecutive columns of this thread's lane of tensor memory: two loads of 32, one wait
+__device__ __forceinline__ void tmem_ld32x2(unsigned taddr, float* v) {
+  unsigned r[64];
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[32 * h + 0]), "=r"(r[32 * h + 1]), "=r"(r[32 * h + 2]), "=r"(r[32 * h + 3]), "=r"(r[32 * h + 4]),
+          "=r"(r[32 * h + 5]), "=r"(r[32 * h + 6]), "=r"(r[32 * h + 7]), "=r"(r[32 * h + 8]), "=r"(r[32 * h + 9]),
+          "=r"(r[32 * h + 10]), "=r"(r[32 * h + 11]), "=r"(r[32 * h + 12]), "=r"(r[32 * h + 13]), "=r"(r[32 * h + 14]),
+          "=r"(r[32 * h + 15]), "=r"(r[32 * h + 16]), "=r"(r[32 * h + 17]), "=r"(r[32 * h + 18]), "=r"(r[32 * h + 19]),
+          "=r"(r[32 * h + 20]), "=r"(r[32 * h + 21]), "=r"(r[32 * h + 22]), "=r"(r[32 * h + 23]), "=r"(r[32 * h + 24]),
+          "=r"(r[32 * h + 25]), "=r"(r[32 * h + 26]), "=r"(r[32 * h + 27]), "=r"(r[32 * h + 28]), "=r"(r[32 * h + 29]),
+          "=r"(r[32 * h + 30]), "=r"(r[32 * h + 31])
+        : "r"(taddr + 32 * h));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
 // 32 consecutive columns of this thread's lane of tensor memory, written
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
   asm volatile(
@@ -959,36 +980,33 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       const int t = first_tile + i;
       if (!wait_or_abort(&bars->s_full[b], (unsigned)(i >> 1) & 1u, abort_flag)) { failed = true; break; }
       tc_fence_after();
-      // The row's 64 scores are read in two halves of 32, the first half twice (once for the
-      // maximum, once for the probabilities): a thread holds 32 scores at a time, so that the
-      // block's eight warps fit two blocks per SM without spills.
+      // The row's 64 scores are read once, both halves requested before either is waited for, and
+      // stay in registers through the maximum and the probabilities (106 + 32 registers: two blocks
+      // per SM still fit).
       const int kb = t * BNK;
       const bool full = pos >= 0 && kb + BNK - 1 <= pos && kb >= lo;
       const bool plain = __all_sync(0xffffffffu, full);
-      float v[32];
-      auto read_half = [&](int hh) {           // scores of keys kb + 32 hh .. + 31, masked ones -inf
-        tmem_ld32(lane_base + 64 * b + 32 * hh, v);
-        if (!plain) {
+      float v[64];
+      tmem_ld32x2(lane_base + 64 * b, v);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_free[b]);    // this warp has read its rows of S(i)
+      if (!plain) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = kb + 32 * hh + j;
-            if (!(key <= pos && key >= lo)) v[j] = -CUDART_INF_F;
-          }
+        for (int j = 0; j < 64; ++j) {
+          const int key = kb + j;
+          if (!(key <= pos && key >= lo)) v[j] = -CUDART_INF_F;
         }
-      };
-      auto max_of_half = [&]() -> float {      // four chains, not one of 32
-        float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+      }
+      float m8[8];
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
+      for (int c = 0; c < 8; ++c) m8[c] = v[c];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) m4[c] = fmaxf(m4[c], v[j + c]);
-        }
-        return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      };
-      read_half(0);
-      const float mx_a = max_of_half();
-      read_half(1);
-      const float mx = fmaxf(mx_a, max_of_half());
+      for (int j = 8; j < 64; j += 8) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) m8[c] = fmaxf(m8[c], v[j + c]);
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
       const float m_new = fmaxf(m_ref, mx * scale_log2);   // the scale is positive: the maximum commutes with it
       const bool grow = m_new > m_ref + kRescale;          // also: the row's first key (m_ref is -inf)
       if (__any_sync(0xffffffffu, grow)) {
@@ -998,8 +1016,6 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
           // thread's probabilities of tile i are written
           if (!wait_or_abort(&bars->o_done[(i - 1) & 1], (unsigned)((i - 1) >> 1) & 1u, abort_flag)) { failed = true; break; }
           tc_fence_after();
-          // the second half of the scores is kept across the rescaling: it goes through the
-          // same 32 registers in two parts
 #pragma unroll
           for (int part = 0; part < DH / 16; ++part) {
             float ov[16];
@@ -1017,27 +1033,19 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       if (i >= 2 && !wait_or_abort(&bars->o_done[b], (unsigned)((i - 2) >> 1) & 1u, abort_flag)) { failed = true; break; }
       unsigned char* pb = p_s + b * kPBytes;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};    // the tile's sum in four chains, added up in a fixed order
-      auto probabilities = [&](int hh) {     // of the half in v: pieces 4 hh .. 4 hh + 3 of row r of P
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          unsigned pk[4];
+      for (int q8 = 0; q8 < 8; ++q8) {       // piece q8 of row r of P: keys 8 q8 .. 8 q8 + 7
+        unsigned pk[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            // a masked score is -inf: its probability comes out as zero
-            const float p0 = ex2(fmaf(v[8 * q4 + 2 * j], scale_log2, -m_use));
-            const float p1 = ex2(fmaf(v[8 * q4 + 2 * j + 1], scale_log2, -m_use));
-            l4[j] += p0 + p1;
-            pk[j] = pack_bf16(p0, p1);
-          }
-          *reinterpret_cast<uint4*>(pb + swz<64>(r, 4 * hh + q4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        for (int j = 0; j < 4; ++j) {
+          // a masked score is -inf: its probability comes out as zero
+          const float p0 = ex2(fmaf(v[8 * q8 + 2 * j], scale_log2, -m_use));
+          const float p1 = ex2(fmaf(v[8 * q8 + 2 * j + 1], scale_log2, -m_use));
+          l4[j] += p0 + p1;
+          pk[j] = pack_bf16(p0, p1);
         }
-      };
-      probabilities(1);
-      read_half(0);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_free[b]);    // this warp has read its rows of S(i) for the last time
-      probabilities(0);
+        *reinterpret_cast<uint4*>(pb + swz<64>(r, q8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
       l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_async_smem();
       tc_fence_before();     // orders the rescaled output before the product that the arrival lets go
