@@ -406,11 +406,18 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const int* __restr
       float x1[VEC], x2[VEC], a[VEC], b[VEC];
       Vec16<T>::load(x + j, x1);
       Vec16<T>::load(x + j + half, x2);
+      // the angles of these VEC pairs, four at a time (j is a multiple of VEC, VEC of 4; the tables' rows
+      // start on 16 bytes when half is a multiple of 4, which the launcher checks)
+      float cs[VEC], sn[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) {
+        *reinterpret_cast<float4*>(cs + e) = *reinterpret_cast<const float4*>(cr + j + e);
+        *reinterpret_cast<float4*>(sn + e) = *reinterpret_cast<const float4*>(sr + j + e);
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        const float c = cr[j + e], sn = sr[j + e];
-        a[e] = x1[e] * c - x2[e] * sn;
-        b[e] = x1[e] * sn + x2[e] * c;
+        a[e] = x1[e] * cs[e] - x2[e] * sn[e];
+        b[e] = x1[e] * sn[e] + x2[e] * cs[e];
       }
       if (head < nq) {
         Vec16<T>::store(x + j, a);
@@ -437,7 +444,8 @@ KVB_EXPORT int kvb_rope_kv_write(void* qkv, const int* positions, const int* tok
   if (T_ <= 0) return 0;
   if (d % 2 || rot % 2 || rot > d) return KVB_ERR_BAD_SIZE;
   const int esz = dtype == KVB_F32 ? 4 : 2;
-  if (cos_t != nullptr && rot == d && (d / 2) % (16 / esz) == 0 && dtype <= KVB_BF16) {
+  if (cos_t != nullptr && rot == d && (d / 2) % (16 / esz) == 0 && dtype <= KVB_BF16 &&
+      ((reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t)) & 15) == 0) {
     const int items = (nq + nkv) * (d / 2) / (16 / esz) + nkv * d / (16 / esz);
     const int th = items >= 192 ? 256 : (items >= 96 ? 128 : 64);
     KVB_DISPATCH_DTYPE(dtype, T, (kvb_launch(rope_kv_write_vec_kernel<T>, dim3(T_), dim3(th), 0, stream, (T*)qkv,

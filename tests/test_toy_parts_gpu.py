@@ -223,3 +223,153 @@ def test_routed_feed_forward_other_position_and_parallel_block(dtype, tol):
     assert pos1 == 30 and pos0 == 21
     r.check_status()
     assert r.manager.check() == ""
+
+
+# ---------------------------------------------------------------------------------
+# A block with more parts than the pre-norm block, and a part inside a part that has
+# weights of its own: what a layer with post-norms and per-head query/key norms needs
+# of the model description, shown with toys that are registered here.
+# ---------------------------------------------------------------------------------
+
+def _register_sandwich():
+    from kv_cache_optimization_for_llm_b200 import ops
+    from kv_cache_optimization_for_llm_b200.models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from kv_cache_optimization_for_llm_b200.parts import register
+    from kv_cache_optimization_for_llm_b200.parts.attention import GroupedQueryAttention
+    from kv_cache_optimization_for_llm_b200.registry import register_architecture
+    from kv_cache_optimization_for_llm_b200.weights.loader import WeightSpec
+
+    @register("block", "toy_sandwich")
+    class SandwichBlock:
+        """``h += post1(mixer(norm1(h))); h += post2(ff(norm2(h)))``: six parts, four of them norms."""
+        part_families = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm",
+                         "feed_forward": "feed_forward", "ff_norm": "norm", "ff_post_norm": "norm"}
+
+        def __init__(self, parts):
+            self.parts = dict(parts)
+
+        def cache_spec(self):
+            return self.parts["mixer"].cache_spec()
+
+        def forward(self, residual, delta, batch, cache):
+            p = self.parts
+            x = p["mixer_norm"].forward(residual, delta)                  # adds what the layer before left pending
+            a = p["mixer"].forward(x, batch, cache)
+            a = self._normed(p["mixer_post_norm"], a)
+            x = p["ff_norm"].forward(residual, a)
+            f = p["feed_forward"].forward(x, batch)
+            return residual, self._normed(p["ff_post_norm"], f)
+
+        @staticmethod
+        def _normed(norm, t):
+            v = t.float()
+            return (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + norm.eps) * norm.weight).to(t.dtype)
+
+    @register("mixer", "toy_qk_norm_attention")
+    class QKNormAttention(GroupedQueryAttention):
+        """The package's attention with an RMSNorm over the head size on every query and key
+        head before the rotation.  The two norms are parts of their own, nested in this
+        part's params (``q_norm``, ``k_norm``), with a weight each that comes from the
+        checkpoint: the model description finds them there, and ``ctx.make`` builds them.
+        params: those of attention, and q_norm, k_norm (PartSpecs of family norm)."""
+        fuses_residual = False
+
+        def __init__(self, params, weights, ctx):
+            super().__init__(params, weights, ctx)
+            self.q_norm = ctx.make("norm", params["q_norm"])
+            self.k_norm = ctx.make("norm", params["k_norm"])
+
+        def forward(self, x, batch, cache, into=None):
+            qkv = ops.linear(x, self.qkv)
+            T = qkv.shape[0]
+            heads = qkv.view(T, self.nq + 2 * self.nkv, self.d)
+            for lo, hi, norm in ((0, self.nq, self.q_norm), (self.nq, self.nq + self.nkv, self.k_norm)):
+                v = heads[:, lo:hi].float()
+                heads[:, lo:hi] = (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + norm.eps) * norm.weight).to(qkv.dtype)
+            cos, sin = self.position.tables()
+            a = ops.attention_step(qkv, cache.k, cache.v, cache.write, batch.block_tables[cache.group], batch,
+                                   self.nq, self.nkv, self.d, self.scale, self.window, self.ctx.max_positions,
+                                   cos, sin, self.position.rotary_dim)
+            return ops.linear(a, self.o)
+
+    def build(cfg):
+        H, V, d = cfg["hidden_size"], cfg["vocab_size"], cfg["head_dim"]
+        norm = lambda name, size=H: PartSpec("rmsnorm", {"size": size, "eps": cfg["eps"]}, {"weight": name}, family="norm")
+        layers = []
+        for i in range(cfg["num_layers"]):
+            p = f"l{i}."
+            rope = PartSpec("rope", {"head_dim": d, "rotary_dim": d, "theta": 300.0, "scaling": None})
+            mixer = PartSpec("toy_qk_norm_attention",
+                             {"hidden_size": H, "num_heads": cfg["heads"], "num_kv_heads": cfg["kv_heads"], "head_dim": d,
+                              "window": None, "position": rope, "q_norm": norm(p + "attn.q_norm", d),
+                              "k_norm": norm(p + "attn.k_norm", d)},
+                             {r: f"{p}attn.{r}" for r in "qkvo"})
+            ff = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": cfg["inter"]},
+                          {"gate": p + "ff.gate", "up": p + "ff.up", "down": p + "ff.down"})
+            layers.append(LayerSpec("toy_sandwich", dict(mixer=mixer, mixer_norm=norm(p + "n1"), mixer_post_norm=norm(p + "p1"),
+                                                         feed_forward=ff, ff_norm=norm(p + "n2"), ff_post_norm=norm(p + "p2"))))
+        return ModelSpec(architecture="ToySandwichForCausalLM", hidden_size=H, vocab_size=V, max_position=cfg["max_pos"],
+                         embedding=PartSpec("token_embedding", {"vocab_size": V, "hidden_size": H}, {"table": "emb"}),
+                         layers=layers, schedule=[ScheduleEntry(i) for i in range(len(layers))],
+                         final_norm=norm("nf"),
+                         lm_head=PartSpec("linear_head", {"vocab_size": V, "hidden_size": H}, {"weight": "emb"}))
+
+    register_architecture("ToySandwichForCausalLM", lambda d: d, build)
+
+
+SANDWICH = {"architectures": ["ToySandwichForCausalLM"], "hidden_size": 72, "vocab_size": 83, "eps": 1e-5, "heads": 3,
+            "kv_heads": 3, "head_dim": 32, "inter": 104, "num_layers": 2, "max_pos": 80}
+
+
+def _plain_sandwich(cfg, w, tokens):
+    T, d, nq, nkv, eps = len(tokens), cfg["head_dim"], cfg["heads"], cfg["kv_heads"], cfg["eps"]
+    cos, sin = P.rope_tables(np.arange(T), P.rope_inv_freq(d, 300.0))
+    h = w["emb"][np.asarray(tokens)]
+    for i in range(cfg["num_layers"]):
+        p = f"l{i}."
+        x = P.rms_norm(h, w[p + "n1"], eps)
+        q = P.rms_norm(P.linear(x, w[p + "attn.q"]).reshape(T, nq, d), w[p + "attn.q_norm"], eps)
+        k = P.rms_norm(P.linear(x, w[p + "attn.k"]).reshape(T, nkv, d), w[p + "attn.k_norm"], eps)
+        v = P.linear(x, w[p + "attn.v"]).reshape(T, nkv, d)
+        a = P.attention(P.apply_rope(q, cos, sin), P.apply_rope(k, cos, sin), v).reshape(T, nq * d)
+        h = h + P.rms_norm(P.linear(a, w[p + "attn.o"]), w[p + "p1"], eps)
+        f = P.swiglu_part(P.rms_norm(h, w[p + "n2"], eps), {"gate_proj.weight": w[p + "ff.gate"],
+                          "up_proj.weight": w[p + "ff.up"], "down_proj.weight": w[p + "ff.down"]}, "")
+        h = h + P.rms_norm(f, w[p + "p2"], eps)
+    return P.linear(P.rms_norm(h, w["nf"], eps), w["emb"])
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 4e-2)])
+def test_block_with_post_norms_and_a_mixer_that_owns_norms(dtype, tol):
+    """Registered, built, loaded by tensor name (the nested norms' weights included) and stepped
+    in portions beside decoded tokens, against a numpy restatement."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    from kv_cache_optimization_for_llm_b200.models.spec import expected_weights
+    from kv_cache_optimization_for_llm_b200.registry import resolve_architecture
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+    _register_sandwich()
+    arch = resolve_architecture(SANDWICH)
+    names = expected_weights(arch.build_spec(arch.parse_config(SANDWICH)))
+    assert names["l1.attn.k_norm"].shape == (32,) and names["l0.p2"].shape == (72,) and len(names) == 2 * 13 + 2
+    d = tempfile.mkdtemp(prefix="kvb200_sandwich_")
+    write_random_model(d, SANDWICH, seed=12, std=0.15)
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    seqs = [np.random.default_rng(s).integers(0, 83, n).tolist() for s, n in ((1, 40), (2, 26))]
+    refs = [_plain_sandwich(SANDWICH, w, s) for s in seqs]
+    scale = max(np.abs(x).max() for x in refs)
+    r = ModelRunner(d, EngineConfig(dtype=dtype, page_size=8, num_pages=12, max_num_seqs=2,
+                                    max_num_batched_tokens=64, max_model_len=80, use_cuda_graphs=False))
+    got = r.step([StepEntry(0, seqs[0][:25], 0, range(25))]).cpu().numpy()
+    assert np.abs(got - refs[0][:25]).max() / scale < tol
+    pos0, pos1 = 25, 0
+    for n1 in (7, 2, 1, 9, 1, 6):
+        entries = [StepEntry(1, seqs[1][pos1:pos1 + n1], pos1, range(n1)), StepEntry(0, [seqs[0][pos0]], pos0, [0])]
+        got = r.step(entries).cpu().numpy()
+        ref = np.concatenate([refs[1][pos1:pos1 + n1], refs[0][pos0:pos0 + 1]])
+        assert np.abs(got - ref).max() / scale < tol, (dtype, pos0, pos1)
+        pos0, pos1 = pos0 + 1, pos1 + n1
+    assert pos1 == 26
+    r.check_status()
+    assert r.manager.check() == ""
