@@ -40,7 +40,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(HERE, "_ref", "paged_attention")
 BINARY = os.path.join(REF_DIR, "tiny-vllm")
 SOURCES = ["main.cu", "engine.cu", "kernels.cu", "model.cu", "utils.cu", "request_queue.cpp"]
-UPSTREAM = "/root/reference/paged_attention"
+UPSTREAM = os.path.join(os.environ.get("KVB200_UPSTREAM_DIR", "/root/reference"), "paged_attention")   # where upstream is checked out
 PAGE_BYTES = 32 * 1024          # BLOCK_BYTES: 16 tokens x 512 x bfloat16 x (K and V), one layer
 MAX_SAFE_PAGES = 65535          # the largest page count whose int offsets do not overflow
 TARGET_PAGES = 61000
