@@ -14,8 +14,8 @@ that run on a CPU.  Run once, by hand, with the upstream checkout at hand:
    32 / 1 / 4 / 8192).
 
 The tests only read the JSON files; nothing at test time needs the upstream tree.
-The rest of the upstream model code cannot be run without a GPU, so beyond these
-two anchors the plain implementation rests on the formulas it cites.
+The rest of the upstream model code cannot be run without a GPU; what its whole engine
+generates on one is recorded by ``make_upstream_tokens.py`` beside this file.
 """
 
 import importlib.util

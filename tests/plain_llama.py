@@ -8,9 +8,14 @@ formula it restates.
 
 The upstream model code cannot run without a GPU (every op is a CUDA kernel or a
 cuBLAS call and every size is a compile-time constant), so the model formulas
-here rest on reading those lines.  Two upstream pieces do run on a CPU and anchor
-this file through ``tests/golden/``: the numpy sampler mirror
-(``python/sampling_reference.py``) and the host half of ``initRopeFrequencies``.
+here were written from reading those lines.  Three things of upstream anchor this
+file through ``tests/golden/``: its numpy sampler mirror
+(``python/sampling_reference.py``) and the host half of ``initRopeFrequencies``,
+which run on a CPU, and the tokens that its unmodified engine, compiled for a
+B200, generated on a Llama-3.2-1B-shaped model with random weights
+(``tests/golden/upstream_tokens_llama1b.json``): ``tests/test_upstream_golden_gpu.py``
+checks that those tokens are the best under the logits of this file and of the
+engine.
 
 Arithmetic is float64 unless a function takes ``dtype``; the engine's float32
 path must agree with it to float32 rounding, the bfloat16 path to bfloat16
