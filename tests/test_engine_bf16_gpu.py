@@ -101,3 +101,50 @@ def test_long_portion_at_head_size_128_through_the_engine():
         print(f"head size 128, 1280-token portion: worst relative error {err:.3e}")
     finally:
         shutil.rmtree(d)
+
+
+LONG_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 515, "hidden_size": 256, "intermediate_size": 384, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "rope_scaling": None,
+    "max_position_embeddings": 2304, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 4e-2)])
+def test_decoding_across_the_edge_of_a_context_class(dtype, tol):
+    """Launches, captured graphs and the width of the block tables come in classes by the step's
+    longest context (up to 2048 tokens, up to 8192, beyond).  Two requests decode side by side
+    from graphs while the longer one grows from 2040 to 2060 tokens, across the first edge: the
+    step switches graph and table width at 2049, the shorter request's logits must not notice."""
+    import tempfile, shutil
+    from kv_cache_optimization_for_llm_b200 import EngineConfig
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+    d = tempfile.mkdtemp(prefix="kvb200_long_")
+    try:
+        write_random_model(d, LONG_D, seed=21, std=0.05, storage_dtype="float32" if dtype == "float32" else "bfloat16")
+        cfg, w = P.read_model_dir(d)
+        rng = np.random.default_rng(9)
+        long_seq, short_seq = rng.integers(0, 515, 2060).tolist(), rng.integers(0, 515, 60).tolist()
+        ref_long = P.forward(cfg, w, long_seq, rows=range(2039, 2060))
+        ref_short = P.forward(cfg, w, short_seq, rows=range(39, 60))
+        r = ModelRunner(d, EngineConfig(dtype=dtype, page_size=16, num_pages=160, max_num_seqs=2,
+                                        max_num_batched_tokens=1100, max_model_len=2304, use_cuda_graphs=True))
+        r.step([StepEntry(0, long_seq[:1024], 0, [])])
+        out = r.step([StepEntry(0, long_seq[1024:2040], 1024, [1015]), StepEntry(1, short_seq[:40], 0, [39])]).cpu().numpy()
+        worst = max(np.abs(out[0] - ref_long[0]).max() / np.abs(ref_long).max(),
+                    np.abs(out[1] - ref_short[0]).max() / np.abs(ref_short).max())
+        for k in range(20):          # contexts 2041 .. 2060 beside 41 .. 60
+            out = r.step([StepEntry(0, [long_seq[2040 + k]], 2040 + k, [0]),
+                          StepEntry(1, [short_seq[40 + k]], 40 + k, [0])]).cpu().numpy()
+            worst = max(worst, np.abs(out[0] - ref_long[1 + k]).max() / np.abs(ref_long).max(),
+                        np.abs(out[1] - ref_short[1 + k]).max() / np.abs(ref_short).max())
+        r.check_status()
+        classes = sorted(key[1] for key in r._graphs)
+        assert classes == [4, 8], classes          # both sides of the edge ran, each from a graph of its own
+        assert worst < tol, worst
+    finally:
+        shutil.rmtree(d)
