@@ -29,29 +29,37 @@ class _Region:
     def __init__(self, nbytes: int, device):
         self.device = device
         self.capacity = max(_ALIGN, -(-int(nbytes) // _ALIGN) * _ALIGN)
-        self.blocks: List[torch.Tensor] = [torch.empty(self.capacity, dtype=torch.uint8, device=device)]
-        self.block, self.offset = 0, 0
+        self.blocks: List[torch.Tensor] = []
+        self.pads: List[int] = []       # bytes in front of each block's first aligned address
+        self._add_block()
+        self.block, self.offset = 0, self.pads[0]
         self.grown = 0
 
+    def _add_block(self) -> None:
+        buf = torch.empty(self.capacity + _ALIGN, dtype=torch.uint8, device=self.device)
+        self.blocks.append(buf)
+        self.pads.append((-buf.data_ptr()) % _ALIGN)
+
     def reset(self) -> None:
-        self.block, self.offset = 0, 0
+        self.block, self.offset = 0, self.pads[0]
 
     def take(self, nbytes: int):
-        """A run of ``nbytes`` bytes, or None if the request is larger than the region was built for."""
+        """A run of ``nbytes`` bytes on a 256-byte boundary, or None if the request is larger than
+        the region was built for."""
         need = -(-nbytes // _ALIGN) * _ALIGN
         if need > self.capacity:
             return None
         while True:
             buf = self.blocks[self.block]
-            if self.offset + need <= buf.numel():
+            if self.offset + need <= self.pads[self.block] + self.capacity:
                 out = buf[self.offset:self.offset + nbytes]
                 self.offset += need
                 return out
             self.block += 1
-            self.offset = 0
             if self.block == len(self.blocks):
-                self.blocks.append(torch.empty(self.capacity, dtype=torch.uint8, device=self.device))
+                self._add_block()
                 self.grown += 1
+            self.offset = self.pads[self.block]
 
 
 class StepArena:
