@@ -301,3 +301,22 @@ def test_long_portion_through_the_products_for_many_rows(mode, monkeypatch):
         got = r.step([StepEntry(0, [seq[i]], i, [0])]).cpu().numpy()
         assert np.abs(got - ref[i:i + 1]).max() / np.abs(ref).max() < 4e-2
     assert ops.launch_count > before
+
+
+def test_graphs_captured_when_the_engine_is_built():
+    """``capture_graphs_at_start``: every decode graph (each batch-size bucket, each class of
+    context length that ``max_model_len`` allows) is captured on dummy rows before any request;
+    generation then captures nothing more and produces the plain implementation's tokens."""
+    from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
+    mdir = model_dir("tiny_a", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    prompts = _prompts(cfg, [5, 11, 17, 3, 8], 41)
+    llm = LLM(mdir, dtype="float32", page_size=4, num_pages=64, max_num_seqs=6, max_num_batched_tokens=32,
+              capture_graphs_at_start=True)
+    r = llm.engine.runner
+    assert r.graph_buckets == [1, 2, 4, 6] and sorted(r._graphs) == [(1, 4), (2, 4), (4, 4), (6, 4)]   # tiny_a: 128 positions, one class
+    assert int(r.status.item()) == 0 and r.manager.check() == "" and r.manager.free_pages(0) == 64
+    got = llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    assert len(r._graphs) == 4                      # nothing was captured on the way
+    for p, g in zip(prompts, got):
+        assert g == P.generate(cfg, w, p, 8)
