@@ -210,20 +210,29 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   }
   const bool own_t = own_page >= 0 && tid < D;              // this thread carries dim `tid` of the new key and value
 
+  // The rotation's angle depends on the position only, and a thread meets one dim of the head in
+  // all its work (the block's threads are a multiple of the head size): fetched before the wait.
+  static_assert(kThreads % D == 0, "a thread must keep its dim of the head");
+  float rot_c = 1.f, rot_s = 0.f;
+  if (!bad && rotary && (tid % D) < rot) {
+    const int dd = tid % D, j = dd < half ? dd : dd - half;
+    rot_c = cos_t[(size_t)pos * half + j];
+    rot_s = sin_t[(size_t)pos * half + j];
+  }
+
   pdl_wait();
   stamp(1);   // the projection in front has finished
   if (own_key_from_this_step) request_first_tiles();
   const __nv_bfloat16* row = qkv + (size_t)q_start[r] * q_row_stride;
   // the owner's loads go out first, so that they are under way while the queries are rotated
-  float nk1 = 0.f, nk2 = 0.f, nc = 1.f, ns = 0.f;
+  float nk1 = 0.f, nk2 = 0.f;
+  const float nc = rot_c, ns = rot_s;
   __nv_bfloat16 nv = __float2bfloat16_rn(0.f);
   if (own_t) {
     const __nv_bfloat16* kh = row + (size_t)(nq + hk) * D;
     const int dd = tid;
     if (rotary && dd < rot) {
       const int j = dd < half ? dd : dd - half;
-      nc = cos_t[(size_t)pos * half + j];
-      ns = sin_t[(size_t)pos * half + j];
       nk1 = to_f32(kh[j]);
       nk2 = to_f32(kh[j + half]);
     } else {
@@ -240,7 +249,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         const __nv_bfloat16* qh = row + (size_t)(hk * G + g) * D;
         if (rotary && dd < rot) {
           const int j = dd < half ? dd : dd - half;
-          const float c = cos_t[(size_t)pos * half + j], sn = sin_t[(size_t)pos * half + j];
+          const float c = rot_c, sn = rot_s;
           const float x1 = to_f32(qh[j]), x2 = to_f32(qh[j + half]);
           val = dd < half ? x1 * c - x2 * sn : x1 * sn + x2 * c;
         } else {

@@ -50,6 +50,8 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=640, help="context length of every request (attention)")
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--spread", action="store_true",
+                    help="timeline: also the 10th and 90th percentile and the extremes over the blocks of each phase")
     a = ap.parse_args(argv)
 
     import numpy as np
@@ -64,7 +66,7 @@ def main(argv=None) -> int:
     if a.what == "attention":
         return _attention_alone(cfg, a.batch, a.context)
     if a.what == "timeline":
-        return _timeline(cfg, a.batch, a.prompt)
+        return _timeline(cfg, a.batch, a.prompt, a.spread)
     page = 16
     need = a.batch * (a.prompt + 64 + a.steps) if a.what == "decode" else a.tokens
     llm = LLM.from_random(cfg, dtype=a.dtype, page_size=page, num_pages=need // page + 64,
@@ -109,7 +111,7 @@ def main(argv=None) -> int:
     return 0
 
 
-def _timeline(cfg, batch: int, prompt: int) -> int:
+def _timeline(cfg, batch: int, prompt: int, spread: bool = False) -> int:
     """Phase stamps of the product and attention kernels inside a captured decode step."""
     import numpy as np
     import torch
@@ -158,7 +160,7 @@ def _timeline(cfg, batch: int, prompt: int) -> int:
     torch.cuda.synchronize()
     gemm_cols = [("first tile", 3), ("last product issued", 4), ("accumulator complete", 5), ("partials here", 7), ("stored", 6)]
     attn_cols = [("queries ready", 2), ("first class walked", 3), ("partials sent", 4), ("cluster met", 5), ("stored", 6)]
-    rows, t_first = {}, None
+    rows, t_first, spreads = {}, None, {}
     for kind, t in captured:
         a = t.cpu().numpy().astype(np.float64)
         a = a[a[:, 0] > 0]
@@ -175,6 +177,14 @@ def _timeline(cfg, batch: int, prompt: int) -> int:
             vals.append((np.median(c) - dep) / 1e3 if len(c) else float("nan"))
         vals.append((a[:, 6].max() - dep) / 1e3)
         rows.setdefault(kind, []).append(vals)
+        if spread:
+            pcs = []
+            for _, col in [("blocks start", 0)] + (attn_cols if is_attn else gemm_cols):
+                c = a[:, col]
+                c = c[c > 0]
+                pcs.append([(f(c) - dep) / 1e3 if len(c) else float("nan") for f in
+                            (np.min, lambda x: np.percentile(x, 10), np.median, lambda x: np.percentile(x, 90), np.max)])
+            spreads.setdefault(kind, []).append(pcs)
         t_last = a[:, 6].max()
     print(f"decode step, batch {batch}: {(t_last - t_first) / 1e3:.1f} us from the first product's first block to the LM head's last store")
     print("microseconds relative to the end of each kernel's wait for the kernel in front (medians over blocks, mean over layers)")
@@ -184,6 +194,10 @@ def _timeline(cfg, batch: int, prompt: int) -> int:
         cols = attn_cols if kind == "decode attention" else gemm_cols
         txt = "  ".join(f"{nm} {x:5.1f}" for (nm, _), x in zip(cols, m[1:-1]))
         print(f"  {kind:32s} x{len(v):3d}  blocks start {m[0]:6.1f}  {txt}  last block done {m[-1]:5.1f}")
+        if spread:
+            sp_mean = np.nanmean(np.array(spreads[kind]), axis=0)      # [phase, 5]
+            for (nm, _), q in zip([("blocks start", 0)] + cols, sp_mean):
+                print(f"      {nm:22s} min {q[0]:6.1f}  p10 {q[1]:6.1f}  median {q[2]:6.1f}  p90 {q[3]:6.1f}  max {q[4]:6.1f}")
     return 0
 
 
