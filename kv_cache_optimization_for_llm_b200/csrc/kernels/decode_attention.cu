@@ -213,6 +213,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   // The rotation's angle depends on the position only, and a thread meets one dim of the head in
   // all its work (the block's threads are a multiple of the head size): fetched before the wait.
   static_assert(kThreads % D == 0, "a thread must keep its dim of the head");
+  const size_t q_row = (size_t)q_start[r];       // the host wrote it, like the lengths: no need to wait for it
   float rot_c = 1.f, rot_s = 0.f;
   if (!bad && rotary && (tid % D) < rot) {
     const int dd = tid % D, j = dd < half ? dd : dd - half;
@@ -223,7 +224,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   pdl_wait();
   stamp(1);   // the projection in front has finished
   if (own_key_from_this_step) request_first_tiles();
-  const __nv_bfloat16* row = qkv + (size_t)q_start[r] * q_row_stride;
+  const __nv_bfloat16* row = qkv + q_row * q_row_stride;
   // the owner's loads go out first, so that they are under way while the queries are rotated
   float nk1 = 0.f, nk2 = 0.f;
   const float nc = rot_c, ns = rot_s;
@@ -466,7 +467,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         a += recv[((size_t)c * GP + g) * PW + dd] * f;
       }
     }
-    out[((size_t)q_start[r] * nq + hk * G + g) * D + dd] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
+    out[(q_row * nq + hk * G + g) * D + dd] = __float2bfloat16_rn(L > 0.f ? a / L : 0.f);
   }
   stamp(6);   // output stored
 }
