@@ -456,6 +456,27 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two float32 operations in one instruction (sm_100: fma.rn.f32x2, add.rn.f32x2; each half is the
+// IEEE operation of the scalar form) and the maximum of three.  The softmax threads are bound by
+// the instructions they issue, not by any one pipe: these halve the multiply-adds and the sums.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)),
+        "l"(reinterpret_cast<unsigned long long&>(c)));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
 __global__ void __launch_bounds__(kThreads, 3)
 paged_flash_attention_tc_kernel(const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
@@ -1000,13 +1021,15 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       }
       float m8[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) m8[c] = v[c];
+      for (int c = 0; c < 8; ++c) m8[c] = max3(v[c], v[8 + c], v[16 + c]);
 #pragma unroll
-      for (int j = 8; j < 64; j += 8) {
+      for (int j = 24; j < 56; j += 16) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) m8[c] = fmaxf(m8[c], v[j + c]);
+        for (int c = 0; c < 8; ++c) m8[c] = max3(m8[c], v[j + c], v[j + 8 + c]);
       }
-      const float mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+#pragma unroll
+      for (int c = 0; c < 8; ++c) m8[c] = fmaxf(m8[c], v[56 + c]);
+      const float mx = max3(max3(m8[0], m8[1], m8[2]), max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
       const float m_new = fmaxf(m_ref, mx * scale_log2);   // the scale is positive: the maximum commutes with it
       const bool grow = m_new > m_ref + kRescale;          // also: the row's first key (m_ref is -inf)
       if (__any_sync(0xffffffffu, grow)) {
@@ -1032,21 +1055,22 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       // the buffer of P(i) was read by P V(i - 2)
       if (i >= 2 && !wait_or_abort(&bars->o_done[b], (unsigned)((i - 2) >> 1) & 1u, abort_flag)) { failed = true; break; }
       unsigned char* pb = p_s + b * kPBytes;
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};    // the tile's sum in four chains, added up in a fixed order
+      float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};   // the tile's sum in four chains, added up in a fixed order
+      const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
 #pragma unroll
       for (int q8 = 0; q8 < 8; ++q8) {       // piece q8 of row r of P: keys 8 q8 .. 8 q8 + 7
         unsigned pk[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           // a masked score is -inf: its probability comes out as zero
-          const float p0 = ex2(fmaf(v[8 * q8 + 2 * j], scale_log2, -m_use));
-          const float p1 = ex2(fmaf(v[8 * q8 + 2 * j + 1], scale_log2, -m_use));
-          l4[j] += p0 + p1;
-          pk[j] = pack_bf16(p0, p1);
+          const float2 t = ffma2(make_float2(v[8 * q8 + 2 * j], v[8 * q8 + 2 * j + 1]), sc2, nm2);
+          const float2 pr = make_float2(ex2(t.x), ex2(t.y));
+          l2[j & 1] = fadd2(l2[j & 1], pr);
+          pk[j] = pack_bf16(pr.x, pr.y);
         }
         *reinterpret_cast<uint4*>(pb + swz<64>(r, q8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      l_run += (l2[0].x + l2[0].y) + (l2[1].x + l2[1].y);
       fence_async_smem();
       tc_fence_before();     // orders the rescaled output before the product that the arrival lets go
       __syncwarp();
