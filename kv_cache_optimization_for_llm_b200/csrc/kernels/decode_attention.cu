@@ -558,8 +558,9 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
   // larger batches (every block then walks several classes and pays its fixed cost once)
   int S = cluster;
   while (S > 1 && (long long)R * nkv * S > 4 * kvb_sm_count()) S >>= 1;
-  // two stages while every block of the grid fits on the GPU at once
-  const bool deep = (long long)R * nkv * S <= 2 * kvb_sm_count();
+  // two stages while every block of the grid fits on the GPU at once (two stages of head size 128
+  // are 128 KB: one block per SM)
+  const bool deep = (long long)R * nkv * S <= (d == 64 ? 2 : 1) * kvb_sm_count();
 #define KVB_DM_ARGS qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, q_start, \
                     ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, S, status, trace, stream
 #define KVB_DM16(GP)                                                        \

@@ -634,7 +634,12 @@ KVB_EXPORT int kvb_gemm_skinny_plan(int M, int N, int K, int* splits, int* n_til
   if (M < 1 || M > 256 || N < 1 || K < 8 || (K & 7)) return KVB_ERR_BAD_SIZE;
   const int tiles = (N + TILE_N - 1) / TILE_N;
   const int k_tiles = (K + TILE_K - 1) / TILE_K;
-  int s = (2 * kvb_sm_count()) / tiles;                 // two blocks per SM in flight
+  // Two blocks fit an SM.  A grid that fills both places of every SM leaves none for the blocks of the
+  // kernel behind it, which then start (and request their first weights) only when this grid ends;
+  // measured at three model sizes, one and a half blocks per SM is the better target, except where it
+  // would leave K unsplit although two blocks per tile still fit (then: two).
+  int s = (3 * kvb_sm_count() / 2) / tiles;
+  if (s < 2 && 2 * tiles <= 2 * kvb_sm_count()) s = 2;
   if (s > k_tiles / 2) s = k_tiles / 2;      // at least two k tiles per block
   if (s > 8) s = 8;                          // the largest portable cluster (clusters of 16 were measured: they
                                              // do not all fit at once, and the second wave costs more than they gain)
