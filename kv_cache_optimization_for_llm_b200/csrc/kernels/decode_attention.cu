@@ -557,7 +557,8 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
   // blocks per cluster: as many as there are classes while the grid stays small, fewer for
   // larger batches (every block then walks several classes and pays its fixed cost once)
   int S = cluster;
-  while (S > 1 && (long long)R * nkv * S > 4 * kvb_sm_count()) S >>= 1;
+  // (an SM holds four blocks of head size 64 with one stage, two of head size 128: no second wave)
+  while (S > 1 && (long long)R * nkv * S > (d == 64 ? 4 : 2) * kvb_sm_count()) S >>= 1;
   // two stages while every block of the grid fits on the GPU at once (two stages of head size 128
   // are 128 KB: one block per SM)
   const bool deep = (long long)R * nkv * S <= (d == 64 ? 2 : 1) * kvb_sm_count();
