@@ -34,6 +34,7 @@ class _Region:
         self._add_block()
         self.block, self.offset = 0, self.pads[0]
         self.grown = 0
+        self.views = {}                 # (block, offset), dtype, shape -> the tensor handed out there
 
     def _add_block(self) -> None:
         buf = torch.empty(self.capacity + _ALIGN, dtype=torch.uint8, device=self.device)
@@ -43,23 +44,45 @@ class _Region:
     def reset(self) -> None:
         self.block, self.offset = 0, self.pads[0]
 
-    def take(self, nbytes: int):
-        """A run of ``nbytes`` bytes on a 256-byte boundary, or None if the request is larger than
-        the region was built for."""
+    def place(self, nbytes: int):
+        """Where a run of ``nbytes`` bytes on a 256-byte boundary lies, as (block, offset), or None
+        if the request is larger than the region was built for."""
         need = -(-nbytes // _ALIGN) * _ALIGN
         if need > self.capacity:
             return None
         while True:
-            buf = self.blocks[self.block]
             if self.offset + need <= self.pads[self.block] + self.capacity:
-                out = buf[self.offset:self.offset + nbytes]
+                at = (self.block, self.offset)
                 self.offset += need
-                return out
+                return at
             self.block += 1
             if self.block == len(self.blocks):
                 self._add_block()
                 self.grown += 1
             self.offset = self.pads[self.block]
+
+    def take(self, nbytes: int):
+        """The run itself, as bytes."""
+        at = self.place(nbytes)
+        if at is None:
+            return None
+        return self.blocks[at[0]][at[1]:at[1] + nbytes]
+
+    def tensor(self, shape: tuple, dtype: torch.dtype, nbytes: int):
+        """A tensor of this shape and type over the next run of bytes.  Steps of one shape ask for the
+        same tensors at the same places again and again: the views are kept (making one costs three
+        calls into torch, which a step without a captured graph pays a hundred times over)."""
+        at = self.place(nbytes)
+        if at is None:
+            return None
+        key = (at, dtype, shape)
+        t = self.views.get(key)
+        if t is None:
+            if len(self.views) > 8192:
+                self.views.clear()
+            t = self.blocks[at[0]][at[1]:at[1] + nbytes].view(dtype).view(shape)
+            self.views[key] = t
+        return t
 
 
 class StepArena:
@@ -86,17 +109,18 @@ class StepArena:
         self.current = self.step
 
     def new(self, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(int(x) for x in shape)
         n = 1
-        for s in shape:
-            n *= int(s)
+        for x in shape:
+            n *= x
         nbytes = n * _ESIZE[dtype]
         if nbytes == 0:
-            return torch.empty(tuple(shape), dtype=dtype, device=self.device)
-        raw = self.current.take(nbytes)
-        if raw is None:
+            return torch.empty(shape, dtype=dtype, device=self.device)
+        t = self.current.tensor(shape, dtype, nbytes)
+        if t is None:
             self.bypassed += 1
-            return torch.empty(tuple(shape), dtype=dtype, device=self.device)
-        return raw.view(dtype).view(tuple(shape))
+            return torch.empty(shape, dtype=dtype, device=self.device)
+        return t
 
     def bytes_held(self) -> int:
         return sum(b.numel() for r in (self.step, *self.halves) for b in r.blocks)

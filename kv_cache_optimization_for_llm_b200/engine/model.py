@@ -54,10 +54,11 @@ class DecoderModel:
         """``arena``: the step's memory (engine/arena.py).  With it, every tensor that the parts
         produce through ``ops`` lies in it: the residual and the logits for the length of the
         step, a layer's tensors until the layer after the next begins."""
-        if arena is None:
-            return self._forward(batch, cache, None)
         from .. import ops
-        with ops.use_arena(arena):
+        if arena is None:
+            with ops.use_current_stream():
+                return self._forward(batch, cache, None)
+        with ops.use_current_stream(), ops.use_arena(arena):
             return self._forward(batch, cache, arena)
 
     def _forward(self, batch, cache, arena) -> torch.Tensor:

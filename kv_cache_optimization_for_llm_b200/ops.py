@@ -75,8 +75,34 @@ def _check(rc: int, what: str) -> None:
     launch_count += 1
 
 
+_step_stream: Optional[c_void_p] = None     # the stream of the running forward pass, looked up once
+_step_capturing: Optional[bool] = None
+
+
+class use_current_stream:
+    """While active, the operators launch on the stream that was current at entry (and know whether
+    it is being captured) without asking torch at every launch: the lookup costs 15 us, a step
+    of a small model has a hundred launches."""
+
+    def __enter__(self):
+        global _step_stream, _step_capturing
+        self.before = (_step_stream, _step_capturing)
+        _step_stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+        _step_capturing = torch.cuda.is_current_stream_capturing()
+        return self
+
+    def __exit__(self, *exc):
+        global _step_stream, _step_capturing
+        _step_stream, _step_capturing = self.before
+        return False
+
+
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    return _step_stream if _step_stream is not None else c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _capturing() -> bool:
+    return _step_capturing if _step_capturing is not None else torch.cuda.is_current_stream_capturing()
 
 
 def _p(t: Optional[torch.Tensor]) -> c_void_p:
@@ -295,7 +321,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
     if isinstance(x, PendingNorm):
         if into is None and fused_norm_rows(x.xb.shape[0], x.dtype) and w.dtype == torch.bfloat16:
             return gemm_skinny_fused(x.xb, w, kernel_status(w.device), row_scale=x,
-                                     x_is_static=torch.cuda.is_current_stream_capturing())
+                                     x_is_static=_capturing())
         if (into is None and wide_fused_rows(x.xb.shape[0], x.dtype) and _wide_ok(x.xb, w, 8)
                 and (out_dtype is None or out_dtype == x.dtype)):
             return gemm_wide(x.xb, w, kernel_status(w.device), row_scale=x)
@@ -307,7 +333,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
     if (into is not None and fused_norm_rows(M, x.dtype) and _skinny_ok(x, FUSED_EPILOGUE_MAX_ROWS) and N % 8 == 0
             and into.dtype == torch.float32 and into.shape == (M, N) and into.is_contiguous()):
         return gemm_skinny_fused(x, w, kernel_status(w.device), into=into,
-                                 x_is_static=torch.cuda.is_current_stream_capturing())
+                                 x_is_static=_capturing())
     if (into is not None and wide_fused_rows(M, x.dtype) and _wide_ok(x, w, 8) and into.dtype == torch.float32
             and into.shape == (M, N) and into.is_contiguous() and N % 4 == 0):
         return gemm_wide(x, w, kernel_status(w.device), into=into)
@@ -321,7 +347,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, into: Op
         return out
     if M <= SKINNY_MAX_ROWS and K % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
         return gemm_skinny(x, w, out_dtype or x.dtype, kernel_status(x.device),
-                           x_is_static=torch.cuda.is_current_stream_capturing())
+                           x_is_static=_capturing())
     if WIDE == "all" and _wide_ok(x, w, 8) and (out_dtype is None or out_dtype == x.dtype):
         return gemm_wide(x, w, kernel_status(x.device))
     choices["library_product"] += 1
@@ -386,7 +412,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, block: int) -> torch.T
     I = gate_up.shape[0] // 2
     if isinstance(x, PendingNorm):
         if fused_norm_rows(x.xb.shape[0], x.dtype) and gate_up.dtype == torch.bfloat16:
-            st, static = kernel_status(gate_up.device), torch.cuda.is_current_stream_capturing()
+            st, static = kernel_status(gate_up.device), _capturing()
             if block == 64 and gate_up.shape[0] % 128 == 0:
                 return gemm_skinny_fused(x.xb, gate_up, st, row_scale=x, epilogue="swiglu", x_is_static=static)
             return silu_mul(gemm_skinny_fused(x.xb, gate_up, st, row_scale=x, x_is_static=static),
@@ -397,7 +423,7 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, block: int) -> torch.T
     if block == 64 and _skinny_ok(x, min(SKINNY_MAX_ROWS, FUSED_EPILOGUE_MAX_ROWS)) \
             and gate_up.shape[0] % 128 == 0:
         return gemm_skinny(x, gate_up, x.dtype, kernel_status(x.device),
-                           x_is_static=torch.cuda.is_current_stream_capturing(), epilogue="swiglu")
+                           x_is_static=_capturing(), epilogue="swiglu")
     if WIDE != "off" and block == 64 and _wide_ok(x, gate_up, 128):
         return gemm_wide(x, gate_up, kernel_status(x.device), epilogue="swiglu")
     return silu_mul(linear(x, gate_up), block=block if block != I else None)
