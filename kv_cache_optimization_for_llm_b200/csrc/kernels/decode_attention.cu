@@ -44,6 +44,13 @@ __device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gm
   const int n = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(n) : "memory");
 }
+// 2^x by the special-function unit alone (exp2f wraps the same instruction in a rescaling for
+// results below 2^-126, which a probability does not need).  ex2(-inf) = 0.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 // Waits until at most N of this thread's committed groups are still under way.
 template <int N> __device__ __forceinline__ void cp_async_wait_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
@@ -91,7 +98,7 @@ __host__ __device__ __forceinline__ int classes_at(int pos) { return pos < 2048 
 // projection has finished), 1 when more blocks per SM matter more (large batches).  The
 // order of the sums is the same for both.
 template <int D, int GP, int kClasses, int kStages>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, D == 64 ? 4 : 2)   // four blocks per SM at head size 64: 128 registers
 decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int write_kv,
                             const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
@@ -348,14 +355,20 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         }
       }
       float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+      if (have != 0xffffffffu) {        // a slice at the context's end or at the window's edge
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = n * 8 + ((lane & 3) << 1) + (e & 1);
+            if (!((have >> key) & 1u)) s[n][e] = -CUDART_INF_F;
+          }
+        }
+      }
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = n * 8 + ((lane & 3) << 1) + (e & 1);
-          if (!((have >> key) & 1u)) s[n][e] = -CUDART_INF_F;
-          mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
-        }
+        for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
       }
       float corr[2], m_use[2];
 #pragma unroll
@@ -364,17 +377,19 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
         const float m_new = fmaxf(m_run[rr], mx[rr]);       // finite: the slice holds at least one key
         m_use[rr] = m_new;
-        corr[rr] = m_run[rr] == -CUDART_INF_F ? 0.f : exp2f(m_run[rr] - m_new);
+        corr[rr] = m_run[rr] == -CUDART_INF_F ? 0.f : ex2(m_run[rr] - m_new);
         m_run[rr] = m_new;
         l_run[rr] *= corr[rr];
       }
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {    // a maximum has grown somewhere in the warp
 #pragma unroll
-      for (int n = 0; n < DT; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+        for (int n = 0; n < DT; ++n) { o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1]; }
+      }
       unsigned pf[2][4];
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
-        const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
-        const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
+        const float p0 = ex2(s[n][0] - m_use[0]), p1 = ex2(s[n][1] - m_use[0]);
+        const float p2 = ex2(s[n][2] - m_use[1]), p3 = ex2(s[n][3] - m_use[1]);
         l_run[0] += p0 + p1;     // each lane keeps the sum of its own columns; the four lanes of a row
         l_run[1] += p2 + p3;     // are added up after the walk
         pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);

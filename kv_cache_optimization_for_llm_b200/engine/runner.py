@@ -10,6 +10,7 @@ wanted places.  Upstream has two separate passes instead, whole packed prompts
 
 from __future__ import annotations
 
+import gc
 from pathlib import Path
 from typing import List, Optional, Sequence
 
@@ -174,8 +175,18 @@ class ModelRunner:
             torch.cuda.current_stream().wait_stream(side)
             before = ops.launch_count
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                out = self.model.forward(batch, self.cache, self.arena)
+            # The collector must not run inside the capture: if it finds an engine that is gone, it
+            # destroys that engine's graphs, which CUDA refuses while a stream is capturing, and the
+            # refusal ends this capture too.  What is garbage now is collected first.
+            gc.collect()
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    out = self.model.forward(batch, self.cache, self.arena)
+            finally:
+                if collecting:
+                    gc.enable()
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
             got = (graph, out, ops.launch_count - before, rows)

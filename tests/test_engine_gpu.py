@@ -320,3 +320,39 @@ def test_graphs_captured_when_the_engine_is_built():
     assert len(r._graphs) == 4                      # nothing was captured on the way
     for p, g in zip(prompts, got):
         assert g == P.generate(cfg, w, p, 8)
+
+
+def test_capture_is_safe_from_the_garbage_collector():
+    """An engine that is gone but still waits for the collector (it sits in a reference cycle) holds
+    captured graphs; destroying them is refused while another stream is capturing, and the refusal
+    would end that capture.  The runner keeps the collector out of its captures: here the first
+    engine becomes garbage, and enough containers are made for the collector to run, in the middle
+    of the second engine's first captured forward pass."""
+    import gc
+    import torch
+    from kv_cache_optimization_for_llm_b200 import LLM, SamplingParams
+    mdir = model_dir("tiny_a", "float32")
+    cfg, w = P.read_model_dir(mdir)
+    prompts = _prompts(cfg, [5, 9], 43)
+    kw = dict(dtype="float32", page_size=4, num_pages=64, max_num_seqs=4, max_num_batched_tokens=32)
+    first = LLM(mdir, capture_graphs_at_start=True, **kw)
+    assert len(first.engine.runner._graphs) > 0
+    first.cycle = first                        # only the collector can free it
+    held = [first]
+    del first
+    second = LLM(mdir, **kw)                   # captures at first use, during generation
+    model = second.engine.runner.model
+    inner, seen = model.forward, []
+
+    def forward(batch, cache, arena=None):
+        if torch.cuda.is_current_stream_capturing() and held:
+            held.clear()
+            seen.append(gc.isenabled())
+            _ = [[] for _ in range(5000)]      # the collector's threshold is passed many times over
+        return inner(batch, cache, arena)
+    model.forward = forward
+    got = second.generate(prompts, SamplingParams(max_tokens=6, ignore_eos=True))
+    assert seen == [False] and len(second.engine.runner._graphs) > 0
+    assert gc.isenabled()
+    for p_, g in zip(prompts, got):
+        assert g == P.generate(cfg, w, p_, 6)
