@@ -761,8 +761,9 @@ int launch(const void* q, int q_row_stride, const void* k_pages, const void* v_p
 //                 edge only, probabilities in bfloat16 to one of two swizzled buffers, the
 //                 output rescaled in tensor memory only when the running maximum has grown by
 //                 2^8.
-// Tensor memory: scores in columns 0..63 and 64..127 (double-buffered), the output in 128..191;
-// 256 columns per block, two blocks per SM.  The roles meet on mbarriers only; every wait is
+// Tensor memory: scores in columns 0..63 and 64..127 (double-buffered), the output from 128 on;
+// 256 columns per block, two blocks per SM at both head sizes (at 128 with two key stages, one
+// value stage and one buffer of probabilities: 96 KB of shared memory).  The roles meet on mbarriers only; every wait is
 // bounded and gives up early when another role has given up.  Needs pages of at least 8 rows
 // (a TMA box of 8 x 64 bfloat16 is the smallest that the 128-byte swizzle repeats over) and
 // 16-byte aligned page pools.
@@ -811,7 +812,7 @@ __device__ __forceinline__ bool wait_or_abort(void* bar, unsigned parity, volati
 // of them.  The scores take DH / 16 products of 16 along the head, the output DH / 64 times 4
 // products of 64 columns each; tensor memory holds the output in columns 128 .. 128 + DH.
 template <int DH>
-__global__ void __launch_bounds__(kWsThreads, DH == 64 ? 2 : 1)
+__global__ void __launch_bounds__(kWsThreads, 2)
 paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                 int box_rows, const __nv_bfloat16* __restrict__ q_base, int q_row_stride,
                                 const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
@@ -823,11 +824,16 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
   constexpr int kSub = DH / 64;                        // sub-tiles of 64 columns in Q, K and V
   constexpr int kQSub = BM * 128, kKVSub = BNK * 128;  // bytes of one sub-tile: rows x 128 bytes
   constexpr int kQB = kSub * kQSub, kKVB = kSub * kKVSub;
+  // Stages of keys and of values and buffers of probabilities: 3, 3 and 2 at head size 64; 2, 1 and 1
+  // at head size 128, where a block then takes 96 KB and two of them fit an SM (eight softmax warps
+  // instead of four).  One value stage is enough: V(i) is requested when P V(i - 1) is over, at the
+  // start of the softmax of tile i, and is needed at its end.
+  constexpr int kKSt = DH == 64 ? 3 : 2, kVSt = DH == 64 ? 3 : 1, kPB = DH == 64 ? 2 : 1;
   unsigned char* q_s = base;                           // [DH/64][128 rows][64]
-  unsigned char* k_s = q_s + kQB;                      // [3][DH/64][64 keys][64]
-  unsigned char* v_s = k_s + kStages * kKVB;           // [3][DH/64][64 keys][64]
-  unsigned char* p_s = v_s + kStages * kKVB;           // [2][128 rows][64 keys]
-  WsBars* bars = reinterpret_cast<WsBars*>(p_s + 2 * kPBytes);
+  unsigned char* k_s = q_s + kQB;                      // [kKSt][DH/64][64 keys][64]
+  unsigned char* v_s = k_s + kKSt * kKVB;              // [kVSt][DH/64][64 keys][64]
+  unsigned char* p_s = v_s + kVSt * kKVB;              // [kPB][128 rows][64 keys]
+  WsBars* bars = reinterpret_cast<WsBars*>(p_s + kPB * kPBytes);
   unsigned* tmem_holder = reinterpret_cast<unsigned*>(bars + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -914,22 +920,22 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       if (kt < n_tiles) {
         const int chunk = (kt * n_box) >> 5;
         if (chunk != chunk_k) { pg_k = pages_of(chunk); chunk_k = chunk; }
-        if (lane == 0 && kt >= kStages &&
-            !wait_or_abort(&bars->k_empty[kt % kStages], (unsigned)(kt / kStages - 1) & 1u, abort_flag))
+        if (lane == 0 && kt >= kKSt &&
+            !wait_or_abort(&bars->k_empty[kt % kKSt], (unsigned)(kt / kKSt - 1) & 1u, abort_flag))
           failed = true;
         failed = __shfl_sync(0xffffffffu, (int)failed, 0) != 0;
         if (failed) break;
-        request(kt, pg_k, k_s + (kt % kStages) * kKVB, &map_k, &bars->k_full[kt % kStages]);
+        request(kt, pg_k, k_s + (kt % kKSt) * kKVB, &map_k, &bars->k_full[kt % kKSt]);
       }
       if (vt >= 0) {
         const int chunk = (vt * n_box) >> 5;
         if (chunk != chunk_v) { pg_v = pages_of(chunk); chunk_v = chunk; }
-        if (lane == 0 && vt >= kStages &&
-            !wait_or_abort(&bars->v_empty[vt % kStages], (unsigned)(vt / kStages - 1) & 1u, abort_flag))
+        if (lane == 0 && vt >= kVSt &&
+            !wait_or_abort(&bars->v_empty[vt % kVSt], (unsigned)(vt / kVSt - 1) & 1u, abort_flag))
           failed = true;
         failed = __shfl_sync(0xffffffffu, (int)failed, 0) != 0;
         if (failed) break;
-        request(vt, pg_v, v_s + (vt % kStages) * kKVB, &map_v, &bars->v_full[vt % kStages]);
+        request(vt, pg_v, v_s + (vt % kVSt) * kKVB, &map_v, &bars->v_full[vt % kVSt]);
       }
     }
   } else if (warp <= 2) {
@@ -943,33 +949,33 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       if (!wait_or_abort(&bars->q_full, 0, abort_flag)) failed = true;
       for (int i = 0; i < n_tiles && !failed; ++i) {
         // S(i) = Q K(i)^T into score buffer i mod 2, which the softmax has read (tile i - 2)
-        if (!wait_or_abort(&bars->k_full[i % kStages], (unsigned)(i / kStages) & 1u, abort_flag)) { failed = true; break; }
+        if (!wait_or_abort(&bars->k_full[i % kKSt], (unsigned)(i / kKSt) & 1u, abort_flag)) { failed = true; break; }
         if (i >= 2 && !wait_or_abort(&bars->s_free[i & 1], (unsigned)((i - 2) >> 1) & 1u, abort_flag)) { failed = true; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {   // 16 of the head per step: sub-tile kk / 4, 32 bytes further along its rows
           const unsigned long long qd = smem_desc_sw128(smem_u32(q_s + (kk >> 2) * kQSub));
-          const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i % kStages) * kKVB + (kk >> 2) * kKVSub));
+          const unsigned long long kd = smem_desc_sw128(smem_u32(k_s + (i % kKSt) * kKVB + (kk >> 2) * kKVSub));
           umma_bf16(tmem + 64 * (i & 1), qd + 2 * (kk & 3), kd + 2 * (kk & 3), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars->k_empty[i % kStages]);
+        umma_commit(&bars->k_empty[i % kKSt]);
         umma_commit(&bars->s_full[i & 1]);
       }
     } else if (warp == 2 && lane == 0) {
       for (int j = 0; j < n_tiles && !failed; ++j) {
         // O += P(j) V(j)
-        if (!wait_or_abort(&bars->p_full[j & 1], (unsigned)(j >> 1) & 1u, abort_flag)) { failed = true; break; }
-        if (!wait_or_abort(&bars->v_full[j % kStages], (unsigned)(j / kStages) & 1u, abort_flag)) { failed = true; break; }
+        if (!wait_or_abort(&bars->p_full[j % kPB], (unsigned)(j / kPB) & 1u, abort_flag)) { failed = true; break; }
+        if (!wait_or_abort(&bars->v_full[j % kVSt], (unsigned)(j / kVSt) & 1u, abort_flag)) { failed = true; break; }
         tc_fence_after();
-        const unsigned long long pd = smem_desc_sw128(smem_u32(p_s + (j & 1) * kPBytes));
+        const unsigned long long pd = smem_desc_sw128(smem_u32(p_s + (j % kPB) * kPBytes));
 #pragma unroll
         for (int sub = 0; sub < kSub; ++sub) {    // output columns 64 sub .. 64 sub + 63 from V's sub-tile
-          const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (j % kStages) * kKVB + sub * kKVSub));
+          const unsigned long long vd = smem_desc_sw128(smem_u32(v_s + (j % kVSt) * kKVB + sub * kKVSub));
 #pragma unroll
           for (int kk = 0; kk < BNK / 16; ++kk)   // 16 keys per step: 32 bytes along a row of P, 16 rows of V
             umma_bf16(tmem + 128 + 64 * sub, pd + 2 * kk, vd + 128 * kk, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&bars->v_empty[j % kStages]);
+        umma_commit(&bars->v_empty[j % kVSt]);
         umma_commit(&bars->o_done[j & 1]);
       }
     }
@@ -1052,9 +1058,9 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
         if (grow) m_ref = m_new;
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;   // a row with no key yet: everything stays zero
-      // the buffer of P(i) was read by P V(i - 2)
-      if (i >= 2 && !wait_or_abort(&bars->o_done[b], (unsigned)((i - 2) >> 1) & 1u, abort_flag)) { failed = true; break; }
-      unsigned char* pb = p_s + b * kPBytes;
+      // the buffer of P(i) was read by P V(i - kPB)
+      if (i >= kPB && !wait_or_abort(&bars->o_done[(i - kPB) & 1], (unsigned)((i - kPB) >> 1) & 1u, abort_flag)) { failed = true; break; }
+      unsigned char* pb = p_s + (i % kPB) * kPBytes;
       float2 l2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};   // the tile's sum in four chains, added up in a fixed order
       const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
 #pragma unroll
@@ -1074,7 +1080,7 @@ paged_flash_attention_ws_kernel(const __grid_constant__ CUtensorMap map_k, const
       fence_async_smem();
       tc_fence_before();     // orders the rescaled output before the product that the arrival lets go
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[b]);
+      if (lane == 0) mbar_arrive(&bars->p_full[i % kPB]);
     }
     if (!failed) {
       if (!wait_or_abort(&bars->o_done[(n_tiles - 1) & 1], (unsigned)((n_tiles - 1) >> 1) & 1u, abort_flag)) failed = true;
@@ -1168,7 +1174,8 @@ int launch_ws(const void* q, int q_row_stride, const void* k_pages, const void* 
   if (e) return e;
   e = pages_map(&mv, v_pages, rows, box_rows, DH);
   if (e) return e;
-  const size_t smem = 1024 + (size_t)BM * DH * 2 + 2 * kStages * (size_t)BNK * DH * 2 + 2 * kPBytes + sizeof(WsBars) + 64;
+  constexpr int kKSt = DH == 64 ? 3 : 2, kVSt = DH == 64 ? 3 : 1, kPB = DH == 64 ? 2 : 1;   // as in the kernel
+  const size_t smem = 1024 + (size_t)BM * DH * 2 + (kKSt + kVSt) * (size_t)BNK * DH * 2 + kPB * kPBytes + sizeof(WsBars) + 64;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(paged_flash_attention_ws_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
