@@ -718,7 +718,11 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
   CUtensorMap mw, mx;
   int e = cached_map(&mw, w, N, K, ldw, TILE_N);
   if (e) return e;
-  e = x_is_static ? cached_map(&mx, x, M, K, ldx, MP) : make_map(&mx, x, M, K, ldx, MP);
+  // The rows' map is kept like the weights': the key names address, shape and box, so an entry can
+  // only ever describe the memory it is looked up for, and a step's tensors lie at the same places
+  // step after step (the flag is kept in the interface; encoding a map costs microseconds per launch).
+  (void)x_is_static;
+  e = cached_map(&mx, x, M, K, ldx, MP);
   if (e) return e;
   static bool attr_set = false;
   if (!attr_set) {
@@ -751,8 +755,8 @@ int gemm_skinny_launch(const void* x, int ldx, const void* w, int ldw, void* out
 
 // C[M,N] = X[M,K] . W[N,K]^T, bfloat16 operands (ldx, ldw in elements, multiples of 8),
 // C bfloat16 (out_f32 = 0) or float32, dense [M,N].  x_is_static: the activation's
-// address is stable (a captured graph), so its tensor map may be cached as the
-// weights' is.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
+// address is stable (a captured graph); no longer needed, since the rows' tensor map is
+// kept by address and shape like the weights'.  trace: nullptr, or [blocks, 8] uint64 for the phase stamps of every
 // block (profiling only).
 // epilogue (see EPI_*): 0 store; 1 SwiGLU on row-interleaved weights, out is bfloat16
 // [M, N/2], N a multiple of 128, M <= 64.
