@@ -54,3 +54,23 @@ def test_a_region_that_is_too_small_grows_once_and_keeps_the_block():
     assert a.bypassed == 1 and big.numel() == 1000 and a.bytes_held() == held
     # nothing at all is a tensor too
     assert a.new((0, 5), torch.float32).shape == (0, 5)
+
+
+def test_a_step_of_the_same_shape_gets_the_same_tensor_objects():
+    """The arena keeps the tensors it has handed out, by place, type and shape: asking again costs a
+    dictionary lookup, and another shape or type at the same place gets a tensor of its own."""
+    a = StepArena("cpu", step_bytes=4096, layer_bytes=4096)
+
+    def step(rows, dtype=torch.bfloat16):
+        a.begin_step()
+        resid = a.new((rows, 16), torch.float32)
+        a.begin_layer()
+        return resid, a.new((rows, 48), dtype), a.new([rows, 16], dtype)
+    first = step(10)
+    again = step(10)
+    assert all(x is y for x, y in zip(first, again))
+    other = step(6)
+    assert other[0] is not first[0] and other[0].shape == (6, 16) and other[0].data_ptr() == first[0].data_ptr()
+    typed = step(10, torch.float32)
+    assert typed[1] is not first[1] and typed[1].dtype == torch.float32 and typed[1].data_ptr() == first[1].data_ptr()
+    assert all(x is y for x, y in zip(step(10), first))     # and the first shape's tensors are still there
