@@ -48,6 +48,8 @@ class StepBatch:
     sampled: Optional[torch.Tensor] = None    # [n] int32 on the device: what ids below zero refer to
     tiles: dict = field(default_factory=dict)  # tokens per tile -> [n, 4] int32 query tiles (request row, first
                                                # token row, tokens, 0) for the heights the mixers asked for
+    num_single: int = 0          # in a step that mixes single tokens with runs: the single tokens' requests come
+                                 # first (rows 0 .. num_single-1 of the requests, of the tokens and of every list of tiles)
 
 
 # Decode launches and captured graphs come in classes by the step's longest context (up to
@@ -162,9 +164,17 @@ class BatchBuilder:
         rstart = h[at["req_start"]:at["req_start"] + R]
         ctx = h[at["ctx_len"]:at["ctx_len"] + R]
         slots = h[at["slots"]:at["slots"] + R]
-        rows: List[int] = []
+        # A step that mixes single tokens (decoding requests) with runs of tokens (prompt portions)
+        # is laid out with the single tokens first, so that a mixer can hand the first rows to the
+        # kernel it has for single tokens and the rest to the one for runs.  The wanted logits keep
+        # the order of the entries as the caller gave them.
+        singles = [i for i, e in enumerate(entries) if len(e.tokens) == 1]
+        mixed = 0 < len(singles) < R
+        order = singles + [i for i, e in enumerate(entries) if len(e.tokens) != 1] if mixed else list(range(R))
+        first_row = [0] * R              # of entry i, as given: the row of its first token
         t = 0
-        for r, e in enumerate(entries):
+        for r, i in enumerate(order):
+            e = entries[i]
             n = len(e.tokens)
             if n == 0:
                 raise ValueError(f"request {e.request_id} brings no token to this step")
@@ -174,13 +184,16 @@ class BatchBuilder:
             qs[r] = t
             rstart[r] = e.start
             ctx[r] = e.start + n
-            slots[r] = cache.slot_of(e.request_id) if r < n_real else scratch_slot
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"request {e.request_id}: wanted place {w} is outside its {n} tokens")
-                rows.append(t + w)
+            slots[r] = cache.slot_of(e.request_id) if i < n_real else scratch_slot
+            first_row[i] = t
             t += n
         qs[R] = T
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise ValueError(f"request {e.request_id}: wanted place {w} is outside its {len(e.tokens)} tokens")
+                rows.append(first_row[i] + w)
         lowest = 0 if sampled is None else -int(sampled.numel())
         if vocab_size is not None and (tok.min() < lowest or tok.max() >= vocab_size):
             raise ValueError(f"a token id is outside the vocabulary of {vocab_size}")
@@ -193,7 +206,10 @@ class BatchBuilder:
             bt = h[off:off + R * cols].reshape(R, cols)
             bt.fill(-1)
             bt[n_real:, :max(1, min(cols, -(-pad_ctx // (self.page_size or pad_ctx))))] = scratch_page
-            for r, e in enumerate(entries[:n_real]):
+            for r, i in enumerate(order):
+                if i >= n_real:          # dummy rows (they follow the real ones: only steps of single tokens are padded)
+                    continue
+                e = entries[i]
                 table = cache.block_table(e.request_id, g)
                 if len(table) > self.max_pages[g]:
                     raise ValueError(f"request {e.request_id} holds {len(table)} pages in group {g}, "
@@ -206,7 +222,8 @@ class BatchBuilder:
         if not decode_only:
             for nt in self.tile_heights:
                 n_tiles = 0
-                for r, e in enumerate(entries):
+                for r, i in enumerate(order):
+                    e = entries[i]
                     a, b = int(qs[r]), int(qs[r]) + len(e.tokens)
                     k = -(-(b - a) // nt)
                     tile = h[off + 4 * n_tiles:off + 4 * (n_tiles + k)].reshape(k, 4)
@@ -240,5 +257,6 @@ class BatchBuilder:
             status=self.status,
             host={"q_start": qs.copy(), "ctx_len": ctx.copy(), "req_start": rstart.copy()},
             sampled=sampled,
+            num_single=len(singles) if mixed else 0,
         )
         return batch

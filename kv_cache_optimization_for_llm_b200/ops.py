@@ -530,15 +530,19 @@ def flash_tiles(batch, group: int, wide: bool) -> torch.Tensor:
 
 
 def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window,
-                    wide: Optional[bool] = None) -> torch.Tensor:
+                    wide: Optional[bool] = None, skip_single: bool = False,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core attention for steps with runs of query tokens (bfloat16).  ``wide``:
     False: 64 query rows per block (mma.sync); True: 128 rows (mma.sync); 2: 128 rows on
     tcgen05 with the scores in tensor memory (head size 64); 3: the same with roles (a TMA
     loader warp, two issuing warps, four softmax warps; head size 64 or 128, pages of at least
     8 rows); None:
-    chosen from the step's size, the head size and the page size."""
+    chosen from the step's size, the head size and the page size.  ``skip_single``: the step's
+    leading single tokens (``batch.num_single``) are somebody else's: their tiles are left out.
+    ``out``: where the rows go; made here if not given."""
     _need_cuda(qkv, k_pages)
-    T = qkv.shape[0]
+    skip = int(batch.num_single) if skip_single else 0
+    T = qkv.shape[0] - skip
     # 128-row tiles when there are enough of them to keep every SM busy, else 64-row tiles
     nt128 = flash_tokens_per_tile(nq // nkv, True)
     if wide is None:
@@ -551,8 +555,9 @@ def flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale
                 wide = 3
             elif d == 64:
                 wide = 2
-    tiles = flash_tiles(batch, nq // nkv, wide)
-    out = new((T, nq * d), qkv.dtype, qkv.device)
+    tiles = flash_tiles(batch, nq // nkv, wide)[skip:]      # a single token is one tile, and they come first
+    if out is None:
+        out = new((qkv.shape[0], nq * d), qkv.dtype, qkv.device)
     rc = lib("flash_attention").kvb_paged_flash_attention(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), _p(block_table), c_int(block_table.shape[1]),
         c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(batch.positions), _p(tiles), c_int(tiles.shape[0]),
@@ -615,18 +620,20 @@ def decode_launch_context(batch) -> int:
 
 def decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table, q_start, ctx_len, cos, sin, rot,
                          nq, nkv, d, scale, window, status, max_ctx: int = 0,
-                         trace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         trace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The attention of a bfloat16 decode step in one launch on tensor cores: rotary
     encoding of query and new key, cache write, attention over 128-key tiles spread over
     a cluster of blocks, merge through distributed shared memory.  No scratch.
     A token's tiles fall into 4 classes below position 2048, 8 below 8192, 16 beyond (head
     size 64), whatever the batch; up to that many blocks share a (request, kv head).
     ``max_ctx``: the longest context of the step if the host knows it (the launch is sized
-    for it), 0 otherwise."""
+    for it), 0 otherwise.  ``out``: where the rows go ([tokens, nq d], the rows of the requests'
+    tokens are written); made here if not given."""
     _need_cuda(qkv, k_pages)
     assert qkv.dtype == torch.bfloat16
     R = ctx_len.numel()
-    out = new((qkv.shape[0], nq * d), qkv.dtype, qkv.device)
+    if out is None:
+        out = new((qkv.shape[0], nq * d), qkv.dtype, qkv.device)
     rc = lib("decode_attention").kvb_decode_attention_mma(
         _p(qkv), c_int(qkv.stride(0)), _p(k_pages), _p(v_pages), c_int(1 if write_kv else 0), _p(block_table),
         c_int(block_table.shape[1]), c_int(k_pages.shape[2]), c_int(k_pages.shape[0]), _p(q_start), _p(ctx_len),
@@ -647,7 +654,8 @@ def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv,
       positions in one fixed order whatever the shape of the step;
     * bfloat16, single tokens only: one fused launch, on tensor cores where the sizes allow
       (head size 64/128), else the FMA form (head size 32);
-    * bfloat16, runs of tokens: rotary/write kernel, then the tensor-core kernel;
+    * bfloat16, runs of tokens: rotary/write kernel, then the tensor-core kernel; single tokens
+      beside them (they are the step's first rows) go to the fused launch of decode steps;
     * sizes neither takes: rotary/write kernel, then the general kernel."""
     group, page_size = nq // nkv, k_pages.shape[2]
     if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_mma_supported(d, group, page_size):
@@ -657,6 +665,20 @@ def attention_step(qkv, k_pages, v_pages, write_kv, block_table, batch, nq, nkv,
     if qkv.dtype == torch.bfloat16 and batch.decode_only and decode_attention_supported(d, group):
         return decode_attention_fused(qkv, k_pages, v_pages, write_kv, block_table, batch.q_start, batch.ctx_len,
                                       cos, sin, rot, nq, nkv, d, scale, window, max_positions, batch.status)
+    ns = int(getattr(batch, "num_single", 0))
+    if (qkv.dtype == torch.bfloat16 and ns > 0 and flash_attention_supported(d, group, page_size)
+            and decode_attention_mma_supported(d, group, page_size)):
+        # Single tokens beside runs: the single tokens (the step's first rows) go to the kernel of
+        # decode steps, which rotates, writes and attends in one launch, the runs to the two kernels
+        # for runs.  As a tile of the kernel for runs a single token would fill 4 of 128 rows.
+        out = new((qkv.shape[0], nq * d), qkv.dtype, qkv.device)
+        decode_attention_mma(qkv, k_pages, v_pages, write_kv, block_table[:ns], batch.q_start[:ns + 1], batch.ctx_len[:ns],
+                             cos, sin, rot, nq, nkv, d, scale, window, batch.status,
+                             max_ctx=decode_launch_context(batch), out=out)
+        rope_kv_write(qkv[ns:], batch.positions[ns:], batch.token_req[ns:], cos, sin, k_pages if write_kv else None,
+                      v_pages if write_kv else None, block_table, page_size, nq, nkv, d, rot, batch.status)
+        return flash_attention(qkv, k_pages, v_pages, block_table, batch, nq, nkv, d, scale, window,
+                               skip_single=True, out=out)
     rope_kv_write(qkv, batch.positions, batch.token_req, cos, sin, k_pages if write_kv else None,
                   v_pages if write_kv else None, block_table, page_size, nq, nkv, d, rot, batch.status)
     if qkv.dtype == torch.bfloat16 and not batch.decode_only and flash_attention_supported(d, group, page_size):

@@ -35,19 +35,28 @@ def test_mixed_step_arrays_tables_and_tiles():
     batch = b.build([StepEntry(7, [10, 11, 12], 40, [2]), StepEntry(3, [99], 0, [0]),
                      StepEntry(4, list(range(50)), 20, [0, 49])], m, vocab_size=100)
     assert batch.num_tokens == 54 and batch.num_reqs == 3 and not batch.decode_only
-    assert batch.token_ids.tolist() == [10, 11, 12, 99] + list(range(50))
-    assert batch.positions.tolist() == [40, 41, 42, 0] + list(range(20, 70))
-    assert batch.token_req.tolist() == [0] * 3 + [1] + [2] * 50
-    assert batch.q_start.tolist() == [0, 3, 4, 54] and batch.ctx_len.tolist() == [43, 1, 70]
-    assert batch.req_start.tolist() == [40, 0, 20] and batch.slots.tolist() == [2, 0, 1]
-    assert batch.logit_rows.tolist() == [2, 3, 4, 53] and batch.num_logits == 4
+    # the request that brings a single token comes first (a mixer hands it to its kernel for single
+    # tokens), the runs follow in the order given
+    assert batch.num_single == 1
+    assert batch.token_ids.tolist() == [99, 10, 11, 12] + list(range(50))
+    assert batch.positions.tolist() == [0, 40, 41, 42] + list(range(20, 70))
+    assert batch.token_req.tolist() == [0] + [1] * 3 + [2] * 50
+    assert batch.q_start.tolist() == [0, 1, 4, 54] and batch.ctx_len.tolist() == [1, 43, 70]
+    assert batch.req_start.tolist() == [0, 40, 20] and batch.slots.tolist() == [0, 2, 1]
+    # the wanted rows keep the caller's order: request 7's third token, request 3's token, request 4's first and last
+    assert batch.logit_rows.tolist() == [3, 0, 4, 53] and batch.num_logits == 4
     assert batch.max_ctx_len == 70 and batch.max_q_len == 50
     bt = batch.block_tables[0]
     assert tuple(bt.shape) == (3, 128)          # the class of contexts up to 2048 tokens, not all 256 columns
-    assert bt[0, :4].tolist() == [5, 9, 2, -1] and bt[1, :2].tolist() == [11, -1] and bt[2, :6].tolist() == [8, 1, 6, 0, 13, -1]
-    # query tiles: consecutive tokens of one request, at most `height` each
-    assert batch.tiles[16].tolist() == [[0, 0, 3, 0], [1, 3, 1, 0], [2, 4, 16, 0], [2, 20, 16, 0], [2, 36, 16, 0], [2, 52, 2, 0]]
-    assert batch.tiles[32].tolist() == [[0, 0, 3, 0], [1, 3, 1, 0], [2, 4, 32, 0], [2, 36, 18, 0]]
+    assert bt[1, :4].tolist() == [5, 9, 2, -1] and bt[0, :2].tolist() == [11, -1] and bt[2, :6].tolist() == [8, 1, 6, 0, 13, -1]
+    # query tiles: consecutive tokens of one request, at most `height` each; the single tokens' tiles first
+    assert batch.tiles[16].tolist() == [[0, 0, 1, 0], [1, 1, 3, 0], [2, 4, 16, 0], [2, 20, 16, 0], [2, 36, 16, 0], [2, 52, 2, 0]]
+    assert batch.tiles[32].tolist() == [[0, 0, 1, 0], [1, 1, 3, 0], [2, 4, 32, 0], [2, 36, 18, 0]]
+    # a step of runs only, or of single tokens only, keeps the order given
+    runs = b.build([StepEntry(7, [10, 11, 12], 40, [2]), StepEntry(4, [1, 2], 20, [])], m, vocab_size=100)
+    assert runs.num_single == 0 and runs.token_ids.tolist() == [10, 11, 12, 1, 2]
+    batch = b.build([StepEntry(7, [10, 11, 12], 40, [2]), StepEntry(3, [99], 0, [0]),
+                     StepEntry(4, list(range(50)), 20, [0, 49])], m, vocab_size=100)
     # everything lies packed in one buffer: the copy is a few hundred integers, not the engine's capacity
     assert b.last_h2d_bytes < 4 * (4 * 56 + 3 * 4 + 4 + 3 * 128 + 4 * 10 + 64)
     assert b.last_h2d_bytes < 4 * b.total // 3
