@@ -226,3 +226,34 @@ def test_many_requests_decode_from_a_graph(model, dtype, n_reqs):
         r.release(base + i)
     print(f"{n_reqs} requests, {dtype}: worst relative error {worst:.3e}")
     assert r.manager.check() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_single_tokens_beside_a_portion_take_the_decode_kernel(model, dtype):
+    """A step that mixes decoding requests with a prompt portion, the entries given in an order that
+    interleaves them: the batch puts the single tokens first, their attention runs in the one-launch
+    kernel of decode steps, the portion's in the kernels for runs, and every logit comes back in the
+    caller's order and agrees with the plain implementation."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    mdir, cfg, w = model
+    rng = np.random.default_rng(23)
+    seqs = {i: rng.integers(0, CFG["vocab_size"], n).tolist() for i, n in ((30, 140), (31, 300), (32, 75), (33, 400))}
+    refs = {i: P.forward(cfg, w, s, rows=[len(s) - 2, len(s) - 1] if i != 33 else [199, 399]) for i, s in seqs.items()}
+    r = _runner(mdir, dtype)
+    # the three decoding requests: all but their last token as one portion each
+    for i in (30, 31, 32):
+        r.step([StepEntry(i, seqs[i][:-1], 0, [len(seqs[i]) - 2])])
+    r.step([StepEntry(33, seqs[33][:200], 0, [199])])
+    ops.choices.clear()
+    got = r.step([StepEntry(30, [seqs[30][-1]], 139, [0]), StepEntry(33, seqs[33][200:], 200, [199]),
+                  StepEntry(31, [seqs[31][-1]], 299, [0]), StepEntry(32, [seqs[32][-1]], 74, [0])]).cpu().numpy()
+    r.check_status()
+    for row, (i, ref_row) in enumerate(((30, 1), (33, 1), (31, 1), (32, 1))):
+        _check(got[row:row + 1], refs[i][ref_row][None, :], dtype, f"request {i} in the mixed step")
+    if dtype == "bfloat16":
+        assert ops.choices["decode_attention_mma"] == LAYERS and ops.choices["flash_attention_0"] + \
+            ops.choices["flash_attention_1"] + ops.choices["flash_attention_2"] + ops.choices["flash_attention_3"] == LAYERS, dict(ops.choices)
+    for i in seqs:
+        r.release(i)
+    assert r.manager.check() == ""
