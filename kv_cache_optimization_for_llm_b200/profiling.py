@@ -17,7 +17,8 @@ microseconds per launch and the bandwidth over the keys and values it has to rea
 Under ``ncu --profile-from-start off`` only the bracketed work is captured.  Fewer
 layers than the full model keep a capture short and its memory small; the kernels and
 their sizes per layer are those of the full model.  The default shape is Llama-3.2-1B
-(the sizes of its config.json); ``--config-json`` takes any other config.json.
+(the sizes of its config.json); ``--shape 3b`` and ``--shape 8b`` are Llama-3.2-3B and
+Llama-3.1-8B, ``--config-json`` takes any other config.json.
 """
 
 from __future__ import annotations
@@ -36,12 +37,23 @@ LLAMA_3_2_1B = {
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
     "max_position_embeddings": 131072, "tie_word_embeddings": True, "hidden_act": "silu",
 }
+_ROPE = {"rope_type": "llama3", "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}
+# The sizes of the config.json files of three Llama models (random weights are made for them).
+SHAPES = {
+    "1b": LLAMA_3_2_1B,
+    "3b": dict(LLAMA_3_2_1B, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, num_key_value_heads=8,
+               head_dim=128, intermediate_size=8192, rope_scaling=dict(_ROPE, factor=32.0)),
+    "8b": dict(LLAMA_3_2_1B, hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+               head_dim=128, intermediate_size=14336, tie_word_embeddings=False, rope_scaling=dict(_ROPE, factor=8.0)),
+}
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=["decode", "prefill", "attention", "timeline"])
     ap.add_argument("--config-json", help="a config.json; default: the Llama-3.2-1B shape")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="1b",
+                    help="the sizes of Llama-3.2-1B, Llama-3.2-3B or Llama-3.1-8B (without --config-json)")
     ap.add_argument("--layers", type=int, default=None, help="override num_hidden_layers")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=512, help="prompt length of the decode requests")
@@ -60,7 +72,7 @@ def main(argv=None) -> int:
     from . import LLM, SamplingParams
     from .engine.batch import StepEntry
 
-    cfg = json.load(open(a.config_json)) if a.config_json else dict(LLAMA_3_2_1B)
+    cfg = json.load(open(a.config_json)) if a.config_json else dict(SHAPES[a.shape])
     if a.layers:
         cfg["num_hidden_layers"] = a.layers
     if a.what == "attention":
