@@ -224,3 +224,15 @@ def test_rotary_part_refuses_a_scaling_it_does_not_know():
     assert ok.shape == (32,)
     with pytest.raises(ValueError, match="yarn"):
         rope_inv_freq(64, 500000.0, {"rope_type": "yarn", "factor": 8.0})
+
+
+def test_the_profiling_tool_and_the_bench_name_the_same_shapes():
+    """``profiling --shape`` and ``bench.py`` build their random models from the same sizes."""
+    import importlib.util
+    import os
+    from kv_cache_optimization_for_llm_b200.profiling import SHAPES
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert SHAPES["1b"] == bench.LLAMA_1B and SHAPES["3b"] == bench.LLAMA_3B and SHAPES["8b"] == bench.LLAMA_8B
+    assert bench.WORKLOADS["serve3b"]["model"] == SHAPES["3b"] and bench.WORKLOADS["stress8b"]["model"] == SHAPES["8b"]
