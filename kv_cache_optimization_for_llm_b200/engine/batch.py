@@ -126,7 +126,7 @@ class BatchBuilder:
 
     def build(self, entries: Sequence[StepEntry], cache, vocab_size: Optional[int] = None,
               pad_reqs_to: int = 0, scratch_page: int = -1, scratch_slot: int = 0,
-              sampled: Optional[torch.Tensor] = None, pad_ctx: int = 1) -> StepBatch:
+              sampled: Optional[torch.Tensor] = None, pad_ctx: int = 1, pad_tokens_to: int = 0) -> StepBatch:
         """``cache`` is the CacheManager; every entry's pages must already cover
         ``start + len(tokens)``.
 
@@ -137,8 +137,22 @@ class BatchBuilder:
         gives the dummy requests a context of that many tokens, all of it the scratch page
         (what a graph captured ahead of any request is shaped with).
 
+        ``pad_tokens_to`` > the tokens of a step's only entry appends dummy tokens (id 0) at the
+        positions behind its run, so that a portion fills a captured graph's fixed shape: they
+        attend to what lies before them, nothing real attends to them, and their keys and values
+        go behind the request's length, into the rest of its last page and, beyond that, into
+        ``scratch_page``, where the next real tokens overwrite them or nobody reads them.
+
         ``sampled``: the device buffer that token ids below zero refer to (see StepEntry);
         without it such ids are refused."""
+        padded_run = 0
+        if pad_tokens_to:
+            if len(entries) != 1 or pad_reqs_to:
+                raise ValueError("only a step of one request can be padded with tokens")
+            e0 = entries[0]
+            padded_run = max(0, pad_tokens_to - len(e0.tokens))
+            if padded_run:
+                entries = [StepEntry(e0.request_id, list(e0.tokens) + [0] * padded_run, e0.start, e0.want)]
         n_real = len(entries)
         if pad_reqs_to > n_real:
             entries = list(entries) + [StepEntry(-1, (0,), max(0, pad_ctx - 1), ()) for _ in range(pad_reqs_to - n_real)]
@@ -216,6 +230,8 @@ class BatchBuilder:
                                      f"tables were sized for {self.max_pages[g]}")
                 n = min(len(table), cols)      # pages beyond the step's longest context are not read
                 bt[r, :n] = table[:n]
+                if padded_run:                 # the dummy tokens' pages behind the request's own
+                    bt[r, n:min(cols, -(-(e.start + len(e.tokens)) // (self.page_size or 1)))] = scratch_page
             off += (R * cols + 3) // 4 * 4
         decode_only = all(len(e.tokens) == 1 for e in entries)
         tile_places = {}

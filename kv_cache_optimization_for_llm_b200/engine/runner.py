@@ -130,8 +130,67 @@ class ModelRunner:
         [wanted, vocab] on the device, in the order of the entries and their ``want``."""
         if self.graph_buckets and all(len(e.tokens) == 1 for e in entries):
             return self._run_decode_graph(entries)
+        if self.graph_buckets and len(entries) == 1:
+            bucket = self._portion_bucket(entries[0])
+            if bucket:
+                return self._run_portion_graph(entries[0], bucket)
         batch = self.builder.build(entries, self.manager, self.vocab_size, sampled=self.sampled[:-1])
         return self.model.forward(batch, self.cache, self.arena)
+
+    # A step that is one request's portion of at most this many tokens is padded to the next of
+    # these lengths and replayed from a captured graph: launched kernel by kernel it is bound by
+    # the host (a hundred and fifty launches), which a prompt that arrives at an idle engine pays
+    # as time to its first token.
+    PORTION_BUCKETS = (16, 32, 64, 128, 256, 512)
+
+    def _portion_bucket(self, e: StepEntry) -> int:
+        n = len(e.tokens)
+        if n < 2 or n > self.PORTION_BUCKETS[-1] or len(e.want) > 1 or self.cache.states or self.page_size_unknown():
+            return 0
+        bucket = next(b for b in self.PORTION_BUCKETS if b >= n)
+        if bucket > self.config.max_num_batched_tokens or e.start + bucket > self.max_model_len:
+            return 0
+        if min(e.tokens) < 0:            # ids that name tokens still on the device belong to single tokens
+            return 0
+        return bucket
+
+    def page_size_unknown(self) -> bool:
+        return self.builder.page_size is None
+
+    def _run_portion_graph(self, e: StepEntry, bucket: int) -> torch.Tensor:
+        """One request's portion, padded with dummy tokens to ``bucket`` and replayed as a CUDA graph
+        (captured at first use, one per bucket and width of the block tables)."""
+        want = tuple(e.want) or (0,)
+        batch = self.builder.build([StepEntry(e.request_id, e.tokens, e.start, want)], self.manager, self.vocab_size,
+                                   scratch_page=self.cache.scratch_page, sampled=self.sampled[:-1], pad_tokens_to=bucket)
+        key = ("portion", bucket, tuple(int(t.shape[1]) for t in batch.block_tables))
+        got = self._graphs.get(key)
+        if got is None:
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.model.forward(batch, self.cache, self.arena)      # warm-up outside the capture
+            torch.cuda.current_stream().wait_stream(side)
+            before = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            gc.collect()                                               # see _run_decode_graph
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    out = self.model.forward(batch, self.cache, self.arena)
+            finally:
+                if collecting:
+                    gc.enable()
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            got = (graph, out, ops.launch_count - before, None)
+            self._graphs[key] = got
+            ops.launch_count = before
+        graph, out, launches, _ = got
+        graph.replay()
+        self.graph_launches += launches
+        return out[:1] if e.want else out[:0]
 
     def capture_decode_graphs(self) -> int:
         """Captures, before any request, the graph of every batch-size bucket for every class of

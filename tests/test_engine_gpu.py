@@ -317,7 +317,7 @@ def test_graphs_captured_when_the_engine_is_built():
     assert r.graph_buckets == [1, 2, 4, 6] and sorted(r._graphs) == [(1, 4), (2, 4), (4, 4), (6, 4)]   # tiny_a: 128 positions, one class
     assert int(r.status.item()) == 0 and r.manager.check() == "" and r.manager.free_pages(0) == 64
     got = llm.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
-    assert len(r._graphs) == 4                      # nothing was captured on the way
+    assert len([k for k in r._graphs if k[0] != "portion"]) == 4      # no decode graph was captured on the way
     for p, g in zip(prompts, got):
         assert g == P.generate(cfg, w, p, 8)
 
@@ -356,3 +356,38 @@ def test_capture_is_safe_from_the_garbage_collector():
     assert gc.isenabled()
     for p_, g in zip(prompts, got):
         assert g == P.generate(cfg, w, p_, 6)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 4e-2)])
+def test_a_lone_portion_is_padded_and_replayed_from_a_graph(dtype, tol):
+    """A step that is one request's portion of up to 512 tokens is padded with dummy tokens to a
+    fixed length and replayed from a captured graph.  The dummy tokens sit behind the run: their
+    keys and values go into the rest of the request's last page and into the scratch page, and the
+    tokens that follow (another portion, then single tokens) overwrite or never see them."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, ops
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    name = "tiny_d" if dtype == "bfloat16" else "tiny_b"
+    mdir = model_dir(name, dtype)
+    cfg, w = P.read_model_dir(mdir)
+    rng = np.random.default_rng(5)
+    seq = rng.integers(0, cfg["vocab_size"], 60).tolist()
+    ref = P.forward(cfg, w, seq)
+    r = ModelRunner(mdir, EngineConfig(dtype=dtype, page_size=4, num_pages=40, max_num_seqs=4, max_num_batched_tokens=64,
+                                       max_model_len=120, use_cuda_graphs=True))
+
+    def close(got, rows):
+        assert np.abs(got.cpu().numpy() - ref[rows]).max() / np.abs(ref).max() < tol
+
+    close(r.step([StepEntry(1, seq[:37], 0, [36])]), [36])          # 37 tokens as 64: 27 dummies behind them
+    assert [k for k in r._graphs if k[0] == "portion"] == [("portion", 64, (30,))]
+    close(r.step([StepEntry(1, seq[37:42], 37, [4])]), [41])        # 5 tokens as 16, over the first dummies' places
+    before = ops.launch_count
+    close(r.step([StepEntry(2, seq[:40], 0, [39])]), [39])          # another request, the same graph again
+    assert ops.launch_count == before and len([k for k in r._graphs if k[0] == "portion"]) == 2
+    for i in range(42, 46):                                          # single tokens behind the portions
+        close(r.step([StepEntry(1, [seq[i]], i, [0])]), [i])
+    assert r.step([StepEntry(2, seq[40:60], 40, [])]).shape[0] == 0   # nothing wanted: nothing comes back
+    close(r.step([StepEntry(2, [7], 60, [0]), StepEntry(1, [seq[46]], 46, [0])])[1:], [46])
+    r.check_status()
+    assert r.manager.check() == ""
