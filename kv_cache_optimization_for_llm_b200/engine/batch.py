@@ -137,25 +137,32 @@ class BatchBuilder:
         gives the dummy requests a context of that many tokens, all of it the scratch page
         (what a graph captured ahead of any request is shaped with).
 
-        ``pad_tokens_to`` > the tokens of a step's only entry appends dummy tokens (id 0) at the
-        positions behind its run, so that a portion fills a captured graph's fixed shape: they
+        ``pad_tokens_to`` > the tokens of a step's only run (its only entry of more than one token;
+        the others may be single tokens) appends dummy tokens (id 0) at the
+        positions behind that run, so that a portion fills a captured graph's fixed shape: they
         attend to what lies before them, nothing real attends to them, and their keys and values
         go behind the request's length, into the rest of its last page and, beyond that, into
         ``scratch_page``, where the next real tokens overwrite them or nobody reads them.
 
         ``sampled``: the device buffer that token ids below zero refer to (see StepEntry);
         without it such ids are refused."""
-        padded_run = 0
+        padded_run, padded_entry = 0, -1
         if pad_tokens_to:
-            if len(entries) != 1 or pad_reqs_to:
-                raise ValueError("only a step of one request can be padded with tokens")
-            e0 = entries[0]
+            runs = [i for i, e in enumerate(entries) if len(e.tokens) != 1]
+            if len(runs) != 1:
+                raise ValueError("only a step with exactly one run of tokens can be padded with tokens")
+            padded_entry = runs[0]
+            e0 = entries[padded_entry]
             padded_run = max(0, pad_tokens_to - len(e0.tokens))
             if padded_run:
-                entries = [StepEntry(e0.request_id, list(e0.tokens) + [0] * padded_run, e0.start, e0.want)]
+                entries = list(entries)
+                entries[padded_entry] = StepEntry(e0.request_id, list(e0.tokens) + [0] * padded_run, e0.start, e0.want)
         n_real = len(entries)
         if pad_reqs_to > n_real:
-            entries = list(entries) + [StepEntry(-1, (0,), max(0, pad_ctx - 1), ()) for _ in range(pad_reqs_to - n_real)]
+            # dummy requests want their logits when the step also holds a run: the rows of logits of
+            # a captured graph are as many as its requests, whichever of them are real
+            entries = list(entries) + [StepEntry(-1, (0,), max(0, pad_ctx - 1), (0,) if pad_tokens_to else ())
+                                       for _ in range(pad_reqs_to - n_real)]
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
         if R == 0 or T == 0:
@@ -219,9 +226,9 @@ class BatchBuilder:
             places.append(off)
             bt = h[off:off + R * cols].reshape(R, cols)
             bt.fill(-1)
-            bt[n_real:, :max(1, min(cols, -(-pad_ctx // (self.page_size or pad_ctx))))] = scratch_page
             for r, i in enumerate(order):
-                if i >= n_real:          # dummy rows (they follow the real ones: only steps of single tokens are padded)
+                if i >= n_real:          # a dummy request: its context is the scratch page
+                    bt[r, :max(1, min(cols, -(-pad_ctx // (self.page_size or pad_ctx))))] = scratch_page
                     continue
                 e = entries[i]
                 table = cache.block_table(e.request_id, g)
@@ -230,7 +237,7 @@ class BatchBuilder:
                                      f"tables were sized for {self.max_pages[g]}")
                 n = min(len(table), cols)      # pages beyond the step's longest context are not read
                 bt[r, :n] = table[:n]
-                if padded_run:                 # the dummy tokens' pages behind the request's own
+                if padded_run and i == padded_entry:   # the dummy tokens' pages behind the request's own
                     bt[r, n:min(cols, -(-(e.start + len(e.tokens)) // (self.page_size or 1)))] = scratch_page
             off += (R * cols + 3) // 4 * 4
         decode_only = all(len(e.tokens) == 1 for e in entries)

@@ -73,6 +73,9 @@ class ModelRunner:
             from ..weights.random_init import random_tensors_on_device
             tensors = random_tensors_on_device(expected_weights(self.spec), int(random_init.get("seed", 0)),
                                                float(random_init.get("std", 0.02)), self.dtype, self.device)
+        self.weight_bytes = sum(int(t.numel()) * t.element_size() for t in tensors.values())
+        self.graph_mixed_steps = (self.weight_bytes <= 4 << 30) if self.config.graph_mixed_steps is None \
+            else bool(self.config.graph_mixed_steps)
         self.max_model_len = int(self.config.max_model_len or self.spec.max_position)
         if self.max_model_len > self.spec.max_position:
             raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's "
@@ -130,10 +133,17 @@ class ModelRunner:
         [wanted, vocab] on the device, in the order of the entries and their ``want``."""
         if self.graph_buckets and all(len(e.tokens) == 1 for e in entries):
             return self._run_decode_graph(entries)
-        if self.graph_buckets and len(entries) == 1:
-            bucket = self._portion_bucket(entries[0])
-            if bucket:
-                return self._run_portion_graph(entries[0], bucket)
+        if self.graph_buckets:
+            runs = [e for e in entries if len(e.tokens) != 1]
+            if len(runs) == 1:
+                bucket = self._portion_bucket(runs[0])
+                singles = len(entries) - 1
+                if bucket and singles == 0:
+                    return self._run_portion_graph(entries[0], bucket)
+                if bucket and self.graph_mixed_steps and len(entries) <= self.config.max_num_seqs:
+                    rb = min(next(b for b in self.graph_buckets if b >= singles), self.config.max_num_seqs - 1)
+                    if rb + bucket <= self.config.max_num_batched_tokens:
+                        return self._run_mixed_graph(entries, runs[0], bucket, rb)
         batch = self.builder.build(entries, self.manager, self.vocab_size, sampled=self.sampled[:-1])
         return self.model.forward(batch, self.cache, self.arena)
 
@@ -191,6 +201,62 @@ class ModelRunner:
         graph.replay()
         self.graph_launches += launches
         return out[:1] if e.want else out[:0]
+
+    def _run_mixed_graph(self, entries: Sequence[StepEntry], run: StepEntry, bucket: int, rb: int) -> torch.Tensor:
+        """Single tokens beside one portion (a short prompt that arrives while others decode, the tail
+        of a long one): the single tokens padded with dummy requests to a batch-size bucket as in
+        ``_run_decode_graph``, the portion with dummy tokens as in ``_run_portion_graph``, replayed as
+        one graph per (bucket of requests, bucket of tokens, width of the block tables).  The graph
+        produces the logits of every single token and of one place of the portion; what was asked
+        for is picked afterwards, in the order of the entries."""
+        singles = [e for e in entries if e is not run]
+        n_single = len(singles)
+        # rb: the bucket of the single tokens' requests (at most max_num_seqs - 1: the portion's request is one too)
+        asked = [StepEntry(e.request_id, e.tokens, e.start, (0,)) for e in singles]
+        asked.append(StepEntry(run.request_id, run.tokens, run.start, tuple(run.want) or (0,)))
+        batch = self.builder.build(asked, self.manager, self.vocab_size, pad_reqs_to=rb + 1,
+                                   scratch_page=self.cache.scratch_page, scratch_slot=self.cache.scratch_slot,
+                                   sampled=self.sampled[:-1], pad_tokens_to=bucket)
+        key = ("mixed", rb, bucket, tuple(int(t.shape[1]) for t in batch.block_tables))
+        got = self._graphs.get(key)
+        if got is None:
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.model.forward(batch, self.cache, self.arena)      # warm-up outside the capture
+            torch.cuda.current_stream().wait_stream(side)
+            before = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            gc.collect()                                               # see _run_decode_graph
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    out = self.model.forward(batch, self.cache, self.arena)
+            finally:
+                if collecting:
+                    gc.enable()
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            got = (graph, out, ops.launch_count - before, None)
+            self._graphs[key] = got
+            ops.launch_count = before
+        graph, out, launches, _ = got
+        graph.replay()
+        self.graph_launches += launches
+        # rows of `out`: the single tokens in their order, then the portion's place, then the dummies
+        keep, k = [], 0
+        for e in entries:
+            if e is run:
+                if e.want:
+                    keep.append(n_single)
+            else:
+                if e.want:
+                    keep.append(k)
+                k += 1
+        if keep == list(range(len(keep))):
+            return out[:len(keep)]
+        return out[keep] if keep else out[:0]
 
     def capture_decode_graphs(self) -> int:
         """Captures, before any request, the graph of every batch-size bucket for every class of

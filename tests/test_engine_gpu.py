@@ -391,3 +391,51 @@ def test_a_lone_portion_is_padded_and_replayed_from_a_graph(dtype, tol):
     close(r.step([StepEntry(2, [7], 60, [0]), StepEntry(1, [seq[46]], 46, [0])])[1:], [46])
     r.check_status()
     assert r.manager.check() == ""
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 4e-2)])
+def test_single_tokens_beside_one_portion_replay_from_a_graph(dtype, tol):
+    """Decoding requests beside one short portion: the requests padded with dummy requests, the
+    portion with dummy tokens, the step replayed from a graph; the logits come back in the order
+    of the entries, whichever of them want any, and a second step of the same shape launches nothing."""
+    from kv_cache_optimization_for_llm_b200 import EngineConfig, ops
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    name = "tiny_d" if dtype == "bfloat16" else "tiny_b"
+    mdir = model_dir(name, dtype)
+    cfg, w = P.read_model_dir(mdir)
+    rng = np.random.default_rng(9)
+    seqs = {i: rng.integers(0, cfg["vocab_size"], n).tolist() for i, n in ((1, 30), (2, 45), (3, 21), (4, 50), (5, 33))}
+    refs = {i: P.forward(cfg, w, s) for i, s in seqs.items()}
+    scale = max(np.abs(r).max() for r in refs.values())
+    r = ModelRunner(mdir, EngineConfig(dtype=dtype, page_size=4, num_pages=80, max_num_seqs=6, max_num_batched_tokens=64,
+                                       max_model_len=120, use_cuda_graphs=True, graph_mixed_steps=True))
+
+    def close(got, want):          # want: [(request, position)]
+        got = got.cpu().numpy()
+        assert got.shape[0] == len(want)
+        for row, (i, pos) in zip(got, want):
+            assert np.abs(row - refs[i][pos]).max() / scale < tol, (i, pos)
+
+    for i in (1, 2, 3):            # three requests up to their last token but two
+        r.step([StepEntry(i, seqs[i][:-2], 0, [])])
+    n = {i: len(seqs[i]) - 2 for i in (1, 2, 3)}
+    # two decoding requests around a 20-token portion of a fourth: 2 -> 2 requests, 20 -> 32 tokens
+    got = r.step([StepEntry(1, [seqs[1][n[1]]], n[1], [0]), StepEntry(4, seqs[4][:20], 0, [19]),
+                  StepEntry(2, [seqs[2][n[2]]], n[2], [0])])
+    close(got, [(1, n[1]), (4, 19), (2, n[2])])
+    assert [k for k in r._graphs if k[0] == "mixed"] == [("mixed", 2, 32, (30,))]
+    n[1] += 1; n[2] += 1
+    # three decoding requests (a bucket of four) beside the next portion; one of them wants nothing
+    got = r.step([StepEntry(4, seqs[4][20:50], 20, [29]), StepEntry(3, [seqs[3][n[3]]], n[3], [0]),
+                  StepEntry(1, [seqs[1][n[1]]], n[1], []), StepEntry(2, [seqs[2][n[2]]], n[2], [0])])
+    close(got, [(4, 49), (3, n[3]), (2, n[2])])
+    n[1] += 1; n[2] += 1; n[3] += 1
+    # the same shape again (one request done: two decoding, bucket of two, 32 tokens): nothing is launched
+    r.release(1); r.release(2)
+    before = ops.launch_count
+    got = r.step([StepEntry(3, [seqs[3][n[3]]], n[3], [0]), StepEntry(5, seqs[5][:31], 0, []), StepEntry(4, [7], 50, [])])
+    close(got, [(3, n[3])])
+    assert ops.launch_count == before and len([k for k in r._graphs if k[0] == "mixed"]) == 2
+    r.check_status()
+    assert r.manager.check() == ""

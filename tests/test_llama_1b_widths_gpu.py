@@ -252,8 +252,9 @@ def test_single_tokens_beside_a_portion_take_the_decode_kernel(model, dtype):
     for row, (i, ref_row) in enumerate(((30, 1), (33, 1), (31, 1), (32, 1))):
         _check(got[row:row + 1], refs[i][ref_row][None, :], dtype, f"request {i} in the mixed step")
     if dtype == "bfloat16":
-        assert ops.choices["decode_attention_mma"] == LAYERS and ops.choices["flash_attention_0"] + \
-            ops.choices["flash_attention_1"] + ops.choices["flash_attention_2"] + ops.choices["flash_attention_3"] == LAYERS, dict(ops.choices)
+        # once per layer when the step is launched, twice (warm-up and capture) when it is replayed from a graph
+        flash = sum(ops.choices[f"flash_attention_{k}"] for k in range(4))
+        assert ops.choices["decode_attention_mma"] == flash and flash in (LAYERS, 2 * LAYERS), dict(ops.choices)
     for i in seqs:
         r.release(i)
     assert r.manager.check() == ""
