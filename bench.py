@@ -224,6 +224,32 @@ def run_prefill(llm, reps, warmup, seed):
     return statistics.median(times)
 
 
+def run_first_token(llm, prompt_len, reps, warmup, seed):
+    """Milliseconds from handing one prompt of ``prompt_len`` tokens to an idle engine to its first
+    token on the host, through add_request and step (median)."""
+    import numpy as np
+    import torch
+    from kv_cache_optimization_for_llm_b200 import SamplingParams
+    eng = llm.engine
+    rng = np.random.default_rng(seed)
+    times = []
+    for k in range(warmup + reps):
+        prompt = rng.integers(0, eng.runner.vocab_size, prompt_len).tolist()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        rid = eng.add_request(prompt, SamplingParams(max_tokens=2, ignore_eos=True))
+        first = None
+        while first is None:
+            for ev in eng.step():
+                if ev.request_id == rid and ev.token is not None and first is None:
+                    first = time.perf_counter()
+        while eng.has_unfinished():
+            eng.step()
+        if k >= warmup:
+            times.append((first - t0) * 1e3)
+    return statistics.median(times)
+
+
 def _pct(xs, p):
     xs = sorted(xs)
     return xs[min(len(xs) - 1, int(round(p / 100.0 * (len(xs) - 1))))] if xs else None
@@ -395,6 +421,11 @@ def main():
         prefill = {"value": round(PREFILL_TOKENS / (ms / 1000.0), 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
                    "frac": round(fl / (ms / 1000.0) / (pk["bf16_tflops"] * 1e12), 4)}
         log(f"  {prefill['value']:.0f} tok/s, {ms:.2f} ms, {prefill['frac']:.3f} of {pk['source']} bf16 peak")
+        log("time to the first token of a lone 128-token prompt")
+        w0 = time.perf_counter()
+        points["first_token_ms_prompt128"] = round(run_first_token(llm, 128, reps=7, warmup=3, seed=13), 3)
+        windows.append((w0, time.perf_counter()))
+        log(f"  {points['first_token_ms_prompt128']:.2f} ms")
     sampler.stop()
     clocks = sampler.summary(windows)
     b_out = 4 * args.batch + 4                                              # sampled ids + the status word
