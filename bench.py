@@ -323,6 +323,7 @@ def run_workload(name, seed=0):
         "ttft_ms": {"p50": round(_pct(ttft, 50), 2), "p99": round(_pct(ttft, 99), 2)},
         "per_token_ms": {"p50": round(_pct(tpot, 50), 3), "p99": round(_pct(tpot, 99), 3)},
         "steps": int(st["steps"]), "preemptions": int(st["preemptions"]), "recomputed_tokens": int(st["recomputed_tokens"]),
+        "step_kinds": st.get("step_kinds"),
         "config": {"model": wl["name"], "layers": cfg["num_hidden_layers"], "hidden_size": cfg["hidden_size"],
                    "heads": f"{cfg['num_attention_heads']}/{cfg['num_key_value_heads']}", "head_dim": cfg["head_dim"],
                    "intermediate_size": cfg["intermediate_size"], "tied_lm_head": bool(cfg["tie_word_embeddings"]),

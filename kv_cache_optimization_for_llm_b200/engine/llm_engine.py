@@ -199,4 +199,5 @@ class LLMEngine:
                 "recomputed_tokens": s.recomputed_tokens, "finished": s.finished,
                 "running": self.scheduler.num_running(), "waiting": self.scheduler.num_waiting(),
                 "free_pages": [m.free_pages(g) for g in range(m.num_groups())],
-                "num_pages": [m.num_pages(g) for g in range(m.num_groups())]}
+                "num_pages": [m.num_pages(g) for g in range(m.num_groups())],
+                "step_kinds": dict(self.runner.step_kinds)}

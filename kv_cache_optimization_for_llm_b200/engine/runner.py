@@ -117,6 +117,7 @@ class ModelRunner:
         self._graphs = {}
         self._graph_pool = None
         self.graph_launches = 0   # kernels of this package launched through graph replays
+        self.step_kinds = {"decode_graph": 0, "portion_graph": 0, "mixed_graph": 0, "launched": 0}   # how steps ran
         self.graph_buckets = []
         if self.config.use_cuda_graphs:
             b = 1
@@ -132,6 +133,7 @@ class ModelRunner:
         """Runs one batch whose pages are already in place.  Returns float32 logits
         [wanted, vocab] on the device, in the order of the entries and their ``want``."""
         if self.graph_buckets and all(len(e.tokens) == 1 for e in entries):
+            self.step_kinds["decode_graph"] += 1
             return self._run_decode_graph(entries)
         if self.graph_buckets:
             runs = [e for e in entries if len(e.tokens) != 1]
@@ -139,11 +141,14 @@ class ModelRunner:
                 bucket = self._portion_bucket(runs[0])
                 singles = len(entries) - 1
                 if bucket and singles == 0:
+                    self.step_kinds["portion_graph"] += 1
                     return self._run_portion_graph(entries[0], bucket)
                 if bucket and self.graph_mixed_steps and len(entries) <= self.config.max_num_seqs:
                     rb = min(next(b for b in self.graph_buckets if b >= singles), self.config.max_num_seqs - 1)
                     if rb + bucket <= self.config.max_num_batched_tokens:
+                        self.step_kinds["mixed_graph"] += 1
                         return self._run_mixed_graph(entries, runs[0], bucket, rb)
+        self.step_kinds["launched"] += 1
         batch = self.builder.build(entries, self.manager, self.vocab_size, sampled=self.sampled[:-1])
         return self.model.forward(batch, self.cache, self.arena)
 
