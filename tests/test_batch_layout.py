@@ -84,3 +84,69 @@ def test_decode_step_padding_rows_and_fixed_places():
     assert far.ctx_len.tolist() == [2049, 2049] and far.positions.tolist() == [2048, 2048]
     assert tuple(far.block_tables[0].shape) == (2, 256)       # the class up to 8192 tokens, capped by the 256 pages of this engine
     assert far.block_tables[0][0, :130].tolist() == [77] * 129 + [-1]
+
+
+def test_random_steps_keep_every_request_together_and_the_wanted_rows_in_order():
+    """Random steps (single tokens and runs in any order, with and without the padding of a graph's
+    fixed shape): every request's tokens stay together and in order, the single tokens' requests come
+    first when runs are present, the wanted rows follow the order of the entries as given, dummy
+    requests and dummy tokens only ever name the scratch page, and real tables are copied unchanged."""
+    rng = np.random.default_rng(123)
+    page = 16
+    for trial in range(200):
+        n_req = int(rng.integers(1, 7))
+        n_runs = int(rng.integers(0, 3)) if n_req > 1 else int(rng.integers(0, 2))
+        kinds = ["run"] * min(n_runs, n_req) + ["single"] * (n_req - min(n_runs, n_req))
+        rng.shuffle(kinds)
+        pad_tokens = kinds.count("run") == 1 and rng.random() < 0.5
+        pad_reqs = (pad_tokens or kinds.count("run") == 0) and rng.random() < 0.5
+        entries, tables, slots = [], {}, {}
+        for i, kind in enumerate(kinds):
+            rid = 100 + i
+            n = 1 if kind == "single" else int(rng.integers(2, 40))
+            start = int(rng.integers(0, 300))
+            toks = rng.integers(1, 90, n).tolist()
+            want = sorted(set(rng.integers(0, n, int(rng.integers(0, 3))).tolist())) if not pad_tokens else [n - 1]
+            entries.append(StepEntry(rid, toks, start, want))
+            tables[rid] = (1000 + 50 * i + np.arange(-(-(start + n) // page))).tolist()
+            slots[rid] = i
+        b = _builder(tile_heights=[16])
+        kw = {}
+        run_len = next((len(e.tokens) for e in entries if len(e.tokens) != 1), 0)
+        if pad_tokens:
+            kw["pad_tokens_to"] = 64 if run_len <= 64 else 0
+            pad_tokens = bool(kw["pad_tokens_to"])
+        if pad_reqs:
+            kw["pad_reqs_to"] = 8
+        batch = b.build(entries, _Manager(tables, slots), vocab_size=100, scratch_page=7777, scratch_slot=99, **kw)
+        R = batch.num_reqs
+        qs, ctx, treq = batch.q_start.tolist(), batch.ctx_len.tolist(), batch.token_req.tolist()
+        toks, pos = batch.token_ids.tolist(), batch.positions.tolist()
+        assert treq == sorted(treq) and qs[-1] == batch.num_tokens            # requests' tokens together, rows ascending
+        lens = [qs[r + 1] - qs[r] for r in range(R)]
+        if any(n != 1 for n in lens) and any(n == 1 for n in lens):
+            first_run = next(r for r in range(R) if lens[r] != 1)
+            assert all(n != 1 for n in lens[first_run:]) and batch.num_single == first_run   # single tokens first
+        else:
+            assert batch.num_single == 0
+        # every real entry is found again, whole and in order, with its table and slot
+        row_of = {}
+        for e in entries:
+            r = next(r for r in range(R) if batch.slots[r].item() == slots[e.request_id] and batch.req_start[r].item() == e.start
+                     and toks[qs[r]:qs[r] + len(e.tokens)] == list(e.tokens))
+            row_of[e.request_id] = r
+            assert pos[qs[r]:qs[r] + len(e.tokens)] == list(range(e.start, e.start + len(e.tokens)))
+            n_pages = len(tables[e.request_id])
+            assert batch.block_tables[0][r, :n_pages].tolist() == tables[e.request_id]
+            rest = batch.block_tables[0][r, n_pages:].tolist()
+            padded = lens[r] - len(e.tokens)
+            assert padded == (kw.get("pad_tokens_to", 0) - len(e.tokens) if pad_tokens and len(e.tokens) != 1 else 0)
+            extra = -(-(e.start + lens[r]) // page) - n_pages if padded else 0
+            assert rest[:max(0, extra)] == [7777] * max(0, extra) and all(x == -1 for x in rest[max(0, extra):])
+            assert ctx[r] == e.start + lens[r]
+        # the wanted rows, in the order of the entries as given (dummy requests' rows follow when they want any)
+        want_rows = [qs[row_of[e.request_id]] + w for e in entries for w in e.want]
+        assert batch.logit_rows.tolist()[:len(want_rows)] == want_rows
+        # dummy requests: one token each, the scratch page and slot
+        for r in set(range(R)) - set(row_of.values()):
+            assert lens[r] == 1 and batch.slots[r].item() == 99 and batch.block_tables[0][r, 0].item() == 7777
