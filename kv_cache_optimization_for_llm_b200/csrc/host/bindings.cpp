@@ -41,15 +41,16 @@ PYBIND11_MODULE(_kvb_host, m) {
       .def("check", &CacheManager::check);
 
   py::class_<SchedulerConfig>(m, "SchedulerConfig")
-      .def(py::init([](int seqs, int tokens, int len, int chunk) {
-             return SchedulerConfig{seqs, tokens, len, chunk};
+      .def(py::init([](int seqs, int tokens, int len, int chunk, int portions) {
+             return SchedulerConfig{seqs, tokens, len, chunk, portions};
            }),
            py::arg("max_num_seqs"), py::arg("max_num_batched_tokens"), py::arg("max_model_len"),
-           py::arg("max_prefill_chunk") = 0)
+           py::arg("max_prefill_chunk") = 0, py::arg("max_portions_per_step") = 0)
       .def_readwrite("max_num_seqs", &SchedulerConfig::max_num_seqs)
       .def_readwrite("max_num_batched_tokens", &SchedulerConfig::max_num_batched_tokens)
       .def_readwrite("max_model_len", &SchedulerConfig::max_model_len)
-      .def_readwrite("max_prefill_chunk", &SchedulerConfig::max_prefill_chunk);
+      .def_readwrite("max_prefill_chunk", &SchedulerConfig::max_prefill_chunk)
+      .def_readwrite("max_portions_per_step", &SchedulerConfig::max_portions_per_step);
 
   py::enum_<FinishReason>(m, "FinishReason")
       .value("NONE", FinishReason::None)

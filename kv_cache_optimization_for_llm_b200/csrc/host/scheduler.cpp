@@ -20,7 +20,7 @@ const char* finish_reason_name(FinishReason r) {
 Scheduler::Scheduler(CacheManager* cache, SchedulerConfig cfg) : cache_(cache), cfg_(cfg) {
   if (!cache_) throw std::invalid_argument("Scheduler: a cache manager is required");
   if (cfg_.max_num_seqs < 1 || cfg_.max_num_batched_tokens < 1 || cfg_.max_model_len < 2 ||
-      cfg_.max_prefill_chunk < 0)
+      cfg_.max_prefill_chunk < 0 || cfg_.max_portions_per_step < 0)
     throw std::invalid_argument("Scheduler: limits must be positive");
 }
 
@@ -137,6 +137,10 @@ Plan Scheduler::schedule() {
   Plan plan;
   int budget = cfg_.max_num_batched_tokens;
   bool preempted_now = false;
+  int portions = 0;   // runs of more than one token in this step
+  auto no_more_portions = [&](int want) {
+    return want > 1 && cfg_.max_portions_per_step > 0 && portions >= cfg_.max_portions_per_step;
+  };
 
   // Running requests first, oldest first: one decode token each, or the next
   // portion of a prompt that is still being read.
@@ -145,6 +149,7 @@ Plan Scheduler::schedule() {
     Req& r = reqs_.at(running_[i]);
     int want = r.closing ? 0 : portion(r, budget);
     if (want <= 0) { ++i; continue; }  // budget spent (or only waiting for its last token): not in this step
+    if (no_more_portions(want)) { ++i; continue; }   // its next portion waits for a step with room for a portion
     bool scheduled = true;
     while (!cache_->extend(r.id, r.computed + want)) {
       // Pages ran out.  The latest arrival among the running gives way, this
@@ -173,6 +178,7 @@ Plan Scheduler::schedule() {
     plan.entries.push_back(std::move(e));
     plan.num_tokens += want;
     budget -= want;
+    if (want > 1) ++portions;
     ++i;
   }
 
@@ -183,6 +189,7 @@ Plan Scheduler::schedule() {
     Req& r = reqs_.at(waiting_.front());
     if (r.pending) break;                // its newest token is not known yet: next step
     if (!running_.empty() && !room_for_all_of(r)) break;   // it would only be dropped again
+    if (no_more_portions(portion(r, budget))) break;
     if (cache_->admit(r.id) < 0) break;  // no state slot free
     int want = portion(r, budget);
     if (!cache_->extend(r.id, want)) {
@@ -209,6 +216,7 @@ Plan Scheduler::schedule() {
     plan.entries.push_back(std::move(e));
     plan.num_tokens += want;
     budget -= want;
+    if (want > 1) ++portions;
   }
   return plan;
 }

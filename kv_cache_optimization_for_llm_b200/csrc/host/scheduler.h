@@ -22,6 +22,7 @@ struct SchedulerConfig {
   int max_num_batched_tokens = 2048;  // tokens one step may carry
   int max_model_len = 4096;           // prompt plus output, at most
   int max_prefill_chunk = 0;          // 0: only the budget limits a prompt portion
+  int max_portions_per_step = 0;      // 0: any number; else at most so many runs of more than one token in a step
 };
 
 enum class FinishReason { None = 0, Stop, Length, ModelLen, CacheExhausted, Aborted };

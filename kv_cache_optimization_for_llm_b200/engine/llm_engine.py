@@ -63,7 +63,7 @@ class LLMEngine:
         self._host = host
         self.scheduler = host.Scheduler(self.runner.manager, host.SchedulerConfig(
             self.config.max_num_seqs, self.config.max_num_batched_tokens, self.runner.max_model_len,
-            self.config.max_prefill_chunk))
+            self.config.max_prefill_chunk, self.config.max_portions_per_step))
         self.sampler = Sampler(self.runner.vocab_size, self.config.max_num_seqs, self.runner.device,
                                self.config.seed, out=self.runner.sampled, status=self.runner.status)
         self._pending_token = int(host.PENDING_TOKEN)

@@ -57,6 +57,33 @@ def test_chunk_cap_and_two_token_portions():
     assert s.finish_reason(0) == H.FinishReason.LENGTH
 
 
+def test_a_cap_on_portions_holds_further_prompts_back_but_not_single_tokens():
+    cache = H.CacheManager([H.GroupSpec(4, 0)], [64], 4)
+    s = H.Scheduler(cache, H.SchedulerConfig(4, 64, 64, 0, max_portions_per_step=1))
+    s.add(0, list(range(9)), 6)
+    s.add(1, list(range(7)), 6)
+    s.add(2, [5], 6)            # a prompt of one token is no portion
+    plan, _ = run_step(s)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(0, 9)]      # 1 waits, and 2 behind it (order of arrival)
+    plan, _ = run_step(s)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(0, 1), (1, 7), (2, 1)]
+    plan, _ = run_step(s)
+    assert [(e.id, len(e.tokens)) for e in plan.entries] == [(0, 1), (1, 1), (2, 1)]
+    # a running request whose prompt is still being cut counts too, and later ones wait for it
+    cache = H.CacheManager([H.GroupSpec(4, 0)], [64], 4)
+    s = H.Scheduler(cache, H.SchedulerConfig(4, 8, 64, 0, max_portions_per_step=1))
+    s.add(0, list(range(12)), 3)
+    s.add(1, list(range(6)), 3)
+    seen = []
+    for _ in range(5):
+        plan, _ = run_step(s)
+        seen.append([(e.id, len(e.tokens)) for e in plan.entries])
+        assert sum(len(e.tokens) > 1 for e in plan.entries) <= 1
+    assert seen[:3] == [[(0, 8)], [(0, 4)], [(0, 1), (1, 6)]]
+    with pytest.raises(Exception):
+        H.Scheduler(cache, H.SchedulerConfig(4, 8, 64, 0, max_portions_per_step=-1))
+
+
 def test_admission_is_fcfs_and_limited_by_seats():
     cache, s = make(seqs=2, slots=2, budget=64)
     for i in range(4):
