@@ -151,11 +151,12 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   // position out (it is placed by hand).  Returns the mask of this warp's keys that are there.
   // Keys that are absent (beyond the context, outside the window) are filled with zeros, so
   // that a probability of zero times whatever lay there before cannot turn into NaN.
-  auto request_tile = [&](int t, int stage, bool skip_pos) -> unsigned {
-    unsigned char* kd = k_s + stage * kTileBytes + warp * 32 * D * 2;
-    unsigned char* vd = v_s + stage * kTileBytes + warp * 32 * D * 2;
+  // In two steps, so that the look-up in the block table (a load whose answer the addresses wait
+  // for) can be started a tile's worth of work before the requests go out.
+  // Step one: where this lane's key of tile t lies.  -1: absent (zero-fill); -2: placed by hand, leave alone.
+  auto locate_key = [&](int t, bool skip_pos) -> long long {
     const int j = t * kTile + warp * 32 + lane;
-    long long off = -1;                      // -1: absent, zero-fill; -2: placed by hand, leave alone
+    long long off = -1;
     if (skip_pos && j == pos) off = -2;
     else if (j <= pos && j >= lo) {
       const int lp = j >> page_shift;
@@ -163,6 +164,12 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
       else off = ((((long long)page * nkv + hk) << page_shift) + (j & page_mask)) * D;
     }
+    return off;
+  };
+  // Step two: the requests.
+  auto request_located = [&](int stage, long long off) -> unsigned {
+    unsigned char* kd = k_s + stage * kTileBytes + warp * 32 * D * 2;
+    unsigned char* vd = v_s + stage * kTileBytes + warp * 32 * D * 2;
 #pragma unroll
     for (int i = 0; i < CPK; ++i) {
       const int c = i * 32 + lane;
@@ -176,6 +183,9 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     }
     return __ballot_sync(0xffffffffu, off >= 0);
   };
+  auto request_tile = [&](int t, int stage, bool skip_pos) -> unsigned {
+    return request_located(stage, locate_key(t, skip_pos));
+  };
 
   // The first tiles of this block's first class: on their way before the projection kernel
   // has finished.  Every thread commits one group per stage at the start of a class and one
@@ -185,12 +195,24 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   int my_first = z;                              // first tile of the class that is being walked
   while (my_first < t_first) my_first += C;
   int n_mine = (z < C && my_first < n_tiles) ? (n_tiles - 1 - my_first) / C + 1 : 0;   // a block beyond the classes has no tile
-  unsigned have0 = 0, have1 = 0;
-  auto request_first_tiles = [&]() {
-    if (n_mine > 0) have0 = request_tile(my_first, 0, write_kv != 0);
-    cp_async_commit();
-    if (kStages > 1) {
-      if (n_mine > 1) have1 = request_tile(my_first + C, 1, write_kv != 0);
+  unsigned have[kStages];                        // per stage: which of this warp's 32 keys are there
+#pragma unroll
+  for (int s = 0; s < kStages; ++s) have[s] = 0u;
+  // (the stage of a tile is known only at run time; these keep the masks in registers all the same)
+  auto have_of = [&](int stage) -> unsigned {
+    unsigned h = have[0];
+#pragma unroll
+    for (int s = 1; s < kStages; ++s) h = stage == s ? have[s] : h;
+    return h;
+  };
+  auto set_have = [&](int stage, unsigned h) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) have[s] = stage == s ? h : have[s];
+  };
+  auto request_first_tiles = [&](bool skip_pos) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      have[s] = n_mine > s ? request_tile(my_first + s * C, s, skip_pos) : 0u;
       cp_async_commit();
     }
   };
@@ -200,7 +222,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   // it does not; so a block whose first tiles hold that position asks for them after the wait.
   const bool own_key_from_this_step = !bad && !write_kv && t_star >= my_first && (t_star - my_first) % C == 0 &&
                                       (t_star - my_first) / C < kStages;
-  if (!own_key_from_this_step) request_first_tiles();
+  if (!own_key_from_this_step) request_first_tiles(write_kv != 0);
 
   // The new key and value are stored by the block that owns their tile; where they go does
   // not depend on the projection in front, so the page is looked up before the wait.
@@ -230,7 +252,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
 
   pdl_wait();
   stamp(1);   // the projection in front has finished
-  if (own_key_from_this_step) request_first_tiles();
+  if (own_key_from_this_step) request_first_tiles(false);
   const __nv_bfloat16* row = qkv + q_row * q_row_stride;
   // the owner's loads go out first, so that they are under way while the queries are rotated
   float nk1 = 0.f, nk2 = 0.f;
@@ -287,7 +309,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
           }
         }
         if (direct) {
-          if (warp == (slot >> 5)) { if (star_i == 0) have0 |= 1u << (slot & 31); else have1 |= 1u << (slot & 31); }
+          if (warp == (slot >> 5)) set_have(star_i, have_of(star_i) | (1u << (slot & 31)));
         }
         else __threadfence();   // a later tile of this block fetches it from L2
       }
@@ -319,13 +341,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     my_first = cls;
     while (my_first < t_first) my_first += C;
     n_mine = my_first < n_tiles ? (n_tiles - 1 - my_first) / C + 1 : 0;
-    have0 = have1 = 0;
-    if (n_mine > 0) have0 = request_tile(my_first, 0, false);
-    cp_async_commit();
-    if (kStages > 1) {
-      if (n_mine > 1) have1 = request_tile(my_first + C, 1, false);
-      cp_async_commit();
-    }
+    request_first_tiles(false);
   }
   float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
   float o[DT][4];
@@ -335,10 +351,13 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     const int stage = i % kStages;
     const unsigned char* kt = k_s + stage * kTileBytes + warp * 32 * D * 2;
     const unsigned char* vt = v_s + stage * kTileBytes + warp * 32 * D * 2;
-    const unsigned have = stage ? have1 : have0;
+    const unsigned hv = have_of(stage);
+    // where the tile lies that takes this one's place in the ring: looked up now, asked for after the products
+    const bool more = i + kStages < n_mine;
+    const long long next_off = more ? locate_key(my_first + (i + kStages) * C, false) : -1;
     cp_async_wait_but<kStages - 1>();
     __syncwarp();
-    if (have != 0u) {
+    if (hv != 0u) {
       float s[4][4];
 #pragma unroll
       for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
@@ -355,13 +374,13 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
         }
       }
       float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
-      if (have != 0xffffffffu) {        // a slice at the context's end or at the window's edge
+      if (hv != 0xffffffffu) {        // a slice at the context's end or at the window's edge
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int key = n * 8 + ((lane & 3) << 1) + (e & 1);
-            if (!((have >> key) & 1u)) s[n][e] = -CUDART_INF_F;
+            if (!((hv >> key) & 1u)) s[n][e] = -CUDART_INF_F;
           }
         }
       }
@@ -409,11 +428,7 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       }
     }
     __syncwarp();   // the slice is read; the next request may overwrite it
-    if (i + kStages < n_mine) {
-      // the new key, if in that tile, is in the cache by now
-      const unsigned h = request_tile(my_first + (i + kStages) * C, stage, false);
-      if (stage) have1 = h; else have0 = h;
-    }
+    if (more) set_have(stage, request_located(stage, next_off));   // the new key, if in that tile, is in the cache by now
     cp_async_commit();
   }
 #pragma unroll
@@ -494,13 +509,18 @@ int log2_exact(int x) {
 }
 
 template <int D, int GP, int kClasses, int kStages>
+constexpr size_t smem_bytes() {
+  constexpr int PW = D + 2;
+  return (size_t)kStages * 2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
+         (size_t)kClasses * GP * PW * 4 + (size_t)4 * GP * PW * 4;
+}
+
+template <int D, int GP, int kClasses, int kStages>
 int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* q_start, const int* ctx_len, const float* cos_t,
            const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv, float scale, int window,
            int blocks_per_cluster, int* status, unsigned long long* trace, cudaStream_t stream) {
-  constexpr int PW = D + 2;
-  const size_t smem = (size_t)kStages * 2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
-                      (size_t)kClasses * GP * PW * 4 + (size_t)4 * GP * PW * 4;
+  const size_t smem = smem_bytes<D, GP, kClasses, kStages>();
   static bool attr_set = false;
   if (!attr_set) {
     if (smem > 48 * 1024) {

@@ -587,6 +587,59 @@ def test_tensor_core_decode_attention_long_contexts():
     assert torch.equal(one[0], out[1])
 
 
+@pytest.mark.parametrize("d,nq,nkv,window,ctx", [(64, 8, 2, None, 9001), (64, 8, 2, 5000, 9100), (64, 32, 2, None, 8300),
+                                                 (128, 8, 2, None, 8500), (128, 8, 2, 3000, 9000)])
+def test_tensor_core_decode_attention_one_request_long_context(d, nq, nkv, window, ctx):
+    """One request beyond 8192 tokens, alone in its launch (the form with two tiles in shared memory per block).
+    The new key and value come with the row and are written to the cache by the kernel; under a window the new
+    key's tile is among the first of its class, so it is also placed into its stage by hand.  One key far back
+    (inside the window) stands out, one just outside it must not be seen.  The same request ten times in one
+    launch takes the form with one tile per block: same bits."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    page_size = 16
+    rng = np.random.default_rng(ctx + d)
+    G = nq // nkv
+    k = as64(dev(rng.normal(size=(ctx, nkv, d)), torch.bfloat16))
+    v = as64(dev(rng.normal(size=(ctx, nkv, d)), torch.bfloat16))
+    q = as64(dev(rng.normal(size=(nq, d)), torch.bfloat16))
+    lo = 0 if window is None else max(0, ctx - window)
+    far = lo + 1
+    k[far, 0] = as64(dev(q[0] * 1.5, torch.bfloat16))
+    if window is not None:
+        k[lo - 1, 0] = as64(dev(q[0] * 3.0, torch.bfloat16))    # just outside the window: must not be seen
+    n_pages = -(-ctx // page_size)
+    table = rng.permutation(n_pages + 3)[:n_pages].astype(np.int32)
+    kp = np.zeros((n_pages + 3, nkv, page_size, d))
+    vp = np.zeros((n_pages + 3, nkv, page_size, d))
+    idx = np.arange(ctx - 1)                                    # the cache holds all but the newest
+    kp[table[idx // page_size], :, idx % page_size] = k[:-1]
+    vp[table[idx // page_size], :, idx % page_size] = v[:-1]
+    ref = np.zeros((nq, d))
+    for h in range(nq):
+        s_ = k[lo:, h // G] @ q[h] / math.sqrt(d)
+        pr = np.exp(s_ - s_.max()); pr /= pr.sum()
+        ref[h] = pr @ v[lo:, h // G]
+    row = np.concatenate([q.reshape(-1), k[-1].reshape(-1), v[-1].reshape(-1)])
+    st = status()
+
+    def run(reps):
+        dkp, dvp = dev(kp, torch.bfloat16), dev(vp, torch.bfloat16)
+        out = ops.decode_attention_mma(
+            dev(np.tile(row, (reps, 1)), torch.bfloat16), dkp, dvp, True, dev(np.tile(table, (reps, 1)), torch.int32),
+            dev(np.arange(reps + 1), torch.int32), dev([ctx] * reps, torch.int32), None, None, 0, nq, nkv, d,
+            1 / math.sqrt(d), window, st, max_ctx=ctx)
+        return out, dkp, dvp
+
+    out, dkp, dvp = run(1)
+    assert int(st.item()) == 0
+    assert rel_err(out[0], ref.reshape(-1)) < TOL["bfloat16"]
+    pos = ctx - 1
+    assert torch.equal(dkp[int(table[pos // page_size]), :, pos % page_size].double().cpu(), torch.from_numpy(k[-1]))
+    assert torch.equal(dvp[int(table[pos // page_size]), :, pos % page_size].double().cpu(), torch.from_numpy(v[-1]))
+    many, _, _ = run(10)
+    assert torch.equal(many, out.repeat(10, 1))
+
+
 @pytest.mark.parametrize("d,nq,nkv", [(64, 8, 2), (128, 6, 2)])
 @pytest.mark.parametrize("window", [100, 129])
 @pytest.mark.parametrize("inside", [False, True])
