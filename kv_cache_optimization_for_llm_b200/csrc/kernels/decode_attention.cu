@@ -14,8 +14,9 @@
 // once for the whole group (upstream fetches them once per query head:
 // paged_attention/src/kernels.cu:150-219).
 //
-// Per block: the keys and values of its first two tiles are requested (cp.async, 16-byte
-// chunks gathered through the block table into two swizzled shared-memory stages) before
+// Per block: the keys and values of its first two tiles are requested (head size 64: cp.async, 16-byte
+// chunks gathered through the block table; head size 128: whole pages by TMA through a tensor map over
+// the layer's pages; either way into two swizzled shared-memory stages) before
 // the block waits for the projection kernel in front of it; then the group's queries are
 // rotated (rotary encoding, float32) and the block that owns the tile of the token's
 // own position rotates the new key, stores key and value in the cache and, when that
@@ -30,13 +31,53 @@
 // S partials in block order and writes the output.  No scratch in global memory,
 // no counters, no spinning.
 #include "common.cuh"
+#include "page_maps.cuh"
 
+#include <cuda.h>
 #include <math_constants.h>
+
+#include <cstdint>
+#include <cstdlib>
 
 namespace {
 
 constexpr int kThreads = 128;
 constexpr int kTile = 128;     // keys per tile (32 per warp)
+constexpr unsigned kSpinLimit = 20u * 1000u * 1000u;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait that also ends at once when the block has given up somewhere else.  false: gave up.
+__device__ __forceinline__ bool mbar_wait_or_abort(void* bar, unsigned parity, volatile int* abort_flag) {
+  for (unsigned i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// One box of a tensor map (x: column, y: row of its first element) into shared memory; the bytes are counted on bar.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+// Orders what this thread did to shared memory by ordinary loads and stores before copies by TMA that follow.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // 16 bytes into shared memory; `valid` false: zeros are written and nothing is read.
 __device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
@@ -82,10 +123,12 @@ __device__ __forceinline__ void st_peer_f32(void* my_smem_ptr, unsigned rank, fl
                : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(my_smem_ptr)), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
-// Byte offset of 16-byte chunk `chunk` of row `row` in a [32][D] bfloat16 tile, chunks
-// XOR-swizzled with the row so that the 8 rows of an 8x8 matrix hit 8 bank groups.
+// Byte offset of 16-byte chunk `chunk` of row `row` in a warp's slice of a tile, 32 rows of D bfloat16:
+// sub-tiles of 64 columns side by side (one at head size 64, two at 128), each [32 rows][128 bytes] with
+// the chunks of a row XOR-swizzled with the row, so that the 8 rows of an 8x8 matrix hit 8 bank groups.
+// This is the 128-byte swizzle of TMA for a sub-tile that starts on a 1024-byte boundary.
 template <int D> __device__ __forceinline__ int swz(int row, int chunk) {
-  return row * (D * 2) + ((chunk ^ (row & 7)) << 4);
+  return (chunk >> 3) * (32 * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
 // How many classes the tiles of a token at position pos fall into: 4 below 2048, 8 below 8192,
@@ -97,9 +140,13 @@ __host__ __device__ __forceinline__ int classes_at(int pos) { return pos < 2048 
 // is resident at once anyway (small batches: the second tile is under way before the
 // projection has finished), 1 when more blocks per SM matter more (large batches).  The
 // order of the sums is the same for both.
-template <int D, int GP, int kClasses, int kStages>
+// kTma: keys and values come page by page (boxes of min(page size, 32) rows) through tensor maps over the
+// layer's pages, counted on one mbarrier per stage and warp; needs pages of at least 8 rows.  Otherwise
+// 16 bytes at a time by cp.async (any page size; an SM holds far fewer bytes under way that way).
+template <int D, int GP, int kClasses, int kStages, bool kTma>
 __global__ void __launch_bounds__(kThreads, D == 64 ? 4 : 2)   // four blocks per SM at head size 64: 128 registers
-decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
+decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const __nv_bfloat16* __restrict__ qkv, int q_row_stride,
                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int write_kv,
                             const int* __restrict__ block_table, int max_pages, int page_shift, int num_pages,
                             const int* __restrict__ q_start, const int* __restrict__ ctx_len,
@@ -110,14 +157,22 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   constexpr int KSTEPS = D / 16;
   constexpr int DT = D / 8;       // n-tiles of the output
   constexpr int PW = D + 2;       // floats per head in a partial: output dims, max, sum
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  // (the swizzle of TMA follows the address: the stages start on a 1024-byte boundary)
+  unsigned char* smem = kTma ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023))
+                             : smem_raw;
   constexpr int kTileBytes = 4 * 32 * D * 2;                   // keys (or values) of one tile
+  constexpr int kSub = D / 64;                                 // sub-tiles of 64 columns
   unsigned char* k_s = smem;                                   // [kStages][4][32][D] bf16, swizzled
   unsigned char* v_s = k_s + kStages * kTileBytes;             // [kStages][4][32][D]
   float* q_s = reinterpret_cast<float*>(v_s + kStages * kTileBytes); // [GP][D] rotated, scaled queries
   float* run = q_s + GP * D;                                   // [GP][PW] this block's partial so far
   float* recv = run + GP * PW;                                 // [kClasses][GP][PW], used in block 0 only
   float* wpart = recv + kClasses * GP * PW;                    // [4][GP][PW] the four warps' partials of a class
+  // kTma only:
+  unsigned long long* full_b = reinterpret_cast<unsigned long long*>(wpart + 4 * GP * PW);   // [kStages][4] bytes of a slice
+  __nv_bfloat16* newkv_s = reinterpret_cast<__nv_bfloat16*>(full_b + kStages * 4);           // [2][D] the new key and value
+  int* abort_flag = reinterpret_cast<int*>(newkv_s + 2 * D);                                 // a wait ran out
 
   pdl_trigger();
   const int hk = blockIdx.x, r = blockIdx.y, z = blockIdx.z;
@@ -147,44 +202,90 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
 
   for (int i = tid; i < GP * PW; i += kThreads) run[i] = ((i % PW) == D) ? -CUDART_INF_F : 0.f;
 
-  // Requests this warp's 32 keys and values of tile t into a stage; `skip_pos`: leave the token's own
-  // position out (it is placed by hand).  Returns the mask of this warp's keys that are there.
-  // Keys that are absent (beyond the context, outside the window) are filled with zeros, so
-  // that a probability of zero times whatever lay there before cannot turn into NaN.
-  // In two steps, so that the look-up in the block table (a load whose answer the addresses wait
-  // for) can be started a tile's worth of work before the requests go out.
-  // Step one: where this lane's key of tile t lies.  -1: absent (zero-fill); -2: placed by hand, leave alone.
+  // Requests this warp's 32 keys and values of tile t into a stage and returns the mask of this warp's
+  // keys that are there.  In two steps, so that the look-up in the block table (a load whose answer the
+  // addresses wait for) can be started a tile's worth of work before the requests go out.
+  //
+  // By cp.async, key by key: `skip_pos` leaves the token's own position out (it is placed by hand); keys
+  // that are absent (beyond the context, outside the window) are filled with zeros, so that a probability
+  // of zero times whatever lay there before cannot turn into NaN.
+  // By TMA, page by page: a slice of 32 keys is 32 / box_rows boxes, lane c looks up and requests box c;
+  // a box without a key in reach, or without a page, is requested beyond the end of the map, where TMA
+  // delivers zeros.  Rows of a box that hold no key in reach (the page's rows beyond the context, or in
+  // front of the window) arrive as they lie in the cache: their scores are masked, and their values
+  // are set to zero once the slice is there.  The row of the token's own position is overwritten then too.
+  const int box_shift = page_shift < 5 ? page_shift : 5;     // kTma: rows per box = min(page size, 32)
+  const int n_box = 32 >> box_shift;
+  const int total_rows = (num_pages * nkv) << page_shift;    // kTma: the first row beyond the map
+  // Step one: where this lane's key (cp.async: an offset in elements; -1: absent, zero-fill; -2: placed by
+  // hand, leave alone) or this lane's box (TMA: a row of the map) of tile t lies.
   auto locate_key = [&](int t, bool skip_pos) -> long long {
-    const int j = t * kTile + warp * 32 + lane;
-    long long off = -1;
-    if (skip_pos && j == pos) off = -2;
-    else if (j <= pos && j >= lo) {
-      const int lp = j >> page_shift;
-      const int page = lp < max_pages ? table[lp] : -1;
-      if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
-      else off = ((((long long)page * nkv + hk) << page_shift) + (j & page_mask)) * D;
+    if constexpr (kTma) {
+      int row = total_rows;
+      const int kj = t * kTile + warp * 32 + (lane << box_shift);
+      if (lane < n_box && kj <= pos && kj + (1 << box_shift) > lo) {
+        const int lp = kj >> page_shift;
+        const int page = lp < max_pages ? table[lp] : -1;
+        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        else row = (((page * nkv) + hk) << page_shift) + (kj & page_mask);
+      }
+      return row;
+    } else {
+      const int j = t * kTile + warp * 32 + lane;
+      long long off = -1;
+      if (skip_pos && j == pos) off = -2;
+      else if (j <= pos && j >= lo) {
+        const int lp = j >> page_shift;
+        const int page = lp < max_pages ? table[lp] : -1;
+        if (page < 0 || page >= num_pages) atomicCAS(status, 0, KVB_STATUS_UNMAPPED_PAGE);
+        else off = ((((long long)page * nkv + hk) << page_shift) + (j & page_mask)) * D;
+      }
+      return off;
     }
-    return off;
   };
   // Step two: the requests.
-  auto request_located = [&](int stage, long long off) -> unsigned {
+  auto request_located = [&](int t, int stage, long long off) -> unsigned {
     unsigned char* kd = k_s + stage * kTileBytes + warp * 32 * D * 2;
     unsigned char* vd = v_s + stage * kTileBytes + warp * 32 * D * 2;
+    if constexpr (kTma) {
+      const int row = (int)off;
+      const int j = t * kTile + warp * 32 + lane;
+      const int box_row = __shfl_sync(0xffffffffu, row, lane >> box_shift);
+      const unsigned there = __ballot_sync(0xffffffffu, j <= pos && j >= lo && box_row != total_rows);
+      if (there != 0u) {
+        // what this warp read from or wrote to the slice by hand comes before the copies that overwrite it
+        fence_proxy_async_smem();
+        __syncwarp();
+        unsigned long long* bar = full_b + stage * 4 + warp;
+        if (lane == 0) mbar_expect_tx(bar, 2u * 32u * D * 2u);
+        __syncwarp();                                          // the bytes are expected before any copy can report
+        if (lane < n_box) {
+          const int at = (lane << box_shift) * 128;
 #pragma unroll
-    for (int i = 0; i < CPK; ++i) {
-      const int c = i * 32 + lane;
-      const int key = c / CPK, part = c % CPK;
-      const long long oj = __shfl_sync(0xffffffffu, off, key);
-      if (oj != -2) {
-        const long long src = oj >= 0 ? oj + part * 8 : 0;
-        cp_async_16_zfill(kd + swz<D>(key, part), k_pages + src, oj >= 0);
-        cp_async_16_zfill(vd + swz<D>(key, part), v_pages + src, oj >= 0);
+          for (int sub = 0; sub < kSub; ++sub) {
+            tma_load_2d(kd + sub * (32 * 128) + at, &map_k, 64 * sub, row, bar);
+            tma_load_2d(vd + sub * (32 * 128) + at, &map_v, 64 * sub, row, bar);
+          }
+        }
       }
+      return there;
+    } else {
+#pragma unroll
+      for (int i = 0; i < CPK; ++i) {
+        const int c = i * 32 + lane;
+        const int key = c / CPK, part = c % CPK;
+        const long long oj = __shfl_sync(0xffffffffu, off, key);
+        if (oj != -2) {
+          const long long src = oj >= 0 ? oj + part * 8 : 0;
+          cp_async_16_zfill(kd + swz<D>(key, part), k_pages + src, oj >= 0);
+          cp_async_16_zfill(vd + swz<D>(key, part), v_pages + src, oj >= 0);
+        }
+      }
+      return __ballot_sync(0xffffffffu, off >= 0);
     }
-    return __ballot_sync(0xffffffffu, off >= 0);
   };
   auto request_tile = [&](int t, int stage, bool skip_pos) -> unsigned {
-    return request_located(stage, locate_key(t, skip_pos));
+    return request_located(t, stage, locate_key(t, skip_pos));
   };
 
   // The first tiles of this block's first class: on their way before the projection kernel
@@ -213,9 +314,19 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
       have[s] = n_mine > s ? request_tile(my_first + s * C, s, skip_pos) : 0u;
-      cp_async_commit();
+      if constexpr (!kTma) cp_async_commit();
     }
   };
+  unsigned parity = 0u;                          // kTma: bit s is the phase that stage s's barrier completes next
+  if constexpr (kTma) {
+    if (tid == 0) {
+      for (int i = 0; i < kStages * 4; ++i) mbar_init(full_b + i, 1);
+      *abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+  }
   // A layer that reads another layer's cache finds the key and value of the token's own
   // position there: the owning layer's attention wrote them earlier in this same step, several
   // launches back.  The wait below orders this kernel behind all of those, a read in front of
@@ -301,17 +412,24 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
           const __nv_bfloat16 kr = __float2bfloat16_rn(val);
           k_pages[dst + dd] = kr;
           v_pages[dst + dd] = nv;
-          if (direct) {
+          if constexpr (kTma) {
+            // kept for the warp that walks the slice of this position: it overwrites the row of the
+            // slice with them once the slice has arrived (the page may have been fetched before this store)
+            newkv_s[dd] = kr;
+            newkv_s[D + dd] = nv;
+          } else if (direct) {
             const int key = slot & 31;
             const int off_b = star_i * kTileBytes + (slot >> 5) * 32 * D * 2 + swz<D>(key, dd >> 3) + (dd & 7) * 2;
             *reinterpret_cast<__nv_bfloat16*>(k_s + off_b) = kr;
             *reinterpret_cast<__nv_bfloat16*>(v_s + off_b) = nv;
           }
         }
-        if (direct) {
-          if (warp == (slot >> 5)) set_have(star_i, have_of(star_i) | (1u << (slot & 31)));
+        if constexpr (!kTma) {
+          if (direct) {
+            if (warp == (slot >> 5)) set_have(star_i, have_of(star_i) | (1u << (slot & 31)));
+          }
+          else __threadfence();   // a later tile of this block fetches it from L2
         }
-        else __threadfence();   // a later tile of this block fetches it from L2
       }
     }
   }
@@ -355,9 +473,35 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
     // where the tile lies that takes this one's place in the ring: looked up now, asked for after the products
     const bool more = i + kStages < n_mine;
     const long long next_off = more ? locate_key(my_first + (i + kStages) * C, false) : -1;
-    cp_async_wait_but<kStages - 1>();
+    bool arrived = true;
+    if constexpr (kTma) {
+      if (hv != 0u) {
+        arrived = mbar_wait_or_abort(full_b + stage * 4 + warp, (parity >> stage) & 1u, abort_flag);
+        arrived = __all_sync(0xffffffffu, arrived);
+        parity ^= 1u << stage;
+        if (arrived) {
+          unsigned char* vw = v_s + stage * kTileBytes + warp * 32 * D * 2;
+          if (hv != 0xffffffffu && !((hv >> lane) & 1u)) {
+            // this lane's key is not in reach: whatever the page holds in its row must not meet a probability of zero
+#pragma unroll
+            for (int c = 0; c < CPK; ++c) *reinterpret_cast<uint4*>(vw + swz<D>(lane, c)) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          const int t_now = my_first + i * C;
+          if (owner && own_page >= 0 && t_now == t_star && warp == ((pos - t_star * kTile) >> 5) && lane < 2 * CPK) {
+            // the new key and value, as this block stored them: lanes 0 .. CPK-1 a chunk of the key each, the next CPK of the value
+            const int key = (pos - t_star * kTile) & 31, c = lane % CPK;
+            unsigned char* dstw = (lane < CPK ? k_s : v_s) + stage * kTileBytes + warp * 32 * D * 2 + swz<D>(key, c);
+            *reinterpret_cast<uint4*>(dstw) = *reinterpret_cast<const uint4*>(newkv_s + (lane < CPK ? 0 : D) + c * 8);
+          }
+        } else if (lane == 0) {
+          atomicCAS(status, 0, KVB_STATUS_WAIT_TIMEOUT);
+        }
+      }
+    } else {
+      cp_async_wait_but<kStages - 1>();
+    }
     __syncwarp();
-    if (hv != 0u) {
+    if (hv != 0u && arrived) {
       float s[4][4];
 #pragma unroll
       for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
@@ -428,8 +572,9 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
       }
     }
     __syncwarp();   // the slice is read; the next request may overwrite it
-    if (more) set_have(stage, request_located(stage, next_off));   // the new key, if in that tile, is in the cache by now
-    cp_async_commit();
+    if (more && arrived) set_have(stage, request_located(my_first + (i + kStages) * C, stage, next_off));
+    else if (more) set_have(stage, 0u);   // (cp.async: the new key, if in that tile, is in the cache by now)
+    if constexpr (!kTma) cp_async_commit();
   }
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
@@ -475,6 +620,10 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ qkv, int q_row_str
   for (int i = tid; i < GP * PW; i += kThreads) st_peer_f32(recv + (size_t)cls * GP * PW + i, 0u, run[i]);
   }   // classes
   stamp(4);   // the block's partials are complete
+  if constexpr (kTma) {
+    // a wait ran out: copies may still be on their way into this block's shared memory
+    if (*abort_flag) { for (int i = 0; i < 2000; ++i) __nanosleep(1000); }
+  }
   // ---- block 0 merges the classes in class order
   cluster_sync_all();
   stamp(5);   // the cluster has met
@@ -508,28 +657,61 @@ int log2_exact(int x) {
   return (1 << s) == x ? s : -1;
 }
 
-template <int D, int GP, int kClasses, int kStages>
+template <int D, int GP, int kClasses, int kStages, bool kTma>
 constexpr size_t smem_bytes() {
   constexpr int PW = D + 2;
   return (size_t)kStages * 2 * 4 * 32 * D * 2 + (size_t)GP * D * 4 + (size_t)GP * PW * 4 +
-         (size_t)kClasses * GP * PW * 4 + (size_t)4 * GP * PW * 4;
+         (size_t)kClasses * GP * PW * 4 + (size_t)4 * GP * PW * 4 +
+         (kTma ? 1024 + (size_t)kStages * 4 * 8 + 2 * D * 2 + 16 : 0);   // alignment, barriers, new key and value, flag
 }
 
-template <int D, int GP, int kClasses, int kStages>
-int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv, const int* block_table,
+// How many clusters of `blocks_per_cluster` blocks of this form the GPU holds at once (0: the query failed).
+template <int D, int GP, int kClasses, int kStages, bool kTma>
+int clusters_at_once(int blocks_per_cluster) {
+  static int answer[17] = {};      // by cluster size; 0: not asked yet, -1: the query failed
+  if (answer[blocks_per_cluster] == 0) {
+    constexpr size_t smem = smem_bytes<D, GP, kClasses, kStages, kTma>();
+    auto* fn = decode_attention_mma_kernel<D, GP, kClasses, kStages, kTma>;
+    int n = -1;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+        cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(1, 1, blocks_per_cluster);
+      cfg.blockDim = dim3(kThreads, 1, 1);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = blocks_per_cluster;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int got = 0;
+      if (cudaOccupancyMaxActiveClusters(&got, fn, &cfg) == cudaSuccess) n = got;
+      else (void)cudaGetLastError();
+    } else {
+      (void)cudaGetLastError();
+    }
+    answer[blocks_per_cluster] = n > 0 ? n : -1;
+  }
+  return answer[blocks_per_cluster] > 0 ? answer[blocks_per_cluster] : 0;
+}
+
+template <int D, int GP, int kClasses, int kStages, bool kTma>
+int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int write_kv, const int* block_table,
            int max_pages, int page_shift, int num_pages, const int* q_start, const int* ctx_len, const float* cos_t,
            const float* sin_t, int table_len, int rot, void* out, int R, int nq, int nkv, float scale, int window,
            int blocks_per_cluster, int* status, unsigned long long* trace, cudaStream_t stream) {
-  const size_t smem = smem_bytes<D, GP, kClasses, kStages>();
+  const size_t smem = smem_bytes<D, GP, kClasses, kStages, kTma>();
   static bool attr_set = false;
   if (!attr_set) {
     if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages>,
+      cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages, kTma>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
     if (kClasses > 8) {   // clusters of 16 are beyond the portable size
-      cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages>,
+      cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<D, GP, kClasses, kStages, kTma>,
                                            cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
       if (e != cudaSuccess) return (int)e;
     }
@@ -550,7 +732,7 @@ int launch(const void* qkv, int q_row_stride, void* k_pages, void* v_pages, int 
   cfg.attrs = attr;
   cfg.numAttrs = kvb_pdl_enabled() ? 2 : 1;
   cudaError_t le = cudaLaunchKernelEx(
-      &cfg, decode_attention_mma_kernel<D, GP, kClasses, kStages>, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
+      &cfg, decode_attention_mma_kernel<D, GP, kClasses, kStages, kTma>, map_k, map_v, (const __nv_bfloat16*)qkv, q_row_stride, (__nv_bfloat16*)k_pages,
       (__nv_bfloat16*)v_pages, write_kv, block_table, max_pages, page_shift, num_pages, q_start, ctx_len, cos_t, sin_t,
       table_len, rot, (__nv_bfloat16*)out, nq, nkv, nq / nkv, scale * 1.4426950408889634f, window, status, trace);
   if (le != cudaSuccess) return (int)le;
@@ -594,26 +776,50 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
   int S = cluster;
   // (an SM holds four blocks of head size 64 with one stage, two of head size 128: no second wave)
   while (S > 1 && (long long)R * nkv * S > (d == 64 ? 4 : 2) * kvb_sm_count()) S >>= 1;
-  // two stages while every block of the grid fits on the GPU at once (two stages of head size 128
-  // are 128 KB: one block per SM)
-  const bool deep = (long long)R * nkv * S <= (d == 64 ? 2 : 1) * kvb_sm_count();
-#define KVB_DM_ARGS qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, q_start, \
+  // Whole pages by TMA at head size 128 where the pages allow it (at least 8 rows, so that a box fills whole
+  // rows of the swizzle pattern; addresses that a tensor map takes); key by key otherwise, at head size 128
+  // then in the one-stage form only.  At head size 64 TMA measured level or slower (batch 8 at 4096 tokens
+  // 18.3 against 16.3 us) and is not built.  KVB200_DECODE_TMA=0 switches it off (tests, comparisons).
+  static const bool tma_off = [] { const char* e = getenv("KVB200_DECODE_TMA"); return e && e[0] == '0'; }();
+  const long long rows = (long long)num_pages * nkv * page_size;
+  const bool tma = !tma_off && d == 128 && page_size >= 8 && rows < (1ll << 31) - 64 &&
+                   reinterpret_cast<uintptr_t>(k_pages) % 16 == 0 && reinterpret_cast<uintptr_t>(v_pages) % 16 == 0;
+  CUtensorMap mk = {}, mv = {};
+  if (tma) {
+    const int box_rows = page_size < 32 ? page_size : 32;
+    int e = kvb_page_maps::pages_map(&mk, k_pages, rows, box_rows, d);
+    if (e) return e;
+    e = kvb_page_maps::pages_map(&mv, v_pages, rows, box_rows, d);
+    if (e) return e;
+  }
+  // Clusters that do not all run at once cost a second round, which doubles the time when the clusters are
+  // few (a GPU holds fewer clusters of 16 than 148 / 16 times the blocks per SM: a cluster stays inside one
+  // GPC).  So, for few clusters: half the blocks per cluster if that lets all run at once; and two stages only
+  // if all clusters run at once with them (they need twice the shared memory).  Clusters of 8 and 16 with two
+  // stages measured well only with one block per SM (head size 64, 64 000 tokens: two requests 97 us with two
+  // stages, 61 us with one; four requests 130 to 150 us against 111 us), small clusters also with two.
+#define KVB_DM_ARGS mk, mv, qkv, q_row_stride, k_pages, v_pages, write_kv, block_table, max_pages, ps, num_pages, q_start, \
                     ctx_len, cos_t, sin_t, table_len, rot, out, R, nq, nkv, scale, window, S, status, trace, stream
-#define KVB_DM16(GP)                                                        \
-  do {                                                                      \
-    if (cluster == 16 && deep) return launch<64, GP, 16, 2>(KVB_DM_ARGS);   \
-    if (cluster == 16) return launch<64, GP, 16, 1>(KVB_DM_ARGS);           \
+#define KVB_FITS(D, GP, CL, ST, TMA, SS) (clusters_at_once<D, GP, CL, ST, TMA>(SS) >= R * nkv)
+#define KVB_PICK(D, GP, CL, TMA)                                                                          \
+  do {                                                                                                    \
+    if (cluster == CL) {                                                                                  \
+      if (R * nkv <= 32 && S > 1 && !KVB_FITS(D, GP, CL, 1, TMA, S) && KVB_FITS(D, GP, CL, 1, TMA, S >> 1)) S >>= 1; \
+      if ((long long)R * nkv * S <= (long long)((D == 64 && S < 8) ? 2 : 1) * kvb_sm_count() &&           \
+          (S == 1 || KVB_FITS(D, GP, CL, 2, TMA, S)))                                                     \
+        return launch<D, GP, CL, 2, TMA>(KVB_DM_ARGS);                                                    \
+      return launch<D, GP, CL, 1, TMA>(KVB_DM_ARGS);                                                      \
+    }                                                                                                     \
   } while (0)
-#define KVB_DM(D, GP)                                                       \
-  do {                                                                      \
-    if (cluster == 4 && deep) return launch<D, GP, 4, 2>(KVB_DM_ARGS);      \
-    if (cluster == 4) return launch<D, GP, 4, 1>(KVB_DM_ARGS);              \
-    if (deep) return launch<D, GP, 8, 2>(KVB_DM_ARGS);                      \
-    return launch<D, GP, 8, 1>(KVB_DM_ARGS);                                \
+#define KVB_DM64(GP) do { KVB_PICK(64, GP, 16, false); KVB_PICK(64, GP, 4, false); KVB_PICK(64, GP, 8, false); } while (0)
+#define KVB_DM128(GP)                                                                                     \
+  do {                                                                                                    \
+    if (tma) { KVB_PICK(128, GP, 4, true); KVB_PICK(128, GP, 8, true); }                                  \
+    if (cluster == 4) return launch<128, GP, 4, 1, false>(KVB_DM_ARGS);                                   \
+    return launch<128, GP, 8, 1, false>(KVB_DM_ARGS);                                                     \
   } while (0)
-  if (d == 64 && cluster == 16) { if (G <= 4) KVB_DM16(4); if (G <= 8) KVB_DM16(8); KVB_DM16(16); }
-  if (d == 64) { if (G <= 4) KVB_DM(64, 4); if (G <= 8) KVB_DM(64, 8); KVB_DM(64, 16); }
-  if (G <= 4) KVB_DM(128, 4);
-  if (G <= 8) KVB_DM(128, 8);
-  KVB_DM(128, 16);
+  if (d == 64) { if (G <= 4) KVB_DM64(4); if (G <= 8) KVB_DM64(8); KVB_DM64(16); }
+  if (G <= 4) KVB_DM128(4);
+  if (G <= 8) KVB_DM128(8);
+  KVB_DM128(16);
 }

@@ -455,7 +455,11 @@ def test_fused_decode_attention(dtype, nq, nkv, d, rot, page_size, window, write
     (8, 2, 64, 64, 16, None, True), (32, 8, 64, 64, 16, None, True), (6, 2, 64, 64, 16, None, True),
     (24, 8, 128, 128, 16, None, True), (8, 2, 64, 32, 8, None, True), (8, 2, 64, 64, 16, 100, True),
     (4, 4, 128, 128, 4, 129, True), (16, 1, 64, 64, 32, None, True), (8, 2, 64, 64, 16, None, False),
-    (12, 2, 64, 64, 16, 1100, True)])
+    (12, 2, 64, 64, 16, 1100, True),
+    # head size 128 fetches whole pages by TMA when a page has at least 8 rows: boxes of 8, 16 and 32 rows,
+    # a window's edge inside a page, a layer that only reads the cache, a group of 16 heads
+    (8, 2, 128, 128, 16, 100, True), (8, 2, 128, 64, 8, 1100, True), (16, 1, 128, 128, 64, None, True),
+    (8, 2, 128, 128, 32, None, False)])
 def test_tensor_core_decode_attention(nq, nkv, d, rot, page_size, window, write):
     """The cluster / tensor-core decode kernel against rotate-then-attend in float64;
     contexts from one token to several tiles per block (more than 8 tiles of 128)."""
