@@ -250,6 +250,59 @@ def run_first_token(llm, prompt_len, reps, warmup, seed):
     return statistics.median(times)
 
 
+def run_value_check(cfg, layers=2):
+    """The numbers behind the timings: a model of the benchmark's widths with ``layers`` layers is written to a
+    temporary folder and its logits, on the paths that the benchmark times (one 2048-token portion; eight
+    requests decoding beside each other from 512-token prompts, replayed from a captured graph), are compared
+    with the plain implementation under tests/ at the limit the tests use for bfloat16."""
+    import shutil
+    import tempfile
+
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama as P
+    from kv_cache_optimization_for_llm_b200 import EngineConfig
+    from kv_cache_optimization_for_llm_b200.engine.batch import StepEntry
+    from kv_cache_optimization_for_llm_b200.engine.runner import ModelRunner
+    from kv_cache_optimization_for_llm_b200.weights import write_random_model
+
+    limit = 4e-2
+    small = dict(cfg)
+    small["num_hidden_layers"] = layers
+    d = tempfile.mkdtemp(prefix="kvb200_bench_check_")
+    try:
+        write_random_model(d, small, seed=0, std=0.02, storage_dtype="bfloat16")
+        pcfg, w = P.read_model_dir(d)
+        r = ModelRunner(d, EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, num_pages=8 * 40 + 140, max_num_seqs=8,
+                                        max_num_batched_tokens=PREFILL_TOKENS, max_model_len=CONTEXT_LEN))
+        rng = np.random.default_rng(5)
+        worst = {}
+
+        def err(got, ref):
+            return float(np.abs(got.astype(np.float64) - ref).max() / np.abs(ref).max())
+
+        seq = rng.integers(0, cfg["vocab_size"], PREFILL_TOKENS).tolist()
+        rows = [0, 777, PREFILL_TOKENS - 1]
+        got = r.step([StepEntry(999, seq, 0, rows)]).float().cpu().numpy()
+        r.release(999)
+        worst["prefill_2048"] = err(got, P.forward(pcfg, w, seq, rows=rows))
+        seqs = [rng.integers(0, cfg["vocab_size"], PROMPT_LEN + 3).tolist() for _ in range(8)]
+        r.step([StepEntry(i, s_[:PROMPT_LEN], 0, []) for i, s_ in enumerate(seqs)][:4])
+        r.step([StepEntry(i, s_[:PROMPT_LEN], 0, []) for i, s_ in enumerate(seqs)][4:])
+        got = None
+        for t in range(PROMPT_LEN, PROMPT_LEN + 3):
+            got = r.step([StepEntry(i, [s_[t]], t, [0]) for i, s_ in enumerate(seqs)]).float().cpu().numpy()
+        ref = np.stack([P.forward(pcfg, w, s_, rows=[PROMPT_LEN + 2])[0] for s_ in seqs])
+        worst["decode_b8"] = err(got, ref)
+        kinds = dict(r.step_kinds)
+    finally:
+        shutil.rmtree(d, ignore_errors=True)
+    ok = all(v < limit for v in worst.values())
+    return {"ok": ok, "limit": limit, "layers": layers, "worst_relative_error": {k: round(v, 5) for k, v in worst.items()},
+            "step_kinds": kinds}
+
+
 def _pct(xs, p):
     xs = sorted(xs)
     return xs[min(len(xs) - 1, int(round(p / 100.0 * (len(xs) - 1))))] if xs else None
@@ -351,6 +404,10 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip batch 1 / 64 and the prefill measurement")
+    ap.add_argument("--check", action="store_true",
+                    help="also compare logits of a 2-layer model of these widths with the plain implementation under "
+                         "tests/ on the timed paths (adds about a minute); the line gets a \"check\" key and the exit "
+                         "code is 1 if the limit is broken")
     ap.add_argument("--workload", default="all", choices=["all", "none", *WORKLOADS],
                     help="the serving workloads measured beside the headline (3B continuous batching, 8B under a "
                          "pool that is too small); one name runs that workload alone and prints its own JSON line")
@@ -474,8 +531,12 @@ def main():
         line["points"] = points
     if workloads:
         line["workloads"] = workloads
+    if args.check:
+        log("logits of a 2-layer model of these widths against the plain implementation")
+        line["check"] = run_value_check(dict(LLAMA_1B))
+        log(f"  {line['check']}")
     print(json.dumps(line), flush=True)
-    return 0
+    return 0 if not args.check or line["check"]["ok"] else 1
 
 
 if __name__ == "__main__":
