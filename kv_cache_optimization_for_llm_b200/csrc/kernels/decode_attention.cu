@@ -62,8 +62,9 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
   return ok != 0;
 }
 // Bounded wait that also ends at once when the block has given up somewhere else.  false: gave up.
-__device__ __forceinline__ bool mbar_wait_or_abort(void* bar, unsigned parity, volatile int* abort_flag) {
-  for (unsigned i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_or_abort(void* bar, unsigned parity, volatile int* abort_flag,
+                                                   unsigned limit = kSpinLimit) {
+  for (unsigned i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u && *abort_flag) return false;
   }
@@ -651,6 +652,28 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   stamp(6);   // output stored
 }
 
+// Two warps wait, with a limit of `polls`, on barriers that nothing ever completes: the first to run out
+// raises the block's flag, the other sees the flag and leaves at once; the first reports what the attention
+// kernel reports when a slice does not arrive.  flags_out[0]: the flag afterwards, [1]: polls the second warp made.
+__global__ void decode_wait_selftest_kernel(unsigned polls, int* status, int* flags_out) {
+  __shared__ unsigned long long bars[2];
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  // warp 1 gets a limit that it could not reach in the test's time: it must leave through the flag
+  const bool ok = mbar_wait_or_abort(&bars[warp], 0, &abort_flag, warp == 0 ? polls : kSpinLimit);
+  if (!ok && warp == 0 && (threadIdx.x & 31) == 0) atomicCAS(status, 0, KVB_STATUS_WAIT_TIMEOUT);
+  __syncthreads();
+  if (threadIdx.x == 0) flags_out[0] = abort_flag;
+  if (threadIdx.x == 32) flags_out[1] = ok ? 1 : 0;
+}
+
 int log2_exact(int x) {
   int s = 0;
   while ((1 << s) < x) ++s;
@@ -822,4 +845,11 @@ KVB_EXPORT int kvb_decode_attention_mma(const void* qkv, int q_row_stride, void*
   if (G <= 4) KVB_DM128(4);
   if (G <= 8) KVB_DM128(8);
   KVB_DM128(16);
+}
+
+// Runs the bounded wait of this file's kernel against barriers that are never completed (see the kernel above);
+// the context stays usable.  For tests of the give-up path.
+KVB_EXPORT int kvb_decode_wait_selftest(unsigned polls, int* status, int* flags_out, cudaStream_t stream) {
+  decode_wait_selftest_kernel<<<1, 64, 0, stream>>>(polls, status, flags_out);
+  return kvb_launch_result();
 }

@@ -844,3 +844,14 @@ def wait_selftest(polls: int, status: torch.Tensor) -> None:
     completes: ``status`` receives the wait-timeout code, the kernel returns."""
     rc = lib("gemm_bf16").kvb_wait_selftest(ctypes.c_uint(int(polls)), _p(status), _stream())
     _check(rc, "wait_selftest")
+
+
+def decode_wait_selftest(polls: int, status: torch.Tensor) -> torch.Tensor:
+    """Runs the decode attention's bounded wait (head size 128 waits for its pages on mbarriers) against barriers
+    that nothing completes: one warp gives up after ``polls`` polls, reports KVB_STATUS_WAIT_TIMEOUT in ``status``
+    and raises the block's flag, by which the other warp leaves.  Returns [flag, whether the other warp's wait
+    claimed success] as an int32 tensor."""
+    flags = torch.full((2,), -1, dtype=torch.int32, device=status.device)
+    rc = lib("decode_attention").kvb_decode_wait_selftest(ctypes.c_uint(int(polls)), _p(status), _p(flags), _stream())
+    _check(rc, "decode_wait_selftest")
+    return flags

@@ -680,3 +680,19 @@ def test_window_edge_with_a_key_that_stands_out(d, nq, nkv, window, inside):
     assert int(st.item()) == 0
     assert rel_err(out, one["ref"]) < TOL["bfloat16"] * 1.5
     assert (np.abs(as64(out)[-1] - spike_value).max() < 0.08) == inside
+
+
+def test_decode_attention_wait_gives_up_and_the_context_stays_usable():
+    """The waits of the page-by-page (TMA) decode attention are bounded: on barriers that nothing completes one
+    warp runs out of polls, the kernel reports it and returns, the block's other warp leaves through the flag;
+    afterwards the same context computes as before."""
+    from kv_cache_optimization_for_llm_b200 import ops
+    st = status()
+    flags = ops.decode_wait_selftest(3000, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 4 and "wait" in ops.STATUS_TEXT[4].lower()
+    assert flags.tolist() == [1, 0]
+    st.zero_()
+    x = torch.arange(64, device="cuda", dtype=torch.float32)
+    assert float((x * 2).sum().item()) == 2 * 63 * 64 / 2 and int(st.item()) == 0
+
