@@ -143,7 +143,8 @@ __host__ __device__ __forceinline__ int classes_at(int pos) { return pos < 2048 
 // order of the sums is the same for both.
 // kTma: keys and values come page by page (boxes of min(page size, 32) rows) through tensor maps over the
 // layer's pages, counted on one mbarrier per stage and warp; needs pages of at least 8 rows.  Otherwise
-// 16 bytes at a time by cp.async (any page size; an SM holds far fewer bytes under way that way).
+// 16 bytes at a time by cp.async (any page size).  The launcher takes TMA at head size 128, where it measured
+// faster, and cp.async at head size 64, where the boxes of a page are 2 KB and it did not.
 template <int D, int GP, int kClasses, int kStages, bool kTma>
 __global__ void __launch_bounds__(kThreads, D == 64 ? 4 : 2)   // four blocks per SM at head size 64: 128 registers
 decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
